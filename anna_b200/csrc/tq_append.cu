@@ -1,0 +1,262 @@
+// Fused TurboQuant append: residual-window ring update + quantize-on-overflow + bit-pack + page scatter.
+//
+// One warp owns one (row, kv head, token) work item.  Items of a row with old length L, T new tokens, window R:
+//   quantize items  p in [max(0, L-R), max(0, L+T-R)) : source is the ring (p < L) or the incoming chunk (p >= L)
+//   window items    p in [max(L, L+T-R), L+T)         : incoming token copied into ring slot p % R
+// A ring slot that is both read (old token being quantized) and written (new token with the same residue) in one
+// call is handled by the reading warp: it loads the old vectors into registers, then stores the new ones.
+#include "tq_common.cuh"
+
+namespace anna {
+
+struct TqAppendParams {
+  const void* k_new;
+  const void* v_new;
+  int64_t stride_b, stride_h, stride_t;
+  uint8_t* pages;
+  const int32_t* block_table;
+  int64_t table_stride;
+  void* window;
+  const int32_t* window_slots;
+  const int32_t* old_lengths;
+  const float* signs1;
+  const float* signs2;
+  const float* centroids;
+  const float* boundaries;
+  int batch, kv_heads, new_tokens, block_size, residual_len, value_group;
+  int64_t num_pages, max_blocks;
+  anna_tq_layout layout;
+  int32_t* status;
+};
+
+constexpr int kAppendWarps = 4;
+
+template <typename T, int D, int BITS>
+__global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAppendParams p) {
+  constexpr int E = D / 32;
+  constexpr int M = BITS - 1;          // index bits
+  constexpr int NB = (1 << M) - 1;     // boundaries
+  constexpr int VS = BITS == 2 ? 2 : 4;  // value storage bits
+  __shared__ float sm_cent[1 << M];
+  if (threadIdx.x < (1 << M)) sm_cent[threadIdx.x] = p.centroids[threadIdx.x];
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int64_t u = (int64_t)blockIdx.x * kAppendWarps + warp;
+
+  const int64_t R = p.residual_len;
+  const int64_t L = p.old_lengths[b];
+  const int64_t Tn = p.new_tokens;
+  const int64_t Lp = L + Tn;
+  const int64_t Lq = L > R ? L - R : 0;
+  const int64_t Lqp = Lp > R ? Lp - R : 0;
+  const int64_t nq = Lqp - Lq;
+  const int64_t wstart = L > Lqp ? L : Lqp;
+  const int64_t nw = Lp - wstart;
+  if (u >= nq + nw) return;
+
+  const int slot = p.window_slots[b];
+  T* ring_k = reinterpret_cast<T*>(p.window) + (((int64_t)slot * 2 + 0) * p.kv_heads + h) * R * D;
+  T* ring_v = reinterpret_cast<T*>(p.window) + (((int64_t)slot * 2 + 1) * p.kv_heads + h) * R * D;
+  const T* in_k = reinterpret_cast<const T*>(p.k_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
+  const T* in_v = reinterpret_cast<const T*>(p.v_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
+  const int e0 = lane * E;
+
+  if (u >= nq) {
+    // window item: plain copy unless the slot's old occupant is quantized (and rewritten) by another warp
+    const int64_t pw = wstart + (u - nq);
+    const int64_t k = (pw - L + R) / R;  // smallest k >= 1 with pw - k*R < L
+    const int64_t p_old = pw - k * R;
+    if (p_old >= Lq) return;
+    const int64_t rs = pw % R;
+    lane_copy<T, E>(in_k + (pw - L) * p.stride_t + e0, ring_k + rs * D + e0);
+    lane_copy<T, E>(in_v + (pw - L) * p.stride_t + e0, ring_v + rs * D + e0);
+    return;
+  }
+
+  // ---- quantize item -------------------------------------------------------------------------------------------
+  const int64_t pos = Lq + u;
+  float x[E], v[E];
+  if (pos < L) {
+    const int64_t rs = pos % R;
+    lane_load<T, E>(ring_k + rs * D + e0, x);
+    lane_load<T, E>(ring_v + rs * D + e0, v);
+    const int64_t k = (wstart - pos + R - 1) / R;
+    const int64_t pw = pos + k * R;  // new occupant of this ring slot, if it arrives in this call
+    if (pw < Lp) {
+      lane_copy<T, E>(in_k + (pw - L) * p.stride_t + e0, ring_k + rs * D + e0);
+      lane_copy<T, E>(in_v + (pw - L) * p.stride_t + e0, ring_v + rs * D + e0);
+    }
+  } else {
+    lane_load<T, E>(in_k + (pos - L) * p.stride_t + e0, x);
+    lane_load<T, E>(in_v + (pos - L) * p.stride_t + e0, v);
+  }
+
+  const int64_t blk = pos / p.block_size;
+  const int tok = (int)(pos % p.block_size);
+  int32_t pid = -1;
+  if (blk < p.max_blocks) pid = p.block_table[(int64_t)b * p.table_stride + blk];
+  if (pid < 0 || pid >= p.num_pages) {
+    if (lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
+    return;
+  }
+  uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
+
+  // ---- keys: normalise, rotate, index, residual sign ------------------------------------------------------------
+  float s1[E], s2[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    s1[j] = p.signs1[e0 + j];
+    s2[j] = p.signs2[e0 + j];
+  }
+  float t[E], w[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) t[j] = __fmul_rn(x[j], x[j]);
+  const float norm = __fsqrt_rn(warp_tree_sum<E>(t));
+  const float inv = __frcp_rn(fmaxf(norm, 1e-20f));
+#pragma unroll
+  for (int j = 0; j < E; ++j) w[j] = s1[j] < 0.0f ? -x[j] : x[j];
+  warp_fwht<E>(w, lane);
+
+  float bnd[NB];
+#pragma unroll
+  for (int k = 0; k < NB; ++k) bnd[k] = p.boundaries[k];
+
+  uint32_t code[E];
+  float e[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float scaled = __fmul_rn(w[j], inv);
+    uint32_t c = 0;
+#pragma unroll
+    for (int k = 0; k < NB; ++k) c += scaled > bnd[k] ? 1u : 0u;
+    code[j] = c;
+    e[j] = __fsub_rn(scaled, sm_cent[c]);
+  }
+#pragma unroll
+  for (int j = 0; j < E; ++j) t[j] = __fmul_rn(e[j], e[j]);
+  constexpr float rsqrt_dim = rsqrt_dim_const<D>();
+  const float rnorm = __fmul_rn(__fsqrt_rn(warp_tree_sum<E>(t)), rsqrt_dim);
+#pragma unroll
+  for (int j = 0; j < E; ++j) e[j] = s2[j] < 0.0f ? -e[j] : e[j];
+  warp_fwht<E>(e, lane);
+
+  uint8_t* krow = chunk + p.layout.off_kcodes + tok * p.layout.key_bytes;
+  if constexpr (BITS == 4) {
+    uint64_t field = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 8u : 0u)) << (4 * j);
+    warp_pack_store<4 * E>(field, krow, lane);
+  } else if constexpr (BITS == 2) {
+    uint64_t field = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 2u : 0u)) << (2 * j);
+    warp_pack_store<2 * E>(field, krow, lane);
+  } else {
+    uint64_t idx_field = 0, sign_field = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      idx_field |= (uint64_t)code[j] << (2 * j);
+      sign_field |= (uint64_t)(e[j] >= 0.0f ? 1u : 0u) << j;
+    }
+    warp_pack_store<2 * E>(idx_field, krow, lane);
+    warp_pack_store<E>(sign_field, krow + D / 4, lane);
+  }
+  if (lane == 0) {
+    reinterpret_cast<float*>(chunk + p.layout.off_knorm)[tok] = norm;
+    reinterpret_cast<float*>(chunk + p.layout.off_krnorm)[tok] = rnorm;
+  }
+
+  // ---- values: per-group min/max -> scale / zero in the cache dtype -> round-half-even codes ---------------------
+  const int lanes_per_group = p.value_group / E;  // power of two, >= 1
+  float lo = v[0], hi = v[0];
+#pragma unroll
+  for (int j = 1; j < E; ++j) {
+    lo = fminf(lo, v[j]);
+    hi = fmaxf(hi, v[j]);
+  }
+  for (int dl = 1; dl < lanes_per_group; dl <<= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, dl));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, dl));
+  }
+  const float levels = (float)((1 << BITS) - 1);
+  const float raw = __fdiv_rn(__fsub_rn(hi, lo), levels);
+  const float scale = round_to_elem<T>(raw < 1e-8f ? 1e-8f : raw);
+  const float zero = round_to_elem<T>(lo);
+  uint64_t vfield = 0;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    float q = rintf(__fdiv_rn(__fsub_rn(v[j], zero), scale));
+    if (!(q >= 0.0f)) q = 0.0f;
+    if (q > levels) q = levels;
+    vfield |= (uint64_t)(uint32_t)q << (VS * j);
+  }
+  warp_pack_store<VS * E>(vfield, chunk + p.layout.off_vdata + tok * p.layout.value_bytes, lane);
+  if (lane % lanes_per_group == 0) {
+    const int g = lane / lanes_per_group;
+    reinterpret_cast<T*>(chunk + p.layout.off_vscale)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(scale);
+    reinterpret_cast<T*>(chunk + p.layout.off_vzero)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(zero);
+  }
+}
+
+}  // namespace anna
+
+using namespace anna;
+
+extern "C" int anna_tq_page_layout(int head_dim, int bits, int block_size, int dtype, int value_group,
+                                   anna_tq_layout* out) {
+  ANNA_REQUIRE(out != nullptr, "anna_tq_page_layout: null output");
+  ANNA_REQUIRE(dtype >= 0 && dtype <= 2, "anna_tq_page_layout: bad dtype code %d", dtype);
+  if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, out))
+    return set_error(ANNA_ERR_INVALID, "anna_tq_page_layout: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim,
+                     bits, block_size, value_group);
+  return ANNA_OK;
+}
+
+extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
+                              int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table,
+                              int64_t table_stride, void* window, const int32_t* window_slots,
+                              const int32_t* old_lengths, const float* signs1, const float* signs2,
+                              const float* centroids, const float* boundaries, int batch, int kv_heads,
+                              int new_tokens, int head_dim, int block_size, int residual_len, int bits,
+                              int value_group, int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,
+                              anna_stream_t stream) {
+  ANNA_REQUIRE(k_new && v_new && window && window_slots && old_lengths && signs1 && signs2 && centroids && boundaries,
+               "anna_tq_append: null pointer argument");
+  ANNA_REQUIRE(batch > 0 && kv_heads > 0 && new_tokens > 0 && residual_len >= 1 && block_size >= 1,
+               "anna_tq_append: sizes must be positive");
+  ANNA_REQUIRE(packed_pages != nullptr || num_pages == 0, "anna_tq_append: null page pool with num_pages > 0");
+  ANNA_REQUIRE(block_table != nullptr || max_blocks == 0, "anna_tq_append: null block table with max_blocks > 0");
+  const int lane_elems = head_dim / 32;
+  ANNA_REQUIRE(lane_elems >= 1 && value_group >= lane_elems && value_group % lane_elems == 0 &&
+                   ((value_group / lane_elems) & (value_group / lane_elems - 1)) == 0 && value_group <= head_dim,
+               "anna_tq_append: value group %d does not fit head_dim %d", value_group, head_dim);
+  const int vec = dtype == ANNA_DTYPE_F32 ? 4 : 8;
+  ANNA_REQUIRE(kn_stride_b % vec == 0 && kn_stride_h % vec == 0 && kn_stride_t % vec == 0,
+               "anna_tq_append: source strides must keep rows 16-byte aligned");
+  TqAppendParams p{};
+  p.k_new = k_new; p.v_new = v_new;
+  p.stride_b = kn_stride_b; p.stride_h = kn_stride_h; p.stride_t = kn_stride_t;
+  p.pages = packed_pages; p.block_table = block_table; p.table_stride = table_stride;
+  p.window = window; p.window_slots = window_slots; p.old_lengths = old_lengths;
+  p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids; p.boundaries = boundaries;
+  p.batch = batch; p.kv_heads = kv_heads; p.new_tokens = new_tokens; p.block_size = block_size;
+  p.residual_len = residual_len; p.value_group = value_group;
+  p.num_pages = num_pages; p.max_blocks = max_blocks; p.status = status;
+  if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, &p.layout))
+    return set_error(ANNA_ERR_INVALID, "anna_tq_append: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim, bits,
+                     block_size, value_group);
+  const int64_t items = 2 * (int64_t)new_tokens;
+  dim3 grid((unsigned)((items + kAppendWarps - 1) / kAppendWarps), (unsigned)kv_heads, (unsigned)batch);
+  return ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
+    return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
+      return ANNA_DISPATCH_TQ_BITS(bits, BITS, [&]() -> int {
+        tq_append_kernel<T, D, BITS><<<grid, kAppendWarps * 32, 0, (cudaStream_t)stream>>>(p);
+        return check_launch("tq_append_kernel");
+      });
+    });
+  });
+}

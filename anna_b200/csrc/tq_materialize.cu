@@ -1,0 +1,141 @@
+// De-quantize packed TurboQuant pages into dense keys / values in the cache dtype (one warp per token-head).
+#include "tq_common.cuh"
+
+namespace anna {
+
+struct TqMaterializeParams {
+  const uint8_t* pages;
+  const int32_t* block_table;
+  int64_t table_stride;
+  const int32_t* quantized_lengths;
+  const float* signs1;
+  const float* signs2;
+  const float* centroids;
+  void* key_out;
+  void* value_out;
+  int64_t out_stride_b, out_stride_h, out_stride_t;
+  int kv_heads, block_size, value_group;
+  int64_t num_pages, max_blocks, max_quantized_len;
+  anna_tq_layout layout;
+};
+
+constexpr int kMaterializeWarps = 4;
+
+template <typename T, int D, int BITS>
+__global__ void __launch_bounds__(kMaterializeWarps * 32) tq_materialize_kernel(const TqMaterializeParams p) {
+  constexpr int E = D / 32;
+  constexpr int M = BITS - 1;
+  constexpr int VS = BITS == 2 ? 2 : 4;
+  __shared__ float sm_cent[1 << M];
+  if (threadIdx.x < (1 << M)) sm_cent[threadIdx.x] = p.centroids[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int64_t t = (int64_t)blockIdx.x * kMaterializeWarps + warp;
+  int64_t lq = p.quantized_lengths[b];
+  lq = min(lq, p.max_quantized_len);
+  if (t >= lq) return;
+  const int64_t blk = t / p.block_size;
+  const int tok = (int)(t % p.block_size);
+  int32_t pid = -1;
+  if (blk < p.max_blocks) pid = p.block_table[(int64_t)b * p.table_stride + blk];
+  if (pid < 0 || pid >= p.num_pages) return;
+  const uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
+  const int e0 = lane * E;
+
+  // ---- keys: k_hat = norm / D * s1 * fwht( centroid[idx] + kappa * rnorm * s2 * fwht(2*sign - 1) ) ------------------
+  const uint8_t* krow = chunk + p.layout.off_kcodes + tok * p.layout.key_bytes;
+  float cent[E], sg[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int d = e0 + j;
+    uint32_t code, sbit;
+    if constexpr (BITS == 4) {
+      const uint32_t field = (krow[d >> 1] >> ((d & 1) * 4)) & 0xFu;
+      code = field & 7u;
+      sbit = field >> 3;
+    } else if constexpr (BITS == 2) {
+      const uint32_t field = (krow[d >> 2] >> ((d & 3) * 2)) & 3u;
+      code = field & 1u;
+      sbit = field >> 1;
+    } else {
+      code = (krow[d >> 2] >> ((d & 3) * 2)) & 3u;
+      sbit = (krow[D / 4 + (d >> 3)] >> (d & 7)) & 1u;
+    }
+    cent[j] = sm_cent[code];
+    sg[j] = sbit ? 1.0f : -1.0f;
+  }
+  const float norm = reinterpret_cast<const float*>(chunk + p.layout.off_knorm)[tok];
+  const float rnorm = reinterpret_cast<const float*>(chunk + p.layout.off_krnorm)[tok];
+  warp_fwht<E>(sg, lane);
+  const float coef = (1.2533141373155001f * rsqrt_dim_const<D>()) * rnorm;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float s2 = p.signs2[e0 + j];
+    cent[j] = fmaf(coef, s2 < 0.0f ? -sg[j] : sg[j], cent[j]);
+  }
+  warp_fwht<E>(cent, lane);
+  const float scale = norm * (1.0f / (float)D);
+  T* kout = reinterpret_cast<T*>(p.key_out) + (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h +
+            t * p.out_stride_t + e0;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float s1 = p.signs1[e0 + j];
+    kout[j] = ElemTraits<T>::from_float(scale * (s1 < 0.0f ? -cent[j] : cent[j]));
+  }
+
+  // ---- values: code * scale + zero ------------------------------------------------------------------------------------
+  const uint8_t* vrow = chunk + p.layout.off_vdata + tok * p.layout.value_bytes;
+  const T* scales = reinterpret_cast<const T*>(chunk + p.layout.off_vscale) + tok * p.layout.groups;
+  const T* zeros = reinterpret_cast<const T*>(chunk + p.layout.off_vzero) + tok * p.layout.groups;
+  T* vout = reinterpret_cast<T*>(p.value_out) + (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h +
+            t * p.out_stride_t + e0;
+  constexpr int kPerByte = 8 / VS;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int d = e0 + j;
+    const uint32_t code = (vrow[d / kPerByte] >> ((d % kPerByte) * VS)) & ((1u << VS) - 1u);
+    const int g = d / p.value_group;
+    const float prod = __fmul_rn((float)code, ElemTraits<T>::to_float(scales[g]));
+    vout[j] = ElemTraits<T>::from_float(__fadd_rn(prod, ElemTraits<T>::to_float(zeros[g])));
+  }
+}
+
+}  // namespace anna
+
+using namespace anna;
+
+extern "C" int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                                   const int32_t* quantized_lengths, const float* signs1, const float* signs2,
+                                   const float* centroids, void* key_out, void* value_out, int64_t out_stride_b,
+                                   int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads, int head_dim,
+                                   int block_size, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
+                                   int64_t max_quantized_len, int dtype, anna_stream_t stream) {
+  ANNA_REQUIRE(packed_pages && block_table && quantized_lengths && signs1 && signs2 && centroids && key_out && value_out,
+               "anna_tq_materialize: null pointer argument");
+  ANNA_REQUIRE(batch > 0 && kv_heads > 0 && block_size >= 1 && max_quantized_len >= 0,
+               "anna_tq_materialize: sizes must be positive");
+  if (max_quantized_len == 0) return ANNA_OK;
+  TqMaterializeParams p{};
+  p.pages = packed_pages; p.block_table = block_table; p.table_stride = table_stride;
+  p.quantized_lengths = quantized_lengths; p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids;
+  p.key_out = key_out; p.value_out = value_out;
+  p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_t = out_stride_t;
+  p.kv_heads = kv_heads; p.block_size = block_size; p.value_group = value_group;
+  p.num_pages = num_pages; p.max_blocks = max_blocks; p.max_quantized_len = max_quantized_len;
+  if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, &p.layout))
+    return set_error(ANNA_ERR_INVALID, "anna_tq_materialize: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim,
+                     bits, block_size, value_group);
+  dim3 grid((unsigned)((max_quantized_len + kMaterializeWarps - 1) / kMaterializeWarps), (unsigned)kv_heads,
+            (unsigned)batch);
+  return ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
+    return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
+      return ANNA_DISPATCH_TQ_BITS(bits, BITS, [&]() -> int {
+        tq_materialize_kernel<T, D, BITS><<<grid, kMaterializeWarps * 32, 0, (cudaStream_t)stream>>>(p);
+        return check_launch("tq_materialize_kernel");
+      });
+    });
+  });
+}

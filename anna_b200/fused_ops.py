@@ -1,0 +1,392 @@
+"""Operator boundary of the decode path: the ``run_*`` wrappers and ``torch.ops.anna.*`` schemas of Anna.
+
+Mirrors the decode part of ``src/anna/model/fused_ops.py`` (:306-323 availability probes, :414-448 library loading,
+:451-609 wrappers) and the schemas the reference registers in
+``src/anna/model/custom_ops/gated_delta_fused_op.sycl:7621-7679``; here they are registered for the CUDA dispatch
+key and forward to the C ABI of ``libanna_b200_kv.so`` with raw pointers on the current CUDA stream.  As in the
+reference there is no CPU fallback: a missing library or op raises ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+from . import _lib
+
+_LOAD_LOCK = threading.Lock()
+_REGISTERED = False
+_LIBRARY: torch.library.Library | None = None
+_LOADED_LIBRARIES: set[str] = set()
+
+_DTYPE_CODES = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+
+SCHEMAS = {
+    "gqa_decode_fused":
+        "(Tensor query, Tensor key, Tensor value, Tensor visible_lengths, float scaling, Tensor? gate=None) -> Tensor",
+    "gqa_decode_splitkv_fused":
+        "(Tensor query, Tensor key, Tensor value, float scaling, int block_size, Tensor? gate=None) -> Tensor",
+    "gqa_decode_splitkv_fused_out":
+        "(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor(b!) partial_stats, "
+        "Tensor(c!) partial_values, float scaling, int block_size, Tensor? gate=None) -> Tensor(a!)",
+    "paged_gqa_decode_fused":
+        "(Tensor query, Tensor key_pages, Tensor value_pages, Tensor page_table, Tensor visible_lengths, "
+        "float scaling, Tensor? gate=None) -> Tensor",
+}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODES[dtype]
+    except KeyError:
+        raise RuntimeError(f"anna_b200 kernels support float16, bfloat16 and float32 inputs, got {dtype}") from None
+
+
+def ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p | None:
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def stream_ptr(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(name: str, **tensors: torch.Tensor | None) -> torch.device:
+    device = None
+    for label, tensor in tensors.items():
+        if tensor is None:
+            continue
+        if not tensor.is_cuda:
+            raise RuntimeError(f"{name}: {label} must be a CUDA tensor (there is no CPU implementation of this op)")
+        if device is None:
+            device = tensor.device
+        elif tensor.device != device:
+            raise RuntimeError(f"{name}: {label} must be on the same device as query")
+    assert device is not None
+    return device
+
+
+def _last_dim_contiguous(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor if tensor.stride(-1) == 1 else tensor.contiguous()
+
+
+def _check_gate(name: str, query: torch.Tensor, gate: torch.Tensor | None):
+    """Validates like validate_gqa_decode_optional_gate (.sycl:1605-1626); returns (tensor, stride_b, stride_h)."""
+    if gate is None:
+        return None, 0, 0
+    heads, dim = int(query.shape[1]), int(query.shape[3])
+    if gate.dtype != query.dtype:
+        raise RuntimeError("gate must match query dtype")
+    if gate.shape[0] != query.shape[0]:
+        raise RuntimeError("gate batch size mismatch")
+    if gate.dim() == 3:
+        if gate.shape[1] != 1 or gate.shape[2] != heads * dim:
+            raise RuntimeError("3D gqa_decode gate must be [batch, 1, num_heads * head_dim]")
+        gate = _last_dim_contiguous(gate)
+        return gate, gate.stride(0), dim
+    if gate.dim() == 4:
+        if gate.shape[1] != heads or gate.shape[2] != 1 or gate.shape[3] != dim:
+            raise RuntimeError("4D gqa_decode gate must match query layout [batch, heads, 1, head_dim]")
+        gate = _last_dim_contiguous(gate)
+        return gate, gate.stride(0), gate.stride(1)
+    raise RuntimeError(
+        "gqa_decode gate must be 3D [batch, 1, num_heads * head_dim] or 4D [batch, heads, 1, head_dim] (query layout)")
+
+
+def _check_query(name: str, query: torch.Tensor) -> torch.Tensor:
+    if query.dim() != 4 or query.shape[2] != 1:
+        raise RuntimeError(f"{name}: query must be [batch, heads, 1, head_dim] (single-token query)")
+    return _last_dim_contiguous(query)
+
+
+class _Scratch:
+    """Per-(device, stream) split-K scratch, grown on demand and reused across calls."""
+
+    def __init__(self) -> None:
+        self._buffers: dict[tuple[int, int], torch.Tensor] = {}
+
+    def get(self, device: torch.device, floats: int) -> torch.Tensor:
+        key = (device.index if device.index is not None else torch.cuda.current_device(),
+               torch.cuda.current_stream(device).cuda_stream)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < floats:
+            buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
+            self._buffers[key] = buf
+        return buf
+
+
+_SCRATCH = _Scratch()
+
+
+def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, kv_heads: int, max_len: int):
+    """(partial_stats, partial_values, chunk_capacity) sized by the library's own plan for this problem."""
+    _, chunks = _lib.decode_plan(batch, kv_heads, max(int(max_len), 1))
+    stats_floats = batch * heads * chunks * 2
+    value_floats = batch * heads * chunks * head_dim
+    buf = _SCRATCH.get(device, stats_floats + value_floats)
+    return buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# op implementations (CUDA dispatch key)
+
+
+def _gqa_decode_dense(name, query, key, value, visible_lengths, scaling, gate, *, output=None, partial_stats=None,
+                      partial_values=None, block_size=0):
+    query = _check_query(name, query)
+    if key.dim() != 4 or value.dim() != 4:
+        raise RuntimeError(f"{name}: key and value must be [batch, kv_heads, key_len, head_dim]")
+    if key.shape != value.shape:
+        raise RuntimeError("key and value must share the same shape")
+    if query.shape[0] != key.shape[0]:
+        raise RuntimeError("query/key batch size mismatch")
+    if query.shape[3] != key.shape[3]:
+        raise RuntimeError("query/key head_dim mismatch")
+    if key.shape[1] < 1 or query.shape[1] % key.shape[1] != 0:
+        raise RuntimeError("query heads must be divisible by kv_heads")
+    if key.shape[2] < 1:
+        raise RuntimeError("key_len must be positive")
+    if not (query.dtype == key.dtype == value.dtype):
+        raise RuntimeError("query, key, and value must share the same dtype")
+    device = _require_cuda(name, query=query, key=key, value=value, visible_lengths=visible_lengths, gate=gate)
+    if visible_lengths is not None:
+        if visible_lengths.dim() != 1 or visible_lengths.shape[0] != query.shape[0]:
+            raise RuntimeError("visible_lengths must be [batch]")
+        if visible_lengths.dtype != torch.long:
+            raise RuntimeError("visible_lengths must be int64")
+        visible_lengths = visible_lengths.contiguous()
+    key = _last_dim_contiguous(key)
+    value = _last_dim_contiguous(value)
+    if value.stride() != key.stride():
+        value = value.contiguous()
+        key = key.contiguous()
+    gate, gate_sb, gate_sh = _check_gate(name, query, gate)
+    batch, heads, _, dim = (int(v) for v in query.shape)
+    kv_heads, key_len = int(key.shape[1]), int(key.shape[2])
+    result = output if output is not None else torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    target = result if result.stride(3) == 1 else torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    if partial_stats is None:
+        partial_stats, partial_values, capacity = split_scratch(device, batch, heads, dim, kv_heads, key_len)
+        chunk_tokens = 0
+    else:
+        capacity = int(partial_stats.shape[2])
+        chunk_tokens = min(max(int(block_size), 16), key_len)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().anna_gqa_decode(
+            ptr(query), query.stride(0), query.stride(1), ptr(key), ptr(value), key.stride(0), key.stride(1),
+            key.stride(2), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(target), target.stride(0),
+            target.stride(1), ptr(partial_stats), ptr(partial_values), capacity, chunk_tokens, batch, heads, kv_heads,
+            key_len, dim, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
+    if target is not result:
+        result.copy_(target)
+    return result
+
+
+def _op_gqa_decode_fused(query, key, value, visible_lengths, scaling, gate=None):
+    if visible_lengths is None:
+        raise RuntimeError("visible_lengths must be [batch]")
+    return _gqa_decode_dense("gqa_decode_fused", query, key, value, visible_lengths, scaling, gate)
+
+
+def _op_gqa_decode_splitkv_fused(query, key, value, scaling, block_size, gate=None):
+    if block_size < 16:
+        raise RuntimeError("gqa_decode_splitkv_fused block_size must be at least 16")
+    return _gqa_decode_dense("gqa_decode_splitkv_fused", query, key, value, None, scaling, gate)
+
+
+def _check_split_workspace(name, query, key_len, block_size, output, partial_stats, partial_values):
+    """validate_gqa_decode_splitkv_workspace_for_length (.sycl:1521-1556)."""
+    batch, heads, _, dim = (int(v) for v in query.shape)
+    effective = min(max(int(block_size), 16), int(key_len))
+    blocks = (int(key_len) + effective - 1) // effective
+    if tuple(output.shape) != tuple(query.shape) or output.dtype != query.dtype or output.device != query.device:
+        raise RuntimeError(f"{name} output must match query shape, dtype and device")
+    for label, tensor, last in (("partial_stats", partial_stats, 2), ("partial_values", partial_values, dim)):
+        if tensor.dim() != 4 or tensor.dtype != torch.float32 or tensor.device != query.device:
+            raise RuntimeError(f"{name} {label} must be a float32 [batch, heads, blocks, {last}] tensor on the query device")
+        if tensor.shape[0] != batch or tensor.shape[1] != heads or tensor.shape[2] < blocks or tensor.shape[3] != last:
+            raise RuntimeError(f"{name} {label} shape/capacity mismatch")
+        if not tensor.is_contiguous():
+            raise RuntimeError(f"{name} {label} must be contiguous")
+    if partial_stats.shape[2] != partial_values.shape[2]:
+        raise RuntimeError(f"{name} partial_stats and partial_values must hold the same number of blocks")
+
+
+def _op_gqa_decode_splitkv_fused_out(query, key, value, output, partial_stats, partial_values, scaling, block_size,
+                                     gate=None):
+    name = "gqa_decode_splitkv_fused_out"
+    if block_size < 16:
+        raise RuntimeError(f"{name} block_size must be at least 16")
+    if query.dim() != 4 or key.dim() != 4:
+        raise RuntimeError(f"{name}: query and key must be 4-D")
+    _check_split_workspace(name, query, key.shape[2], block_size, output, partial_stats, partial_values)
+    return _gqa_decode_dense(name, query, key, value, None, scaling, gate, output=output, partial_stats=partial_stats,
+                             partial_values=partial_values, block_size=block_size)
+
+
+def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visible_lengths, scaling, gate=None):
+    name = "paged_gqa_decode_fused"
+    query = _check_query(name, query)
+    if key_pages.dim() != 4 or value_pages.dim() != 4:
+        raise RuntimeError("key_pages and value_pages must be [pages, kv_heads, block_size, head_dim]")
+    if key_pages.shape != value_pages.shape:
+        raise RuntimeError("key_pages and value_pages must share the same shape")
+    if page_table.dim() != 2 or page_table.shape[0] != query.shape[0]:
+        raise RuntimeError("page_table must be [batch, max_blocks]")
+    if visible_lengths.dim() != 1 or visible_lengths.shape[0] != query.shape[0]:
+        raise RuntimeError("visible_lengths must be [batch]")
+    if key_pages.shape[0] < 1 or key_pages.shape[1] < 1 or key_pages.shape[2] < 1:
+        raise RuntimeError("pages, kv_heads and block_size must be positive")
+    if query.shape[1] % key_pages.shape[1] != 0:
+        raise RuntimeError("query heads must be divisible by kv_heads")
+    if query.shape[3] != key_pages.shape[3]:
+        raise RuntimeError("query/key_pages head_dim mismatch")
+    if not (query.dtype == key_pages.dtype == value_pages.dtype):
+        raise RuntimeError("query, key_pages, and value_pages must share the same dtype")
+    if page_table.dtype != torch.int32:
+        raise RuntimeError("page_table must be int32")
+    if visible_lengths.dtype != torch.long:
+        raise RuntimeError("visible_lengths must be int64")
+    device = _require_cuda(name, query=query, key_pages=key_pages, value_pages=value_pages, page_table=page_table,
+                           visible_lengths=visible_lengths, gate=gate)
+    key_pages = key_pages.contiguous()
+    value_pages = value_pages.contiguous()
+    if page_table.stride(1) != 1:
+        page_table = page_table.contiguous()
+    visible_lengths = visible_lengths.contiguous()
+    gate, gate_sb, gate_sh = _check_gate(name, query, gate)
+    batch, heads, _, dim = (int(v) for v in query.shape)
+    pages, kv_heads, block = int(key_pages.shape[0]), int(key_pages.shape[1]), int(key_pages.shape[2])
+    max_blocks = int(page_table.shape[1])
+    out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    if max_blocks == 0:
+        return out.zero_()
+    stats, values, capacity = split_scratch(device, batch, heads, dim, kv_heads, max_blocks * block)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().anna_paged_gqa_decode(
+            ptr(query), query.stride(0), query.stride(1), ptr(key_pages), ptr(value_pages), ptr(page_table),
+            page_table.stride(0), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(out), out.stride(0),
+            out.stride(1), ptr(stats), ptr(values), capacity, 0, batch, heads, kv_heads, dim, block, pages,
+            max_blocks, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
+    return out
+
+
+_IMPLS = {
+    "gqa_decode_fused": _op_gqa_decode_fused,
+    "gqa_decode_splitkv_fused": _op_gqa_decode_splitkv_fused,
+    "gqa_decode_splitkv_fused_out": _op_gqa_decode_splitkv_fused_out,
+    "paged_gqa_decode_fused": _op_paged_gqa_decode_fused,
+}
+
+
+def _meta_like_query(query, *args, **kwargs):
+    return torch.empty_like(query)
+
+
+def _register_ops() -> None:
+    global _REGISTERED, _LIBRARY
+    if _REGISTERED:
+        return
+    library = torch.library.Library("anna", "FRAGMENT")
+    for name, schema in SCHEMAS.items():
+        library.define(name + schema)
+        library.impl(name, _IMPLS[name], "CUDA")
+        if not name.endswith("_out"):
+            library.impl(name, _meta_like_query, "Meta")
+    _LIBRARY = library
+    _REGISTERED = True
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# public surface (names follow src/anna/model/fused_ops.py)
+
+
+def maybe_load_gated_delta_library(path: str | os.PathLike[str] | None = None) -> bool:
+    """Load libanna_b200_kv.so and register the ``anna::`` decode ops; True when they are available.
+
+    ``path`` and ``ANNA_GATED_DELTA_OP_LIB`` are accepted for call-site compatibility with the reference
+    (fused_ops.py:414-448); the library that is loaded is always the one built next to this package.
+    """
+    with _LOAD_LOCK:
+        if _REGISTERED:
+            return True
+        try:
+            _lib.lib()
+        except RuntimeError:
+            return False
+        _register_ops()
+        _LOADED_LIBRARIES.add(str(_lib.library_path()))
+    return True
+
+
+def loaded_fused_library_paths() -> tuple[str, ...]:
+    return tuple(sorted(_LOADED_LIBRARIES))
+
+
+def _op(name: str):
+    namespace = getattr(torch.ops, "anna", None)
+    if namespace is None or not _REGISTERED:
+        return None
+    return getattr(namespace, name, None)
+
+
+def gqa_decode_fused_is_available() -> bool:
+    return _op("gqa_decode_fused") is not None
+
+
+def gqa_decode_splitkv_fused_is_available() -> bool:
+    return _op("gqa_decode_splitkv_fused") is not None
+
+
+def gqa_decode_splitkv_fused_out_is_available() -> bool:
+    return _op("gqa_decode_splitkv_fused_out") is not None
+
+
+def gqa_decode_splitkv_turboquant_fused_out_is_available() -> bool:
+    return _op("gqa_decode_splitkv_turboquant_fused_out") is not None
+
+
+def paged_gqa_decode_fused_is_available() -> bool:
+    return _op("paged_gqa_decode_fused") is not None
+
+
+def _resolve(name: str):
+    op = _op(name)
+    if op is None:
+        maybe_load_gated_delta_library()
+        op = _op(name)
+    if op is None:
+        raise RuntimeError(
+            f"Anna {name} op is not registered. Build the CUDA library first (python -m anna_b200.build); "
+            "there is no CPU fallback for this op.")
+    return op
+
+
+def run_gqa_decode_fused(*, query, key, value, visible_lengths, scaling, gate=None):
+    op = _resolve("gqa_decode_fused")
+    if gate is None:
+        return op(query, key, value, visible_lengths, float(scaling))
+    return op(query, key, value, visible_lengths, float(scaling), gate)
+
+
+def run_gqa_decode_splitkv_fused(*, query, key, value, scaling, block_size, gate=None):
+    op = _resolve("gqa_decode_splitkv_fused")
+    if gate is None:
+        return op(query, key, value, float(scaling), int(block_size))
+    return op(query, key, value, float(scaling), int(block_size), gate)
+
+
+def run_gqa_decode_splitkv_fused_out(*, query, key, value, output, partial_stats, partial_values, scaling, block_size,
+                                     gate=None):
+    op = _resolve("gqa_decode_splitkv_fused_out")
+    if gate is None:
+        return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size))
+    return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size), gate)
+
+
+def run_paged_gqa_decode_fused(*, query, key_pages, value_pages, page_table, visible_lengths, scaling, gate=None):
+    op = _resolve("paged_gqa_decode_fused")
+    if gate is None:
+        return op(query, key_pages, value_pages, page_table, visible_lengths, float(scaling))
+    return op(query, key_pages, value_pages, page_table, visible_lengths, float(scaling), gate)

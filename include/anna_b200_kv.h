@@ -1,0 +1,182 @@
+/*
+ * anna_b200_kv.h - C ABI of libanna_b200_kv.so: the quantized paged KV-cache path of Anna for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes, element strides and a CUDA stream, enqueues its kernels on
+ * that stream without synchronising, and returns an int status (0 = ok).  A non-zero status comes with a message
+ * from anna_kv_last_error().  Nothing here allocates or frees device memory; scratch is passed in by the caller.  No entry point ever traps or aborts the device: bad page ids are skipped and recorded in the
+ * optional device status word.
+ *
+ * Citations name the interface of the reference (funkpopo/Anna) that each entry point stands in for.
+ */
+#ifndef ANNA_B200_KV_H_
+#define ANNA_B200_KV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of q / K / V / metadata tensors */
+#define ANNA_DTYPE_F32 0
+#define ANNA_DTYPE_F16 1
+#define ANNA_DTYPE_BF16 2
+
+/* status codes */
+#define ANNA_OK 0
+#define ANNA_ERR_INVALID 1     /* bad argument (shape, stride, null pointer) */
+#define ANNA_ERR_UNSUPPORTED 2 /* combination not compiled in (head_dim, dtype, group size) */
+#define ANNA_ERR_CUDA 3        /* a CUDA runtime call failed */
+#define ANNA_ERR_WORKSPACE 4   /* caller-provided scratch is too small */
+
+/* bits of the device status word written by kernels (OR-ed in, never cleared by the library) */
+#define ANNA_DEV_BAD_PAGE 1u   /* a block-table entry needed by a write was < 0 or >= num_pages */
+
+typedef void* anna_stream_t; /* cudaStream_t */
+
+/* Message of the last non-zero status returned on the calling thread. */
+const char* anna_kv_last_error(void);
+int anna_kv_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
+ * (row, query head, chunk) leaves a partial in caller-owned float32 buffers
+ *   partial_stats  [B, Hq, chunk_capacity, 2]   (running max, denominator)
+ *   partial_values [B, Hq, chunk_capacity, D]
+ * which a second pass merges: the workspace contract of gqa_decode_splitkv_fused_out
+ * (src/anna/model/custom_ops/gated_delta_fused_op.sycl:4634-4706, :1521-1556; capacity may exceed the need).
+ * chunk_tokens > 0 is used as given (the reference's `block_size`, src/anna/model/turboquant.py:22);
+ * chunk_tokens == 0 asks the library to choose.  Context lengths are only known on the device, so the choice is
+ * made from the host-visible upper bound: anna_decode_plan(batch, kv_heads, max_len) returns the chunk length the
+ * library will use and the number of chunks the scratch must hold.
+ */
+int anna_decode_plan(int batch, int kv_heads, int64_t max_len, int* chunk_tokens, int* num_chunks);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Unquantized paged cache.
+ */
+
+/*
+ * Write T new tokens per row into paged K/V: token (past_lengths[b] + t) of row b goes to
+ * pages[page_table[b][pos / S], h, pos % S, :].  Batched form of Qwen3DynamicCache._write_pages
+ * (src/anna/model/ops.py:748-777).
+ *   k_new, v_new   [B, Hkv, T, D] with element strides (kn_stride_b, kn_stride_h, kn_stride_t); last dim contiguous
+ *   key_pages, value_pages  [P, Hkv, S, D] contiguous
+ *   page_table     int32 [B, table_stride >= blocks];   past_lengths  int32 [B]
+ *   status         optional device int32 (may be NULL): ANNA_DEV_BAD_PAGE is OR-ed in when a page id is invalid
+ */
+int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
+                        int64_t kn_stride_t, void* key_pages, void* value_pages, const int32_t* page_table,
+                        int64_t table_stride, const int32_t* past_lengths, int batch, int kv_heads, int new_tokens,
+                        int head_dim, int block_size, int64_t num_pages, int64_t max_blocks, int dtype,
+                        int32_t* status, anna_stream_t stream);
+
+/*
+ * Single-token GQA decode over paged K/V.  Stands in for torch.ops.anna.paged_gqa_decode_fused
+ * (gated_delta_fused_op.sycl:5206-5360, schema :7670-7679): same masking (entries < 0 or >= P are skipped,
+ * visible length clamped to [0, max_blocks * S]), fp32 online softmax, optional sigmoid(gate) epilogue, rows with
+ * no visible key give zeros.  Split-K over the context with a second combine pass.
+ *   q, out         [B, Hq, D] with element strides (stride_b, stride_h); last dim contiguous
+ *   gate           NULL or [B, Hq, D] with element strides (gate_stride_b, gate_stride_h)
+ *   visible_lengths int64 [B]
+ *   partial_stats, partial_values, chunk_capacity, chunk_tokens: split-K scratch (see above); the plan bound is
+ *                  max_blocks * block_size tokens
+ */
+int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* key_pages,
+                          const void* value_pages, const int32_t* page_table, int64_t table_stride,
+                          const int64_t* visible_lengths, const void* gate, int64_t gate_stride_b,
+                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                          float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
+                          int batch, int q_heads, int kv_heads, int head_dim, int block_size, int64_t num_pages,
+                          int64_t max_blocks, float scaling, int dtype, anna_stream_t stream);
+
+/*
+ * Single-token GQA decode over dense K/V [B, Hkv, L, D] (arbitrary batch/head/token strides, last dim contiguous)
+ * with per-row visible lengths.  Stands in for torch.ops.anna.gqa_decode_fused (gated_delta_fused_op.sycl:4339-4479)
+ * and, with visible_lengths == NULL (all L keys visible), for gqa_decode_splitkv_fused / _out (:4494-4769).
+ */
+int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* key, const void* value,
+                    int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t, const int64_t* visible_lengths,
+                    const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out, int64_t out_stride_b,
+                    int64_t out_stride_h, float* partial_stats, float* partial_values, int chunk_capacity,
+                    int chunk_tokens, int batch, int q_heads, int kv_heads, int64_t key_len, int head_dim,
+                    float scaling, int dtype, anna_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * TurboQuant packed paged cache.
+ *
+ * Packed pool: uint8 [P, Hkv, chunk_bytes]; one chunk holds S tokens of one kv head:
+ *   key codes  S x (D*bits/8)  | key norms S x f32 | key residual norms S x f32 |
+ *   value codes S x (D*sb/8)   | value scales S x (D/group) x dtype | value zeros S x (D/group) x dtype
+ * (sb = 2 for bits == 2 else 4, as in quantize_turboquant_values, src/anna/model/turboquant.py:214), every
+ * sub-array starting on a 16-byte boundary and the chunk padded to 128 bytes; anna_tq_page_layout reports the
+ * offsets.  Quantized token j of a row lives in block j / S of the row's table, slot j % S.
+ * The newest `residual_len` tokens of a row stay un-quantized in a ring: window [slots, 2, Hkv, R, D] (index 0 =
+ * keys, 1 = values), token position p in ring slot p % R.
+ */
+typedef struct anna_tq_layout {
+  int32_t key_bytes;   /* packed key bytes per token */
+  int32_t value_bytes; /* packed value bytes per token */
+  int32_t groups;      /* value groups per token */
+  int32_t off_kcodes, off_knorm, off_krnorm, off_vdata, off_vscale, off_vzero;
+  int32_t chunk_bytes;
+} anna_tq_layout;
+
+int anna_tq_page_layout(int head_dim, int bits, int block_size, int dtype, int value_group, anna_tq_layout* out);
+
+/*
+ * Append T tokens per row: the batched, fused form of TurboQuantKVRow.append (src/anna/model/turboquant.py:1027-1140)
+ * driven by Qwen3DynamicCache._update_turboquant_layer (src/anna/model/ops.py:618-660).  With L = old_lengths[b] and
+ * L' = L + T, every token whose position falls below L' - R and that is not yet quantized is rotated, indexed,
+ * sign-projected, value-quantized (turboquant.py:199-230, :255-272) and bit-packed straight into its page; tokens that
+ * stay inside the window are written to the ring.  A ring slot is read before the same warp overwrites it.
+ *   k_new, v_new  [B, Hkv, T, D] element strides (kn_stride_b, kn_stride_h, kn_stride_t)
+ *   old_lengths   int32 [B] (lengths before this call);  window_slots int32 [B] (ring index of each row)
+ *   signs1, signs2  float32 [D] (+1 / -1): rotation and QJL sign vectors;  centroids float32 [2^(bits-1)];
+ *   boundaries    float32 [2^(bits-1) - 1]
+ */
+int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
+                   int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                   void* window, const int32_t* window_slots, const int32_t* old_lengths, const float* signs1,
+                   const float* signs2, const float* centroids, const float* boundaries, int batch, int kv_heads,
+                   int new_tokens, int head_dim, int block_size, int residual_len, int bits, int value_group,
+                   int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status, anna_stream_t stream);
+
+/*
+ * Single-token GQA decode over [packed quantized prefix | un-quantized window].  Batched, paged form of
+ * TurboQuantKVRow.decode_attention (src/anna/model/turboquant.py:1181-1293) /
+ * Qwen3DynamicCache.turboquant_single_token_decode_attention (src/anna/model/ops.py:1024-1070) and of
+ * torch.ops.anna.gqa_decode_splitkv_turboquant_fused_out (gated_delta_fused_op.sycl:4771-5094), except that keys are
+ * scored from their packed codes in the rotated basis (the identity of turboquant_key_attention_scores,
+ * turboquant.py:290-332) instead of from a dense de-quantized copy.
+ *   lengths   int32 [B]: total tokens per row (quantized = max(0, L - R), window = min(L, R)); L == 0 gives zeros
+ *   the split-K plan bound is max_blocks * block_size + residual_len tokens
+ */
+int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* packed_pages,
+                         const int32_t* block_table, int64_t table_stride, const void* window,
+                         const int32_t* window_slots, const int32_t* lengths, const float* signs1,
+                         const float* signs2, const float* centroids, const void* gate, int64_t gate_stride_b,
+                         int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                         float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
+                         int batch, int q_heads, int kv_heads, int head_dim, int block_size, int residual_len,
+                         int bits, int value_group, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                         anna_stream_t stream);
+
+/*
+ * De-quantize the packed prefix of each row to dense [B, Hkv, Lq_max, D] keys and values in the cache dtype (element
+ * strides out_stride_b / _h / _t; rows shorter than max_quantized_len are left untouched beyond their length).
+ * Stands in for TurboQuantKVRow._materialize_quantized_prefix (src/anna/model/turboquant.py:925-984), i.e.
+ * dequantize_turboquant_keys (:275-287) + dequantize_turboquant_values (:233-252).
+ */
+int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                        const int32_t* quantized_lengths, const float* signs1, const float* signs2,
+                        const float* centroids, void* key_out, void* value_out, int64_t out_stride_b,
+                        int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads, int head_dim,
+                        int block_size, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
+                        int64_t max_quantized_len, int dtype, anna_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANNA_B200_KV_H_ */

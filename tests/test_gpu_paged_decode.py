@@ -1,0 +1,167 @@
+"""GPU parity of the un-quantized decode ops against the CPU oracle.
+
+Shapes follow the reference's kernel tests (tests/test_fused_op_xpu.py:490-944): dense decode with ragged visible
+lengths, split-KV with strided K/V and fused gate, caller-owned workspace, paged decode with a block table.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from anna_b200 import fused_ops
+from tests.helpers import ATOL, error_stats, reference_decode, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _pack_paged_kv(key, value, *, block_size, permute_seed=None):
+    batch, heads, key_len, dim = key.shape
+    per_row = (key_len + block_size - 1) // block_size
+    total = batch * per_row
+    order = torch.arange(total)
+    if permute_seed is not None:
+        order = torch.randperm(total, generator=torch.Generator().manual_seed(permute_seed))
+    key_pages = key.new_zeros((total, heads, block_size, dim))
+    value_pages = value.new_zeros((total, heads, block_size, dim))
+    table = torch.full((batch, per_row), -1, dtype=torch.int32, device=key.device)
+    for b in range(batch):
+        for blk in range(per_row):
+            pid = int(order[b * per_row + blk])
+            start = blk * block_size
+            take = min(block_size, key_len - start)
+            key_pages[pid, :, :take] = key[b, :, start:start + take]
+            value_pages[pid, :, :take] = value[b, :, start:start + take]
+            table[b, blk] = pid
+    return key_pages, value_pages, table
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("heads,kv_heads,dim,key_len", [(8, 2, 64, 19), (16, 4, 256, 777), (8, 8, 128, 130),
+                                                        (16, 2, 128, 300)])
+def test_gqa_decode_fused_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, key_len):
+    torch.manual_seed(0)
+    query = torch.randn(2, heads, 1, dim, device=cuda_device, dtype=dtype)
+    key = torch.randn(2, kv_heads, key_len, dim, device=cuda_device, dtype=dtype)
+    value = torch.randn(2, kv_heads, key_len, dim, device=cuda_device, dtype=dtype)
+    visible = torch.tensor([key_len, max(1, key_len * 2 // 3)], device=cuda_device, dtype=torch.long)
+    out = fused_ops.run_gqa_decode_fused(query=query, key=key, value=value, visible_lengths=visible,
+                                         scaling=dim ** -0.5)
+    expected = reference_decode(query, key, value, visible.tolist(), dim ** -0.5)
+    assert out.shape == query.shape and out.dtype == dtype
+    np.testing.assert_allclose(to_np(out), expected, atol=ATOL[dtype], rtol=ATOL[dtype])
+
+
+def test_gqa_decode_fused_gate_layouts_agree(cuda_device):
+    torch.manual_seed(11)
+    batch, heads, dim = 2, 8, 64
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    key = torch.randn(batch, 2, 23, dim, device=cuda_device, dtype=torch.bfloat16)
+    value = torch.randn_like(key)
+    visible = torch.tensor([23, 17], device=cuda_device, dtype=torch.long)
+    gate_3d = torch.randn(batch, 1, heads * dim, device=cuda_device, dtype=torch.bfloat16)
+    gate_4d = gate_3d.view(batch, 1, heads, dim).transpose(1, 2)
+    out_3d = fused_ops.run_gqa_decode_fused(query=query, key=key, value=value, visible_lengths=visible,
+                                            scaling=dim ** -0.5, gate=gate_3d)
+    out_4d = fused_ops.run_gqa_decode_fused(query=query, key=key, value=value, visible_lengths=visible,
+                                            scaling=dim ** -0.5, gate=gate_4d)
+    expected = reference_decode(query, key, value, visible.tolist(), dim ** -0.5, gate=gate_4d)
+    assert torch.equal(out_3d, out_4d)
+    np.testing.assert_allclose(to_np(out_4d), expected, atol=3e-2, rtol=3e-2)
+
+
+def test_splitkv_accepts_strided_kv_and_fuses_gate(cuda_device):
+    torch.manual_seed(20)
+    heads, kv_heads, dim, key_len, capacity = 8, 2, 64, 257, 512
+    query = torch.randn(1, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    key_storage = torch.empty(1, kv_heads, capacity, dim, device=cuda_device, dtype=torch.bfloat16)
+    value_storage = torch.empty_like(key_storage)
+    key_storage[:, :, :key_len].normal_()
+    value_storage[:, :, :key_len].normal_()
+    key, value = key_storage[:, :, :key_len], value_storage[:, :, :key_len]
+    gate = torch.randn(1, 1, heads * dim, device=cuda_device, dtype=torch.bfloat16).view(1, 1, heads, dim).transpose(1, 2)
+    assert not key.is_contiguous()
+    out = fused_ops.run_gqa_decode_splitkv_fused(query=query, key=key, value=value, scaling=dim ** -0.5,
+                                                 block_size=64, gate=gate)
+    expected = reference_decode(query, key, value, [key_len], dim ** -0.5, gate=gate)
+    np.testing.assert_allclose(to_np(out), expected, atol=3e-2, rtol=3e-2)
+
+
+def test_splitkv_out_reuses_workspace_and_accepts_strided_query(cuda_device):
+    torch.manual_seed(22)
+    heads, kv_heads, dim, key_len, block = 8, 2, 64, 193, 64
+    blocks = (key_len + block - 1) // block
+    query = torch.randn(1, heads, 1, dim * 2, device=cuda_device, dtype=torch.bfloat16)[..., ::2]
+    key = torch.randn(1, kv_heads, 256, dim, device=cuda_device, dtype=torch.bfloat16)[:, :, :key_len]
+    value = torch.randn(1, kv_heads, 256, dim, device=cuda_device, dtype=torch.bfloat16)[:, :, :key_len]
+    output = torch.empty_like(query)
+    stats = torch.empty(1, heads, blocks + 2, 2, device=cuda_device, dtype=torch.float32)
+    values = torch.empty(1, heads, blocks + 2, dim, device=cuda_device, dtype=torch.float32)
+    assert not query.is_contiguous()
+    returned = fused_ops.run_gqa_decode_splitkv_fused_out(query=query, key=key, value=value, output=output,
+                                                          partial_stats=stats, partial_values=values,
+                                                          scaling=dim ** -0.5, block_size=block)
+    expected = reference_decode(query, key, value, [key_len], dim ** -0.5)
+    assert returned.untyped_storage().data_ptr() == output.untyped_storage().data_ptr()
+    np.testing.assert_allclose(to_np(output), expected, atol=3e-2, rtol=3e-2)
+
+
+def test_splitkv_out_rejects_small_workspace(cuda_device):
+    query = torch.randn(1, 8, 1, 64, device=cuda_device, dtype=torch.bfloat16)
+    key = torch.randn(1, 2, 200, 64, device=cuda_device, dtype=torch.bfloat16)
+    stats = torch.empty(1, 8, 2, 2, device=cuda_device, dtype=torch.float32)
+    values = torch.empty(1, 8, 2, 64, device=cuda_device, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="capacity"):
+        fused_ops.run_gqa_decode_splitkv_fused_out(query=query, key=key, value=key.clone(),
+                                                   output=torch.empty_like(query), partial_stats=stats,
+                                                   partial_values=values, scaling=0.125, block_size=64)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("heads,kv_heads,dim,key_len,block", [(16, 4, 256, 4096, 32), (32, 8, 128, 1000, 16),
+                                                             (8, 2, 64, 45, 16)])
+def test_paged_decode_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, key_len, block):
+    torch.manual_seed(0)
+    batch = 3
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=dtype)
+    key = torch.randn(batch, kv_heads, key_len, dim, device=cuda_device, dtype=dtype)
+    value = torch.randn(batch, kv_heads, key_len, dim, device=cuda_device, dtype=dtype)
+    key_pages, value_pages, table = _pack_paged_kv(key, value, block_size=block, permute_seed=5)
+    visible = torch.tensor([key_len, key_len // 2 + 1, 1], device=cuda_device, dtype=torch.long)
+    gate = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=dtype)
+    out = fused_ops.run_paged_gqa_decode_fused(query=query, key_pages=key_pages, value_pages=value_pages,
+                                               page_table=table, visible_lengths=visible, scaling=dim ** -0.5,
+                                               gate=gate)
+    expected = reference_decode(query, key, value, visible.tolist(), dim ** -0.5, gate=gate)
+    max_abs, rel = error_stats(to_np(out), expected)
+    assert max_abs <= ATOL[dtype] * 2 and rel <= ATOL[dtype], (max_abs, rel)
+
+
+def test_paged_decode_skips_holes_and_zero_rows(cuda_device):
+    """Entries < 0 are skipped and a row without visible keys gives zeros (.sycl:5310-5313, :5342)."""
+    torch.manual_seed(3)
+    heads, kv_heads, dim, block = 8, 2, 64, 16
+    key = torch.randn(2, kv_heads, 64, dim, device=cuda_device, dtype=torch.bfloat16)
+    value = torch.randn_like(key)
+    query = torch.randn(2, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    key_pages, value_pages, table = _pack_paged_kv(key, value, block_size=block)
+    table[0, 1] = -1
+    visible = torch.tensor([64, 0], device=cuda_device, dtype=torch.long)
+    out = fused_ops.run_paged_gqa_decode_fused(query=query, key_pages=key_pages, value_pages=value_pages,
+                                               page_table=table, visible_lengths=visible, scaling=dim ** -0.5)
+    keep = [t for t in range(64) if not (16 <= t < 32)]
+    expected = reference_decode(query[:1], key[:1, :, keep], value[:1, :, keep], [len(keep)], dim ** -0.5)
+    np.testing.assert_allclose(to_np(out[:1]), expected, atol=2e-2, rtol=2e-2)
+    assert torch.count_nonzero(out[1]) == 0
+
+
+def test_ops_reject_cpu_tensors_and_bad_shapes(cuda_device):
+    query = torch.randn(1, 8, 1, 64)
+    key = torch.randn(1, 2, 5, 64)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        fused_ops.run_gqa_decode_fused(query=query, key=key, value=key, visible_lengths=torch.tensor([5]), scaling=1.0)
+    q = torch.randn(1, 6, 1, 64, device=cuda_device, dtype=torch.bfloat16)
+    k = torch.randn(1, 4, 5, 64, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="divisible"):
+        fused_ops.run_gqa_decode_fused(query=q, key=k, value=k, visible_lengths=torch.tensor([5], device=cuda_device),
+                                       scaling=1.0)
