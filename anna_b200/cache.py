@@ -278,8 +278,6 @@ class Qwen3DynamicCache:
         """Append ``[B, Hkv, T, D]`` keys / values; returns ``(K | None, V | None, past_lengths)`` (ops.py:662-746)."""
         if key_states.shape != value_states.shape or key_states.dim() != 4:
             raise ValueError("update expects matching [batch, kv_heads, tokens, head_dim] key and value tensors")
-        if not key_states.is_cuda:
-            raise RuntimeError("anna_b200 caches live on a CUDA device; there is no CPU fallback for update().")
         if self.uses_turboquant_for_layer(layer_idx):
             return self._update_turboquant_layer(key_states, value_states, layer_idx,
                                                  require_dense_cache=require_dense_cache)
@@ -325,6 +323,8 @@ class Qwen3DynamicCache:
         if value_states.stride() != key_states.stride():
             key_states, value_states = key_states.contiguous(), value_states.contiguous()
         device = key_states.device
+        if device.type != "cuda":
+            raise RuntimeError("anna_b200 caches live on a CUDA device; there is no CPU fallback for update().")
         batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
         past_dev = _i32(past, device)
         assert layer.key_pages is not None and layer.value_pages is not None

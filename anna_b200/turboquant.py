@@ -32,9 +32,15 @@ def _i32(values, device: torch.device) -> torch.Tensor:
     return torch.tensor(values, dtype=torch.int32, device=device)
 
 
+def _require_cuda(tensor: torch.Tensor, what: str) -> None:
+    if tensor.device.type != "cuda":
+        raise RuntimeError(f"{what}: tensors must live on a CUDA device; there is no CPU fallback for this path.")
+
+
 def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_states: torch.Tensor,
                      table_dev: torch.Tensor | None, slots: list[int], past: list[int]) -> None:
     """Append ``[B, Hkv, T, D]`` to B rows of one layer: ring update + quantize-on-overflow + page scatter."""
+    _require_cuda(key_states, "TurboQuant append")
     key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
     if value_states.stride() != key_states.stride():
         key_states, value_states = key_states.contiguous(), value_states.contiguous()
@@ -58,6 +64,7 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
                      slots: list[int], lengths: list[int], scaling: float,
                      gate: torch.Tensor | None) -> torch.Tensor:
     """Decode ``[B, Hq, 1, D]`` queries against B rows of one layer (packed prefix + window ring)."""
+    _require_cuda(query_states, "TurboQuant decode")
     query = query_states if query_states.stride(3) == 1 else query_states.contiguous()
     if gate is not None and gate.stride(3) != 1:
         gate = gate.contiguous()
@@ -87,6 +94,7 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
 def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, quantized_lengths: list[int],
                           key_out: torch.Tensor, value_out: torch.Tensor) -> None:
     """De-quantize the packed prefix of B rows into dense ``[B, Hkv, Lq_max, D]`` tensors (strided views allowed)."""
+    _require_cuda(key_out, "TurboQuant materialize")
     device = key_out.device
     if key_out.stride() != value_out.stride() or key_out.stride(3) != 1:
         raise ValueError("materialize outputs must share strides and be contiguous in the last dimension")
@@ -171,8 +179,6 @@ class TurboQuantKVRow:
                 f"TurboQuantKVRow key/value shape mismatch: {tuple(key_states.shape)} vs {tuple(value_states.shape)}")
         if key_states.shape[1] <= 0:
             return
-        if not key_states.is_cuda:
-            raise RuntimeError("TurboQuantKVRow lives on a CUDA device; there is no CPU fallback.")
         if not self.initialized:
             pool = self.pool or TurboQuantLayerPool(block_size=16)
             self._bind(pool, kv_heads=int(key_states.shape[0]), head_dim=int(key_states.shape[-1]),

@@ -1,0 +1,119 @@
+"""GPU: the cache object end to end on the un-quantized paged path and the TurboQuant dense views."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from anna_b200 import KVCacheConfig, Qwen3DynamicCache, Qwen3PageAllocator, fused_ops
+from tests.helpers import TqPair, outlier_kv, reference_decode, to_np
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def test_paged_update_then_decode_matches_oracle(cuda_device):
+    """Config-2-like: ragged rows, pages handed out by the allocator, decode through paged_attention_state."""
+    torch.manual_seed(0)
+    config = KVCacheConfig(num_hidden_layers=2, cache_block_size=16)
+    allocator = Qwen3PageAllocator(config)
+    lengths = [37, 16, 90]
+    heads, kv_heads, dim = 16, 4, 128
+    caches, dense = [], []
+    for n in lengths:  # prefill one row at a time, as the scheduler does, then stack
+        cache = Qwen3DynamicCache(config, allocator=allocator)
+        k = torch.randn(1, kv_heads, n, dim, device=cuda_device, dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        gathered_k, gathered_v, past = cache.update(k, v, 1)
+        assert past.tolist() == [0] and torch.equal(gathered_k, k) and torch.equal(gathered_v, v)
+        caches.append(cache)
+        dense.append((k, v))
+    stacked = Qwen3DynamicCache.stack(caches, config)
+    for step in range(3):
+        k1 = torch.randn(3, kv_heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+        v1 = torch.randn_like(k1)
+        none_k, none_v, past = stacked.update(k1, v1, 1, require_dense_cache=False)
+        assert none_k is None and none_v is None and past.tolist() == [n + step for n in lengths]
+        dense = [(torch.cat((k, k1[i:i + 1]), dim=2), torch.cat((v, v1[i:i + 1]), dim=2))
+                 for i, (k, v) in enumerate(dense)]
+        key_pages, value_pages, table, visible = stacked.paged_attention_state(1)
+        assert table.dtype == torch.int32 and visible.tolist() == [n + step + 1 for n in lengths]
+        query = torch.randn(3, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+        out = fused_ops.run_paged_gqa_decode_fused(query=query, key_pages=key_pages, value_pages=value_pages,
+                                                   page_table=table, visible_lengths=visible, scaling=dim ** -0.5)
+        for i, (k, v) in enumerate(dense):
+            want = reference_decode(query[i:i + 1], k, v, [k.shape[2]], dim ** -0.5)
+            np.testing.assert_allclose(to_np(out[i:i + 1]), want, atol=2e-2, rtol=2e-2)
+    gathered_k, gathered_v, visible = stacked._gather_layer_cache(1)
+    for i, (k, v) in enumerate(dense):
+        assert torch.equal(gathered_k[i, :, :k.shape[2]], k[0]) and torch.equal(gathered_v[i, :, :v.shape[2]], v[0])
+        assert torch.count_nonzero(gathered_k[i, :, k.shape[2]:]) == 0
+    clone = stacked.clone()
+    assert clone.page_tables[1] != stacked.page_tables[1]
+    ck, cv, _ = clone._gather_layer_cache(1)
+    assert torch.equal(ck, gathered_k) and torch.equal(cv, gathered_v)
+    used = allocator.layers[1].used_pages()
+    clone.release()
+    assert allocator.layers[1].used_pages() < used
+    stacked.release()
+    assert allocator.layers[1].used_pages() == 0 and allocator.layers[0].capacity() == 0
+
+
+def test_paged_block_tables_on_device_match_reference(cuda_device):
+    want = json.loads((GOLDEN / "paged_block_tables.json").read_text())
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=16)
+    cache = Qwen3DynamicCache(config, batch_size=2)
+    kv = torch.zeros(2, 2, 40, 64, device=cuda_device, dtype=torch.bfloat16)
+    cache.update(kv, kv, 0, require_dense_cache=False)
+    for _ in range(9):
+        cache.update(kv[:, :, :1], kv[:, :, :1], 0, require_dense_cache=False)
+    state = cache.paged_attention_state(0)
+    assert state[2].cpu().tolist() == want["after_9_steps"]
+
+
+def test_prefix_shared_pages_are_not_rewritten(cuda_device):
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=4)
+    allocator = Qwen3PageAllocator(config)
+    prompt = torch.arange(10).reshape(1, 10)
+    first = Qwen3DynamicCache(config, allocator=allocator)
+    first.set_prompt_token_ids(prompt)
+    k = torch.randn(1, 2, 10, 64, device=cuda_device, dtype=torch.bfloat16)
+    first.update(k, k, 0, require_dense_cache=False)
+    second = Qwen3DynamicCache(config, allocator=allocator)
+    second.set_prompt_token_ids(prompt)
+    other = torch.randn_like(k)
+    got_k, _, _ = second.update(other, other, 0)
+    assert second.page_tables[0][0][:2] == first.page_tables[0][0][:2]
+    assert torch.equal(got_k[:, :, :8], k[:, :, :8])      # shared blocks keep the first sequence's bytes
+    assert torch.equal(got_k[:, :, 8:], other[:, :, 8:])  # the private tail is this sequence's
+
+
+def test_turboquant_dense_view_and_lifecycle(cuda_device):
+    """update(require_dense_cache=True) returns [de-quantized prefix | exact window] (ops.py:642-660)."""
+    pair = TqPair(device=cuda_device, batch=2, kv_heads=2, head_dim=128, bits=4, residual_len=4, block_size=16,
+                  dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(3)
+    k = outlier_kv(gen, (2, 2, 21, 128), torch.bfloat16)
+    v = outlier_kv(gen, (2, 2, 21, 128), torch.bfloat16)
+    dense_k, dense_v, past = pair.cache.update(k.to(cuda_device), v.to(cuda_device), 0)
+    for b, row in enumerate(pair.rows):
+        row.append(to_np(k[b]), to_np(v[b]))
+        want_k, want_v = row.materialize()
+        np.testing.assert_array_equal(to_np(dense_v[b]), want_v)
+        np.testing.assert_array_equal(to_np(dense_k[b, :, 17:]), want_k[:, 17:])
+        np.testing.assert_allclose(to_np(dense_k[b]), want_k, atol=6e-2, rtol=2e-2)
+    assert float(((dense_k.float().cpu() - k.float()) ** 2).mean()) < 1.0  # tests/test_model_shapes.py:374
+    assert past.tolist() == [0, 0] and dense_k.shape == (2, 2, 21, 128)
+    pair.assert_bit_exact()
+    pool = pair.pool
+    clone = pair.cache.clone()
+    assert pool.used_pages() == 4 and clone.turboquant_rows[0][0].block_table != pair.cache.turboquant_rows[0][0].block_table
+    ck, cv, _ = clone._gather_layer_cache(0)
+    assert torch.equal(ck, dense_k) and torch.equal(cv, dense_v)
+    clone.release()
+    pair.cache.release()
+    assert pool.used_pages() == 0
+    assert pair.cache.allocator.trim() > 0 and pool.packed_pages is None
