@@ -42,19 +42,19 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32,
                                     c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),
     "anna_paged_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_i64,
-                                      c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32,
-                                      c_i64, c_i64, c_f32, c_i32, c_ptr]),
+                                      c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i32,
+                                      c_i32, c_i64, c_i64, c_f32, c_i32, c_ptr]),
     "anna_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64,
-                                c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i32,
-                                c_f32, c_i32, c_ptr]),
+                                c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i64,
+                                c_i32, c_f32, c_i32, c_ptr]),
     "anna_tq_page_layout": (c_i32, [c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.POINTER(TqLayout)]),
     "anna_tq_append": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr,
                                c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,
                                c_i64, c_i32, c_ptr, c_ptr]),
     "anna_tq_paged_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                      c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32,
-                                     c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_f32,
-                                     c_i32, c_ptr]),
+                                     c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64,
+                                     c_f32, c_i32, c_ptr]),
     "anna_tq_materialize": (c_i32, [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64,
                                     c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i64, c_i32, c_ptr]),
 }

@@ -1,29 +1,8 @@
 // Single-token GQA decode over un-quantized K/V: paged pools or dense strided tensors.
 #include "decode_core.cuh"
+#include "decode_params.cuh"
 
 namespace anna {
-
-struct DenseDecodeParams {
-  const void* q;
-  int64_t q_stride_b, q_stride_h;
-  const void* key;
-  const void* value;
-  // paged addressing (page_table != nullptr): element offset = page_id * page_stride + (t % S) * D
-  const int32_t* page_table;
-  int64_t table_stride;
-  int64_t page_stride;
-  int64_t num_pages;
-  int block_size;
-  // dense addressing: element offset = b * kv_stride_b + h * kv_stride_h + t * kv_stride_t
-  int64_t kv_stride_b, kv_stride_h, kv_stride_t;
-  const int64_t* visible_lengths;  // may be null in dense mode: all `max_len` keys visible
-  int64_t max_len;
-  float* stats;
-  float* values;
-  int q_heads, kv_heads, groups;
-  int chunk_tokens, num_chunks, chunk_capacity;
-  float scaling;
-};
 
 template <typename T, int D, int G>
 __global__ void __launch_bounds__(kDecodeThreads)
@@ -120,8 +99,8 @@ static int launch_dense_split(const DenseDecodeParams& p, int batch, cudaStream_
 
 static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_stride_b, int64_t gate_stride_h,
                             void* out, int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
-                            float* partial_values, int chunk_capacity, int chunk_tokens_in, int batch, int head_dim,
-                            int dtype, cudaStream_t stream) {
+                            float* partial_values, int chunk_capacity, int chunk_tokens_in, int32_t* split_counters,
+                            int batch, int head_dim, int dtype, cudaStream_t stream) {
   int chunk_tokens = 0, num_chunks = 0;
   int rc = resolve_split(batch, p.kv_heads, p.max_len, chunk_tokens_in, chunk_capacity, partial_stats, partial_values,
                          &chunk_tokens, &num_chunks);
@@ -132,12 +111,20 @@ static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_
   p.chunk_tokens = chunk_tokens;
   p.num_chunks = num_chunks;
   p.chunk_capacity = chunk_capacity;
-  const int gpad = padded_group(p.groups);
-  rc = ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
-    return ANNA_DISPATCH_DIM(head_dim, D, [&]() -> int {
-      return ANNA_DISPATCH_GROUP(gpad, G, [&]() -> int { return launch_dense_split<T, D, G>(p, batch, stream); });
+  if (dense_split_mma_applicable(p, head_dim, dtype)) {
+    if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
+      p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
+      return launch_dense_split_mma(p, batch, head_dim, dtype, stream);
+    }
+    rc = launch_dense_split_mma(p, batch, head_dim, dtype, stream);
+  } else {
+    const int gpad = padded_group(p.groups);
+    rc = ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
+      return ANNA_DISPATCH_DIM(head_dim, D, [&]() -> int {
+        return ANNA_DISPATCH_GROUP(gpad, G, [&]() -> int { return launch_dense_split<T, D, G>(p, batch, stream); });
+      });
     });
-  });
+  }
   if (rc != ANNA_OK) return rc;
   return launch_split_combine(ws, nullptr, p.visible_lengths, p.visible_lengths ? -1 : p.max_len, p.max_len, gate,
                               gate_stride_b, gate_stride_h, out, out_stride_b, out_stride_h, batch, p.q_heads,
@@ -173,7 +160,8 @@ extern "C" int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t 
                                      const int64_t* visible_lengths, const void* gate, int64_t gate_stride_b,
                                      int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
                                      float* partial_stats, float* partial_values, int chunk_capacity,
-                                     int chunk_tokens, int batch, int q_heads, int kv_heads, int head_dim,
+                                     int chunk_tokens, int32_t* split_counters, int batch, int q_heads, int kv_heads,
+                                     int head_dim,
                                      int block_size, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
                                      anna_stream_t stream) {
   ANNA_REQUIRE(q && key_pages && value_pages && page_table && visible_lengths && out,
@@ -189,12 +177,15 @@ extern "C" int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t 
   p.page_table = page_table; p.table_stride = table_stride;
   p.page_stride = (int64_t)kv_heads * block_size * head_dim;
   p.num_pages = num_pages; p.block_size = block_size;
+  p.block_shift = -1;
+  for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == block_size) p.block_shift = sh;
   p.visible_lengths = visible_lengths;
   p.max_len = max_blocks * (int64_t)block_size;
   p.q_heads = q_heads; p.kv_heads = kv_heads; p.groups = q_heads / kv_heads;
   p.scaling = scaling;
   return run_dense_decode(p, gate, gate_stride_b, gate_stride_h, out, out_stride_b, out_stride_h, partial_stats,
-                          partial_values, chunk_capacity, chunk_tokens, batch, head_dim, dtype, (cudaStream_t)stream);
+                          partial_values, chunk_capacity, chunk_tokens, split_counters, batch, head_dim, dtype,
+                          (cudaStream_t)stream);
 }
 
 extern "C" int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* key,
@@ -202,7 +193,8 @@ extern "C" int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stri
                                const int64_t* visible_lengths, const void* gate, int64_t gate_stride_b,
                                int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
                                float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
-                               int batch, int q_heads, int kv_heads, int64_t key_len, int head_dim, float scaling,
+                               int32_t* split_counters, int batch, int q_heads, int kv_heads, int64_t key_len,
+                               int head_dim, float scaling,
                                int dtype, anna_stream_t stream) {
   ANNA_REQUIRE(q && key && value && out, "anna_gqa_decode: null pointer argument");
   ANNA_REQUIRE(batch > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
@@ -215,11 +207,13 @@ extern "C" int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stri
   p.q = q; p.q_stride_b = q_stride_b; p.q_stride_h = q_stride_h;
   p.key = key; p.value = value;
   p.page_table = nullptr;
+  p.block_size = 1; p.block_shift = 0;
   p.kv_stride_b = kv_stride_b; p.kv_stride_h = kv_stride_h; p.kv_stride_t = kv_stride_t;
   p.visible_lengths = visible_lengths;
   p.max_len = key_len;
   p.q_heads = q_heads; p.kv_heads = kv_heads; p.groups = q_heads / kv_heads;
   p.scaling = scaling;
   return run_dense_decode(p, gate, gate_stride_b, gate_stride_h, out, out_stride_b, out_stride_h, partial_stats,
-                          partial_values, chunk_capacity, chunk_tokens, batch, head_dim, dtype, (cudaStream_t)stream);
+                          partial_values, chunk_capacity, chunk_tokens, split_counters, batch, head_dim, dtype,
+                          (cudaStream_t)stream);
 }

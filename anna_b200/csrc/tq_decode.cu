@@ -291,7 +291,8 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
                                     const float* signs1, const float* signs2, const float* centroids,
                                     const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out,
                                     int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
-                                    float* partial_values, int chunk_capacity, int chunk_tokens_in, int batch, int q_heads, int kv_heads, int head_dim,
+                                    float* partial_values, int chunk_capacity, int chunk_tokens_in,
+                                    int32_t* split_counters, int batch, int q_heads, int kv_heads, int head_dim,
                                     int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
                                     int64_t max_blocks, float scaling, int dtype, anna_stream_t stream) {
   ANNA_REQUIRE(q && window && window_slots && lengths && signs1 && signs2 && centroids && out,
@@ -301,6 +302,7 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   ANNA_REQUIRE(batch > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                "anna_tq_paged_decode: query heads (%d) must be a positive multiple of kv heads (%d)", q_heads, kv_heads);
   ANNA_REQUIRE(residual_len >= 1 && block_size >= 1 && max_blocks >= 0, "anna_tq_paged_decode: bad geometry");
+  (void)split_counters;
   const int vec = dtype == ANNA_DTYPE_F32 ? 4 : 8;
   ANNA_REQUIRE(value_group % vec == 0, "anna_tq_paged_decode: value group %d must be a multiple of %d", value_group, vec);
   TqDecodeParams p{};

@@ -101,18 +101,34 @@ def _check_query(name: str, query: torch.Tensor) -> torch.Tensor:
 
 
 class _Scratch:
-    """Per-(device, stream) split-K scratch, grown on demand and reused across calls."""
+    """Per-(device, stream) split-K scratch, grown on demand and reused across calls.
+
+    Holds the float partial buffers and the int32 arrival counters of the fused merge.  The counters are zeroed when
+    they are allocated and are left at zero by every launch, so they are never cleared again."""
 
     def __init__(self) -> None:
         self._buffers: dict[tuple[int, int], torch.Tensor] = {}
+        self._counters: dict[tuple[int, int], torch.Tensor] = {}
+
+    @staticmethod
+    def _key(device: torch.device) -> tuple[int, int]:
+        return (device.index if device.index is not None else torch.cuda.current_device(),
+                torch.cuda.current_stream(device).cuda_stream)
 
     def get(self, device: torch.device, floats: int) -> torch.Tensor:
-        key = (device.index if device.index is not None else torch.cuda.current_device(),
-               torch.cuda.current_stream(device).cuda_stream)
+        key = self._key(device)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < floats:
             buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
             self._buffers[key] = buf
+        return buf
+
+    def counters(self, device: torch.device, count: int) -> torch.Tensor:
+        key = self._key(device)
+        buf = self._counters.get(key)
+        if buf is None or buf.numel() < count:
+            buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+            self._counters[key] = buf
         return buf
 
 
@@ -120,12 +136,14 @@ _SCRATCH = _Scratch()
 
 
 def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, kv_heads: int, max_len: int):
-    """(partial_stats, partial_values, chunk_capacity) sized by the library's own plan for this problem."""
+    """(partial_stats, partial_values, chunk_capacity, counters) sized by the library's own plan for this problem."""
     _, chunks = _lib.decode_plan(batch, kv_heads, max(int(max_len), 1))
     stats_floats = batch * heads * chunks * 2
     value_floats = batch * heads * chunks * head_dim
     buf = _SCRATCH.get(device, stats_floats + value_floats)
-    return buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks
+    group_tiles = (heads // kv_heads + 7) // 8
+    counters = _SCRATCH.counters(device, batch * kv_heads * group_tiles)
+    return buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks, counters
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -167,17 +185,18 @@ def _gqa_decode_dense(name, query, key, value, visible_lengths, scaling, gate, *
     result = output if output is not None else torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     target = result if result.stride(3) == 1 else torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     if partial_stats is None:
-        partial_stats, partial_values, capacity = split_scratch(device, batch, heads, dim, kv_heads, key_len)
+        partial_stats, partial_values, capacity, counters = split_scratch(device, batch, heads, dim, kv_heads, key_len)
         chunk_tokens = 0
     else:
         capacity = int(partial_stats.shape[2])
         chunk_tokens = min(max(int(block_size), 16), key_len)
+        counters = None
     with torch.cuda.device(device):
         _lib.check(_lib.lib().anna_gqa_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(key), ptr(value), key.stride(0), key.stride(1),
             key.stride(2), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(target), target.stride(0),
-            target.stride(1), ptr(partial_stats), ptr(partial_values), capacity, chunk_tokens, batch, heads, kv_heads,
-            key_len, dim, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
+            target.stride(1), ptr(partial_stats), ptr(partial_values), capacity, chunk_tokens, ptr(counters), batch,
+            heads, kv_heads, key_len, dim, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
     if target is not result:
         result.copy_(target)
     return result
@@ -262,13 +281,13 @@ def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visibl
     out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     if max_blocks == 0:
         return out.zero_()
-    stats, values, capacity = split_scratch(device, batch, heads, dim, kv_heads, max_blocks * block)
+    stats, values, capacity, counters = split_scratch(device, batch, heads, dim, kv_heads, max_blocks * block)
     with torch.cuda.device(device):
         _lib.check(_lib.lib().anna_paged_gqa_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(key_pages), ptr(value_pages), ptr(page_table),
             page_table.stride(0), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(out), out.stride(0),
-            out.stride(1), ptr(stats), ptr(values), capacity, 0, batch, heads, kv_heads, dim, block, pages,
-            max_blocks, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
+            out.stride(1), ptr(stats), ptr(values), capacity, 0, ptr(counters), batch, heads, kv_heads, dim, block,
+            pages, max_blocks, float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
     return out
 
 

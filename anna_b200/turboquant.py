@@ -78,14 +78,14 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
     max_len = max_blocks * pool.block_size + pool.residual_len
-    stats, values, capacity = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len)
+    stats, values, capacity, counters = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len)
     with torch.cuda.device(device):
         _lib.check(_lib.lib().anna_tq_paged_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
             ptr(pool.window), ptr(meta[1]), ptr(meta[0]), ptr(tables.signs1), ptr(tables.signs2),
             ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
             0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
-            capacity, 0, batch, heads, pool.kv_heads, dim, pool.block_size, pool.residual_len, pool.bits,
+            capacity, 0, ptr(counters), batch, heads, pool.kv_heads, dim, pool.block_size, pool.residual_len, pool.bits,
             pool.value_group, pool.capacity(), max_blocks, float(scaling), dtype_code(query.dtype),
             stream_ptr(device)), "anna_tq_paged_decode")
     return out

@@ -82,7 +82,7 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -240,13 +240,23 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
         return out
 
     # ---- device-resident timing ------------------------------------------------------------------------------------
-    for _ in range(args.warmup):
-        decode(step_resident(), False)
+    # The clock sampler starts before warm-up; after the W warm-up steps the same decode launch is repeated (no
+    # append, so no extra pages) until nvidia-smi has delivered samples under this load, then the K timed steps run
+    # back to back with the sampler still on.
     sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    state = None
+    for _ in range(args.warmup):
+        state = step_resident()
+        decode(state, False)
+    spin_deadline = time.perf_counter() + 3.0
+    while not args.no_clock_spin and len(sampler.lines) < 8 and time.perf_counter() < spin_deadline:
+        for _ in range(50):
+            decode(state, False)
+        torch.cuda.synchronize(device)
     decode_events: list = []
     torch.cuda.synchronize(device)
     dist.barrier()
-    sampler.start()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
     for _ in range(args.steps):
@@ -343,18 +353,41 @@ def run_turboquant_extra(device, *, name: str, batch: int, q_heads: int, kv_head
     gen = torch.Generator(device=device).manual_seed(7)
     key_bytes = dim * bits // 8 + 8
     value_bytes = dim // (4 if bits == 2 else 2) + 2 * (dim // 32) * 2
-    done, bulk_ms, bulk_tokens = 0, None, 0
+    from anna_b200.turboquant import launch_tq_append
+
+    cache.reserve_sequence_capacity(context + 64)
+    done, bulk_ms, bulk_api_ms, bulk_tokens = 0, None, None, 0
     while done < context:
         tokens = min(chunk, context - done)
         k = torch.randn(batch, kv_heads, tokens, dim, device=device, dtype=torch.bfloat16, generator=gen)
         v = torch.randn(batch, kv_heads, tokens, dim, device=device, dtype=torch.bfloat16, generator=gen)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        cache.update(k, v, 0, require_dense_cache=False)
-        stop.record()
-        torch.cuda.synchronize()
-        if done > 0 and tokens == chunk:
+        if done == 0:
+            cache.update(k, v, 0, require_dense_cache=False)  # binds rows, sizes the pool
+            pool = cache.allocator.turboquant_layers[0]
+            pool.ensure_capacity(batch * ((context + 64 + page - 1) // page) + 16)
+        elif tokens == chunk and bulk_ms is None:
+            # host bookkeeping first, then the launch alone between two events
+            rows = cache.turboquant_rows[0]
+            past = [row.length for row in rows]
+            for row in rows:
+                row._reserve_blocks(row.length + tokens)
+            table = cache._sync_page_table_layer_buffer(0, batch_size=batch, device=device)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            launch_tq_append(pool, k, v, table, [row.slot for row in rows], past)
+            stop.record()
+            torch.cuda.synchronize()
             bulk_ms, bulk_tokens = start.elapsed_time(stop), tokens
+            for idx, row in enumerate(rows):
+                row._length += tokens
+                cache.layer_lengths[0][idx] = row.length
+        else:
+            t0 = time.perf_counter()
+            cache.update(k, v, 0, require_dense_cache=False)
+            torch.cuda.synchronize()
+            if tokens == chunk:
+                bulk_api_ms = (time.perf_counter() - t0) * 1e3
         done += tokens
         del k, v
     q = torch.randn(batch, q_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
@@ -375,8 +408,10 @@ def run_turboquant_extra(device, *, name: str, batch: int, q_heads: int, kv_head
            "step_tokens_per_s": batch / ((decode_ms + append_ms) / 1e3)}
     if bulk_ms:
         bulk_bytes = batch * kv_heads * bulk_tokens * (2 * dim * 2 + key_bytes + value_bytes)
-        out.update({"bulk_append_tokens": bulk_tokens, "bulk_append_ms": bulk_ms,
-                    "quant_append_GBps": bulk_bytes / (bulk_ms / 1e3) / 1e9})
+        out.update({"bulk_append_tokens": bulk_tokens, "bulk_append_kernel_ms": bulk_ms,
+                    "bulk_append_api_ms_host_timed": bulk_api_ms, "quant_append_algorithmic_bytes": bulk_bytes,
+                    "quant_append_GBps": bulk_bytes / (bulk_ms / 1e3) / 1e9,
+                    "quant_append_frac_of_measured_peak": bulk_bytes / (bulk_ms / 1e3) / 1e9 / peak})
     cache.release()
     cache.allocator.trim()
     return out
@@ -506,6 +541,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extras", action="store_true", help="skip the TurboQuant configurations")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-clock-spin", action="store_true",
+                        help="do not repeat the decode launch while waiting for clock samples (for profiler runs)")
     parser.add_argument("--profile-case", choices=("paged", "tq4", "tq3", "tq2"), default=None,
                         help="run one small decode case a few times and exit (meant to be wrapped by ncu)")
     args = parser.parse_args()

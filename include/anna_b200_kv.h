@@ -50,6 +50,11 @@ int anna_kv_abi_version(void);
  * chunk_tokens == 0 asks the library to choose.  Context lengths are only known on the device, so the choice is
  * made from the host-visible upper bound: anna_decode_plan(batch, kv_heads, max_len) returns the chunk length the
  * library will use and the number of chunks the scratch must hold.
+ *
+ * split_counters (optional, may be NULL): int32 [B, Hkv * ceil(G / 8)] that is all-zero on entry.  When given (and
+ * the plan has at most 512 chunks) the 16-bit tensor-core path merges the partials inside the split kernel: the last
+ * CTA to finish a (row, kv-head group) does the merge and puts the counter back to zero, so the buffer can be reused
+ * by the next call on the same stream without clearing.  Without it a second small kernel does the merge.
  */
 int anna_decode_plan(int batch, int kv_heads, int64_t max_len, int* chunk_tokens, int* num_chunks);
 
@@ -88,8 +93,9 @@ int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                           const int64_t* visible_lengths, const void* gate, int64_t gate_stride_b,
                           int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
                           float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
-                          int batch, int q_heads, int kv_heads, int head_dim, int block_size, int64_t num_pages,
-                          int64_t max_blocks, float scaling, int dtype, anna_stream_t stream);
+                          int32_t* split_counters, int batch, int q_heads, int kv_heads, int head_dim,
+                          int block_size, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                          anna_stream_t stream);
 
 /*
  * Single-token GQA decode over dense K/V [B, Hkv, L, D] (arbitrary batch/head/token strides, last dim contiguous)
@@ -100,8 +106,8 @@ int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const
                     int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t, const int64_t* visible_lengths,
                     const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out, int64_t out_stride_b,
                     int64_t out_stride_h, float* partial_stats, float* partial_values, int chunk_capacity,
-                    int chunk_tokens, int batch, int q_heads, int kv_heads, int64_t key_len, int head_dim,
-                    float scaling, int dtype, anna_stream_t stream);
+                    int chunk_tokens, int32_t* split_counters, int batch, int q_heads, int kv_heads, int64_t key_len,
+                    int head_dim, float scaling, int dtype, anna_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * TurboQuant packed paged cache.
@@ -159,9 +165,9 @@ int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, 
                          const float* signs2, const float* centroids, const void* gate, int64_t gate_stride_b,
                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
                          float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
-                         int batch, int q_heads, int kv_heads, int head_dim, int block_size, int residual_len,
-                         int bits, int value_group, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
-                         anna_stream_t stream);
+                         int32_t* split_counters, int batch, int q_heads, int kv_heads, int head_dim, int block_size,
+                         int residual_len, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
+                         float scaling, int dtype, anna_stream_t stream);
 
 /*
  * De-quantize the packed prefix of each row to dense [B, Hkv, Lq_max, D] keys and values in the cache dtype (element
