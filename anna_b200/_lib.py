@@ -53,8 +53,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                c_i64, c_i32, c_ptr, c_ptr]),
     "anna_tq_paged_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                      c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32,
-                                     c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64,
-                                     c_f32, c_i32, c_ptr]),
+                                     c_ptr, c_ptr, c_size, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,
+                                     c_i64, c_f32, c_i32, c_ptr]),
+    "anna_tq_decode_plan": (c_i32, [c_i32, c_i32, c_i64, c_i32, c_i32, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
     "anna_tq_materialize": (c_i32, [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64,
                                     c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i64, c_i32, c_ptr]),
 }
@@ -104,6 +105,14 @@ def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
     chunks = c_i32(0)
     check(lib().anna_decode_plan(batch, kv_heads, max_len, ctypes.byref(chunk), ctypes.byref(chunks)),
           "anna_decode_plan")
+    return int(chunk.value), int(chunks.value)
+
+
+def tq_decode_plan(batch: int, kv_heads: int, max_blocks: int, block_size: int, residual_len: int) -> tuple[int, int]:
+    chunk = c_i32(0)
+    chunks = c_i32(0)
+    check(lib().anna_tq_decode_plan(batch, kv_heads, max_blocks, block_size, residual_len, ctypes.byref(chunk),
+                                    ctypes.byref(chunks)), "anna_tq_decode_plan")
     return int(chunk.value), int(chunks.value)
 
 

@@ -326,7 +326,7 @@ class Qwen3DynamicCache:
         if device.type != "cuda":
             raise RuntimeError("anna_b200 caches live on a CUDA device; there is no CPU fallback for update().")
         batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
-        past_dev = _i32(past, device)
+        past_dev = torch.tensor(past, dtype=torch.int64, device=device)
         assert layer.key_pages is not None and layer.value_pages is not None
         with torch.cuda.device(device):
             _lib.check(_lib.lib().anna_paged_kv_write(

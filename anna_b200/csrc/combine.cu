@@ -22,6 +22,7 @@ struct CombineParams {
   const int32_t* lengths32;
   const int64_t* lengths64;
   int64_t fixed_len, max_len;
+  int window;  // > 0: chunks = ceil(min(L, window) / c) + ceil(max(L - window, 0) / c)
   const void* gate;
   int64_t gate_stride_b, gate_stride_h;
   void* out;
@@ -35,7 +36,13 @@ __global__ void __launch_bounds__(128) split_combine_kernel(const CombineParams 
   const int b = blockIdx.y;
   int64_t len = p.lengths32 ? (int64_t)p.lengths32[b] : (p.lengths64 ? p.lengths64[b] : p.fixed_len);
   len = max((int64_t)0, min(len, p.max_len));
-  const int chunks = (int)((len + p.chunk_tokens - 1) / p.chunk_tokens);
+  int chunks;
+  if (p.window > 0) {
+    const int64_t win = min(len, (int64_t)p.window);
+    chunks = (int)((win + p.chunk_tokens - 1) / p.chunk_tokens + (len - win + p.chunk_tokens - 1) / p.chunk_tokens);
+  } else {
+    chunks = (int)((len + p.chunk_tokens - 1) / p.chunk_tokens);
+  }
   const int64_t part = ((int64_t)b * p.q_heads + h) * p.chunk_capacity;
   const float* stats = p.stats + part * 2;
   const float* values = p.values + part * p.head_dim;
@@ -95,13 +102,13 @@ int resolve_split(int batch, int kv_heads, int64_t max_len, int chunk_tokens_in,
 }
 
 int launch_split_combine(const SplitWorkspace& ws, const int32_t* lengths32, const int64_t* lengths64,
-                         int64_t fixed_len, int64_t max_len, const void* gate, int64_t gate_stride_b,
+                         int64_t fixed_len, int64_t max_len, int window, const void* gate, int64_t gate_stride_b,
                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h, int batch,
                          int q_heads, int head_dim, int chunk_tokens, int num_chunks, int dtype,
                          cudaStream_t stream) {
   CombineParams p{};
   p.stats = ws.stats; p.values = ws.values;
-  p.lengths32 = lengths32; p.lengths64 = lengths64; p.fixed_len = fixed_len; p.max_len = max_len;
+  p.lengths32 = lengths32; p.lengths64 = lengths64; p.fixed_len = fixed_len; p.max_len = max_len; p.window = window;
   p.gate = gate; p.gate_stride_b = gate_stride_b; p.gate_stride_h = gate_stride_h;
   p.out = out; p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h;
   p.q_heads = q_heads; p.head_dim = head_dim; p.chunk_tokens = chunk_tokens; p.num_chunks = num_chunks;

@@ -158,9 +158,10 @@ int resolve_split(int batch, int kv_heads, int64_t max_len, int chunk_tokens_in,
                   const float* partial_stats, const float* partial_values, int* chunk_tokens, int* num_chunks);
 
 // Launches the combine pass (defined in combine.cu).  lengths32 / lengths64: at most one is non-null; with both
-// null every row has fixed_len keys.  max_len clamps like the split pass.
+// null every row has fixed_len keys.  max_len clamps like the split pass.  window > 0 selects the TurboQuant slot
+// count (window chunks + packed chunks).
 int launch_split_combine(const SplitWorkspace& ws, const int32_t* lengths32, const int64_t* lengths64,
-                         int64_t fixed_len, int64_t max_len, const void* gate, int64_t gate_stride_b,
+                         int64_t fixed_len, int64_t max_len, int window, const void* gate, int64_t gate_stride_b,
                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h, int batch,
                          int q_heads, int head_dim, int chunk_tokens, int num_chunks, int dtype, cudaStream_t stream);
 

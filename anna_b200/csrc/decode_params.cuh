@@ -20,6 +20,7 @@ struct DenseDecodeParams {
   int block_shift;  // log2(block_size) when it is a power of two, else -1
   // dense addressing: element offset = b * kv_stride_b + h * kv_stride_h + t * kv_stride_t
   int64_t kv_stride_b, kv_stride_h, kv_stride_t;
+  int ring_len;  // > 0: token t sits at (t % ring_len) * head_dim (window ring of a TurboQuant row)
   const int64_t* visible_lengths;  // may be null in dense mode: all `max_len` keys visible
   int64_t max_len;
   float* stats;

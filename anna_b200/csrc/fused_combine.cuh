@@ -27,9 +27,9 @@ __device__ __forceinline__ void fused_combine_tail(const FusedCombine& fc, int b
                                                    int active_chunks, int chunk_capacity, const float* stats,
                                                    const float* values, float* smem_weights /* [8][kFusedMaxChunks] */) {
   __shared__ int s_is_last;
-  __threadfence();
-  __syncthreads();
+  __syncthreads();  // all partial stores of this CTA are ordered before the fence below
   if (threadIdx.x == 0) {
+    __threadfence();
     int32_t* counter = fc.counters + (int64_t)b * gridDim.y + blockIdx.y;
     const int prev = atomicAdd(counter, 1);
     s_is_last = (prev == active_chunks - 1) ? 1 : 0;

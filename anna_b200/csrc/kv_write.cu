@@ -11,7 +11,7 @@ struct KvWriteParams {
   void* value_pages;
   const int32_t* page_table;
   int64_t table_stride;
-  const int32_t* past_lengths;
+  const int64_t* past_lengths;
   int batch, kv_heads, new_tokens, head_dim, block_size;
   int64_t num_pages, max_blocks;
   int32_t* status;
@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(256) paged_kv_write_kernel(const KvWriteParams
     rest /= p.new_tokens;
     const int h = (int)(rest % p.kv_heads);
     const int b = (int)(rest / p.kv_heads);
-    const int64_t pos = (int64_t)p.past_lengths[b] + t;
+    const int64_t pos = p.past_lengths[b] + t;
     const int64_t blk = pos / p.block_size;
     const int slot = (int)(pos % p.block_size);
     int32_t pid = -1;
@@ -55,7 +55,7 @@ using namespace anna;
 
 extern "C" int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                                    int64_t kn_stride_t, void* key_pages, void* value_pages,
-                                   const int32_t* page_table, int64_t table_stride, const int32_t* past_lengths,
+                                   const int32_t* page_table, int64_t table_stride, const int64_t* past_lengths,
                                    int batch, int kv_heads, int new_tokens, int head_dim, int block_size,
                                    int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,
                                    anna_stream_t stream) {

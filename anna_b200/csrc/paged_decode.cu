@@ -126,7 +126,7 @@ static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_
     });
   }
   if (rc != ANNA_OK) return rc;
-  return launch_split_combine(ws, nullptr, p.visible_lengths, p.visible_lengths ? -1 : p.max_len, p.max_len, gate,
+  return launch_split_combine(ws, nullptr, p.visible_lengths, p.visible_lengths ? -1 : p.max_len, p.max_len, 0, gate,
                               gate_stride_b, gate_stride_h, out, out_stride_b, out_stride_h, batch, p.q_heads,
                               head_dim, chunk_tokens, num_chunks, dtype, stream);
 }

@@ -17,8 +17,8 @@ struct TqAppendParams {
   const int32_t* block_table;
   int64_t table_stride;
   void* window;
-  const int32_t* window_slots;
-  const int32_t* old_lengths;
+  const int64_t* window_slots;
+  const int64_t* old_lengths;
   const float* signs1;
   const float* signs2;
   const float* centroids;
@@ -58,9 +58,9 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
   const int64_t nw = Lp - wstart;
   if (u >= nq + nw) return;
 
-  const int slot = p.window_slots[b];
-  T* ring_k = reinterpret_cast<T*>(p.window) + (((int64_t)slot * 2 + 0) * p.kv_heads + h) * R * D;
-  T* ring_v = reinterpret_cast<T*>(p.window) + (((int64_t)slot * 2 + 1) * p.kv_heads + h) * R * D;
+  const int64_t slot = p.window_slots[b];
+  T* ring_k = reinterpret_cast<T*>(p.window) + ((slot * 2 + 0) * p.kv_heads + h) * R * D;
+  T* ring_v = reinterpret_cast<T*>(p.window) + ((slot * 2 + 1) * p.kv_heads + h) * R * D;
   const T* in_k = reinterpret_cast<const T*>(p.k_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
   const T* in_v = reinterpret_cast<const T*>(p.v_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
   const int e0 = lane * E;
@@ -218,8 +218,8 @@ extern "C" int anna_tq_page_layout(int head_dim, int bits, int block_size, int d
 
 extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                               int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table,
-                              int64_t table_stride, void* window, const int32_t* window_slots,
-                              const int32_t* old_lengths, const float* signs1, const float* signs2,
+                              int64_t table_stride, void* window, const int64_t* window_slots,
+                              const int64_t* old_lengths, const float* signs1, const float* signs2,
                               const float* centroids, const float* boundaries, int batch, int kv_heads,
                               int new_tokens, int head_dim, int block_size, int residual_len, int bits,
                               int value_group, int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,

@@ -6,30 +6,9 @@
 // the original basis.  Values are de-quantized in registers as code * scale + zero.
 #include "decode_core.cuh"
 #include "tq_common.cuh"
+#include "tq_decode_params.cuh"
 
 namespace anna {
-
-struct TqDecodeParams {
-  const void* q;
-  int64_t q_stride_b, q_stride_h;
-  const uint8_t* pages;
-  const int32_t* block_table;
-  int64_t table_stride;
-  const void* window;
-  const int32_t* window_slots;
-  const int32_t* lengths;
-  const float* signs1;
-  const float* signs2;
-  const float* centroids;
-  float* stats;
-  float* values;
-  int q_heads, kv_heads, groups;
-  int block_size, residual_len, value_group;
-  int64_t num_pages, max_blocks, max_len;
-  int chunk_tokens, num_chunks, chunk_capacity;
-  float scaling;
-  anna_tq_layout layout;
-};
 
 // Bits of COUNT consecutive coordinates starting at `first` in a row packed with WIDTH bits per coordinate.
 template <int COUNT, int WIDTH>
@@ -68,11 +47,26 @@ __global__ void __launch_bounds__(kDecodeThreads) tq_decode_split_kernel(const T
 
   int64_t len = p.lengths[b];
   len = max((int64_t)0, min(len, p.max_len));
-  const int64_t t0 = (int64_t)chunk * p.chunk_tokens;
-  if (t0 >= len) return;
-  const int64_t t1 = min(len, t0 + p.chunk_tokens);
+  if (len == 0) return;
   const int64_t R = p.residual_len;
   const int64_t Lq = len > R ? len - R : 0;
+  const int active_window = (int)((len - Lq + p.chunk_tokens - 1) / p.chunk_tokens);
+  // slots [0, num_window_chunks) walk the window ring, the others the packed prefix; partials are written so that
+  // the active slots of a row stay contiguous: [window chunks | packed chunks]
+  int64_t t0, t1;
+  int out_slot;
+  if (chunk < p.num_window_chunks) {
+    if (chunk >= active_window) return;
+    t0 = Lq + (int64_t)chunk * p.chunk_tokens;
+    t1 = min(len, t0 + p.chunk_tokens);
+    out_slot = chunk;
+  } else {
+    const int packed_chunk = chunk - p.num_window_chunks;
+    t0 = (int64_t)packed_chunk * p.chunk_tokens;
+    if (t0 >= Lq) return;
+    t1 = min(Lq, t0 + p.chunk_tokens);
+    out_slot = active_window + packed_chunk;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -244,9 +238,9 @@ __global__ void __launch_bounds__(kDecodeThreads) tq_decode_split_kernel(const T
   const int64_t w_begin = max(t0, Lq);
   if (w_begin < t1) {
     load_query_from_smem<T, D, G>(st, q_smem, dl, p.scaling);
-    const int slot = p.window_slots[b];
-    const T* ring_k = reinterpret_cast<const T*>(p.window) + (((int64_t)slot * 2 + 0) * p.kv_heads + kvh) * R * D;
-    const T* ring_v = reinterpret_cast<const T*>(p.window) + (((int64_t)slot * 2 + 1) * p.kv_heads + kvh) * R * D;
+    const int64_t slot = p.window_slots[b];
+    const T* ring_k = reinterpret_cast<const T*>(p.window) + ((slot * 2 + 0) * p.kv_heads + kvh) * R * D;
+    const T* ring_v = reinterpret_cast<const T*>(p.window) + ((slot * 2 + 1) * p.kv_heads + kvh) * R * D;
     constexpr int kStep = kDecodeWarps * Cfg::kTpw * kUnroll;
     for (int64_t base = w_begin + warp * (Cfg::kTpw * kUnroll); base < t1; base += kStep) {
       int64_t off[kUnroll];
@@ -260,7 +254,7 @@ __global__ void __launch_bounds__(kDecodeThreads) tq_decode_split_kernel(const T
   }
   __syncthreads();  // every warp is done with q_smem before the merge reuses shared memory
 
-  const int64_t part = ((int64_t)b * p.q_heads + hq0) * p.chunk_capacity + chunk;
+  const int64_t part = ((int64_t)b * p.q_heads + hq0) * p.chunk_capacity + out_slot;
   cta_merge_store<T, D, G>(st, smem, warp, sub, dl, g_count, p.stats + part * 2, p.values + part * D,
                            (int64_t)p.chunk_capacity * 2, (int64_t)p.chunk_capacity * D);
 }
@@ -287,12 +281,13 @@ using namespace anna;
 
 extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                     const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                                    const void* window, const int32_t* window_slots, const int32_t* lengths,
+                                    const void* window, const int64_t* window_slots, const int64_t* lengths,
                                     const float* signs1, const float* signs2, const float* centroids,
                                     const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out,
                                     int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
                                     float* partial_values, int chunk_capacity, int chunk_tokens_in,
-                                    int32_t* split_counters, int batch, int q_heads, int kv_heads, int head_dim,
+                                    int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes,
+                                    int batch, int q_heads, int kv_heads, int head_dim,
                                     int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
                                     int64_t max_blocks, float scaling, int dtype, anna_stream_t stream) {
   ANNA_REQUIRE(q && window && window_slots && lengths && signs1 && signs2 && centroids && out,
@@ -302,7 +297,6 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   ANNA_REQUIRE(batch > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                "anna_tq_paged_decode: query heads (%d) must be a positive multiple of kv heads (%d)", q_heads, kv_heads);
   ANNA_REQUIRE(residual_len >= 1 && block_size >= 1 && max_blocks >= 0, "anna_tq_paged_decode: bad geometry");
-  (void)split_counters;
   const int vec = dtype == ANNA_DTYPE_F32 ? 4 : 8;
   ANNA_REQUIRE(value_group % vec == 0, "anna_tq_paged_decode: value group %d must be a multiple of %d", value_group, vec);
   TqDecodeParams p{};
@@ -312,6 +306,8 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids;
   p.q_heads = q_heads; p.kv_heads = kv_heads; p.groups = q_heads / kv_heads;
   p.block_size = block_size; p.residual_len = residual_len; p.value_group = value_group;
+  p.block_shift = -1;
+  for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == block_size) p.block_shift = sh;
   p.num_pages = num_pages; p.max_blocks = max_blocks;
   p.max_len = max_blocks * (int64_t)block_size + residual_len;
   p.scaling = scaling;
@@ -319,12 +315,39 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
     return set_error(ANNA_ERR_INVALID, "anna_tq_paged_decode: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim,
                      bits, block_size, value_group);
   int chunk_tokens = 0, num_chunks = 0;
-  int rc = resolve_split(batch, kv_heads, p.max_len, chunk_tokens_in, chunk_capacity, partial_stats, partial_values,
-                         &chunk_tokens, &num_chunks);
-  if (rc != ANNA_OK) return rc;
+  int rc;
+  if (chunk_tokens_in > 0) {
+    chunk_tokens = chunk_tokens_in;
+    const int64_t nw = (residual_len + chunk_tokens - 1) / chunk_tokens;
+    const int64_t nq = (max_blocks * (int64_t)block_size + chunk_tokens - 1) / chunk_tokens;
+    num_chunks = (int)(nw + nq);
+  } else {
+    rc = anna_tq_decode_plan(batch, kv_heads, max_blocks, block_size, residual_len, &chunk_tokens, &num_chunks);
+    if (rc != ANNA_OK) return rc;
+  }
+  if (partial_stats == nullptr || partial_values == nullptr)
+    return set_error(ANNA_ERR_WORKSPACE, "anna_tq_paged_decode needs partial_stats and partial_values scratch buffers");
+  if (num_chunks > chunk_capacity)
+    return set_error(ANNA_ERR_WORKSPACE, "split-K scratch holds %d chunks per head, %d needed", chunk_capacity, num_chunks);
   SplitWorkspace ws{partial_stats, partial_values, chunk_capacity};
   p.stats = ws.stats; p.values = ws.values;
   p.chunk_tokens = chunk_tokens; p.num_chunks = num_chunks; p.chunk_capacity = chunk_capacity;
+  p.num_window_chunks = (residual_len + chunk_tokens - 1) / chunk_tokens;
+  {
+    const size_t need = (size_t)batch * kv_heads * ((p.groups + 7) / 8) * 32 * (head_dim / 16) * 16;
+    p.query_frags = (query_scratch != nullptr && query_scratch_bytes >= need) ? query_scratch : nullptr;
+  }
+  if (tq_split_mma_applicable(p, head_dim, dtype)) {
+    if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
+      p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
+      return launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
+    }
+    rc = launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
+    if (rc != ANNA_OK) return rc;
+    return launch_split_combine(ws, nullptr, p.lengths, -1, p.max_len, residual_len, gate, gate_stride_b, gate_stride_h,
+                                out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,
+                                dtype, (cudaStream_t)stream);
+  }
   const int gpad = padded_group(p.groups);
   rc = ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
     return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
@@ -336,7 +359,23 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
     });
   });
   if (rc != ANNA_OK) return rc;
-  return launch_split_combine(ws, p.lengths, nullptr, -1, p.max_len, gate, gate_stride_b, gate_stride_h, out,
-                              out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks, dtype,
-                              (cudaStream_t)stream);
+  return launch_split_combine(ws, nullptr, p.lengths, -1, p.max_len, residual_len, gate, gate_stride_b, gate_stride_h,
+                              out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,
+                              dtype, (cudaStream_t)stream);
+}
+
+extern "C" int anna_tq_decode_plan(int batch, int kv_heads, int64_t max_blocks, int block_size, int residual_len,
+                                   int* chunk_tokens, int* num_chunks) {
+  ANNA_REQUIRE(max_blocks >= 0 && block_size >= 1 && residual_len >= 1, "anna_tq_decode_plan: bad geometry");
+  ANNA_REQUIRE(batch > 0 && kv_heads > 0, "anna_tq_decode_plan: batch and kv_heads must be positive");
+  ANNA_REQUIRE(chunk_tokens != nullptr && num_chunks != nullptr, "anna_tq_decode_plan: null output pointer");
+  const int64_t max_q = max_blocks * (int64_t)block_size;
+  // Packed tokens are 3-6x smaller than 16-bit ones and every CTA pays a fixed fragment-load / merge cost, so the
+  // chunks are longer than for the un-quantized path: the largest of 1024 ... 64 tokens that still gives ~8 CTAs per SM.
+  const int64_t streams = (int64_t)batch * kv_heads;
+  int64_t ct = 1024;
+  while (ct > 64 && streams * ((max_q + residual_len + ct - 1) / ct) < 148 * 8) ct >>= 1;
+  *chunk_tokens = (int)ct;
+  *num_chunks = (int)((residual_len + ct - 1) / ct + (max_q + ct - 1) / ct);
+  return ANNA_OK;
 }

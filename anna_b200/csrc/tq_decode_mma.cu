@@ -1,0 +1,690 @@
+// Tensor-core split pass of single-token GQA decode over packed TurboQuant pages (16-bit cache dtypes).
+//
+// A CTA (4 warps) owns one (row, kv head, chunk).  Chunks that cover the un-quantized window ring run the dense
+// tensor-core body (dense_mma_body.cuh); chunks over the packed prefix run the path below.  Per warp and 16-token tile:
+//
+//   packed bytes of the tile --cp.async--> shared (2 stages per warp)
+//   K codes -> fp16 A fragments in registers: byte-permute (PRMT) table lookups turn 4-bit / 2-bit fields into
+//              centroid values and +-1 signs, two tokens x D/4 coordinates per lane, no shared-memory round trip
+//   S1[16 tok x 8 heads] = centroid(K) . Q1^T      S2 = sign(K) . Q2^T        (2 x D/16 mma.sync m16n8k16, fp16)
+//   score = norm * (S1 + rnorm * S2)   with Q1 = fwht(s1*q) * scaling / sqrt(D)  (times c0 for 1-bit indices)
+//                                           Q2 = fwht(s2*fwht(s1*q)) * scaling * sqrt(pi/2) / D^1.5
+//   online softmax in fp32 on the C fragments; P packed to fp16 and transposed with movmatrix
+//   V codes -> fp16 (magic-number trick) -> (code * scale + zero) in fp16 pairs -> A fragments of V^T
+//   O^T[D x 8 heads] += V^T . P^T                                              (D/16 mma.sync)
+//
+// The K-dimension slots of the two score products are free to permute, so each lane takes the coordinates whose
+// codes it can unpack with the fewest instructions; Q1 / Q2 fragments are gathered with the same permutation.
+#include "dense_mma_body.cuh"
+#include "tq_common.cuh"
+#include "tq_decode_params.cuh"
+
+#include <cstdlib>
+
+namespace anna {
+
+// Byte permute and logic helpers are plain intrinsics / C so that the compiler can fold the constant selectors,
+// masks and magic numbers into immediates instead of keeping them in registers.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) { return (x & mask) | bits; }
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
+                            *reinterpret_cast<const __half2*>(&c));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// N consecutive 32-bit words from shared memory with the widest aligned load (the address is N*4-byte aligned).
+template <int N>
+__device__ __forceinline__ void lds_words(const uint8_t* ptr, uint32_t (&dst)[N]) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const uint4 v = reinterpret_cast<const uint4*>(ptr)[i];
+      dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+    }
+  } else if constexpr (N == 2) {
+    const uint2 v = *reinterpret_cast<const uint2*>(ptr);
+    dst[0] = v.x; dst[1] = v.y;
+  } else {
+    static_assert(N == 1, "unsupported word count");
+    dst[0] = *reinterpret_cast<const uint32_t*>(ptr);
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T, int D, int BITS>
+struct TqMmaCfg {
+  static constexpr int kSteps = D / 16;
+  static constexpr int kGroups = D / 32;                       // value group size is 32 on this path
+  static constexpr int kKeyBytes = D * BITS / 8;               // packed key bytes per token
+  static constexpr int kIdxBytes = BITS == 3 ? D / 4 : kKeyBytes;  // first plane (all of it unless BITS == 3)
+  static constexpr int kSignBytes = BITS == 3 ? D / 8 : 0;     // separate sign plane of the 3-bit format
+  static constexpr int kValBytes = D / (BITS == 2 ? 4 : 2);
+  // stage layout (bytes): the layout of a 16-token chunk, so a tile of a 16-token page is one linear copy
+  static constexpr int kOffKey = 0;
+  static constexpr int kOffNorm = 16 * kKeyBytes;
+  static constexpr int kOffRnorm = kOffNorm + 64;
+  static constexpr int kOffVal = kOffRnorm + 64;
+  static constexpr int kOffScale = kOffVal + 16 * kValBytes;
+  static constexpr int kOffZero = kOffScale + 16 * kGroups * 2;
+  static constexpr int kStageBytes = (kOffZero + 16 * kGroups * 2 + 127) / 128 * 128;
+  static constexpr int kStages = 2;
+  static constexpr int kWarpSmem = kStages * kStageBytes;
+  static constexpr int kPackedSmem = kMmaWarps * kWarpSmem;
+  static constexpr int kMergeSmem = (2 * kMmaWarps * 8 + kMmaWarps * 8 * (D + 4)) * 4;
+  static constexpr int kTailSmem = 8 * kFusedMaxChunks * 4;
+  static constexpr int kSmemBytes0 = kPackedSmem > kMergeSmem ? kPackedSmem : kMergeSmem;
+  static constexpr int kSmemBytes = kSmemBytes0 > kTailSmem ? kSmemBytes0 : kTailSmem;
+  // per-lane key code words per token (this lane's D/4 coordinates)
+  static constexpr int kIdxWords = BITS == 4 ? D / 32 : D / 64;
+  static constexpr int kSignWords = BITS == 3 ? D / 128 : 0;
+  static constexpr int kValWords = BITS == 2 ? D / 128 : D / 64;  // per token, this lane's D/8 dims
+  static_assert(D == 128 || D == 256, "tensor-core TurboQuant decode is built for head_dim 128 and 256");
+};
+
+// Coordinate that lane `tig` feeds into slot k (0..3 = 2tig, 2tig+1, 2tig+8, 2tig+9) of k-step s.
+template <int D, int BITS>
+__device__ __forceinline__ int idx_coord(int tig, int s, int k) {
+  constexpr int kRun = D / 4;
+  if constexpr (BITS == 4) return tig * kRun + 4 * s + k;
+  if constexpr (BITS == 3) return tig * kRun + 8 * (s / 2) + 2 * k + (s % 2);
+  return tig * kRun + 16 * (s / 4) + 8 * ((s % 4) / 2) + 2 * k + (s % 2);
+}
+template <int D, int BITS>
+__device__ __forceinline__ int sign_coord(int tig, int s, int k) {
+  constexpr int kRun = D / 4;
+  if constexpr (BITS == 3) return tig * kRun + 16 * (s / 4) + (s % 4) + 4 * k;
+  return idx_coord<D, BITS>(tig, s, k);
+}
+
+// Rotates the queries of one (row, kv-head group) and stores them as fp16 B fragments in the register order of the
+// split kernel: [row][group][lane][step][q1 b0, q1 b1, q2 b0, q2 b1].  Q1 = fwht(s1*q) / sqrt(D), Q2 = fwht(s2*fwht(s1*q)) / D.
+template <typename T, int D, int BITS>
+__global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const TqDecodeParams p) {
+  constexpr int E = D / 32;
+  constexpr int kSteps = D / 16;
+  __shared__ float q_rot[2][8][D];
+  const int group_tiles = (p.groups + 7) / 8;
+  const int kvh = blockIdx.x / group_tiles;
+  const int g0 = (blockIdx.x % group_tiles) * 8;
+  const int g_count = min(8, p.groups - g0);
+  const int b = blockIdx.y;
+  const int hq0 = kvh * p.groups + g0;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const T* q_ptr = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b;
+  for (int g = warp; g < 8; g += kMmaWarps) {
+    float w[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const int d = lane * E + j;
+      w[j] = g < g_count ? ElemTraits<T>::to_float(q_ptr[(int64_t)(hq0 + g) * p.q_stride_h + d]) : 0.0f;
+      if (p.signs1[d] < 0.0f) w[j] = -w[j];
+    }
+    warp_fwht<E>(w, lane);
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const int d = lane * E + j;
+      q_rot[0][g][d] = w[j];
+      if (p.signs2[d] < 0.0f) w[j] = -w[j];
+    }
+    warp_fwht<E>(w, lane);
+#pragma unroll
+    for (int j = 0; j < E; ++j) q_rot[1][g][lane * E + j] = w[j];
+  }
+  __syncthreads();
+  const float inv_sqrt_d = rsqrt_dim_const<D>();
+  const float inv_d = inv_sqrt_d * inv_sqrt_d;
+  uint4* out = reinterpret_cast<uint4*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * 32 * kSteps;
+  for (int item = threadIdx.x; item < 32 * kSteps; item += kMmaThreads) {
+    const int ln = item / kSteps;
+    const int s = item % kSteps;
+    const int gid = ln >> 2, tig = ln & 3;
+    const float* r1 = q_rot[0][gid];
+    const float* r2 = q_rot[1][gid];
+    uint4 v;
+    v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * inv_sqrt_d, r1[idx_coord<D, BITS>(tig, s, 1)] * inv_sqrt_d);
+    v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * inv_sqrt_d, r1[idx_coord<D, BITS>(tig, s, 3)] * inv_sqrt_d);
+    v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * inv_d, r2[sign_coord<D, BITS>(tig, s, 1)] * inv_d);
+    v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * inv_d, r2[sign_coord<D, BITS>(tig, s, 3)] * inv_d);
+    out[item] = v;
+  }
+}
+
+// Split pass over the un-quantized window ring of every row: the dense tensor-core body with ring addressing.
+// Grid (num_window_chunks, kv_heads * group tiles, batch).  Also writes the zero output of empty rows.
+template <typename T, int D>
+__global__ void __launch_bounds__(kMmaThreads, MmaCfg<D>::kMinBlocks) tq_window_split_mma_kernel(const TqDecodeParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int slot = blockIdx.x;
+  const int group_tiles = (p.groups + 7) / 8;
+  const int kvh = blockIdx.y / group_tiles;
+  const int g0 = (blockIdx.y % group_tiles) * 8;
+  const int g_count = min(8, p.groups - g0);
+  const int b = blockIdx.z;
+  const int hq0 = kvh * p.groups + g0;
+  int64_t len64 = p.lengths[b];
+  len64 = max((int64_t)0, min(len64, p.max_len));
+  const int len = (int)len64;
+  const int R = p.residual_len;
+  const int Lq = len > R ? len - R : 0;
+  const int active_window = (len - Lq + p.chunk_tokens - 1) / p.chunk_tokens;
+  const int active_chunks = active_window + (Lq + p.chunk_tokens - 1) / p.chunk_tokens;
+  if (len == 0) {
+    if (p.fused.counters != nullptr && slot == 0) fused_write_zero_row<T, D, kMmaThreads>(p.fused, b, hq0, g_count);
+    return;
+  }
+  if (slot >= active_window) return;
+  DenseDecodeParams dp{};
+  dp.q = p.q; dp.q_stride_b = p.q_stride_b; dp.q_stride_h = p.q_stride_h;
+  const int64_t ring_elems = (int64_t)R * D;
+  const int64_t slot_base = p.window_slots[b] * 2 * p.kv_heads * ring_elems;
+  dp.key = reinterpret_cast<const T*>(p.window) + slot_base;
+  dp.value = reinterpret_cast<const T*>(p.window) + slot_base + (int64_t)p.kv_heads * ring_elems;
+  dp.page_table = nullptr;
+  dp.kv_stride_b = 0; dp.kv_stride_h = ring_elems; dp.kv_stride_t = D;
+  dp.ring_len = R;
+  dp.block_size = 1; dp.block_shift = 0;
+  dp.stats = p.stats; dp.values = p.values;
+  dp.q_heads = p.q_heads; dp.kv_heads = p.kv_heads; dp.groups = p.groups;
+  dp.chunk_tokens = p.chunk_tokens; dp.num_chunks = p.num_chunks; dp.chunk_capacity = p.chunk_capacity;
+  dp.scaling = p.scaling;
+  dp.fused = p.fused;
+  const int t0 = Lq + slot * p.chunk_tokens;
+  const int t1 = min(len, t0 + p.chunk_tokens);
+  dense_split_mma_body<T, D>(dp, smem_raw, b, kvh, g0, g_count, t0, t1, slot, active_chunks);
+}
+
+template <typename T, int D, int BITS>
+__global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split_mma_kernel(const TqDecodeParams p) {
+  using Cfg = TqMmaCfg<T, D, BITS>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+
+  const int slot = blockIdx.x;
+  const int group_tiles = (p.groups + 7) / 8;
+  const int kvh = blockIdx.y / group_tiles;
+  const int g0 = (blockIdx.y % group_tiles) * 8;
+  const int g_count = min(8, p.groups - g0);
+  const int b = blockIdx.z;
+  const int hq0 = kvh * p.groups + g0;
+
+  int64_t len64 = p.lengths[b];
+  len64 = max((int64_t)0, min(len64, p.max_len));
+  const int len = (int)len64;
+  const int R = p.residual_len;
+  const int Lq = len > R ? len - R : 0;
+  const int win = len - Lq;
+  const int active_window = (win + p.chunk_tokens - 1) / p.chunk_tokens;
+  const int active_packed = (Lq + p.chunk_tokens - 1) / p.chunk_tokens;
+  const int active_chunks = active_window + active_packed;
+  if (len == 0 || slot < p.num_window_chunks) return;  // window chunks run in tq_window_split_mma_kernel
+
+  // ---- packed chunks ------------------------------------------------------------------------------------------------------
+  const int chunk = slot - p.num_window_chunks;
+  const int t0 = chunk * p.chunk_tokens;
+  if (t0 >= Lq) return;
+  const int t1 = min(Lq, t0 + p.chunk_tokens);
+  const int out_slot = active_window + chunk;  // active slots stay contiguous: [window | packed]
+  const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int gid = lane >> 2;
+  const int tig = lane & 3;
+  // Q fragments (fp16) were prepared by tq_prepare_queries_kernel in exactly this lane's register order:
+  //   [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]
+  uint32_t q1f[Cfg::kSteps][2], q2f[Cfg::kSteps][2];
+  {
+    const uint4* frag = reinterpret_cast<const uint4*>(p.query_frags) +
+                        (((int64_t)b * gridDim.y + blockIdx.y) * 32 + lane) * Cfg::kSteps;
+#pragma unroll
+    for (int s = 0; s < Cfg::kSteps; ++s) {
+      const uint4 v = __ldg(frag + s);
+      q1f[s][0] = v.x; q1f[s][1] = v.y; q2f[s][0] = v.z; q2f[s][1] = v.w;
+    }
+  }
+  // score (log2 units) = norm * (k1 * S1 + k2 * rnorm * S2) with S1 = Q1/sqrt(D) . c, S2 = Q2/D . sign:
+  //   q.k_hat = norm/D * [Q1.c + sqrt(pi/2)/sqrt(D) * rnorm * Q2.sign]
+  //           = norm * [ (1/sqrt(D)) * S1 + sqrt(pi/2)/sqrt(D) * rnorm * S2 ]
+  const float inv_sqrt_d = rsqrt_dim_const<D>();
+  const float log2e = 1.4426950408889634f;
+  const float k1 = (BITS == 2 ? __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d;
+  const float k2 = p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d;
+
+  // centroid lookup tables for PRMT: low bytes and high bytes of the fp16 centroids (up to 8 entries)
+  uint32_t lut_lo[2] = {0u, 0u}, lut_hi[2] = {0u, 0u};
+  if constexpr (BITS != 2) {
+    constexpr int kEntries = 1 << (BITS - 1);
+#pragma unroll
+    for (int e = 0; e < kEntries; ++e) {
+      const __half h = __float2half_rn(__ldg(p.centroids + e));
+      const uint32_t bits = (uint32_t)__half_as_ushort(h);
+      lut_lo[e / 4] |= (bits & 0xffu) << (8 * (e % 4));
+      lut_hi[e / 4] |= (bits >> 8) << (8 * (e % 4));
+    }
+    if constexpr (BITS == 3) {  // 4 entries: mirror them so that PRMT may pick from either operand
+      lut_lo[1] = lut_lo[0];
+      lut_hi[1] = lut_hi[0];
+    }
+  }
+  constexpr uint32_t kSignLut = 0x00003CBCu;   // byte 0: high byte of fp16 -1.0, byte 1: high byte of +1.0
+  // 2-bit format: a nibble holds two fields [s1 i1 s0 i0]; after masking with 0x5 it is 0, 1, 4 or 5
+  constexpr uint32_t kEvenLut0 = 0x3CBC3CBCu, kEvenLut1 = 0x3CBC3CBCu;  // entry v: bit 0 set -> +1
+  constexpr uint32_t kOddLut0 = 0xBCBCBCBCu, kOddLut1 = 0x3C3C3C3Cu;    // entry v: bit 2 set -> +1
+
+  const uint32_t warp_smem_u32 = smem_u32(smem_raw + warp * Cfg::kWarpSmem);
+  const uint8_t* warp_smem = smem_raw + warp * Cfg::kWarpSmem;
+  const int32_t* table_row = p.block_table + (int64_t)b * p.table_stride;
+  // Issue the async copies of one 16-token tile: six contiguous runs of the page chunk (codes, norms, residual
+  // norms, value codes, scales, zeros), each landing at the same relative place of the stage.
+  const uint32_t block_size = (uint32_t)p.block_size;
+  const int block_shift = p.block_shift;
+  auto issue_tile = [&](int tile, int stage) {
+    const int ts = t0 + tile * kTileTokens;
+    const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
+    const int s0 = ts - (int)(blk * block_size);          // first slot of the tile inside its page
+    const int32_t pid = table_row[blk];
+    const bool ok = pid >= 0 && pid < p.num_pages;
+    const uint8_t* chunk_ptr = p.pages + ((int64_t)(ok ? pid : 0) * p.kv_heads + kvh) * p.layout.chunk_bytes + lane * 16;
+    const uint32_t dst = warp_smem_u32 + stage * Cfg::kStageBytes + lane * 16;
+    const int bytes = ok ? 16 : 0;
+    {
+      const uint8_t* src = chunk_ptr + p.layout.off_kcodes + s0 * Cfg::kKeyBytes;
+#pragma unroll
+      for (int i = 0; i < (Cfg::kKeyBytes + 31) / 32; ++i)
+        if (Cfg::kKeyBytes % 32 == 0 || lane + 32 * i < Cfg::kKeyBytes) cp_async16(dst + Cfg::kOffKey + i * 512, src + i * 512, bytes);
+    }
+    {
+      const uint8_t* src = chunk_ptr + p.layout.off_vdata + s0 * Cfg::kValBytes;
+#pragma unroll
+      for (int i = 0; i < (Cfg::kValBytes + 31) / 32; ++i)
+        if (Cfg::kValBytes % 32 == 0 || lane + 32 * i < Cfg::kValBytes) cp_async16(dst + Cfg::kOffVal + i * 512, src + i * 512, bytes);
+    }
+    {
+      constexpr int kMetaUnits = Cfg::kGroups * 2;  // 16-byte units per metadata array (scales, zeros)
+      static_assert(kMetaUnits <= 16, "metadata copy assumes at most 16 units per array");
+      // lanes 0-3: norms, 4-7: residual norms (same lane*16 offset trick: subtract the lane base for 4-7)
+      if (lane < 4) cp_async16(dst + Cfg::kOffNorm, chunk_ptr + p.layout.off_knorm + 4 * s0, bytes);
+      else if (lane < 8) cp_async16(dst + Cfg::kOffRnorm - 64, chunk_ptr + p.layout.off_krnorm + 4 * s0 - 64, bytes);
+      if (lane < kMetaUnits)
+        cp_async16(dst + Cfg::kOffScale, chunk_ptr + p.layout.off_vscale + s0 * Cfg::kGroups * 2, bytes);
+      else if (lane >= 16 && lane < 16 + kMetaUnits)
+        cp_async16(dst + Cfg::kOffZero - 256, chunk_ptr + p.layout.off_vzero + s0 * Cfg::kGroups * 2 - 256, bytes);
+    }
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+  float o_acc[Cfg::kSteps][4];
+#pragma unroll
+  for (int j = 0; j < Cfg::kSteps; ++j)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o_acc[j][r] = 0.0f;
+
+  const int my_tiles = num_tiles > warp ? (num_tiles - warp + kMmaWarps - 1) / kMmaWarps : 0;
+  if (my_tiles > 0) issue_tile(warp, 0);
+  cp_async_commit();
+
+  // this lane's value dims: D/8 consecutive dims starting at gid * D/8, all inside value group (gid * D/8) / 32
+  const int v_group = (gid * (D / 8)) / 32;
+
+  for (int n = 0; n < my_tiles; ++n) {
+    __syncwarp();
+    if (n + 1 < my_tiles) issue_tile(warp + (n + 1) * kMmaWarps, (n + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+
+    const int tile = warp + n * kMmaWarps;
+    const int ts = t0 + tile * kTileTokens;
+    int valid = min(kTileTokens, t1 - ts);
+    {
+      const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
+      const int32_t pid = table_row[blk];
+      if (pid < 0 || pid >= p.num_pages) valid = 0;
+    }
+    const uint8_t* st = warp_smem + (n & 1) * Cfg::kStageBytes;
+
+    // ---- scores ------------------------------------------------------------------------------------------------------
+    float s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    {
+      uint32_t iw_lo[Cfg::kIdxWords], iw_hi[Cfg::kIdxWords];  // rows gid and gid + 8
+      const uint8_t* row_lo = st + Cfg::kOffKey + gid * Cfg::kKeyBytes + tig * (Cfg::kIdxWords * 4);
+      const uint8_t* row_hi = row_lo + 8 * Cfg::kKeyBytes;
+      lds_words<Cfg::kIdxWords>(row_lo, iw_lo);
+      lds_words<Cfg::kIdxWords>(row_hi, iw_hi);
+      if constexpr (BITS == 4) {
+#pragma unroll
+        for (int s = 0; s < Cfg::kSteps; ++s) {
+          const uint32_t wl = iw_lo[s / 2] >> (16 * (s % 2));
+          const uint32_t wh = iw_hi[s / 2] >> (16 * (s % 2));
+          uint32_t a[4];
+          {
+            const uint32_t sl = wl & 0x7777u, sh = wh & 0x7777u;
+            const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
+            const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
+            a[0] = prmt(lo_l, hi_l, 0x5140u);
+            a[1] = prmt(lo_h, hi_h, 0x5140u);
+            a[2] = prmt(lo_l, hi_l, 0x7362u);
+            a[3] = prmt(lo_h, hi_h, 0x7362u);
+          }
+          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
+          {
+            const uint32_t gl = prmt(kSignLut, 0u, (wl >> 3) & 0x1111u);
+            const uint32_t gh = prmt(kSignLut, 0u, (wh >> 3) & 0x1111u);
+            a[0] = prmt(gl, 0u, 0x1404u);
+            a[1] = prmt(gh, 0u, 0x1404u);
+            a[2] = prmt(gl, 0u, 0x3424u);
+            a[3] = prmt(gh, 0u, 0x3424u);
+          }
+          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
+        }
+      } else if constexpr (BITS == 2) {
+#pragma unroll
+        for (int s = 0; s < Cfg::kSteps; ++s) {
+          const uint32_t wl = iw_lo[s / 4] >> (16 * ((s % 4) / 2));
+          const uint32_t wh = iw_hi[s / 4] >> (16 * ((s % 4) / 2));
+          const uint32_t la = (s % 2) ? kOddLut0 : kEvenLut0;
+          const uint32_t lb = (s % 2) ? kOddLut1 : kEvenLut1;
+          uint32_t a[4];
+          {
+            const uint32_t gl = prmt(la, lb, wl & 0x5555u);
+            const uint32_t gh = prmt(la, lb, wh & 0x5555u);
+            a[0] = prmt(gl, 0u, 0x1404u);
+            a[1] = prmt(gh, 0u, 0x1404u);
+            a[2] = prmt(gl, 0u, 0x3424u);
+            a[3] = prmt(gh, 0u, 0x3424u);
+          }
+          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
+          {
+            const uint32_t gl = prmt(la, lb, (wl >> 1) & 0x5555u);
+            const uint32_t gh = prmt(la, lb, (wh >> 1) & 0x5555u);
+            a[0] = prmt(gl, 0u, 0x1404u);
+            a[1] = prmt(gh, 0u, 0x1404u);
+            a[2] = prmt(gl, 0u, 0x3424u);
+            a[3] = prmt(gh, 0u, 0x3424u);
+          }
+          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
+        }
+      } else {
+        uint32_t sw_lo[Cfg::kSignWords], sw_hi[Cfg::kSignWords];
+        const uint8_t* srow_lo = st + Cfg::kOffKey + gid * Cfg::kKeyBytes + Cfg::kIdxBytes + tig * (Cfg::kSignWords * 4);
+        const uint8_t* srow_hi = srow_lo + 8 * Cfg::kKeyBytes;
+        lds_words<Cfg::kSignWords>(srow_lo, sw_lo);
+        lds_words<Cfg::kSignWords>(srow_hi, sw_hi);
+#pragma unroll
+        for (int s = 0; s < Cfg::kSteps; ++s) {
+          // 2-bit indices: half-word s / 2 of the lane's run, even (s % 2 == 0) or odd fields
+          const uint32_t wl = iw_lo[s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
+          const uint32_t wh = iw_hi[s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
+          uint32_t a[4];
+          {
+            const uint32_t sl = wl & 0x3333u, sh = wh & 0x3333u;
+            const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
+            const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
+            a[0] = prmt(lo_l, hi_l, 0x5140u);
+            a[1] = prmt(lo_h, hi_h, 0x5140u);
+            a[2] = prmt(lo_l, hi_l, 0x7362u);
+            a[3] = prmt(lo_h, hi_h, 0x7362u);
+          }
+          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
+          {
+            // sign plane: coordinates 16 * (s / 4) + (s % 4) + 4k of the lane's run
+            const uint32_t xl = sw_lo[s / 8] >> (16 * ((s / 4) % 2) + (s % 4));
+            const uint32_t xh = sw_hi[s / 8] >> (16 * ((s / 4) % 2) + (s % 4));
+            const uint32_t gl = prmt(kSignLut, 0u, xl & 0x1111u);
+            const uint32_t gh = prmt(kSignLut, 0u, xh & 0x1111u);
+            a[0] = prmt(gl, 0u, 0x1404u);
+            a[1] = prmt(gh, 0u, 0x1404u);
+            a[2] = prmt(gl, 0u, 0x3424u);
+            a[3] = prmt(gh, 0u, 0x3424u);
+          }
+          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
+        }
+      }
+    }
+    const float* norms = reinterpret_cast<const float*>(st + Cfg::kOffNorm);
+    const float* rnorms = reinterpret_cast<const float*>(st + Cfg::kOffRnorm);
+    const bool ok_lo = gid < valid, ok_hi = gid + 8 < valid;
+    float s[4];
+    {
+      const float n_lo = norms[gid], r_lo = rnorms[gid], n_hi = norms[gid + 8], r_hi = rnorms[gid + 8];
+      s[0] = ok_lo ? n_lo * fmaf(k2 * r_lo, s2[0], k1 * s1[0]) : -INFINITY;
+      s[1] = ok_lo ? n_lo * fmaf(k2 * r_lo, s2[1], k1 * s1[1]) : -INFINITY;
+      s[2] = ok_hi ? n_hi * fmaf(k2 * r_hi, s2[2], k1 * s1[2]) : -INFINITY;
+      s[3] = ok_hi ? n_hi * fmaf(k2 * r_hi, s2[3], k1 * s1[3]) : -INFINITY;
+    }
+
+    // ---- online softmax ---------------------------------------------------------------------------------------------------
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+    for (int d = 4; d <= 16; d <<= 1) {
+      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+    }
+    const float m_new[2] = {fmaxf(m_run[0], mx[0]), fmaxf(m_run[1], mx[1])};
+    const bool grew = (m_new[0] > m_run[0]) || (m_new[1] > m_run[1]);
+    const float m_safe[2] = {m_new[0] == -INFINITY ? 0.0f : m_new[0], m_new[1] == -INFINITY ? 0.0f : m_new[1]};
+    if (__any_sync(0xffffffffu, grew)) {
+      const float a0 = fast_exp2(m_run[0] - m_safe[0]);
+      const float a1 = fast_exp2(m_run[1] - m_safe[1]);
+      l_run[0] *= a0;
+      l_run[1] *= a1;
+#pragma unroll
+      for (int j = 0; j < Cfg::kSteps; ++j) {
+        o_acc[j][0] *= a0;
+        o_acc[j][1] *= a1;
+        o_acc[j][2] *= a0;
+        o_acc[j][3] *= a1;
+      }
+      m_run[0] = m_new[0];
+      m_run[1] = m_new[1];
+    }
+    const float p0 = fast_exp2(s[0] - m_safe[0]);
+    const float p1 = fast_exp2(s[1] - m_safe[1]);
+    const float p2 = fast_exp2(s[2] - m_safe[0]);
+    const float p3 = fast_exp2(s[3] - m_safe[1]);
+    l_run[0] += p0 + p2;
+    l_run[1] += p1 + p3;
+    const uint32_t pb0 = movmatrix_trans(pack2<__half>(p0, p1));  // tokens 2tig, 2tig+1 of head gid
+    const uint32_t pb1 = movmatrix_trans(pack2<__half>(p2, p3));  // tokens 2tig+8, 2tig+9
+
+    // ---- values: lane holds tokens {2tig, 2tig+1} and {2tig+8, 2tig+9}, dims gid*D/8 .. +D/8 ---------------------------------
+    const int tok_a = 2 * tig, tok_c = 2 * tig + 8;
+    uint32_t sc_pair[2], zp_pair[2];
+    {
+      const T* scales = reinterpret_cast<const T*>(st + Cfg::kOffScale);
+      const T* zeros = reinterpret_cast<const T*>(st + Cfg::kOffZero);
+      auto meta = [&](const T* arr, int tok) -> float {
+        return tok < valid ? ElemTraits<T>::to_float(arr[tok * Cfg::kGroups + v_group]) : 0.0f;
+      };
+      sc_pair[0] = pack2<__half>(meta(scales, tok_a), meta(scales, tok_a + 1));
+      sc_pair[1] = pack2<__half>(meta(scales, tok_c), meta(scales, tok_c + 1));
+      zp_pair[0] = pack2<__half>(meta(zeros, tok_a), meta(zeros, tok_a + 1));
+      zp_pair[1] = pack2<__half>(meta(zeros, tok_c), meta(zeros, tok_c + 1));
+    }
+    const uint8_t* vbase = st + Cfg::kOffVal + gid * (Cfg::kValWords * 4);
+    uint32_t vw[4][Cfg::kValWords];  // tokens a, a+1, c, c+1
+    lds_words<Cfg::kValWords>(vbase + tok_a * Cfg::kValBytes, vw[0]);
+    lds_words<Cfg::kValWords>(vbase + (tok_a + 1) * Cfg::kValBytes, vw[1]);
+    lds_words<Cfg::kValWords>(vbase + tok_c * Cfg::kValBytes, vw[2]);
+    lds_words<Cfg::kValWords>(vbase + (tok_c + 1) * Cfg::kValBytes, vw[3]);
+    if constexpr (BITS != 2) {
+      // 4-bit codes: one 16-bit half-word = 4 dims; x packs the same 4 dims of two tokens (low / high half)
+      constexpr uint32_t kMagicLo = 0x64006400u, kMagicHi = 0x54005400u;  // 1024 + n, 64 + n
+#pragma unroll
+      for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
+        const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
+        uint32_t r[2][4];
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {
+          const uint32_t x = prmt(vw[2 * pr][hw / 2], vw[2 * pr + 1][hw / 2], sel);
+          const uint32_t y = x >> 8;
+          r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000F000Fu, kMagicLo), kMagicLo), sc_pair[pr], zp_pair[pr]);
+          r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00F000F0u, kMagicHi), kMagicHi), sc_pair[pr], zp_pair[pr]);
+          r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000F000Fu, kMagicLo), kMagicLo), sc_pair[pr], zp_pair[pr]);
+          r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00F000F0u, kMagicHi), kMagicHi), sc_pair[pr], zp_pair[pr]);
+        }
+        // dims 4hw + {0,1} -> m-tile 2hw (rows gid, gid+8); dims 4hw + {2,3} -> m-tile 2hw + 1
+        const uint32_t a_even[4] = {r[0][0], r[0][1], r[1][0], r[1][1]};
+        const uint32_t a_odd[4] = {r[0][2], r[0][3], r[1][2], r[1][3]};
+        mma_m16n8k16<__half>(o_acc[2 * hw], a_even, pb0, pb1);
+        mma_m16n8k16<__half>(o_acc[2 * hw + 1], a_odd, pb0, pb1);
+      }
+    } else {
+      // 2-bit codes: one 16-bit half-word = 8 dims
+      constexpr uint32_t kM0 = 0x64006400u, kM1 = 0x5C005C00u, kM2 = 0x54005400u, kM3 = 0x4C004C00u, kM4 = 0x44004400u;
+#pragma unroll
+      for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
+        const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
+        uint32_t r[2][8];
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {
+          const uint32_t x = prmt(vw[2 * pr][hw / 2], vw[2 * pr + 1][hw / 2], sel);
+          const uint32_t y = x >> 10;
+          r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00030003u, kM0), kM0), sc_pair[pr], zp_pair[pr]);
+          r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000C000Cu, kM1), kM1), sc_pair[pr], zp_pair[pr]);
+          r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00300030u, kM2), kM2), sc_pair[pr], zp_pair[pr]);
+          r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00C000C0u, kM3), kM3), sc_pair[pr], zp_pair[pr]);
+          r[pr][4] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x03000300u, kM4), kM4), sc_pair[pr], zp_pair[pr]);
+          r[pr][5] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00030003u, kM0), kM0), sc_pair[pr], zp_pair[pr]);
+          r[pr][6] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000C000Cu, kM1), kM1), sc_pair[pr], zp_pair[pr]);
+          r[pr][7] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00300030u, kM2), kM2), sc_pair[pr], zp_pair[pr]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // dims 8hw + {2q, 2q+1} -> m-tile 4hw + q
+          const uint32_t a[4] = {r[0][2 * q], r[0][2 * q + 1], r[1][2 * q], r[1][2 * q + 1]};
+          mma_m16n8k16<__half>(o_acc[4 * hw + q], a, pb0, pb1);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- merge the four warps; m-tile j holds dims gid*D/8 + 2j (row gid) and + 2j + 1 (row gid + 8) --------------------------
+#pragma unroll
+  for (int d = 4; d <= 16; d <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+  }
+  __syncthreads();
+  float* sm_m = reinterpret_cast<float*>(smem_raw);
+  float* sm_l = sm_m + kMmaWarps * 8;
+  float* sm_o = sm_l + kMmaWarps * 8;
+  constexpr int kPad = D + 4;
+  if (gid == 0) {
+    sm_m[warp * 8 + 2 * tig] = m_run[0];
+    sm_m[warp * 8 + 2 * tig + 1] = m_run[1];
+    sm_l[warp * 8 + 2 * tig] = l_run[0];
+    sm_l[warp * 8 + 2 * tig + 1] = l_run[1];
+  }
+#pragma unroll
+  for (int j = 0; j < Cfg::kSteps; ++j) {
+    float* base = sm_o + (warp * 8) * kPad;
+    const int dim = gid * (D / 8) + 2 * j;
+    base[(2 * tig) * kPad + dim] = o_acc[j][0];
+    base[(2 * tig + 1) * kPad + dim] = o_acc[j][1];
+    base[(2 * tig) * kPad + dim + 1] = o_acc[j][2];
+    base[(2 * tig + 1) * kPad + dim + 1] = o_acc[j][3];
+  }
+  __syncthreads();
+  const int64_t part = ((int64_t)b * p.q_heads + hq0) * p.chunk_capacity + out_slot;
+  float* stats_out = p.stats + part * 2;
+  float* values_out = p.values + part * D;
+  for (int item = threadIdx.x; item < g_count * D; item += kMmaThreads) {
+    const int g = item / D;
+    const int d = item % D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) m_all = fmaxf(m_all, sm_m[w * 8 + g]);
+    const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
+    float l_all = 0.0f, o_all = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) {
+      const float wgt = exp2f(sm_m[w * 8 + g] - m_ref);
+      l_all += sm_l[w * 8 + g] * wgt;
+      o_all += sm_o[(w * 8 + g) * kPad + d] * wgt;
+    }
+    values_out[(int64_t)g * p.chunk_capacity * D + d] = o_all;
+    if (d == 0) {
+      stats_out[(int64_t)g * p.chunk_capacity * 2 + 0] = m_all * 0.6931471805599453f;
+      stats_out[(int64_t)g * p.chunk_capacity * 2 + 1] = l_all;
+    }
+  }
+  if (p.fused.counters != nullptr) {
+    const int64_t head0 = ((int64_t)b * p.q_heads + hq0) * p.chunk_capacity;
+    __syncthreads();
+    fused_combine_tail<T, D, kMmaThreads>(p.fused, b, hq0, g_count, active_chunks, p.chunk_capacity,
+                                          p.stats + head0 * 2, p.values + head0 * D,
+                                          reinterpret_cast<float*>(smem_raw));
+  }
+}
+
+template <typename T, int D, int BITS>
+static int launch_tq_mma(const TqDecodeParams& p, int batch, cudaStream_t stream) {
+  using Cfg = TqMmaCfg<T, D, BITS>;
+  auto kernel = tq_decode_split_mma_kernel<T, D, BITS>;
+  static bool configured[64] = {};
+  int device = 0;
+  ANNA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !configured[device]) {
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(tq_window_split_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         MmaCfg<D>::kSmemBytes));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  const int group_tiles = (p.groups + 7) / 8;
+  dim3 prep_grid((unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
+  tq_prepare_queries_kernel<T, D, BITS><<<prep_grid, kMmaThreads, 0, stream>>>(p);
+  int rc = check_launch("tq_prepare_queries_kernel");
+  if (rc != ANNA_OK) return rc;
+  dim3 window_grid((unsigned)p.num_window_chunks, (unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
+  tq_window_split_mma_kernel<T, D><<<window_grid, kMmaThreads, MmaCfg<D>::kSmemBytes, stream>>>(p);
+  rc = check_launch("tq_window_split_mma_kernel");
+  if (rc != ANNA_OK) return rc;
+  if (p.num_chunks > p.num_window_chunks) {
+    dim3 grid((unsigned)p.num_chunks, (unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
+    kernel<<<grid, kMmaThreads, Cfg::kSmemBytes, stream>>>(p);
+    rc = check_launch("tq_decode_split_mma_kernel");
+  }
+  return rc;
+}
+
+bool tq_split_mma_applicable(const TqDecodeParams& p, int head_dim, int dtype) {
+  static const bool disabled = [] {
+    const char* flag = std::getenv("ANNA_B200_DISABLE_MMA");
+    return flag != nullptr && flag[0] != '\0' && flag[0] != '0';
+  }();
+  if (disabled) return false;
+  if (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16) return false;
+  if (head_dim != 128 && head_dim != 256) return false;
+  if (p.value_group != 32 || p.block_size % kTileTokens != 0 || p.chunk_tokens % kTileTokens != 0) return false;
+  if (p.max_len >= (int64_t)1 << 31 || p.query_frags == nullptr) return false;
+  return true;
+}
+
+int launch_tq_split_mma(const TqDecodeParams& p, int batch, int head_dim, int bits, int dtype, cudaStream_t stream) {
+#define ANNA_TQ_MMA_CASE(TYPE, DIM, BITS_) \
+  if (head_dim == DIM && bits == BITS_) return launch_tq_mma<TYPE, DIM, BITS_>(p, batch, stream);
+  if (dtype == ANNA_DTYPE_BF16) {
+    ANNA_TQ_MMA_CASE(__nv_bfloat16, 128, 2) ANNA_TQ_MMA_CASE(__nv_bfloat16, 128, 3) ANNA_TQ_MMA_CASE(__nv_bfloat16, 128, 4)
+    ANNA_TQ_MMA_CASE(__nv_bfloat16, 256, 2) ANNA_TQ_MMA_CASE(__nv_bfloat16, 256, 3) ANNA_TQ_MMA_CASE(__nv_bfloat16, 256, 4)
+  } else {
+    ANNA_TQ_MMA_CASE(__half, 128, 2) ANNA_TQ_MMA_CASE(__half, 128, 3) ANNA_TQ_MMA_CASE(__half, 128, 4)
+    ANNA_TQ_MMA_CASE(__half, 256, 2) ANNA_TQ_MMA_CASE(__half, 256, 3) ANNA_TQ_MMA_CASE(__half, 256, 4)
+  }
+#undef ANNA_TQ_MMA_CASE
+  return set_error(ANNA_ERR_UNSUPPORTED, "no tensor-core TurboQuant decode for head_dim %d, %d bits", head_dim, bits);
+}
+
+}  // namespace anna

@@ -1,0 +1,39 @@
+// Parameters of the TurboQuant decode split kernels (CUDA-core and tensor-core).
+#pragma once
+
+#include "common.cuh"
+#include "fused_combine.cuh"
+
+namespace anna {
+
+struct TqDecodeParams {
+  const void* q;
+  int64_t q_stride_b, q_stride_h;
+  const uint8_t* pages;
+  const int32_t* block_table;
+  int64_t table_stride;
+  const void* window;
+  const int64_t* window_slots;
+  const int64_t* lengths;
+  const float* signs1;
+  const float* signs2;
+  const float* centroids;
+  float* stats;
+  float* values;
+  int q_heads, kv_heads, groups;
+  int block_size, residual_len, value_group;
+  int block_shift;  // log2(block_size) when it is a power of two, else -1
+  int64_t num_pages, max_blocks, max_len;
+  int chunk_tokens, num_chunks, chunk_capacity;
+  int num_window_chunks;  // split-K slots [0, num_window_chunks) cover the window ring, the rest the packed prefix
+  float scaling;
+  anna_tq_layout layout;
+  FusedCombine fused;
+  void* query_frags;  // scratch for the rotated fp16 query fragments (tensor-core path), or nullptr
+};
+
+// Tensor-core split pass (tq_decode_mma.cu): 16-bit cache dtypes, head_dim 128 / 256, value group 32, page size % 16 == 0.
+bool tq_split_mma_applicable(const TqDecodeParams& p, int head_dim, int dtype);
+int launch_tq_split_mma(const TqDecodeParams& p, int batch, int head_dim, int bits, int dtype, cudaStream_t stream);
+
+}  // namespace anna

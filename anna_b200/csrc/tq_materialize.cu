@@ -7,7 +7,7 @@ struct TqMaterializeParams {
   const uint8_t* pages;
   const int32_t* block_table;
   int64_t table_stride;
-  const int32_t* quantized_lengths;
+  const int64_t* quantized_lengths;
   const float* signs1;
   const float* signs2;
   const float* centroids;
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(kMaterializeWarps * 32) tq_materialize_kernel(
 using namespace anna;
 
 extern "C" int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                                   const int32_t* quantized_lengths, const float* signs1, const float* signs2,
+                                   const int64_t* quantized_lengths, const float* signs1, const float* signs2,
                                    const float* centroids, void* key_out, void* value_out, int64_t out_stride_b,
                                    int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads, int head_dim,
                                    int block_size, int bits, int value_group, int64_t num_pages, int64_t max_blocks,

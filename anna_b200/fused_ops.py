@@ -109,6 +109,7 @@ class _Scratch:
     def __init__(self) -> None:
         self._buffers: dict[tuple[int, int], torch.Tensor] = {}
         self._counters: dict[tuple[int, int], torch.Tensor] = {}
+        self._byte_buffers: dict[tuple[int, int], torch.Tensor] = {}
 
     @staticmethod
     def _key(device: torch.device) -> tuple[int, int]:
@@ -123,6 +124,14 @@ class _Scratch:
             self._buffers[key] = buf
         return buf
 
+    def bytes(self, device: torch.device, count: int) -> torch.Tensor:
+        key = self._key(device)
+        buf = self._byte_buffers.get(key)
+        if buf is None or buf.numel() < count:
+            buf = torch.empty(max(count, 1 << 20), dtype=torch.uint8, device=device)
+            self._byte_buffers[key] = buf
+        return buf
+
     def counters(self, device: torch.device, count: int) -> torch.Tensor:
         key = self._key(device)
         buf = self._counters.get(key)
@@ -135,9 +144,31 @@ class _Scratch:
 _SCRATCH = _Scratch()
 
 
-def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, kv_heads: int, max_len: int):
-    """(partial_stats, partial_values, chunk_capacity, counters) sized by the library's own plan for this problem."""
-    _, chunks = _lib.decode_plan(batch, kv_heads, max(int(max_len), 1))
+def query_scratch(device: torch.device, batch: int, heads: int, kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Scratch for the rotated query fragments of the packed tensor-core decode."""
+    group_tiles = (heads // kv_heads + 7) // 8
+    return _SCRATCH.bytes(device, batch * kv_heads * group_tiles * head_dim * 32)
+
+
+_PLAN_CACHE: dict[tuple, int] = {}
+
+
+def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, kv_heads: int, max_len: int,
+                  *, turboquant: tuple[int, int, int] | None = None):
+    """(partial_stats, partial_values, chunk_capacity, counters) sized by the library's own plan for this problem.
+
+    ``turboquant=(max_blocks, block_size, residual_len)`` selects the plan of the packed decode (window chunks +
+    packed chunks) instead of the plan for ``max_len`` tokens."""
+    key = (batch, kv_heads, int(max_len), turboquant)
+    chunks = _PLAN_CACHE.get(key)
+    if chunks is None:
+        if turboquant is None:
+            _, chunks = _lib.decode_plan(batch, kv_heads, max(int(max_len), 1))
+        else:
+            _, chunks = _lib.tq_decode_plan(batch, kv_heads, *turboquant)
+        if len(_PLAN_CACHE) > 4096:
+            _PLAN_CACHE.clear()
+        _PLAN_CACHE[key] = chunks
     stats_floats = batch * heads * chunks * 2
     value_floats = batch * heads * chunks * head_dim
     buf = _SCRATCH.get(device, stats_floats + value_floats)

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .fused_ops import dtype_code, ptr, split_scratch, stream_ptr
+from .fused_ops import dtype_code, ptr, query_scratch, split_scratch, stream_ptr
 from .pools import TurboQuantLayerPool, resolve_value_group_size
 from .tq_tables import key_tables
 
@@ -32,6 +32,10 @@ def _i32(values, device: torch.device) -> torch.Tensor:
     return torch.tensor(values, dtype=torch.int32, device=device)
 
 
+def _i64(values, device: torch.device) -> torch.Tensor:
+    return torch.tensor(values, dtype=torch.int64, device=device)
+
+
 def _require_cuda(tensor: torch.Tensor, what: str) -> None:
     if tensor.device.type != "cuda":
         raise RuntimeError(f"{what}: tensors must live on a CUDA device; there is no CPU fallback for this path.")
@@ -47,7 +51,7 @@ def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_
     device = key_states.device
     batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    meta = _i32([past, slots], device)
+    meta = _i64([past, slots], device)
     assert pool.window is not None
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
@@ -73,19 +77,22 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     if query.dtype != pool.dtype:
         raise RuntimeError(f"query dtype {query.dtype} must match the cache dtype {pool.dtype}")
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    meta = _i32([lengths, slots], device)
+    meta = _i64([lengths, slots], device)
     out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
     max_len = max_blocks * pool.block_size + pool.residual_len
-    stats, values, capacity, counters = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len)
+    stats, values, capacity, counters = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len,
+                                                      turboquant=(max_blocks, pool.block_size, pool.residual_len))
+    frags = query_scratch(device, batch, heads, pool.kv_heads, dim)
     with torch.cuda.device(device):
         _lib.check(_lib.lib().anna_tq_paged_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
             ptr(pool.window), ptr(meta[1]), ptr(meta[0]), ptr(tables.signs1), ptr(tables.signs2),
             ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
             0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
-            capacity, 0, ptr(counters), batch, heads, pool.kv_heads, dim, pool.block_size, pool.residual_len, pool.bits,
+            capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads, pool.kv_heads, dim, pool.block_size,
+            pool.residual_len, pool.bits,
             pool.value_group, pool.capacity(), max_blocks, float(scaling), dtype_code(query.dtype),
             stream_ptr(device)), "anna_tq_paged_decode")
     return out
@@ -100,7 +107,7 @@ def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, qu
         raise ValueError("materialize outputs must share strides and be contiguous in the last dimension")
     batch, kv_heads, max_lq, dim = (int(v) for v in key_out.shape)
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    lq_dev = _i32(quantized_lengths, device)
+    lq_dev = _i64(quantized_lengths, device)
     with torch.cuda.device(device):
         _lib.check(_lib.lib().anna_tq_materialize(
             ptr(pool.packed_pages), ptr(table_dev), table_dev.stride(0), ptr(lq_dev), ptr(tables.signs1),

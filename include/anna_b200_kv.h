@@ -68,12 +68,12 @@ int anna_decode_plan(int batch, int kv_heads, int64_t max_len, int* chunk_tokens
  * (src/anna/model/ops.py:748-777).
  *   k_new, v_new   [B, Hkv, T, D] with element strides (kn_stride_b, kn_stride_h, kn_stride_t); last dim contiguous
  *   key_pages, value_pages  [P, Hkv, S, D] contiguous
- *   page_table     int32 [B, table_stride >= blocks];   past_lengths  int32 [B]
+ *   page_table     int32 [B, table_stride >= blocks];   past_lengths  int64 [B]
  *   status         optional device int32 (may be NULL): ANNA_DEV_BAD_PAGE is OR-ed in when a page id is invalid
  */
 int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                         int64_t kn_stride_t, void* key_pages, void* value_pages, const int32_t* page_table,
-                        int64_t table_stride, const int32_t* past_lengths, int batch, int kv_heads, int new_tokens,
+                        int64_t table_stride, const int64_t* past_lengths, int batch, int kv_heads, int new_tokens,
                         int head_dim, int block_size, int64_t num_pages, int64_t max_blocks, int dtype,
                         int32_t* status, anna_stream_t stream);
 
@@ -138,13 +138,13 @@ int anna_tq_page_layout(int head_dim, int bits, int block_size, int dtype, int v
  * sign-projected, value-quantized (turboquant.py:199-230, :255-272) and bit-packed straight into its page; tokens that
  * stay inside the window are written to the ring.  A ring slot is read before the same warp overwrites it.
  *   k_new, v_new  [B, Hkv, T, D] element strides (kn_stride_b, kn_stride_h, kn_stride_t)
- *   old_lengths   int32 [B] (lengths before this call);  window_slots int32 [B] (ring index of each row)
+ *   old_lengths   int64 [B] (lengths before this call);  window_slots int64 [B] (ring index of each row)
  *   signs1, signs2  float32 [D] (+1 / -1): rotation and QJL sign vectors;  centroids float32 [2^(bits-1)];
  *   boundaries    float32 [2^(bits-1) - 1]
  */
 int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                    int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                   void* window, const int32_t* window_slots, const int32_t* old_lengths, const float* signs1,
+                   void* window, const int64_t* window_slots, const int64_t* old_lengths, const float* signs1,
                    const float* signs2, const float* centroids, const float* boundaries, int batch, int kv_heads,
                    int new_tokens, int head_dim, int block_size, int residual_len, int bits, int value_group,
                    int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status, anna_stream_t stream);
@@ -156,18 +156,26 @@ int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, in
  * torch.ops.anna.gqa_decode_splitkv_turboquant_fused_out (gated_delta_fused_op.sycl:4771-5094), except that keys are
  * scored from their packed codes in the rotated basis (the identity of turboquant_key_attention_scores,
  * turboquant.py:290-332) instead of from a dense de-quantized copy.
- *   lengths   int32 [B]: total tokens per row (quantized = max(0, L - R), window = min(L, R)); L == 0 gives zeros
- *   the split-K plan bound is max_blocks * block_size + residual_len tokens
+ *   lengths   int64 [B]: total tokens per row (quantized = max(0, L - R), window = min(L, R)); L == 0 gives zeros
+ *   query_scratch: optional device scratch of at least B * Hkv * ceil(G / 8) * head_dim * 32 bytes; the tensor-core
+ *   path stores the rotated queries there (as fp16 MMA fragments) before the split pass.  Without it, or for fp32
+ *   caches, head_dim 64, value groups other than 32 or page sizes that are not a multiple of 16, the CUDA-core path runs.
+ *   split-K slots: anna_tq_decode_plan gives the chunk length and the slot count (window chunks first, then the
+ *   chunks of the packed prefix); scratch and counters as for the other decode entry points
  */
+int anna_tq_decode_plan(int batch, int kv_heads, int64_t max_blocks, int block_size, int residual_len,
+                        int* chunk_tokens, int* num_chunks);
+
 int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* packed_pages,
                          const int32_t* block_table, int64_t table_stride, const void* window,
-                         const int32_t* window_slots, const int32_t* lengths, const float* signs1,
+                         const int64_t* window_slots, const int64_t* lengths, const float* signs1,
                          const float* signs2, const float* centroids, const void* gate, int64_t gate_stride_b,
                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
                          float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
-                         int32_t* split_counters, int batch, int q_heads, int kv_heads, int head_dim, int block_size,
-                         int residual_len, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
-                         float scaling, int dtype, anna_stream_t stream);
+                         int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes, int batch,
+                         int q_heads, int kv_heads, int head_dim, int block_size, int residual_len, int bits,
+                         int value_group, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                         anna_stream_t stream);
 
 /*
  * De-quantize the packed prefix of each row to dense [B, Hkv, Lq_max, D] keys and values in the cache dtype (element
@@ -176,7 +184,7 @@ int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, 
  * dequantize_turboquant_keys (:275-287) + dequantize_turboquant_values (:233-252).
  */
 int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                        const int32_t* quantized_lengths, const float* signs1, const float* signs2,
+                        const int64_t* quantized_lengths, const float* signs1, const float* signs2,
                         const float* centroids, void* key_out, void* value_out, int64_t out_stride_b,
                         int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads, int head_dim,
                         int block_size, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
