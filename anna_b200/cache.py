@@ -24,7 +24,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import _lib
-from .fused_ops import dtype_code, ptr, stream_ptr
+from .fused_ops import MetadataUploader, dtype_code, on_device, ptr, stream_ptr
 from .pools import Qwen3PagedLayerAllocator, TurboQuantLayerPool
 from .prefix_block_cache import PrefixBlockPool
 from .turboquant import VALID_KV_CACHE_QUANT_BITS, TurboQuantKVRow, launch_tq_append, launch_tq_decode
@@ -145,8 +145,9 @@ class Qwen3DynamicCache:
         self.page_table_caches: list[torch.Tensor | None] = [None] * layers
         self.page_table_capacities: list[int] = [0] * layers
         self._table_rows_synced: list[list[int] | None] = [None] * layers  # blocks already on the device per row
-        self._length_cache: list[tuple[list[int], torch.Tensor] | None] = [None] * layers
-        self._slot_cache: list[tuple[list[int], torch.Tensor] | None] = [None] * layers
+        self._table_blocks_total: list[int] = [-1] * layers                # sum of table lengths at the last sync
+        # per layer: (lengths list, slots list | None, int64 device tensor [past; now; (slots)]) of the last append
+        self._step_meta: list[tuple[list[int], list[int] | None, torch.Tensor] | None] = [None] * layers
         self.seen_tokens = 0
         self.rope_deltas: torch.Tensor | None = None
         self.reserved_seq_capacity = 0
@@ -233,14 +234,24 @@ class Qwen3DynamicCache:
 
         Only rows whose table grew since the last call are uploaded."""
         tables = self._tables_of(layer_idx)
-        required = max((len(t) for t in tables), default=0)
+        total = 0
+        required = 0
+        for table in tables:
+            n = len(table)
+            total += n
+            if n > required:
+                required = n
         if required <= 0:
             self.page_table_caches[layer_idx] = None
             self.page_table_capacities[layer_idx] = 0
             self._table_rows_synced[layer_idx] = None
+            self._table_blocks_total[layer_idx] = -1
             return None
         buffer = self.page_table_caches[layer_idx]
         synced = self._table_rows_synced[layer_idx]
+        if (buffer is not None and synced is not None and buffer.shape[0] == batch_size and buffer.device == device
+                and buffer.shape[1] >= required and self._table_blocks_total[layer_idx] == total):
+            return buffer[:, :required]  # nothing was appended since the last sync
         if (buffer is None or buffer.shape[0] != batch_size or buffer.device != device
                 or buffer.shape[1] < required or synced is None):
             capacity = max(required, max(1, self.page_table_capacities[layer_idx] * 2))
@@ -252,6 +263,7 @@ class Qwen3DynamicCache:
             self.page_table_caches[layer_idx] = buffer
             self.page_table_capacities[layer_idx] = capacity
             self._table_rows_synced[layer_idx] = [len(t) for t in tables]
+            self._table_blocks_total[layer_idx] = total
             return buffer[:, :required]
         flat_index: list[int] = []
         flat_value: list[int] = []
@@ -263,8 +275,13 @@ class Qwen3DynamicCache:
                 flat_value.extend(table[have:])
                 synced[row_idx] = len(table)
         if flat_index:
-            index = torch.tensor(flat_index, dtype=torch.long, device=device)
-            buffer.view(-1).index_copy_(0, index, _i32(flat_value, device))
+            if device.type == "cuda":
+                patch = MetadataUploader.for_device(device).upload([flat_index, flat_value])
+                buffer.view(-1).index_copy_(0, patch[0], patch[1].to(torch.int32))
+            else:
+                index = torch.tensor(flat_index, dtype=torch.long, device=device)
+                buffer.view(-1).index_copy_(0, index, _i32(flat_value, device))
+        self._table_blocks_total[layer_idx] = total
         return buffer[:, :required]
 
     def _lengths_on_device(self, layer_idx: int, lengths: list[int], device: torch.device,
@@ -285,7 +302,6 @@ class Qwen3DynamicCache:
         self._ensure_batch_size(batch_size)
         device = key_states.device
         past = list(self.layer_lengths[layer_idx])
-        past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         reserved_length = max(append_length, self.reserved_seq_capacity)
         hint = (reserved_length + self.block_size - 1) // self.block_size
         if hint > 0:
@@ -305,20 +321,31 @@ class Qwen3DynamicCache:
                 table.extend(self.allocator.allocate(layer_idx, blocks - len(table), key_template=key_states,
                                                      value_template=value_states))
             self.layer_lengths[layer_idx][batch_idx] = required
-        self.seen_tokens = max(self.get_seq_lengths().tolist(), default=0)
+        lengths = self.layer_lengths[layer_idx]
+        self.seen_tokens = max(self.seen_tokens, max(lengths, default=0))
+        if device.type == "cuda":
+            meta = MetadataUploader.for_device(device).upload([past, lengths])
+            self._step_meta[layer_idx] = (list(lengths), None, meta)
+            past_lengths = meta[0]
+        else:
+            meta = None
+            past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
         layer = self.allocator.layers[layer_idx]
         if table_dev is not None:
             for start, end in segments:
                 if end > start:
+                    whole = start == 0 and end == append_length
                     self._launch_page_write(layer, key_states[:, :, start:end, :], value_states[:, :, start:end, :],
-                                            table_dev, [p + start for p in past])
+                                            table_dev, [p + start for p in past],
+                                            past_dev=past_lengths if whole and meta is not None else None)
         if not require_dense_cache:
             return None, None, past_lengths
         gathered_key, gathered_value, _ = self._gather_layer_cache(layer_idx)
         return gathered_key, gathered_value, past_lengths
 
-    def _launch_page_write(self, layer: Qwen3PagedLayerAllocator, key_states, value_states, table_dev, past):
+    def _launch_page_write(self, layer: Qwen3PagedLayerAllocator, key_states, value_states, table_dev, past,
+                           past_dev: torch.Tensor | None = None):
         key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
         if value_states.stride() != key_states.stride():
             key_states, value_states = key_states.contiguous(), value_states.contiguous()
@@ -326,9 +353,10 @@ class Qwen3DynamicCache:
         if device.type != "cuda":
             raise RuntimeError("anna_b200 caches live on a CUDA device; there is no CPU fallback for update().")
         batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
-        past_dev = torch.tensor(past, dtype=torch.int64, device=device)
+        if past_dev is None:
+            past_dev = MetadataUploader.for_device(device).upload([past])[0]
         assert layer.key_pages is not None and layer.value_pages is not None
-        with torch.cuda.device(device):
+        with on_device(device):
             _lib.check(_lib.lib().anna_paged_kv_write(
                 ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
                 ptr(layer.key_pages), ptr(layer.value_pages), ptr(table_dev), table_dev.stride(0), ptr(past_dev),
@@ -391,7 +419,6 @@ class Qwen3DynamicCache:
                        residual_len=self.kv_cache_residual_len, dtype=key_states.dtype, device=device)
         rows = self.turboquant_rows[layer_idx]
         past = list(self.layer_lengths[layer_idx])
-        past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         missing = sum(1 for row in rows if row is None)
         if missing:
             pool.ensure_slot_capacity(pool.slot_capacity() - len(pool.free_slots) + missing)
@@ -402,13 +429,22 @@ class Qwen3DynamicCache:
                 row._bind(pool, kv_heads=kv_heads, head_dim=head_dim, dtype=key_states.dtype, device=device)
                 rows[batch_idx] = row
             row._reserve_blocks(row.length + append_length)
+        slots = [row.slot for row in rows]
+        lengths = self.layer_lengths[layer_idx]
+        for batch_idx, row in enumerate(rows):
+            row._length += append_length
+            lengths[batch_idx] = row._length
+        meta = None
+        if device.type == "cuda":
+            meta = MetadataUploader.for_device(device).upload([past, lengths, slots])
+            self._step_meta[layer_idx] = (list(lengths), slots, meta)
+            past_lengths = meta[0]
+        else:
+            past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         if append_length > 0:
             table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
-            launch_tq_append(pool, key_states, value_states, table_dev, [row.slot for row in rows], past)
-            for batch_idx, row in enumerate(rows):
-                row._length += append_length
-                self.layer_lengths[layer_idx][batch_idx] = row.length
-        self.seen_tokens = max(self.get_seq_lengths().tolist(), default=0)
+            launch_tq_append(pool, key_states, value_states, table_dev, slots, past, meta=meta)
+        self.seen_tokens = max(self.seen_tokens, max(lengths, default=0))
         if not require_dense_cache:
             return None, None, past_lengths
         keys, values, _ = self._gather_layer_cache(layer_idx)
@@ -438,7 +474,11 @@ class Qwen3DynamicCache:
         table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch, device=device)
         lengths = [0 if row is None else row.length for row in rows]
         slots = [0 if row is None else row.slot for row in rows]
-        return launch_tq_decode(pool, query_states, table_dev, slots, lengths, scaling, gate)
+        cached = self._step_meta[layer_idx]
+        meta = None
+        if cached is not None and cached[0] == lengths and cached[1] == slots and cached[2].device == device:
+            meta = cached[2]
+        return launch_tq_decode(pool, query_states, table_dev, slots, lengths, scaling, gate, meta=meta)
 
     # -- dense views -------------------------------------------------------------------------------------------------------
 
@@ -460,7 +500,11 @@ class Qwen3DynamicCache:
         page_table = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
         if page_table is None:
             return None
-        visible_lengths = torch.tensor(lengths, dtype=torch.long, device=device)
+        cached = self._step_meta[layer_idx]
+        if cached is not None and cached[0] == lengths and cached[2].device == device:
+            visible_lengths = cached[2][1]
+        else:
+            visible_lengths = torch.tensor(lengths, dtype=torch.long, device=device)
         return layer.key_pages, layer.value_pages, page_table, visible_lengths
 
     def _gather_layer_cache(self, layer_idx: int):
@@ -638,6 +682,8 @@ class Qwen3DynamicCache:
             self.page_table_caches[layer_idx] = None
             self.page_table_capacities[layer_idx] = 0
             self._table_rows_synced[layer_idx] = None
+            self._table_blocks_total[layer_idx] = -1
+            self._step_meta[layer_idx] = None
         self.seen_tokens = 0
         self.rope_deltas = None
         self.reserved_seq_capacity = 0

@@ -52,6 +52,78 @@ def stream_ptr(device: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+class on_device:
+    """``with on_device(dev):`` makes ``dev`` the current CUDA device, skipping the switch when it already is."""
+
+    __slots__ = ("index", "previous")
+
+    def __init__(self, device: torch.device) -> None:
+        self.index = device.index if device.index is not None else torch.cuda.current_device()
+        self.previous = -1
+
+    def __enter__(self) -> None:
+        current = torch.cuda.current_device()
+        if current != self.index:
+            self.previous = current
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc) -> None:
+        if self.previous >= 0:
+            torch.cuda.set_device(self.previous)
+
+
+class MetadataUploader:
+    """Small per-step integer metadata (lengths, ring slots) goes to the GPU through a ring of pinned host buffers
+    with one asynchronous copy per call, instead of a synchronous ``torch.tensor(list, device=...)`` per array."""
+
+    _instances: dict[int, "MetadataUploader"] = {}
+
+    def __init__(self, device: torch.device, slots: int = 16) -> None:
+        self.device = device
+        self.slots = slots
+        self.capacity = 0
+        self.buffers: list[torch.Tensor] = []
+        self.views: list = []
+        self.events: list[torch.cuda.Event | None] = []
+        self.next = 0
+
+    @classmethod
+    def for_device(cls, device: torch.device) -> "MetadataUploader":
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        inst = cls._instances.get(index)
+        if inst is None:
+            inst = cls._instances[index] = cls(torch.device("cuda", index))
+        return inst
+
+    def _ensure(self, count: int) -> None:
+        if count <= self.capacity:
+            return
+        self.capacity = max(1024, 2 * count)
+        self.buffers = [torch.empty(self.capacity, dtype=torch.int64).pin_memory() for _ in range(self.slots)]
+        self.views = [buf.numpy() for buf in self.buffers]
+        self.events = [None] * self.slots
+
+    def upload(self, rows: list[list[int]]) -> torch.Tensor:
+        """int64 [len(rows), len(rows[0])] on the device; the copy is ordered on the current stream."""
+        width = len(rows[0])
+        count = len(rows) * width
+        self._ensure(count)
+        slot = self.next
+        self.next = (slot + 1) % self.slots
+        event = self.events[slot]
+        if event is not None:
+            event.synchronize()  # the previous copy out of this buffer has finished (normally long ago)
+        view = self.views[slot]
+        for idx, row in enumerate(rows):
+            view[idx * width:(idx + 1) * width] = row
+        out = torch.empty((len(rows), width), dtype=torch.int64, device=self.device)
+        out.view(-1).copy_(self.buffers[slot][:count], non_blocking=True)
+        if event is None:
+            event = self.events[slot] = torch.cuda.Event()
+        event.record()
+        return out
+
+
 def _require_cuda(name: str, **tensors: torch.Tensor | None) -> torch.device:
     device = None
     for label, tensor in tensors.items():
@@ -222,7 +294,7 @@ def _gqa_decode_dense(name, query, key, value, visible_lengths, scaling, gate, *
         capacity = int(partial_stats.shape[2])
         chunk_tokens = min(max(int(block_size), 16), key_len)
         counters = None
-    with torch.cuda.device(device):
+    with on_device(device):
         _lib.check(_lib.lib().anna_gqa_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(key), ptr(value), key.stride(0), key.stride(1),
             key.stride(2), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(target), target.stride(0),
@@ -313,7 +385,7 @@ def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visibl
     if max_blocks == 0:
         return out.zero_()
     stats, values, capacity, counters = split_scratch(device, batch, heads, dim, kv_heads, max_blocks * block)
-    with torch.cuda.device(device):
+    with on_device(device):
         _lib.check(_lib.lib().anna_paged_gqa_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(key_pages), ptr(value_pages), ptr(page_table),
             page_table.stride(0), ptr(visible_lengths), ptr(gate), gate_sb, gate_sh, ptr(out), out.stride(0),
@@ -414,14 +486,16 @@ def _resolve(name: str):
 
 
 def run_gqa_decode_fused(*, query, key, value, visible_lengths, scaling, gate=None):
-    op = _resolve("gqa_decode_fused")
+    _resolve("gqa_decode_fused")
+    op = _op_gqa_decode_fused  # same function the dispatcher would reach for CUDA tensors
     if gate is None:
         return op(query, key, value, visible_lengths, float(scaling))
     return op(query, key, value, visible_lengths, float(scaling), gate)
 
 
 def run_gqa_decode_splitkv_fused(*, query, key, value, scaling, block_size, gate=None):
-    op = _resolve("gqa_decode_splitkv_fused")
+    _resolve("gqa_decode_splitkv_fused")
+    op = _op_gqa_decode_splitkv_fused  # same function the dispatcher would reach for CUDA tensors
     if gate is None:
         return op(query, key, value, float(scaling), int(block_size))
     return op(query, key, value, float(scaling), int(block_size), gate)
@@ -429,14 +503,16 @@ def run_gqa_decode_splitkv_fused(*, query, key, value, scaling, block_size, gate
 
 def run_gqa_decode_splitkv_fused_out(*, query, key, value, output, partial_stats, partial_values, scaling, block_size,
                                      gate=None):
-    op = _resolve("gqa_decode_splitkv_fused_out")
+    _resolve("gqa_decode_splitkv_fused_out")
+    op = _op_gqa_decode_splitkv_fused_out  # same function the dispatcher would reach for CUDA tensors
     if gate is None:
         return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size))
     return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size), gate)
 
 
 def run_paged_gqa_decode_fused(*, query, key_pages, value_pages, page_table, visible_lengths, scaling, gate=None):
-    op = _resolve("paged_gqa_decode_fused")
+    _resolve("paged_gqa_decode_fused")
+    op = _op_paged_gqa_decode_fused  # same function the dispatcher would reach for CUDA tensors
     if gate is None:
         return op(query, key_pages, value_pages, page_table, visible_lengths, float(scaling))
     return op(query, key_pages, value_pages, page_table, visible_lengths, float(scaling), gate)

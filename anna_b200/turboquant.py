@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .fused_ops import dtype_code, ptr, query_scratch, split_scratch, stream_ptr
+from .fused_ops import MetadataUploader, dtype_code, on_device, ptr, query_scratch, split_scratch, stream_ptr
 from .pools import TurboQuantLayerPool, resolve_value_group_size
 from .tq_tables import key_tables
 
@@ -42,8 +42,11 @@ def _require_cuda(tensor: torch.Tensor, what: str) -> None:
 
 
 def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_states: torch.Tensor,
-                     table_dev: torch.Tensor | None, slots: list[int], past: list[int]) -> None:
-    """Append ``[B, Hkv, T, D]`` to B rows of one layer: ring update + quantize-on-overflow + page scatter."""
+                     table_dev: torch.Tensor | None, slots: list[int], past: list[int],
+                     meta: torch.Tensor | None = None) -> None:
+    """Append ``[B, Hkv, T, D]`` to B rows of one layer: ring update + quantize-on-overflow + page scatter.
+
+    ``meta`` (optional) is an int64 device tensor whose row 0 holds ``past`` and whose last row holds ``slots``."""
     _require_cuda(key_states, "TurboQuant append")
     key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
     if value_states.stride() != key_states.stride():
@@ -51,23 +54,26 @@ def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_
     device = key_states.device
     batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    meta = _i64([past, slots], device)
+    if meta is None:
+        meta = MetadataUploader.for_device(device).upload([past, slots])
     assert pool.window is not None
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
-    with torch.cuda.device(device):
+    with on_device(device):
         _lib.check(_lib.lib().anna_tq_append(
             ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
-            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(meta[1]), ptr(meta[0]),
+            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(meta[-1]), ptr(meta[0]),
             ptr(tables.signs1), ptr(tables.signs2), ptr(tables.centroids), ptr(tables.boundaries), batch, kv_heads,
             tokens, dim, pool.block_size, pool.residual_len, pool.bits, pool.value_group, pool.capacity(), max_blocks,
             dtype_code(key_states.dtype), ptr(pool.status), stream_ptr(device)), "anna_tq_append")
 
 
 def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, table_dev: torch.Tensor | None,
-                     slots: list[int], lengths: list[int], scaling: float,
-                     gate: torch.Tensor | None) -> torch.Tensor:
-    """Decode ``[B, Hq, 1, D]`` queries against B rows of one layer (packed prefix + window ring)."""
+                     slots: list[int], lengths: list[int], scaling: float, gate: torch.Tensor | None,
+                     meta: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode ``[B, Hq, 1, D]`` queries against B rows of one layer (packed prefix + window ring).
+
+    ``meta`` (optional) is an int64 device tensor whose row -2 holds ``lengths`` and whose last row holds ``slots``."""
     _require_cuda(query_states, "TurboQuant decode")
     query = query_states if query_states.stride(3) == 1 else query_states.contiguous()
     if gate is not None and gate.stride(3) != 1:
@@ -77,7 +83,8 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     if query.dtype != pool.dtype:
         raise RuntimeError(f"query dtype {query.dtype} must match the cache dtype {pool.dtype}")
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    meta = _i64([lengths, slots], device)
+    if meta is None:
+        meta = MetadataUploader.for_device(device).upload([lengths, slots])
     out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
@@ -85,10 +92,10 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     stats, values, capacity, counters = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len,
                                                       turboquant=(max_blocks, pool.block_size, pool.residual_len))
     frags = query_scratch(device, batch, heads, pool.kv_heads, dim)
-    with torch.cuda.device(device):
+    with on_device(device):
         _lib.check(_lib.lib().anna_tq_paged_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
-            ptr(pool.window), ptr(meta[1]), ptr(meta[0]), ptr(tables.signs1), ptr(tables.signs2),
+            ptr(pool.window), ptr(meta[-1]), ptr(meta[-2]), ptr(tables.signs1), ptr(tables.signs2),
             ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
             0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
             capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads, pool.kv_heads, dim, pool.block_size,
@@ -108,7 +115,7 @@ def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, qu
     batch, kv_heads, max_lq, dim = (int(v) for v in key_out.shape)
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
     lq_dev = _i64(quantized_lengths, device)
-    with torch.cuda.device(device):
+    with on_device(device):
         _lib.check(_lib.lib().anna_tq_materialize(
             ptr(pool.packed_pages), ptr(table_dev), table_dev.stride(0), ptr(lq_dev), ptr(tables.signs1),
             ptr(tables.signs2), ptr(tables.centroids), ptr(key_out), ptr(value_out), key_out.stride(0),
