@@ -44,6 +44,10 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_paged_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_i64,
                                       c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i32,
                                       c_i32, c_i64, c_i64, c_f32, c_i32, c_ptr]),
+    "anna_noalloc_scratch_bytes": (c_size, []),
+    "anna_paged_gqa_decode_noalloc": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64,
+                                              c_i64, c_ptr, c_i64, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,
+                                              c_i64, c_f32, c_i32, c_ptr]),
     "anna_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64,
                                 c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i64,
                                 c_i32, c_f32, c_i32, c_ptr]),

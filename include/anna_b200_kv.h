@@ -98,6 +98,28 @@ int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                           anna_stream_t stream);
 
 /*
+ * Paged decode without caller scratch (no counterpart in the reference).  Same inputs, outputs and result as
+ * anna_paged_gqa_decode, for hosts that cannot allocate device memory themselves (a plugin working inside another
+ * engine's memory pool, a caller whose allocator is locked): the split-K partials and arrival counters live in a
+ * fixed 16 MiB array that is part of the library's device image, so every GPU that loads the library holds those
+ * 16 MiB until the process exits.  The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Problems whose plan needs more than the array (anna_noalloc_scratch_bytes()) are rejected with
+ *     ANNA_ERR_WORKSPACE; batch * kv_heads * ceil(G / 8) must also stay within 16384.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside of any stream capture.
+ *   - All calls share the one array.  Calls that can overlap on the GPU (different streams, no ordering between
+ *     them) race on it; order them or use anna_paged_gqa_decode with separate scratch.
+ */
+size_t anna_noalloc_scratch_bytes(void);
+int anna_paged_gqa_decode_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* key_pages,
+                                  const void* value_pages, const int32_t* page_table, int64_t table_stride,
+                                  const int64_t* visible_lengths, const void* gate, int64_t gate_stride_b,
+                                  int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                                  int batch, int q_heads, int kv_heads, int head_dim, int block_size,
+                                  int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                                  anna_stream_t stream);
+
+/*
  * Single-token GQA decode over dense K/V [B, Hkv, L, D] (arbitrary batch/head/token strides, last dim contiguous)
  * with per-row visible lengths.  Stands in for torch.ops.anna.gqa_decode_fused (gated_delta_fused_op.sycl:4339-4479)
  * and, with visible_lengths == NULL (all L keys visible), for gqa_decode_splitkv_fused / _out (:4494-4769).
