@@ -14,6 +14,7 @@ from .fused_ops import (
     run_gqa_decode_fused,
     run_gqa_decode_splitkv_fused,
     run_gqa_decode_splitkv_fused_out,
+    run_gqa_decode_splitkv_turboquant_fused_out,
     run_paged_gqa_decode_fused,
 )
 from .pools import Qwen3PagedLayerAllocator, TurboQuantLayerPool, resolve_value_group_size
@@ -27,5 +28,5 @@ __all__ = [
     "gqa_decode_splitkv_fused_is_available", "gqa_decode_splitkv_fused_out_is_available",
     "gqa_decode_splitkv_turboquant_fused_out_is_available", "paged_gqa_decode_fused_is_available",
     "run_gqa_decode_fused", "run_gqa_decode_splitkv_fused", "run_gqa_decode_splitkv_fused_out",
-    "run_paged_gqa_decode_fused",
+    "run_gqa_decode_splitkv_turboquant_fused_out", "run_paged_gqa_decode_fused",
 ]

@@ -31,6 +31,11 @@ SCHEMAS = {
     "gqa_decode_splitkv_fused_out":
         "(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor(b!) partial_stats, "
         "Tensor(c!) partial_values, float scaling, int block_size, Tensor? gate=None) -> Tensor(a!)",
+    "gqa_decode_splitkv_turboquant_fused_out":
+        "(Tensor query, Tensor quantized_key, Tensor value_data, Tensor value_scales, Tensor value_zeros, "
+        "Tensor residual_key, Tensor residual_value, Tensor(a!) output, Tensor(b!) partial_stats, "
+        "Tensor(c!) partial_values, float scaling, int value_bits, int value_group_size, int block_size, "
+        "Tensor? gate=None) -> Tensor(a!)",
     "paged_gqa_decode_fused":
         "(Tensor query, Tensor key_pages, Tensor value_pages, Tensor page_table, Tensor visible_lengths, "
         "float scaling, Tensor? gate=None) -> Tensor",
@@ -347,6 +352,84 @@ def _op_gqa_decode_splitkv_fused_out(query, key, value, output, partial_stats, p
                              partial_values=partial_values, block_size=block_size)
 
 
+def _op_gqa_decode_splitkv_turboquant_fused_out(query, quantized_key, value_data, value_scales, value_zeros,
+                                                residual_key, residual_value, output, partial_stats, partial_values,
+                                                scaling, value_bits, value_group_size, block_size, gate=None):
+    """validate_gqa_decode_splitkv_turboquant_inputs (.sycl:1447-1501) + launch."""
+    name = "gqa_decode_splitkv_turboquant_fused_out"
+    query = _check_query(name, query)
+    for label, tensor in (("quantized_key", quantized_key), ("value_data", value_data), ("value_scales", value_scales),
+                          ("value_zeros", value_zeros), ("residual_key", residual_key),
+                          ("residual_value", residual_value)):
+        if tensor.dim() != 4:
+            raise RuntimeError(f"{label} must be a 4-D tensor [batch, kv_heads, tokens, ...]")
+    if query.shape[0] != quantized_key.shape[0] or query.shape[0] != residual_key.shape[0]:
+        raise RuntimeError("query/quantized_key/residual_key batch size mismatch")
+    if residual_key.shape != residual_value.shape:
+        raise RuntimeError("residual_key and residual_value must share the same shape")
+    if quantized_key.shape[1] != residual_key.shape[1]:
+        raise RuntimeError("quantized and residual KV head count mismatch")
+    if query.shape[1] % quantized_key.shape[1] != 0:
+        raise RuntimeError("query heads must be divisible by kv_heads")
+    if query.shape[3] != quantized_key.shape[3] or query.shape[3] != residual_key.shape[3]:
+        raise RuntimeError("query/key head_dim mismatch")
+    if quantized_key.shape[2] < 1:
+        raise RuntimeError("gqa_decode_splitkv_turboquant_fused requires a non-empty quantized prefix")
+    if value_data.shape[:3] != quantized_key.shape[:3] or value_scales.shape[:3] != quantized_key.shape[:3]:
+        raise RuntimeError("value_data / value_scales must match quantized_key in batch, heads and quantized_len")
+    if value_zeros.shape != value_scales.shape:
+        raise RuntimeError("value_zeros shape must match value_scales")
+    if value_bits not in (2, 3, 4):
+        raise RuntimeError("TurboQuant value_bits must be 2, 3, or 4")
+    dim = int(query.shape[3])
+    if value_group_size <= 0 or dim % value_group_size != 0 or value_scales.shape[3] * value_group_size != dim:
+        raise RuntimeError("TurboQuant value_group_size must evenly divide head_dim and match value_scales")
+    per_byte = 4 if value_bits == 2 else 2
+    if value_data.shape[3] * per_byte < dim:
+        raise RuntimeError("TurboQuant packed value width is smaller than head_dim")
+    if block_size < 16:
+        raise RuntimeError("gqa_decode_splitkv_turboquant_fused block_size must be at least 16")
+    if value_data.dtype != torch.uint8:
+        raise RuntimeError("TurboQuant value_data must be uint8")
+    if not (query.dtype == quantized_key.dtype == residual_key.dtype == residual_value.dtype == value_scales.dtype
+            == value_zeros.dtype):
+        raise RuntimeError("query, keys, residual values, value_scales, and value_zeros must share the same dtype")
+    device = _require_cuda(name, query=query, quantized_key=quantized_key, value_data=value_data,
+                           value_scales=value_scales, value_zeros=value_zeros, residual_key=residual_key,
+                           residual_value=residual_value, gate=gate)
+    quantized_len, residual_len = int(quantized_key.shape[2]), int(residual_key.shape[2])
+    _check_split_workspace(name, query, quantized_len + residual_len, block_size, output, partial_stats, partial_values)
+    quantized_key = _last_dim_contiguous(quantized_key)
+    value_data = _last_dim_contiguous(value_data)
+    value_scales = _last_dim_contiguous(value_scales)
+    value_zeros = _last_dim_contiguous(value_zeros)
+    if value_zeros.stride() != value_scales.stride():
+        value_scales, value_zeros = value_scales.contiguous(), value_zeros.contiguous()
+    residual_key = _last_dim_contiguous(residual_key)
+    residual_value = _last_dim_contiguous(residual_value)
+    if residual_value.stride() != residual_key.stride():
+        residual_key, residual_value = residual_key.contiguous(), residual_value.contiguous()
+    gate, gate_sb, gate_sh = _check_gate(name, query, gate)
+    batch, heads = int(query.shape[0]), int(query.shape[1])
+    kv_heads = int(quantized_key.shape[1])
+    target = output if output.stride(3) == 1 else torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    chunk_tokens = min(max(int(block_size), 16), quantized_len + residual_len)
+    with on_device(device):
+        _lib.check(_lib.lib().anna_gqa_decode_turboquant_values(
+            ptr(query), query.stride(0), query.stride(1), ptr(quantized_key), quantized_key.stride(0),
+            quantized_key.stride(1), quantized_key.stride(2), ptr(value_data), value_data.stride(0),
+            value_data.stride(1), value_data.stride(2), ptr(value_scales), ptr(value_zeros), value_scales.stride(0),
+            value_scales.stride(1), value_scales.stride(2), ptr(residual_key) if residual_len else None,
+            ptr(residual_value) if residual_len else None, residual_key.stride(0), residual_key.stride(1),
+            residual_key.stride(2), ptr(gate), gate_sb, gate_sh, ptr(target), target.stride(0), target.stride(1),
+            ptr(partial_stats), ptr(partial_values), int(partial_stats.shape[2]), chunk_tokens, batch, heads, kv_heads,
+            quantized_len, residual_len, dim, int(value_bits), int(value_group_size), float(scaling),
+            dtype_code(query.dtype), stream_ptr(device)), name)
+    if target is not output:
+        output.copy_(target)
+    return output
+
+
 def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visible_lengths, scaling, gate=None):
     name = "paged_gqa_decode_fused"
     query = _check_query(name, query)
@@ -398,6 +481,7 @@ _IMPLS = {
     "gqa_decode_fused": _op_gqa_decode_fused,
     "gqa_decode_splitkv_fused": _op_gqa_decode_splitkv_fused,
     "gqa_decode_splitkv_fused_out": _op_gqa_decode_splitkv_fused_out,
+    "gqa_decode_splitkv_turboquant_fused_out": _op_gqa_decode_splitkv_turboquant_fused_out,
     "paged_gqa_decode_fused": _op_paged_gqa_decode_fused,
 }
 
@@ -508,6 +592,15 @@ def run_gqa_decode_splitkv_fused_out(*, query, key, value, output, partial_stats
     if gate is None:
         return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size))
     return op(query, key, value, output, partial_stats, partial_values, float(scaling), int(block_size), gate)
+
+
+def run_gqa_decode_splitkv_turboquant_fused_out(*, query, quantized_key, value_data, value_scales, value_zeros,
+                                                residual_key, residual_value, output, partial_stats, partial_values,
+                                                scaling, value_bits, value_group_size, block_size, gate=None):
+    _resolve("gqa_decode_splitkv_turboquant_fused_out")
+    return _op_gqa_decode_splitkv_turboquant_fused_out(
+        query, quantized_key, value_data, value_scales, value_zeros, residual_key, residual_value, output,
+        partial_stats, partial_values, float(scaling), int(value_bits), int(value_group_size), int(block_size), gate)
 
 
 def run_paged_gqa_decode_fused(*, query, key_pages, value_pages, page_table, visible_lengths, scaling, gate=None):

@@ -212,6 +212,27 @@ int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table,
                         int block_size, int bits, int value_group, int64_t num_pages, int64_t max_blocks,
                         int64_t max_quantized_len, int dtype, anna_stream_t stream);
 
+/*
+ * Single-token GQA decode over (dense de-quantized keys | packed values | un-quantized residual), the exact operand
+ * set of torch.ops.anna.gqa_decode_splitkv_turboquant_fused_out (gated_delta_fused_op.sycl:4771-5094, schema
+ * :7652-7669, validator :1447-1501).  All tensors carry element strides for batch / head / token; last dim contiguous.
+ *   quantized_key [B, Hkv, Lq, D];  value_data uint8 [B, Hkv, Lq, D / per_byte] (per_byte = 4 for 2 bits, else 2);
+ *   value_scales / value_zeros [B, Hkv, Lq, D / value_group] in the query dtype (shared strides);
+ *   residual_key / residual_value [B, Hkv, Lr, D] (may be NULL when Lr == 0);  scratch as for the other decode calls
+ */
+int anna_gqa_decode_turboquant_values(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                      const void* quantized_key, int64_t qk_stride_b, int64_t qk_stride_h,
+                                      int64_t qk_stride_t, const uint8_t* value_data, int64_t vd_stride_b,
+                                      int64_t vd_stride_h, int64_t vd_stride_t, const void* value_scales,
+                                      const void* value_zeros, int64_t vs_stride_b, int64_t vs_stride_h,
+                                      int64_t vs_stride_t, const void* residual_key, const void* residual_value,
+                                      int64_t r_stride_b, int64_t r_stride_h, int64_t r_stride_t, const void* gate,
+                                      int64_t gate_stride_b, int64_t gate_stride_h, void* out, int64_t out_stride_b,
+                                      int64_t out_stride_h, float* partial_stats, float* partial_values,
+                                      int chunk_capacity, int chunk_tokens, int batch, int q_heads, int kv_heads,
+                                      int64_t quantized_len, int64_t residual_len, int head_dim, int value_bits,
+                                      int value_group, float scaling, int dtype, anna_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -165,3 +165,35 @@ def test_ops_reject_cpu_tensors_and_bad_shapes(cuda_device):
     with pytest.raises(RuntimeError, match="divisible"):
         fused_ops.run_gqa_decode_fused(query=q, key=k, value=k, visible_lengths=torch.tensor([5], device=cuda_device),
                                        scaling=1.0)
+
+
+@pytest.mark.parametrize("value_bits", [2, 3, 4])
+def test_splitkv_turboquant_out_matches_reference_case(cuda_device, value_bits):
+    """The reference's own kernel test (tests/test_fused_op_xpu.py:647-703): Hq=8, Hkv=2, D=64, Lq=77, R=5, group 16,
+    strided query, oversized workspace, fused gate; inputs and expected output come from the reference run on CPU."""
+    from pathlib import Path
+
+    data = np.load(Path(__file__).resolve().parent / "golden" / "splitkv_turboquant_case.npz")
+    p = f"b{value_bits}_"
+    bf = lambda name: torch.from_numpy(data[p + name]).to(cuda_device).to(torch.bfloat16)  # noqa: E731
+    storage = torch.zeros(1, 8, 1, 128, device=cuda_device, dtype=torch.bfloat16)
+    storage[..., ::2] = bf("query")
+    query = storage[..., ::2]
+    assert not query.is_contiguous()
+    vdata = torch.from_numpy(data[p + "vdata"]).to(cuda_device).unsqueeze(0)
+    output = torch.empty_like(query)
+    blocks = (82 + 63) // 64
+    stats = torch.empty(1, 8, blocks + 1, 2, device=cuda_device, dtype=torch.float32)
+    values = torch.empty(1, 8, blocks + 1, 64, device=cuda_device, dtype=torch.float32)
+    returned = fused_ops.run_gqa_decode_splitkv_turboquant_fused_out(
+        query=query, quantized_key=bf("qkey"), value_data=vdata, value_scales=bf("vscales").unsqueeze(0),
+        value_zeros=bf("vzeros").unsqueeze(0), residual_key=bf("rkey"), residual_value=bf("rvalue"), output=output,
+        partial_stats=stats, partial_values=values, scaling=64 ** -0.5, value_bits=value_bits, value_group_size=16,
+        block_size=64, gate=bf("gate"))
+    assert returned.untyped_storage().data_ptr() == output.untyped_storage().data_ptr()
+    np.testing.assert_allclose(to_np(output), data[p + "ref"], atol=4e-2, rtol=4e-2)
+    assert fused_ops.gqa_decode_splitkv_turboquant_fused_out_is_available()
+    via_torch_ops = torch.ops.anna.gqa_decode_splitkv_turboquant_fused_out(
+        query, bf("qkey"), vdata, bf("vscales").unsqueeze(0), bf("vzeros").unsqueeze(0), bf("rkey"), bf("rvalue"),
+        torch.empty_like(query), stats, values, 64 ** -0.5, value_bits, 16, 64, bf("gate"))
+    assert torch.equal(via_torch_ops, output)
