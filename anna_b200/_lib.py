@@ -39,8 +39,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_kv_last_error": (ctypes.c_char_p, []),
     "anna_kv_abi_version": (c_i32, []),
     "anna_decode_plan": (c_i32, [c_i32, c_i32, c_i64, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
-    "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32,
-                                    c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),
+    "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i32,
+                                    c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),
     "anna_paged_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_i64,
                                       c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i32,
                                       c_i32, c_i64, c_i64, c_f32, c_i32, c_ptr]),
@@ -53,7 +53,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                 c_i32, c_f32, c_i32, c_ptr]),
     "anna_tq_page_layout": (c_i32, [c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.POINTER(TqLayout)]),
     "anna_tq_append": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr,
-                               c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,
+                               c_ptr, c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,
                                c_i64, c_i32, c_ptr, c_ptr]),
     "anna_tq_paged_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                      c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32,

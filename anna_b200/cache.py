@@ -117,6 +117,47 @@ def _i32(values, device: torch.device) -> torch.Tensor:
     return torch.tensor(values, dtype=torch.int32, device=device)
 
 
+class _DeviceLengths:
+    """Row lengths (and TurboQuant ring slots) of one layer, kept on the device between steps.
+
+    ``rows`` is a small ring of int64 ``[B]`` tensors; ``rows[pos]`` mirrors the host list ``host``.  An append reads
+    ``rows[pos]`` as the lengths before the call and lets the kernel write the lengths after it into the next row of
+    the ring, so a steady decode loop uploads no metadata at all.  Tensors handed out from the ring stay valid until
+    the ring wraps (``DEPTH - 1`` further appends to the same layer)."""
+
+    DEPTH = 4
+    __slots__ = ("rows", "pos", "host", "slots_dev", "slots_host", "device")
+
+    def __init__(self, batch: int, device: torch.device) -> None:
+        self.rows = list(torch.zeros((self.DEPTH, batch), dtype=torch.int64, device=device).unbind(0))
+        self.pos = 0
+        self.host: list[int] | None = None
+        self.slots_dev: torch.Tensor | None = None
+        self.slots_host: list[int] | None = None
+        self.device = device
+
+    def current(self, lengths: list[int]) -> torch.Tensor | None:
+        """Device copy of ``lengths`` if the ring holds exactly these values."""
+        return self.rows[self.pos] if self.host == lengths else None
+
+    def before_append(self, past: list[int]) -> tuple[torch.Tensor, torch.Tensor]:
+        """(lengths before the append on the device, ring row that will receive the lengths after it)."""
+        past_dev = self.current(past)
+        if past_dev is None:
+            past_dev = MetadataUploader.for_device(self.device).upload([past])[0]
+        return past_dev, self.rows[(self.pos + 1) % self.DEPTH]
+
+    def after_append(self, lengths: list[int]) -> None:
+        self.pos = (self.pos + 1) % self.DEPTH
+        self.host = list(lengths)
+
+    def slots(self, slots: list[int]) -> torch.Tensor:
+        if self.slots_dev is None or self.slots_host != slots:
+            self.slots_dev = MetadataUploader.for_device(self.device).upload([slots])[0]
+            self.slots_host = list(slots)
+        return self.slots_dev
+
+
 class Qwen3DynamicCache:
     def __init__(self, config, *, allocator: Qwen3PageAllocator | None = None, batch_size: int = 0,
                  kv_cache_quantization: str = "none", kv_cache_quant_bits: int = 4, kv_cache_residual_len: int = 128):
@@ -146,8 +187,11 @@ class Qwen3DynamicCache:
         self.page_table_capacities: list[int] = [0] * layers
         self._table_rows_synced: list[list[int] | None] = [None] * layers  # blocks already on the device per row
         self._table_blocks_total: list[int] = [-1] * layers                # sum of table lengths at the last sync
-        # per layer: (lengths list, slots list | None, int64 device tensor [past; now; (slots)]) of the last append
-        self._step_meta: list[tuple[list[int], list[int] | None, torch.Tensor] | None] = [None] * layers
+        self._dev_lengths: list[_DeviceLengths | None] = [None] * layers  # device mirror of layer_lengths
+        # per layer: tokens every row can still take without a new page (None = unknown), and the block-table view
+        # returned by the last sync (valid while no table has changed)
+        self._page_headroom: list[int | None] = [None] * layers
+        self._table_view: list[torch.Tensor | None] = [None] * layers
         self.seen_tokens = 0
         self.rope_deltas: torch.Tensor | None = None
         self.reserved_seq_capacity = 0
@@ -173,6 +217,7 @@ class Qwen3DynamicCache:
 
     def reserve_sequence_capacity(self, seq_length: int) -> None:
         self.reserved_seq_capacity = max(0, int(seq_length))
+        self._page_headroom = [None] * len(self._page_headroom)  # tables may have to grow at the next append
 
     @property
     def has_previous_state(self) -> bool:
@@ -301,51 +346,81 @@ class Qwen3DynamicCache:
         batch_size, kv_heads, append_length, head_dim = (int(v) for v in key_states.shape)
         self._ensure_batch_size(batch_size)
         device = key_states.device
-        past = list(self.layer_lengths[layer_idx])
-        reserved_length = max(append_length, self.reserved_seq_capacity)
-        hint = (reserved_length + self.block_size - 1) // self.block_size
-        if hint > 0:
-            self.allocator.ensure_capacity(layer_idx, hint * batch_size, key_template=key_states,
-                                           value_template=value_states)
+        past = self.layer_lengths[layer_idx]
         use_prefix_share = self._prefix_kv_share and batch_size == 1 and self._prompt_token_ids is not None
         segments = [(0, append_length)]  # token ranges of this append that must be written
-        for batch_idx in range(batch_size):
-            current = self.layer_lengths[layer_idx][batch_idx]
-            required = current + append_length
-            table = self.page_tables[layer_idx][batch_idx]
-            if use_prefix_share:
-                segments = self._map_prefix_shared_blocks(key_states, value_states, layer_idx, batch_idx,
-                                                          append_length)
-            blocks = (max(required, self.reserved_seq_capacity) + self.block_size - 1) // self.block_size
-            if len(table) < blocks:
-                table.extend(self.allocator.allocate(layer_idx, blocks - len(table), key_template=key_states,
-                                                     value_template=value_states))
-            self.layer_lengths[layer_idx][batch_idx] = required
-        lengths = self.layer_lengths[layer_idx]
-        self.seen_tokens = max(self.seen_tokens, max(lengths, default=0))
-        if device.type == "cuda":
-            meta = MetadataUploader.for_device(device).upload([past, lengths])
-            self._step_meta[layer_idx] = (list(lengths), None, meta)
-            past_lengths = meta[0]
+        headroom = self._page_headroom[layer_idx]
+        table_dev = None
+        if headroom is not None and headroom >= append_length and not use_prefix_share:
+            # steady decode: every row still has room in its last page, so no table changes
+            self._page_headroom[layer_idx] = headroom - append_length
+            lengths = [n + append_length for n in past]
+            self.layer_lengths[layer_idx] = lengths
+            table_dev = self._table_view[layer_idx]
         else:
-            meta = None
-            past_lengths = torch.tensor(past, device=device, dtype=torch.long)
-        table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
+            reserved_length = max(append_length, self.reserved_seq_capacity)
+            hint = (reserved_length + self.block_size - 1) // self.block_size
+            if hint > 0:
+                self.allocator.ensure_capacity(layer_idx, hint * batch_size, key_template=key_states,
+                                               value_template=value_states)
+            lengths = list(past)
+            headroom = None
+            for batch_idx in range(batch_size):
+                required = past[batch_idx] + append_length
+                table = self.page_tables[layer_idx][batch_idx]
+                if use_prefix_share:
+                    segments = self._map_prefix_shared_blocks(key_states, value_states, layer_idx, batch_idx,
+                                                              append_length)
+                blocks = (max(required, self.reserved_seq_capacity) + self.block_size - 1) // self.block_size
+                if len(table) < blocks:
+                    table.extend(self.allocator.allocate(layer_idx, blocks - len(table), key_template=key_states,
+                                                         value_template=value_states))
+                lengths[batch_idx] = required
+                room = len(table) * self.block_size - required
+                headroom = room if headroom is None or room < headroom else headroom
+            self.layer_lengths[layer_idx] = lengths
+            self._page_headroom[layer_idx] = headroom
+            self._table_view[layer_idx] = None
+        newest = max(lengths, default=0)
+        if newest > self.seen_tokens:
+            self.seen_tokens = newest
+        if device.type == "cuda":
+            state = self._device_lengths_of(layer_idx, batch_size, device)
+            past_lengths, new_lengths = state.before_append(past)
+        else:  # bookkeeping only (the launch below refuses CPU tensors)
+            state = None
+            past_lengths, new_lengths = torch.tensor(past, device=device, dtype=torch.long), None
+        if table_dev is None:
+            table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
+            self._table_view[layer_idx] = table_dev
         layer = self.allocator.layers[layer_idx]
-        if table_dev is not None:
-            for start, end in segments:
-                if end > start:
-                    whole = start == 0 and end == append_length
-                    self._launch_page_write(layer, key_states[:, :, start:end, :], value_states[:, :, start:end, :],
-                                            table_dev, [p + start for p in past],
-                                            past_dev=past_lengths if whole and meta is not None else None)
+        if table_dev is not None and append_length > 0:
+            if segments == [(0, append_length)]:
+                self._launch_page_write(layer, key_states, value_states, table_dev, past, past_dev=past_lengths,
+                                        new_lengths_dev=new_lengths)
+                if state is not None:
+                    state.after_append(lengths)
+            else:
+                for start, end in segments:
+                    if end > start:
+                        self._launch_page_write(layer, key_states[:, :, start:end, :],
+                                                value_states[:, :, start:end, :], table_dev,
+                                                [p + start for p in past])
+                if state is not None:
+                    state.host = None  # the ring does not hold the new lengths
         if not require_dense_cache:
             return None, None, past_lengths
         gathered_key, gathered_value, _ = self._gather_layer_cache(layer_idx)
         return gathered_key, gathered_value, past_lengths
 
+    def _device_lengths_of(self, layer_idx: int, batch_size: int, device: torch.device) -> _DeviceLengths:
+        state = self._dev_lengths[layer_idx]
+        if state is None or state.device != device or int(state.rows[0].shape[0]) != batch_size:
+            state = self._dev_lengths[layer_idx] = _DeviceLengths(batch_size, device)
+        return state
+
     def _launch_page_write(self, layer: Qwen3PagedLayerAllocator, key_states, value_states, table_dev, past,
-                           past_dev: torch.Tensor | None = None):
+                           past_dev: torch.Tensor | None = None, new_lengths_dev: torch.Tensor | None = None):
         key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
         if value_states.stride() != key_states.stride():
             key_states, value_states = key_states.contiguous(), value_states.contiguous()
@@ -360,7 +435,7 @@ class Qwen3DynamicCache:
             _lib.check(_lib.lib().anna_paged_kv_write(
                 ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
                 ptr(layer.key_pages), ptr(layer.value_pages), ptr(table_dev), table_dev.stride(0), ptr(past_dev),
-                batch, kv_heads, tokens, dim, self.block_size, layer.capacity(), int(table_dev.shape[1]),
+                ptr(new_lengths_dev), batch, kv_heads, tokens, dim, self.block_size, layer.capacity(), int(table_dev.shape[1]),
                 dtype_code(key_states.dtype), None, stream_ptr(device)), "anna_paged_kv_write")
 
     def _map_prefix_shared_blocks(self, key_states, value_states, layer_idx: int, batch_idx: int,
@@ -434,16 +509,19 @@ class Qwen3DynamicCache:
         for batch_idx, row in enumerate(rows):
             row._length += append_length
             lengths[batch_idx] = row._length
-        meta = None
         if device.type == "cuda":
-            meta = MetadataUploader.for_device(device).upload([past, lengths, slots])
-            self._step_meta[layer_idx] = (list(lengths), slots, meta)
-            past_lengths = meta[0]
-        else:
+            state = self._device_lengths_of(layer_idx, batch_size, device)
+            past_lengths, new_lengths = state.before_append(past)
+            slots_dev = state.slots(slots)
+        else:  # bookkeeping only (the launch below refuses CPU tensors)
+            state, slots_dev, new_lengths = None, None, None
             past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         if append_length > 0:
             table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
-            launch_tq_append(pool, key_states, value_states, table_dev, slots, past, meta=meta)
+            launch_tq_append(pool, key_states, value_states, table_dev, slots, past, slots_dev=slots_dev,
+                             past_dev=past_lengths if state is not None else None, new_lengths_dev=new_lengths)
+            if state is not None:
+                state.after_append(lengths)
         self.seen_tokens = max(self.seen_tokens, max(lengths, default=0))
         if not require_dense_cache:
             return None, None, past_lengths
@@ -474,11 +552,13 @@ class Qwen3DynamicCache:
         table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch, device=device)
         lengths = [0 if row is None else row.length for row in rows]
         slots = [0 if row is None else row.slot for row in rows]
-        cached = self._step_meta[layer_idx]
-        meta = None
-        if cached is not None and cached[0] == lengths and cached[1] == slots and cached[2].device == device:
-            meta = cached[2]
-        return launch_tq_decode(pool, query_states, table_dev, slots, lengths, scaling, gate, meta=meta)
+        state = self._dev_lengths[layer_idx]
+        lengths_dev = slots_dev = None
+        if state is not None and state.device == device:
+            lengths_dev = state.current(lengths)
+            slots_dev = state.slots(slots)
+        return launch_tq_decode(pool, query_states, table_dev, slots, lengths, scaling, gate, slots_dev=slots_dev,
+                                lengths_dev=lengths_dev)
 
     # -- dense views -------------------------------------------------------------------------------------------------------
 
@@ -497,13 +577,16 @@ class Qwen3DynamicCache:
         if required <= 0 or max(lengths, default=0) <= 0:
             return None
         device = layer.key_pages.device
-        page_table = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
-        if page_table is None:
-            return None
-        cached = self._step_meta[layer_idx]
-        if cached is not None and cached[0] == lengths and cached[2].device == device:
-            visible_lengths = cached[2][1]
-        else:
+        page_table = self._table_view[layer_idx]
+        if page_table is None or page_table.device != device:
+            page_table = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
+            if page_table is None:
+                return None
+            if self._page_headroom[layer_idx] is not None:  # tables are known not to change before the next append
+                self._table_view[layer_idx] = page_table
+        state = self._dev_lengths[layer_idx]
+        visible_lengths = None if state is None or state.device != device else state.current(lengths)
+        if visible_lengths is None:
             visible_lengths = torch.tensor(lengths, dtype=torch.long, device=device)
         return layer.key_pages, layer.value_pages, page_table, visible_lengths
 
@@ -683,7 +766,9 @@ class Qwen3DynamicCache:
             self.page_table_capacities[layer_idx] = 0
             self._table_rows_synced[layer_idx] = None
             self._table_blocks_total[layer_idx] = -1
-            self._step_meta[layer_idx] = None
+            self._dev_lengths[layer_idx] = None
+            self._page_headroom[layer_idx] = None
+            self._table_view[layer_idx] = None
         self.seen_tokens = 0
         self.rope_deltas = None
         self.reserved_seq_capacity = 0

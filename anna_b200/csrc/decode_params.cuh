@@ -34,5 +34,8 @@ struct DenseDecodeParams {
 // Tensor-core split pass (paged_decode_mma.cu): 16-bit dtypes, head_dim 64 / 128 / 256.
 bool dense_split_mma_applicable(const DenseDecodeParams& p, int head_dim, int dtype);
 int launch_dense_split_mma(const DenseDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream);
+// one resident wave with an even share of tiles per CTA; needs the fused merge and the library's own split plan
+bool dense_balanced_mma_applicable(const DenseDecodeParams& p, int batch);
+int launch_dense_balanced_mma(const DenseDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream);
 
 }  // namespace anna

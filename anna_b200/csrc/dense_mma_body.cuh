@@ -27,13 +27,14 @@ struct MmaCfg {
 };
 
 // Split pass over tokens [t0, t1) of (row b, kv head kvh, query heads g0 .. g0 + g_count) for one CTA of kMmaThreads
-// threads; the partial goes to split-K slot `slot`, and with a fused merge the CTA counts as one of `active_chunks`.
+// threads; the partial goes to split-K slot `slot`, and with a fused merge it counts as one of the `active_chunks`
+// arrivals on counters[counter_index].
 // Token t lives at element offset: paged -> page_table / block_size; ring_len > 0 -> (t % ring_len) * D; else
 // t * kv_stride_t, all relative to the (row, kv head) base the caller put into p.key / p.value.
 template <typename T, int D>
 __device__ __forceinline__ void dense_split_mma_body(const DenseDecodeParams& p, uint8_t* smem_raw, int b, int kvh,
                                                      int g0, int g_count, int t0, int t1, int slot,
-                                                     int active_chunks) {
+                                                     int active_chunks, int64_t counter_index) {
   using Cfg = MmaCfg<D>;
   const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
 
@@ -298,7 +299,7 @@ __device__ __forceinline__ void dense_split_mma_body(const DenseDecodeParams& p,
     __syncthreads();  // the epilogue buffers above are dead; reuse shared memory for the merge weights
     fused_combine_tail<T, D, kMmaThreads>(p.fused, b, hq0, g_count, active_chunks, p.chunk_capacity,
                                           p.stats + head0 * 2, p.values + head0 * D,
-                                          reinterpret_cast<float*>(smem_raw));
+                                          reinterpret_cast<float*>(smem_raw), counter_index);
   }
 }
 

@@ -11,7 +11,7 @@
 namespace anna {
 
 struct FusedCombine {
-  int32_t* counters;   // [batch, gridDim.y] zero on entry; nullptr selects the two-pass path
+  int32_t* counters;   // [batch, kv heads x groups-of-8] zero on entry; nullptr selects the two-pass path
   void* out;
   int64_t out_stride_b, out_stride_h;
   const void* gate;
@@ -20,17 +20,19 @@ struct FusedCombine {
 
 constexpr int kFusedMaxChunks = 512;  // weights of one head are staged in shared memory
 
-// Called by all threads of the CTA after they wrote their partial.  `active_chunks` = CTAs that contribute to this
-// (row, group); stats / values point at chunk 0 of query head hq0.  Natural-log stats.  THREADS = blockDim.x.
+// Called by all threads of the CTA after they wrote their partial.  `active_chunks` = partials that contribute to this
+// (row, group), whose arrivals are counted in counters[counter_index]; stats / values point at chunk 0 of query head
+// hq0.  Natural-log stats.  THREADS = blockDim.x.
 template <typename T, int D, int THREADS>
 __device__ __forceinline__ void fused_combine_tail(const FusedCombine& fc, int b, int hq0, int g_count,
                                                    int active_chunks, int chunk_capacity, const float* stats,
-                                                   const float* values, float* smem_weights /* [8][kFusedMaxChunks] */) {
+                                                   const float* values, float* smem_weights /* [8][kFusedMaxChunks] */,
+                                                   int64_t counter_index) {
   __shared__ int s_is_last;
   __syncthreads();  // all partial stores of this CTA are ordered before the fence below
   if (threadIdx.x == 0) {
     __threadfence();
-    int32_t* counter = fc.counters + (int64_t)b * gridDim.y + blockIdx.y;
+    int32_t* counter = fc.counters + counter_index;
     const int prev = atomicAdd(counter, 1);
     s_is_last = (prev == active_chunks - 1) ? 1 : 0;
     if (s_is_last) *counter = 0;

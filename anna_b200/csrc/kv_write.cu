@@ -12,6 +12,7 @@ struct KvWriteParams {
   const int32_t* page_table;
   int64_t table_stride;
   const int64_t* past_lengths;
+  int64_t* new_lengths;
   int batch, kv_heads, new_tokens, head_dim, block_size;
   int64_t num_pages, max_blocks;
   int32_t* status;
@@ -31,7 +32,9 @@ __global__ void __launch_bounds__(256) paged_kv_write_kernel(const KvWriteParams
     rest /= p.new_tokens;
     const int h = (int)(rest % p.kv_heads);
     const int b = (int)(rest / p.kv_heads);
-    const int64_t pos = p.past_lengths[b] + t;
+    const int64_t past = p.past_lengths[b];
+    if (p.new_lengths != nullptr && (piece | t | h) == 0) p.new_lengths[b] = past + p.new_tokens;
+    const int64_t pos = past + t;
     const int64_t blk = pos / p.block_size;
     const int slot = (int)(pos % p.block_size);
     int32_t pid = -1;
@@ -56,11 +59,12 @@ using namespace anna;
 extern "C" int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                                    int64_t kn_stride_t, void* key_pages, void* value_pages,
                                    const int32_t* page_table, int64_t table_stride, const int64_t* past_lengths,
-                                   int batch, int kv_heads, int new_tokens, int head_dim, int block_size,
+                                   int64_t* new_lengths, int batch, int kv_heads, int new_tokens, int head_dim, int block_size,
                                    int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,
                                    anna_stream_t stream) {
   ANNA_REQUIRE(k_new && v_new && key_pages && value_pages && page_table && past_lengths,
                "anna_paged_kv_write: null pointer argument");
+  ANNA_REQUIRE(new_lengths != past_lengths, "anna_paged_kv_write: new_lengths must not alias past_lengths");
   ANNA_REQUIRE(batch > 0 && kv_heads > 0 && new_tokens > 0 && block_size > 0 && num_pages > 0 && max_blocks > 0,
                "anna_paged_kv_write: sizes must be positive");
   const int vec = dtype == ANNA_DTYPE_F32 ? 4 : 8;
@@ -69,7 +73,7 @@ extern "C" int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t
   ANNA_REQUIRE(kn_stride_b % vec == 0 && kn_stride_h % vec == 0 && kn_stride_t % vec == 0,
                "anna_paged_kv_write: source strides must keep rows 16-byte aligned");
   KvWriteParams p{k_new, v_new, kn_stride_b, kn_stride_h, kn_stride_t, key_pages, value_pages, page_table,
-                  table_stride, past_lengths, batch, kv_heads, new_tokens, head_dim, block_size, num_pages,
+                  table_stride, past_lengths, new_lengths, batch, kv_heads, new_tokens, head_dim, block_size, num_pages,
                   max_blocks, status};
   const int64_t total = (int64_t)batch * kv_heads * new_tokens * (head_dim / vec);
   int64_t blocks = (total + 255) / 256;

@@ -19,6 +19,7 @@ struct TqAppendParams {
   void* window;
   const int64_t* window_slots;
   const int64_t* old_lengths;
+  int64_t* new_lengths;
   const float* signs1;
   const float* signs2;
   const float* centroids;
@@ -51,6 +52,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
   const int64_t L = p.old_lengths[b];
   const int64_t Tn = p.new_tokens;
   const int64_t Lp = L + Tn;
+  if (p.new_lengths != nullptr && (blockIdx.x | blockIdx.y | threadIdx.x) == 0) p.new_lengths[b] = Lp;
   const int64_t Lq = L > R ? L - R : 0;
   const int64_t Lqp = Lp > R ? Lp - R : 0;
   const int64_t nq = Lqp - Lq;
@@ -219,13 +221,14 @@ extern "C" int anna_tq_page_layout(int head_dim, int bits, int block_size, int d
 extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                               int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table,
                               int64_t table_stride, void* window, const int64_t* window_slots,
-                              const int64_t* old_lengths, const float* signs1, const float* signs2,
-                              const float* centroids, const float* boundaries, int batch, int kv_heads,
+                              const int64_t* old_lengths, int64_t* new_lengths, const float* signs1,
+                              const float* signs2, const float* centroids, const float* boundaries, int batch, int kv_heads,
                               int new_tokens, int head_dim, int block_size, int residual_len, int bits,
                               int value_group, int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,
                               anna_stream_t stream) {
   ANNA_REQUIRE(k_new && v_new && window && window_slots && old_lengths && signs1 && signs2 && centroids && boundaries,
                "anna_tq_append: null pointer argument");
+  ANNA_REQUIRE(new_lengths != old_lengths, "anna_tq_append: new_lengths must not alias old_lengths");
   ANNA_REQUIRE(batch > 0 && kv_heads > 0 && new_tokens > 0 && residual_len >= 1 && block_size >= 1,
                "anna_tq_append: sizes must be positive");
   ANNA_REQUIRE(packed_pages != nullptr || num_pages == 0, "anna_tq_append: null page pool with num_pages > 0");
@@ -241,7 +244,7 @@ extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_s
   p.k_new = k_new; p.v_new = v_new;
   p.stride_b = kn_stride_b; p.stride_h = kn_stride_h; p.stride_t = kn_stride_t;
   p.pages = packed_pages; p.block_table = block_table; p.table_stride = table_stride;
-  p.window = window; p.window_slots = window_slots; p.old_lengths = old_lengths;
+  p.window = window; p.window_slots = window_slots; p.old_lengths = old_lengths; p.new_lengths = new_lengths;
   p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids; p.boundaries = boundaries;
   p.batch = batch; p.kv_heads = kv_heads; p.new_tokens = new_tokens; p.block_size = block_size;
   p.residual_len = residual_len; p.value_group = value_group;

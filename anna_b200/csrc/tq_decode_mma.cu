@@ -201,7 +201,8 @@ __global__ void __launch_bounds__(kMmaThreads, MmaCfg<D>::kMinBlocks) tq_window_
   dp.fused = p.fused;
   const int t0 = Lq + slot * p.chunk_tokens;
   const int t1 = min(len, t0 + p.chunk_tokens);
-  dense_split_mma_body<T, D>(dp, smem_raw, b, kvh, g0, g_count, t0, t1, slot, active_chunks);
+  dense_split_mma_body<T, D>(dp, smem_raw, b, kvh, g0, g_count, t0, t1, slot, active_chunks,
+                             (int64_t)b * gridDim.y + blockIdx.y);
 }
 
 template <typename T, int D, int BITS>
@@ -626,7 +627,7 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
     __syncthreads();
     fused_combine_tail<T, D, kMmaThreads>(p.fused, b, hq0, g_count, active_chunks, p.chunk_capacity,
                                           p.stats + head0 * 2, p.values + head0 * D,
-                                          reinterpret_cast<float*>(smem_raw));
+                                          reinterpret_cast<float*>(smem_raw), (int64_t)b * gridDim.y + blockIdx.y);
   }
 }
 

@@ -49,12 +49,21 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise RuntimeError(f"anna_b200 kernels support float16, bfloat16 and float32 inputs, got {dtype}") from None
 
 
-def ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p | None:
-    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """Device address for a ``void*`` argument (ctypes turns an int into the pointer, None into NULL)."""
+    return None if tensor is None else tensor.data_ptr()
 
 
-def stream_ptr(device: torch.device) -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def stream_ptr(device: torch.device) -> int | None:
+    """Handle of the current CUDA stream of ``device`` (None = the legacy default stream)."""
+    index = device.index
+    if index is None:
+        index = torch.cuda.current_device()
+    handle = _raw_stream(index) if _raw_stream is not None else torch.cuda.current_stream(device).cuda_stream
+    return handle or None
 
 
 class on_device:
@@ -191,7 +200,7 @@ class _Scratch:
     @staticmethod
     def _key(device: torch.device) -> tuple[int, int]:
         return (device.index if device.index is not None else torch.cuda.current_device(),
-                torch.cuda.current_stream(device).cuda_stream)
+                stream_ptr(device) or 0)
 
     def get(self, device: torch.device, floats: int) -> torch.Tensor:
         key = self._key(device)
@@ -199,6 +208,7 @@ class _Scratch:
         if buf is None or buf.numel() < floats:
             buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
             self._buffers[key] = buf
+            _SPLIT_CACHE.clear()  # cached views point into the old buffer
         return buf
 
     def bytes(self, device: torch.device, count: int) -> torch.Tensor:
@@ -215,9 +225,11 @@ class _Scratch:
         if buf is None or buf.numel() < count:
             buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
             self._counters[key] = buf
+            _SPLIT_CACHE.clear()
         return buf
 
 
+_SPLIT_CACHE: dict[tuple, tuple] = {}  # split_scratch results by problem shape, device and stream
 _SCRATCH = _Scratch()
 
 
@@ -236,6 +248,10 @@ def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, k
 
     ``turboquant=(max_blocks, block_size, residual_len)`` selects the plan of the packed decode (window chunks +
     packed chunks) instead of the plan for ``max_len`` tokens."""
+    cache_key = (device.index, stream_ptr(device), batch, heads, head_dim, kv_heads, max_len, turboquant)
+    hit = _SPLIT_CACHE.get(cache_key)
+    if hit is not None:
+        return hit
     key = (batch, kv_heads, int(max_len), turboquant)
     chunks = _PLAN_CACHE.get(key)
     if chunks is None:
@@ -251,7 +267,11 @@ def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, k
     buf = _SCRATCH.get(device, stats_floats + value_floats)
     group_tiles = (heads // kv_heads + 7) // 8
     counters = _SCRATCH.counters(device, batch * kv_heads * group_tiles)
-    return buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks, counters
+    if len(_SPLIT_CACHE) > 256:
+        _SPLIT_CACHE.clear()
+    result = (buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks, counters)
+    _SPLIT_CACHE[cache_key] = result
+    return result
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -455,11 +475,14 @@ def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visibl
         raise RuntimeError("visible_lengths must be int64")
     device = _require_cuda(name, query=query, key_pages=key_pages, value_pages=value_pages, page_table=page_table,
                            visible_lengths=visible_lengths, gate=gate)
-    key_pages = key_pages.contiguous()
-    value_pages = value_pages.contiguous()
+    if not key_pages.is_contiguous():
+        key_pages = key_pages.contiguous()
+    if not value_pages.is_contiguous():
+        value_pages = value_pages.contiguous()
     if page_table.stride(1) != 1:
         page_table = page_table.contiguous()
-    visible_lengths = visible_lengths.contiguous()
+    if visible_lengths.stride(0) != 1:
+        visible_lengths = visible_lengths.contiguous()
     gate, gate_sb, gate_sh = _check_gate(name, query, gate)
     batch, heads, _, dim = (int(v) for v in query.shape)
     pages, kv_heads, block = int(key_pages.shape[0]), int(key_pages.shape[1]), int(key_pages.shape[2])

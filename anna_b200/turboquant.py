@@ -42,11 +42,13 @@ def _require_cuda(tensor: torch.Tensor, what: str) -> None:
 
 
 def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_states: torch.Tensor,
-                     table_dev: torch.Tensor | None, slots: list[int], past: list[int],
-                     meta: torch.Tensor | None = None) -> None:
+                     table_dev: torch.Tensor | None, slots: list[int], past: list[int], *,
+                     slots_dev: torch.Tensor | None = None, past_dev: torch.Tensor | None = None,
+                     new_lengths_dev: torch.Tensor | None = None) -> None:
     """Append ``[B, Hkv, T, D]`` to B rows of one layer: ring update + quantize-on-overflow + page scatter.
 
-    ``meta`` (optional) is an int64 device tensor whose row 0 holds ``past`` and whose last row holds ``slots``."""
+    ``slots_dev`` / ``past_dev`` (optional, int64 ``[B]`` on the device) are copies of ``slots`` / ``past`` that the
+    caller already holds there; ``new_lengths_dev`` (optional) receives ``past + T`` from the kernel."""
     _require_cuda(key_states, "TurboQuant append")
     key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
     if value_states.stride() != key_states.stride():
@@ -54,26 +56,29 @@ def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_
     device = key_states.device
     batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    if meta is None:
+    if slots_dev is None or past_dev is None:
         meta = MetadataUploader.for_device(device).upload([past, slots])
+        past_dev = meta[0] if past_dev is None else past_dev
+        slots_dev = meta[1] if slots_dev is None else slots_dev
     assert pool.window is not None
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
     with on_device(device):
         _lib.check(_lib.lib().anna_tq_append(
             ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
-            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(meta[-1]), ptr(meta[0]),
-            ptr(tables.signs1), ptr(tables.signs2), ptr(tables.centroids), ptr(tables.boundaries), batch, kv_heads,
+            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(slots_dev), ptr(past_dev),
+            ptr(new_lengths_dev), ptr(tables.signs1), ptr(tables.signs2), ptr(tables.centroids), ptr(tables.boundaries), batch, kv_heads,
             tokens, dim, pool.block_size, pool.residual_len, pool.bits, pool.value_group, pool.capacity(), max_blocks,
             dtype_code(key_states.dtype), ptr(pool.status), stream_ptr(device)), "anna_tq_append")
 
 
 def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, table_dev: torch.Tensor | None,
-                     slots: list[int], lengths: list[int], scaling: float, gate: torch.Tensor | None,
-                     meta: torch.Tensor | None = None) -> torch.Tensor:
+                     slots: list[int], lengths: list[int], scaling: float, gate: torch.Tensor | None, *,
+                     slots_dev: torch.Tensor | None = None, lengths_dev: torch.Tensor | None = None) -> torch.Tensor:
     """Decode ``[B, Hq, 1, D]`` queries against B rows of one layer (packed prefix + window ring).
 
-    ``meta`` (optional) is an int64 device tensor whose row -2 holds ``lengths`` and whose last row holds ``slots``."""
+    ``slots_dev`` / ``lengths_dev`` (optional, int64 ``[B]`` on the device) are copies of ``slots`` / ``lengths``
+    that the caller already holds there."""
     _require_cuda(query_states, "TurboQuant decode")
     query = query_states if query_states.stride(3) == 1 else query_states.contiguous()
     if gate is not None and gate.stride(3) != 1:
@@ -83,8 +88,10 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     if query.dtype != pool.dtype:
         raise RuntimeError(f"query dtype {query.dtype} must match the cache dtype {pool.dtype}")
     tables = key_tables(head_dim=dim, bits=pool.bits, device=device)
-    if meta is None:
+    if slots_dev is None or lengths_dev is None:
         meta = MetadataUploader.for_device(device).upload([lengths, slots])
+        lengths_dev = meta[0] if lengths_dev is None else lengths_dev
+        slots_dev = meta[1] if slots_dev is None else slots_dev
     out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
@@ -95,7 +102,7 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
     with on_device(device):
         _lib.check(_lib.lib().anna_tq_paged_decode(
             ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
-            ptr(pool.window), ptr(meta[-1]), ptr(meta[-2]), ptr(tables.signs1), ptr(tables.signs2),
+            ptr(pool.window), ptr(slots_dev), ptr(lengths_dev), ptr(tables.signs1), ptr(tables.signs2),
             ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
             0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
             capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads, pool.kv_heads, dim, pool.block_size,

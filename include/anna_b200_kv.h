@@ -69,13 +69,15 @@ int anna_decode_plan(int batch, int kv_heads, int64_t max_len, int* chunk_tokens
  *   k_new, v_new   [B, Hkv, T, D] with element strides (kn_stride_b, kn_stride_h, kn_stride_t); last dim contiguous
  *   key_pages, value_pages  [P, Hkv, S, D] contiguous
  *   page_table     int32 [B, table_stride >= blocks];   past_lengths  int64 [B]
+ *   new_lengths    optional int64 [B] (may be NULL, must not alias past_lengths): receives past_lengths[b] + T, so a
+ *                  decode loop can keep its lengths on the device instead of uploading them every step
  *   status         optional device int32 (may be NULL): ANNA_DEV_BAD_PAGE is OR-ed in when a page id is invalid
  */
 int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                         int64_t kn_stride_t, void* key_pages, void* value_pages, const int32_t* page_table,
-                        int64_t table_stride, const int64_t* past_lengths, int batch, int kv_heads, int new_tokens,
-                        int head_dim, int block_size, int64_t num_pages, int64_t max_blocks, int dtype,
-                        int32_t* status, anna_stream_t stream);
+                        int64_t table_stride, const int64_t* past_lengths, int64_t* new_lengths, int batch,
+                        int kv_heads, int new_tokens, int head_dim, int block_size, int64_t num_pages,
+                        int64_t max_blocks, int dtype, int32_t* status, anna_stream_t stream);
 
 /*
  * Single-token GQA decode over paged K/V.  Stands in for torch.ops.anna.paged_gqa_decode_fused
@@ -161,15 +163,17 @@ int anna_tq_page_layout(int head_dim, int bits, int block_size, int dtype, int v
  * stay inside the window are written to the ring.  A ring slot is read before the same warp overwrites it.
  *   k_new, v_new  [B, Hkv, T, D] element strides (kn_stride_b, kn_stride_h, kn_stride_t)
  *   old_lengths   int64 [B] (lengths before this call);  window_slots int64 [B] (ring index of each row)
+ *   new_lengths   optional int64 [B] (may be NULL, must not alias old_lengths): receives old_lengths[b] + T
  *   signs1, signs2  float32 [D] (+1 / -1): rotation and QJL sign vectors;  centroids float32 [2^(bits-1)];
  *   boundaries    float32 [2^(bits-1) - 1]
  */
 int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                    int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                   void* window, const int64_t* window_slots, const int64_t* old_lengths, const float* signs1,
-                   const float* signs2, const float* centroids, const float* boundaries, int batch, int kv_heads,
-                   int new_tokens, int head_dim, int block_size, int residual_len, int bits, int value_group,
-                   int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status, anna_stream_t stream);
+                   void* window, const int64_t* window_slots, const int64_t* old_lengths, int64_t* new_lengths,
+                   const float* signs1, const float* signs2, const float* centroids, const float* boundaries,
+                   int batch, int kv_heads, int new_tokens, int head_dim, int block_size, int residual_len, int bits,
+                   int value_group, int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,
+                   anna_stream_t stream);
 
 /*
  * Single-token GQA decode over [packed quantized prefix | un-quantized window].  Batched, paged form of

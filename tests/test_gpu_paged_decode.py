@@ -137,6 +137,107 @@ def test_paged_decode_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, k
     assert max_abs <= ATOL[dtype] * 2 and rel <= ATOL[dtype], (max_abs, rel)
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim", [(32, 2, 128), (8, 4, 64), (4, 1, 256)])
+def test_paged_decode_split_schedules_agree(cuda_device, heads, kv_heads, dim):
+    """The three split schedules of the C entry point (even share of tiles per CTA with the in-kernel merge, fixed
+    chunks with the in-kernel merge, fixed chunks with the separate merge launch) against the oracle, on ragged rows
+    that include empty ones, groups wider than one 8-head tile and the smallest legal scratch."""
+    from anna_b200 import _lib
+    from anna_b200.fused_ops import dtype_code, on_device, ptr, stream_ptr
+
+    torch.manual_seed(11)
+    block, key_len = 16, 1500
+    lengths = [key_len, 0, 1, 17, 640, 0, 1499, 256, 33]
+    batch = len(lengths)
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    key = torch.randn(batch, kv_heads, key_len, dim, device=cuda_device, dtype=torch.bfloat16)
+    value = torch.randn_like(key)
+    key_pages, value_pages, table = _pack_paged_kv(key, value, block_size=block, permute_seed=2)
+    visible = torch.tensor(lengths, device=cuda_device, dtype=torch.long)
+    expected = reference_decode(query, key, value, lengths, dim ** -0.5)
+    max_blocks = int(table.shape[1])
+    _, plan_chunks = _lib.decode_plan(batch, kv_heads, max_blocks * block)
+    fixed = 64
+    fixed_chunks = (max_blocks * block + fixed - 1) // fixed
+    group_tiles = (heads // kv_heads + 7) // 8
+
+    def run(chunk_tokens, capacity, fused):
+        stats = torch.empty(batch, heads, capacity, 2, device=cuda_device, dtype=torch.float32)
+        values = torch.empty(batch, heads, capacity, dim, device=cuda_device, dtype=torch.float32)
+        counters = torch.zeros(batch * kv_heads * group_tiles, device=cuda_device, dtype=torch.int32)
+        out = torch.full_like(query, float("nan"))
+        for _ in range(2):  # the second call checks that the counters came back to zero
+            with on_device(cuda_device):
+                _lib.check(_lib.lib().anna_paged_gqa_decode(
+                    ptr(query), query.stride(0), query.stride(1), ptr(key_pages), ptr(value_pages), ptr(table),
+                    table.stride(0), ptr(visible), None, 0, 0, ptr(out), out.stride(0), out.stride(1), ptr(stats),
+                    ptr(values), capacity, chunk_tokens, ptr(counters) if fused else None, batch, heads, kv_heads, dim,
+                    block, int(key_pages.shape[0]), max_blocks, dim ** -0.5, dtype_code(query.dtype),
+                    stream_ptr(cuda_device)), "anna_paged_gqa_decode")
+        assert torch.count_nonzero(counters) == 0
+        return to_np(out)
+
+    results = {
+        "even share": run(0, plan_chunks, True),
+        "fixed chunks, merged in kernel": run(fixed, fixed_chunks, True),
+        "fixed chunks, merge launch": run(fixed, fixed_chunks, False),
+    }
+    for label, got in results.items():
+        assert np.isfinite(got).all(), label
+        max_abs, rel = error_stats(got, expected)
+        assert max_abs <= ATOL[torch.bfloat16] * 2 and rel <= ATOL[torch.bfloat16], (label, max_abs, rel)
+        for row, length in enumerate(lengths):
+            if length == 0:
+                assert not got[row].any(), (label, row)
+
+
+def test_paged_decode_even_share_respects_scratch_capacity(cuda_device):
+    """Many short rows and one long one: an even share of tiles would cut the long row into more partials than the
+    planned scratch (two slots per head here) holds, so the share must grow instead."""
+    from anna_b200 import _lib
+    from anna_b200.fused_ops import dtype_code, on_device, ptr, stream_ptr
+
+    torch.manual_seed(12)
+    batch, heads, kv_heads, dim, block, max_blocks = 512, 16, 8, 64, 16, 128
+    chunk, capacity = _lib.decode_plan(batch, kv_heads, max_blocks * block)
+    assert capacity == 2
+    pages = max_blocks + batch
+    key_pages = torch.randn(pages, kv_heads, block, dim, device=cuda_device, dtype=torch.bfloat16)
+    value_pages = torch.randn_like(key_pages)
+    table = torch.full((batch, max_blocks), -1, dtype=torch.int32, device=cuda_device)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(4)).to(torch.int32).to(cuda_device)
+    long_row = 200
+    table[long_row] = order[:max_blocks]
+    others = [b for b in range(batch) if b != long_row]
+    table[others, 0] = order[max_blocks:max_blocks + len(others)]
+    lengths = torch.full((batch,), 16, dtype=torch.long)
+    lengths[long_row] = max_blocks * block - 3
+    lengths[7] = 0
+    visible = lengths.to(cuda_device)
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+
+    def run(chunk_tokens, slots, fused):
+        stats = torch.empty(batch, heads, slots, 2, device=cuda_device, dtype=torch.float32)
+        values = torch.empty(batch, heads, slots, dim, device=cuda_device, dtype=torch.float32)
+        counters = torch.zeros(batch * kv_heads, device=cuda_device, dtype=torch.int32)
+        out = torch.full_like(query, float("nan"))
+        with on_device(cuda_device):
+            _lib.check(_lib.lib().anna_paged_gqa_decode(
+                ptr(query), query.stride(0), query.stride(1), ptr(key_pages), ptr(value_pages), ptr(table),
+                table.stride(0), ptr(visible), None, 0, 0, ptr(out), out.stride(0), out.stride(1), ptr(stats),
+                ptr(values), slots, chunk_tokens, ptr(counters) if fused else None, batch, heads, kv_heads, dim, block,
+                pages, max_blocks, dim ** -0.5, dtype_code(query.dtype), stream_ptr(cuda_device)),
+                "anna_paged_gqa_decode")
+        assert torch.count_nonzero(counters) == 0
+        return to_np(out)
+
+    even = run(0, capacity, True)
+    fixed = run(256, max_blocks * block // 256, False)
+    assert np.isfinite(even).all()
+    np.testing.assert_allclose(even, fixed, atol=2e-2, rtol=2e-2)
+    assert not even[7].any()
+
+
 def test_paged_decode_skips_holes_and_zero_rows(cuda_device):
     """Entries < 0 are skipped and a row without visible keys gives zeros (.sycl:5310-5313, :5342)."""
     torch.manual_seed(3)

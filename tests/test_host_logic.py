@@ -23,15 +23,15 @@ def launches(monkeypatch):
     """Replace the CUDA launches by recorders."""
     calls = {"page_write": [], "tq_append": [], "tq_decode": []}
 
-    def fake_page_write(self, layer, key_states, value_states, table_dev, past, past_dev=None):
+    def fake_page_write(self, layer, key_states, value_states, table_dev, past, **device_copies):
         calls["page_write"].append({"tokens": int(key_states.shape[2]), "past": list(past),
                                     "table": table_dev.clone()})
 
-    def fake_tq_append(pool, key_states, value_states, table_dev, slots, past, meta=None):
+    def fake_tq_append(pool, key_states, value_states, table_dev, slots, past, **device_copies):
         calls["tq_append"].append({"tokens": int(key_states.shape[2]), "slots": list(slots), "past": list(past),
                                    "table": None if table_dev is None else table_dev.clone()})
 
-    def fake_tq_decode(pool, query, table_dev, slots, lengths, scaling, gate, meta=None):
+    def fake_tq_decode(pool, query, table_dev, slots, lengths, scaling, gate, **device_copies):
         calls["tq_decode"].append({"slots": list(slots), "lengths": list(lengths)})
         return torch.zeros_like(query)
 
