@@ -38,6 +38,7 @@ class TqLayout(ctypes.Structure):
 SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_kv_last_error": (ctypes.c_char_p, []),
     "anna_kv_abi_version": (c_i32, []),
+    "anna_kv_device_faults": (c_i32, [ctypes.POINTER(c_i32)]),
     "anna_decode_plan": (c_i32, [c_i32, c_i32, c_i64, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
     "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i32,
                                     c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),
@@ -98,6 +99,13 @@ def lib() -> ctypes.CDLL:
             fn.argtypes = argtypes
         _LIB = handle
     return _LIB
+
+
+def device_faults() -> int:
+    """Bounded in-kernel waits that expired on the current device (0 in a healthy run); synchronises the device."""
+    count = c_i32(0)
+    check(lib().anna_kv_device_faults(ctypes.byref(count)), "anna_kv_device_faults")
+    return int(count.value)
 
 
 def last_error() -> str:

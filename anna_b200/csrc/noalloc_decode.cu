@@ -54,7 +54,7 @@ extern "C" int anna_paged_gqa_decode_noalloc(const void* q, int64_t q_stride_b, 
   int rc = anna_decode_plan(batch, kv_heads, max_blocks * (int64_t)block_size, &chunk_tokens, &num_chunks);
   if (rc != ANNA_OK) return rc;
   const size_t group_tiles = (size_t)(q_heads / kv_heads + 7) / 8;
-  const size_t counter_bytes = sizeof(int32_t) * (size_t)batch * kv_heads * group_tiles;
+  const size_t counter_bytes = 2 * sizeof(int32_t) * (size_t)batch * kv_heads * group_tiles;  // arrivals + cursors
   const size_t heads = (size_t)batch * q_heads;
   const size_t stats_bytes = sizeof(float) * heads * num_chunks * 2;
   const size_t values_bytes = sizeof(float) * heads * num_chunks * head_dim;

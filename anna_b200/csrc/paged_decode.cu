@@ -114,8 +114,12 @@ static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_
   if (dense_split_mma_applicable(p, head_dim, dtype)) {
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
       p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
-      if (chunk_tokens_in <= 0 && dense_balanced_mma_applicable(p, batch))
-        return launch_dense_balanced_mma(p, batch, head_dim, dtype, stream);
+      if (chunk_tokens_in <= 0) {
+        rc = try_launch_paged_decode_tma(p, batch, head_dim, dtype, stream);
+        if (rc != ANNA_ERR_UNSUPPORTED) return rc;
+        if (dense_balanced_mma_applicable(p, batch))
+          return launch_dense_balanced_mma(p, batch, head_dim, dtype, stream);
+      }
       return launch_dense_split_mma(p, batch, head_dim, dtype, stream);
     }
     rc = launch_dense_split_mma(p, batch, head_dim, dtype, stream);

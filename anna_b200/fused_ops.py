@@ -262,14 +262,14 @@ def split_scratch(device: torch.device, batch: int, heads: int, head_dim: int, k
         if len(_PLAN_CACHE) > 4096:
             _PLAN_CACHE.clear()
         _PLAN_CACHE[key] = chunks
-    stats_floats = batch * heads * chunks * 2
+    stats_floats = (batch * heads * chunks * 2 + 3) // 4 * 4  # keeps the value partials 16-byte aligned
     value_floats = batch * heads * chunks * head_dim
     buf = _SCRATCH.get(device, stats_floats + value_floats)
     group_tiles = (heads // kv_heads + 7) // 8
-    counters = _SCRATCH.counters(device, batch * kv_heads * group_tiles)
+    counters = _SCRATCH.counters(device, 2 * batch * kv_heads * group_tiles)  # arrival counters + tile cursors
     if len(_SPLIT_CACHE) > 256:
         _SPLIT_CACHE.clear()
-    result = (buf[:stats_floats], buf[stats_floats:stats_floats + value_floats], chunks, counters)
+    result = (buf[:batch * heads * chunks * 2], buf[stats_floats:stats_floats + value_floats], chunks, counters)
     _SPLIT_CACHE[cache_key] = result
     return result
 

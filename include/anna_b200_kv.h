@@ -39,6 +39,13 @@ typedef void* anna_stream_t; /* cudaStream_t */
 const char* anna_kv_last_error(void);
 int anna_kv_abi_version(void);
 
+/*
+ * Health counter: how many bounded waits inside the kernels expired on the current device since the library was
+ * loaded (every wait on an asynchronous copy has an iteration limit; a kernel whose wait expires still terminates,
+ * but its output is not valid).  0 in a healthy run.  Synchronises the device.  No counterpart in the reference.
+ */
+int anna_kv_device_faults(int* count);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
  * (row, query head, chunk) leaves a partial in caller-owned float32 buffers
@@ -51,10 +58,11 @@ int anna_kv_abi_version(void);
  * made from the host-visible upper bound: anna_decode_plan(batch, kv_heads, max_len) returns the chunk length the
  * library will use and the number of chunks the scratch must hold.
  *
- * split_counters (optional, may be NULL): int32 [B, Hkv * ceil(G / 8)] that is all-zero on entry.  When given (and
- * the plan has at most 512 chunks) the 16-bit tensor-core path merges the partials inside the split kernel: the last
- * CTA to finish a (row, kv-head group) does the merge and puts the counter back to zero, so the buffer can be reused
- * by the next call on the same stream without clearing.  Without it a second small kernel does the merge.
+ * split_counters (optional, may be NULL): int32 [2, B, Hkv * ceil(G / 8)] that is all-zero on entry (arrival counters,
+ * then tile cursors).  When given (and the plan has at most 512 chunks) the 16-bit tensor-core path merges the
+ * partials inside the split kernel: whoever finishes a (row, kv-head group) last does the merge and puts the counters
+ * back to zero, so the buffer can be reused by the next call on the same stream without clearing.  Without it a second
+ * small kernel does the merge.
  */
 int anna_decode_plan(int batch, int kv_heads, int64_t max_len, int* chunk_tokens, int* num_chunks);
 

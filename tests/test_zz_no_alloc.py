@@ -38,7 +38,7 @@ def _decode_both(device, seed, batch, heads, kv_heads, dim, block, max_blocks, d
     chunk, chunks = _lib.decode_plan(batch, kv_heads, max_blocks * block)
     stats = torch.empty(batch, heads, chunks, 2, device=device, dtype=torch.float32)
     values = torch.empty(batch, heads, chunks, dim, device=device, dtype=torch.float32)
-    counters = torch.zeros(batch * kv_heads * ((heads // kv_heads + 7) // 8), device=device, dtype=torch.int32)
+    counters = torch.zeros(2 * batch * kv_heads * ((heads // kv_heads + 7) // 8), device=device, dtype=torch.int32)
     want = torch.empty_like(query)
     _lib.check(lib.anna_paged_gqa_decode(
         _ptr(query), query.stride(0), query.stride(1), _ptr(key_pages), _ptr(value_pages), _ptr(table),
