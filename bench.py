@@ -39,6 +39,10 @@ import torch  # noqa: E402
 METRIC = "kv_decode_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read + dram__bytes_write of the decode kernel over its algorithmic bytes, from the ncu capture of
+# `--profile-case paged` (same kernel and shape at half the batch); traffic grows with the bytes streamed.
+NCU_TRAFFIC_RATIO = 1.019
+NCU_TRAFFIC_SOURCE = "ncu capture of --profile-case paged (253.9 MB moved for 249.2 MB algorithmic), scaled by bytes"
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -319,7 +323,8 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
         "gpu_launches": 3 * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "dense_decode_balanced_mma_kernel (split pass with the merge fused into its tail)",
+                     "traffic": int(algo_bytes * NCU_TRAFFIC_RATIO), "traffic_source": NCU_TRAFFIC_SOURCE,
+                     "peak_kind": peak_kind, "kernel": "dense_decode_balanced_mma_kernel (split pass with the merge fused into its tail)",
                      "algorithmic_bytes_per_launch": algo_bytes, "launch_ms": kernel_ms,
                      "frac_of_8TBps_nominal": achieved / 8000.0},
     }
@@ -498,22 +503,34 @@ def run_reference_arm(args, dist: Dist) -> dict | None:
 
 
 def run_profile_case(case: str, device) -> dict:
-    from anna_b200 import KVCacheConfig, Qwen3DynamicCache, fused_ops
+    from anna_b200 import KVCacheConfig, Qwen3DynamicCache, Qwen3PageAllocator, fused_ops
 
     gen = torch.Generator(device=device).manual_seed(3)
     if case == "paged":
-        batch, q_heads, kv_heads, dim, page, context = 16, 32, 8, 128, 16, 4096
+        # half of the headline batch: 16 ragged rows drawn like cfg2's, block tables a permutation of the pool
+        batch, q_heads, kv_heads, dim, page = 16, 32, 8, 128, 16
+        lengths = cfg2_lengths(7, batch)
         config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
-        cache = Qwen3DynamicCache(config, batch_size=batch)
-        k = torch.randn(batch, kv_heads, context, dim, device=device, dtype=torch.bfloat16, generator=gen)
-        v = torch.randn(batch, kv_heads, context, dim, device=device, dtype=torch.bfloat16, generator=gen)
-        cache.update(k, v, 0, require_dense_cache=False)
+        allocator = Qwen3PageAllocator(config)
+        template = torch.empty(1, kv_heads, 1, dim, device=device, dtype=torch.bfloat16)
+        layer = allocator.layers[0]
+        layer.ensure_capacity(sum((n + page - 1) // page for n in lengths) + 8, key_template=template,
+                              value_template=template)
+        layer.free_pages[:] = torch.randperm(layer.capacity(), generator=torch.Generator().manual_seed(8)).tolist()
+        rows = []
+        for n in lengths:
+            row = Qwen3DynamicCache(config, allocator=allocator)
+            k = torch.randn(1, kv_heads, n, dim, device=device, dtype=torch.bfloat16, generator=gen)
+            v = torch.randn(1, kv_heads, n, dim, device=device, dtype=torch.bfloat16, generator=gen)
+            row.update(k, v, 0, require_dense_cache=False)
+            rows.append(row)
+        cache = Qwen3DynamicCache.stack(rows, config)
         q = torch.randn(batch, q_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
         key_pages, value_pages, table, visible = cache.paged_attention_state(0)
         fn = lambda: fused_ops.run_paged_gqa_decode_fused(  # noqa: E731
             query=q, key_pages=key_pages, value_pages=value_pages, page_table=table, visible_lengths=visible,
             scaling=dim ** -0.5)
-        algo = batch * kv_heads * context * 2 * dim * 2
+        algo = sum(lengths) * kv_heads * 2 * dim * 2
     else:
         bits = {"tq4": 4, "tq3": 3, "tq2": 2}[case]
         batch, q_heads, kv_heads, dim, page, context = (32, 16, 2, 256, 16, 8320) if bits == 2 else \
