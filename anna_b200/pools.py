@@ -29,13 +29,17 @@ class _PageBook:
 
     def take(self, num_pages: int, capacity: int) -> tuple[list[int], int, list[int]]:
         """Pop up to num_pages from the free list; returns (page ids, new capacity, ids created by growth)."""
+        count = min(max(int(num_pages), 0), len(self.free_pages))
         out: list[int] = []
-        while self.free_pages and len(out) < num_pages:
-            page_id = self.free_pages.pop()
-            if self.refcount.get(page_id, 0) != 0:
-                raise RuntimeError(f"Invariant violated: free list page {page_id} has non-zero refcount.")
-            self.refcount[page_id] = 1
-            out.append(page_id)
+        if count > 0:
+            # the last `count` entries of the free list, most recently freed first (the same order as repeated pop())
+            out = self.free_pages[-count:]
+            out.reverse()
+            del self.free_pages[-count:]
+            stale = self.refcount.keys() & out
+            if stale:
+                raise RuntimeError(f"Invariant violated: free list page {min(stale)} has non-zero refcount.")
+            self.refcount.update(dict.fromkeys(out, 1))
         missing = num_pages - len(out)
         new_capacity = capacity
         fresh: list[int] = []
@@ -44,10 +48,8 @@ class _PageBook:
             new_capacity = capacity + grow_by
             new_ids = list(range(capacity, new_capacity))
             fresh = new_ids[:missing]
-            for page_id in reversed(new_ids[missing:]):
-                self.free_pages.append(page_id)
-            for page_id in fresh:
-                self.refcount[page_id] = 1
+            self.free_pages.extend(reversed(new_ids[missing:]))
+            self.refcount.update(dict.fromkeys(fresh, 1))
             out.extend(fresh)
         return out, new_capacity, fresh
 
@@ -58,8 +60,7 @@ class _PageBook:
         missing = required - capacity
         grow_by = max(missing, capacity or 16)
         new_capacity = capacity + grow_by
-        for page_id in reversed(range(capacity, new_capacity)):
-            self.free_pages.append(page_id)
+        self.free_pages.extend(reversed(range(capacity, new_capacity)))
         return new_capacity
 
     def retain(self, page_id: int) -> None:

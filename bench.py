@@ -333,6 +333,108 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# KV-head-sharded variant of cfg5 (--variant kvhead): every rank holds all sequences but only its KV heads
+
+
+def run_kvhead_variant(args, dist: Dist, device) -> dict:
+    """TurboQuant 4-bit decode, all sequences on every rank, Hkv / N KV heads per rank, one all-gather of the outputs
+    per step.  Total work is fixed, so the scaling is "strong"."""
+    from anna_b200 import KVCacheConfig, Qwen3DynamicCache
+    from anna_b200.sharding import HeadGather, shard_kv_heads
+
+    q_heads, kv_heads, dim, page, bits, residual = 32, 8, 128, 16, 4, 128
+    batch, context = args.kvhead_batch, args.kvhead_context
+    shard = shard_kv_heads(q_heads, kv_heads, dist.world, dist.rank)
+    local_kv, local_q = shard.kv_stop - shard.kv_start, shard.q_stop - shard.q_start
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
+    gather = HeadGather() if dist.enabled else (lambda out: out)
+
+    def build(rows: int, tokens: int, kv_slice: slice, seed: int):
+        cache = Qwen3DynamicCache(config, batch_size=rows, kv_cache_quantization="turboquant",
+                                  kv_cache_quant_bits=bits, kv_cache_residual_len=residual)
+        cache.reserve_sequence_capacity(tokens + 8 * (args.steps + args.warmup) + 64)
+        gen = torch.Generator(device=device).manual_seed(seed)  # the same stream of numbers on every rank
+        done = 0
+        while done < tokens:
+            step = min(2048, tokens - done)
+            k = torch.randn(rows, kv_heads, step, dim, device=device, dtype=torch.bfloat16, generator=gen)
+            v = torch.randn(rows, kv_heads, step, dim, device=device, dtype=torch.bfloat16, generator=gen)
+            cache.update(k[:, kv_slice], v[:, kv_slice], 0, require_dense_cache=False)
+            done += step
+            del k, v
+        return cache
+
+    # self-check on a small problem: gathered sharded outputs == the unsharded computation of the same data
+    check_rows, check_tokens = 2, 700
+    full = build(check_rows, check_tokens, slice(0, kv_heads), seed=5)
+    part = build(check_rows, check_tokens, slice(shard.kv_start, shard.kv_stop), seed=5)
+    q_check = torch.randn(check_rows, q_heads, 1, dim, device=device, dtype=torch.bfloat16,
+                          generator=torch.Generator(device=device).manual_seed(6))
+    want = full.turboquant_single_token_decode_attention(0, q_check, scaling=dim ** -0.5,
+                                                         num_key_value_groups=q_heads // kv_heads)
+    got = gather(part.turboquant_single_token_decode_attention(0, shard.slice_q(q_check), scaling=dim ** -0.5,
+                                                               num_key_value_groups=q_heads // kv_heads))
+    check_err = float((got.float() - want.float()).abs().max())
+    if not check_err <= 2e-2:
+        raise RuntimeError(f"KV-head-sharded decode disagrees with the unsharded one: max abs {check_err}")
+    full.release()
+    part.release()
+
+    cache = build(batch, context, slice(shard.kv_start, shard.kv_stop), seed=11)
+    gen = torch.Generator(device=device).manual_seed(12)
+    q = torch.randn(batch, q_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    k1 = torch.randn(batch, kv_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    v1 = torch.randn(batch, kv_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    q_local, k_local, v_local = shard.slice_q(q), shard.slice_kv(k1), shard.slice_kv(v1)
+
+    def step():
+        cache.update(k_local, v_local, 0, require_dense_cache=False)
+        local = cache.turboquant_single_token_decode_attention(0, q_local, scaling=dim ** -0.5,
+                                                               num_key_value_groups=q_heads // kv_heads)
+        return gather(local)
+
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(args.steps):
+        out = step()
+    end.record()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    clocks = sampler.stop()
+    step_ms = dist.max(begin.elapsed_time(end), device) / args.steps
+    key_bytes = dim * bits // 8 + 8
+    value_bytes = dim // 2 + 2 * (dim // 32) * 2
+    per_rank_bytes = batch * local_kv * ((context - residual) * (key_bytes + value_bytes) + residual * 2 * dim * 2)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = per_rank_bytes / (step_ms / 1e3) / 1e9
+    cache.release()
+    return {
+        "metric": METRIC, "value": batch / (step_ms / 1e3), "unit": UNIT, "n_gpus": dist.world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded N(0,1) bf16)",
+        "config": {"workload": "cfg5 variant: TurboQuant 4-bit, KV heads sharded, outputs all-gathered", "batch": batch,
+                   "q_heads": q_heads, "kv_heads": kv_heads, "head_dim": dim, "bits": bits, "context": context,
+                   "page_size": page, "residual_len": residual, "append_per_step": 1,
+                   "kv_heads_per_rank": local_kv, "q_heads_per_rank": local_q,
+                   "parallelism": f"kv-head-sharded x{dist.world}, one all-gather of [B, Hq/N, D] per step",
+                   "l2_policy": f"{per_rank_bytes / 1e6:.0f} MB of packed KV per rank and step exceed the 126 MB L2"},
+        "gpu_launches": 4 * args.steps, "clocks": clocks,
+        "self_check": {"max_abs_vs_unsharded": check_err, "rows": check_rows, "context": check_tokens},
+        "roofline": {"bound": "hbm (issue-bound today)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "tq_decode_split_mma_kernel (whole step incl. append and all-gather)",
+                     "algorithmic_bytes_per_launch": per_rank_bytes, "launch_ms": step_ms},
+        "out_shape": list(out.shape),
+    }
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # TurboQuant extras (single GPU): packed decode and fused append, device-timed
 
 
@@ -531,6 +633,20 @@ def run_profile_case(case: str, device) -> dict:
             query=q, key_pages=key_pages, value_pages=value_pages, page_table=table, visible_lengths=visible,
             scaling=dim ** -0.5)
         algo = sum(lengths) * kv_heads * 2 * dim * 2
+    elif case == "tqappend":
+        # bulk append: 2048 new tokens on top of 2176 cached ones, all 2048 oldest window/incoming tokens get packed
+        batch, kv_heads, dim, page, tokens = 16, 8, 128, 16, 2048
+        config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
+        cache = Qwen3DynamicCache(config, batch_size=batch, kv_cache_quantization="turboquant",
+                                  kv_cache_quant_bits=4, kv_cache_residual_len=128)
+        cache.reserve_sequence_capacity(2176 + 8 * tokens)
+        k = torch.randn(batch, kv_heads, 2176, dim, device=device, dtype=torch.bfloat16, generator=gen)
+        cache.update(k, torch.randn_like(k), 0, require_dense_cache=False)
+        k = torch.randn(batch, kv_heads, tokens, dim, device=device, dtype=torch.bfloat16, generator=gen)
+        v = torch.randn(batch, kv_heads, tokens, dim, device=device, dtype=torch.bfloat16, generator=gen)
+        fn = lambda: cache.update(k, v, 0, require_dense_cache=False)  # noqa: E731
+        packed = dim * 4 // 8 + 8 + dim // 2 + 2 * (dim // 32) * 2
+        algo = batch * kv_heads * tokens * (2 * 2 * dim * 2 + packed)  # ring/incoming read + ring write + packed write
     else:
         bits = {"tq4": 4, "tq3": 3, "tq2": 2}[case]
         batch, q_heads, kv_heads, dim, page, context = (32, 16, 2, 256, 16, 8320) if bits == 2 else \
@@ -559,9 +675,14 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extras", action="store_true", help="skip the TurboQuant configurations")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--variant", choices=("sequence", "kvhead"), default="sequence",
+                        help="sequence: rows sharded over ranks (default, the headline); kvhead: the TurboQuant 4-bit "
+                             "decode with KV heads sharded over ranks and an all-gather of the outputs")
+    parser.add_argument("--kvhead-batch", type=int, default=128)
+    parser.add_argument("--kvhead-context", type=int, default=32768)
     parser.add_argument("--no-clock-spin", action="store_true",
                         help="do not repeat the decode launch while waiting for clock samples (for profiler runs)")
-    parser.add_argument("--profile-case", choices=("paged", "tq4", "tq3", "tq2"), default=None,
+    parser.add_argument("--profile-case", choices=("paged", "tq4", "tq3", "tq2", "tqappend"), default=None,
                         help="run one small decode case a few times and exit (meant to be wrapped by ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -586,6 +707,13 @@ def main() -> None:
     dist = Dist(args.gpus, use_cuda=True)
     device = torch.device("cuda", dist.local_rank)
     torch.cuda.set_device(device)
+    if args.variant == "kvhead":
+        result = run_kvhead_variant(args, dist, device)
+        dist.barrier()
+        if dist.rank == 0:
+            print(json.dumps(result))
+        dist.close()
+        return
     result = run_cfg2_gpu(args, dist, device)
 
     if dist.rank == 0 and dist.world == 1:

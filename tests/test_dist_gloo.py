@@ -9,7 +9,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from anna_b200.sharding import aggregate_throughput, balance_by_tokens, shard_sequences
+from anna_b200.sharding import (HeadGather, aggregate_throughput, balance_by_tokens, shard_kv_heads,
+                                shard_sequences)
 
 
 def _free_port() -> int:
@@ -57,3 +58,36 @@ def test_shard_rule_and_balancing():
     loads = [sum(lengths[i] for i in bucket) for bucket in owners]
     assert max(loads) - min(loads) <= 1024
     assert aggregate_throughput([64, 64], [0.5, 1.0]) == 128.0
+
+
+def _head_worker(rank: int, world: int, port: int):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        batch, q_heads, kv_heads, dim = 3, 8, 4, 16
+        shard = shard_kv_heads(q_heads, kv_heads, world, rank)
+        full = torch.arange(batch * q_heads * dim, dtype=torch.float32).view(batch, q_heads, 1, dim)
+        kv = torch.arange(batch * kv_heads * 5 * dim, dtype=torch.float32).view(batch, kv_heads, 5, dim)
+        assert shard.slice_kv(kv).shape[1] == kv_heads // world and shard.slice_q(full).shape[1] == q_heads // world
+        gather = HeadGather()
+        for _ in range(2):  # the second call reuses the buffers
+            out = gather(shard.slice_q(full))
+            assert out.shape == full.shape and torch.equal(out, full)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_head_shards_and_output_gather_world2():
+    mp.spawn(_head_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_kv_head_shard_rule():
+    shards = [shard_kv_heads(32, 8, 8, r) for r in range(8)]
+    assert [(s.kv_start, s.kv_stop, s.q_start, s.q_stop) for s in shards][:2] == [(0, 1, 0, 4), (1, 2, 4, 8)]
+    assert shards[-1].q_stop == 32
+    with pytest.raises(ValueError):
+        shard_kv_heads(32, 8, 3, 0)
+    with pytest.raises(ValueError):
+        shard_kv_heads(30, 8, 2, 0)
