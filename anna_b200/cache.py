@@ -21,6 +21,7 @@ from __future__ import annotations
 import os
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -300,11 +301,11 @@ class Qwen3DynamicCache:
         if (buffer is None or buffer.shape[0] != batch_size or buffer.device != device
                 or buffer.shape[1] < required or synced is None):
             capacity = max(required, max(1, self.page_table_capacities[layer_idx] * 2))
-            host = torch.full((batch_size, capacity), -1, dtype=torch.int32)
+            host = np.full((batch_size, capacity), -1, dtype=np.int32)
             for row_idx, table in enumerate(tables):
                 if table:
-                    host[row_idx, : len(table)] = torch.tensor(table, dtype=torch.int32)
-            buffer = host.to(device)
+                    host[row_idx, : len(table)] = table
+            buffer = torch.from_numpy(host).to(device)
             self.page_table_caches[layer_idx] = buffer
             self.page_table_capacities[layer_idx] = capacity
             self._table_rows_synced[layer_idx] = [len(t) for t in tables]

@@ -25,13 +25,19 @@ struct TqAppendParams {
   const float* centroids;
   const float* boundaries;
   int batch, kv_heads, new_tokens, block_size, residual_len, value_group;
+  int block_shift, residual_shift;  // log2 when the value is a power of two, else -1
+  int u_chunks;                     // CTAs along the item axis of one (row, kv head)
   int64_t num_pages, max_blocks;
   anna_tq_layout layout;
   int32_t* status;
 };
 
-constexpr int kAppendWarps = 4;
+constexpr int kAppendWarps = 8;
 
+// A CTA belongs to one (row, kv head); its warps stride over that head's 2 * new_tokens items, so everything that does
+// not depend on the item -- sign vectors, boundaries, centroids, lengths, ring and pool bases -- is set up once per
+// warp.  Positions are 32-bit (the host rejects longer contexts) and divisions by the window length and the page size
+// are shifts when those are powers of two.
 template <typename T, int D, int BITS>
 __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAppendParams p) {
   constexpr int E = D / 32;
@@ -43,164 +49,167 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
   __syncthreads();
 
   const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
+  const int e0 = lane * E;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int64_t u = (int64_t)blockIdx.x * kAppendWarps + warp;
-
-  const int64_t R = p.residual_len;
-  const int64_t L = p.old_lengths[b];
-  const int64_t Tn = p.new_tokens;
-  const int64_t Lp = L + Tn;
-  if (p.new_lengths != nullptr && (blockIdx.x | blockIdx.y | threadIdx.x) == 0) p.new_lengths[b] = Lp;
-  const int64_t Lq = L > R ? L - R : 0;
-  const int64_t Lqp = Lp > R ? Lp - R : 0;
-  const int64_t nq = Lqp - Lq;
-  const int64_t wstart = L > Lqp ? L : Lqp;
-  const int64_t nw = Lp - wstart;
-  if (u >= nq + nw) return;
-
-  const int64_t slot = p.window_slots[b];
-  T* ring_k = reinterpret_cast<T*>(p.window) + ((slot * 2 + 0) * p.kv_heads + h) * R * D;
-  T* ring_v = reinterpret_cast<T*>(p.window) + ((slot * 2 + 1) * p.kv_heads + h) * R * D;
-  const T* in_k = reinterpret_cast<const T*>(p.k_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
-  const T* in_v = reinterpret_cast<const T*>(p.v_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h;
-  const int e0 = lane * E;
-
-  if (u >= nq) {
-    // window item: plain copy unless the slot's old occupant is quantized (and rewritten) by another warp
-    const int64_t pw = wstart + (u - nq);
-    const int64_t k = (pw - L + R) / R;  // smallest k >= 1 with pw - k*R < L
-    const int64_t p_old = pw - k * R;
-    if (p_old >= Lq) return;
-    const int64_t rs = pw % R;
-    lane_copy<T, E>(in_k + (pw - L) * p.stride_t + e0, ring_k + rs * D + e0);
-    lane_copy<T, E>(in_v + (pw - L) * p.stride_t + e0, ring_v + rs * D + e0);
-    return;
-  }
-
-  // ---- quantize item -------------------------------------------------------------------------------------------
-  const int64_t pos = Lq + u;
-  float x[E], v[E];
-  if (pos < L) {
-    const int64_t rs = pos % R;
-    lane_load<T, E>(ring_k + rs * D + e0, x);
-    lane_load<T, E>(ring_v + rs * D + e0, v);
-    const int64_t k = (wstart - pos + R - 1) / R;
-    const int64_t pw = pos + k * R;  // new occupant of this ring slot, if it arrives in this call
-    if (pw < Lp) {
-      lane_copy<T, E>(in_k + (pw - L) * p.stride_t + e0, ring_k + rs * D + e0);
-      lane_copy<T, E>(in_v + (pw - L) * p.stride_t + e0, ring_v + rs * D + e0);
-    }
-  } else {
-    lane_load<T, E>(in_k + (pos - L) * p.stride_t + e0, x);
-    lane_load<T, E>(in_v + (pos - L) * p.stride_t + e0, v);
-  }
-
-  const int64_t blk = pos / p.block_size;
-  const int tok = (int)(pos % p.block_size);
-  int32_t pid = -1;
-  if (blk < p.max_blocks) pid = p.block_table[(int64_t)b * p.table_stride + blk];
-  if (pid < 0 || pid >= p.num_pages) {
-    if (lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
-    return;
-  }
-  uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
-
-  // ---- keys: normalise, rotate, index, residual sign ------------------------------------------------------------
-  float s1[E], s2[E];
+  // bit j: coordinate e0 + j is negated by the rotation (low byte) / by the QJL projection (next byte)
+  uint32_t flips = 0;
 #pragma unroll
   for (int j = 0; j < E; ++j) {
-    s1[j] = p.signs1[e0 + j];
-    s2[j] = p.signs2[e0 + j];
+    flips |= (p.signs1[e0 + j] < 0.0f ? 1u : 0u) << j;
+    flips |= (p.signs2[e0 + j] < 0.0f ? 1u : 0u) << (8 + j);
   }
-  float t[E], w[E];
-#pragma unroll
-  for (int j = 0; j < E; ++j) t[j] = __fmul_rn(x[j], x[j]);
-  const float norm = __fsqrt_rn(warp_tree_sum<E>(t));
-  const float inv = __frcp_rn(fmaxf(norm, 1e-20f));
-#pragma unroll
-  for (int j = 0; j < E; ++j) w[j] = s1[j] < 0.0f ? -x[j] : x[j];
-  warp_fwht<E>(w, lane);
-
   float bnd[NB];
 #pragma unroll
   for (int k = 0; k < NB; ++k) bnd[k] = p.boundaries[k];
-
-  uint32_t code[E];
-  float e[E];
-#pragma unroll
-  for (int j = 0; j < E; ++j) {
-    const float scaled = __fmul_rn(w[j], inv);
-    uint32_t c = 0;
-#pragma unroll
-    for (int k = 0; k < NB; ++k) c += scaled > bnd[k] ? 1u : 0u;
-    code[j] = c;
-    e[j] = __fsub_rn(scaled, sm_cent[c]);
-  }
-#pragma unroll
-  for (int j = 0; j < E; ++j) t[j] = __fmul_rn(e[j], e[j]);
   constexpr float rsqrt_dim = rsqrt_dim_const<D>();
-  const float rnorm = __fmul_rn(__fsqrt_rn(warp_tree_sum<E>(t)), rsqrt_dim);
-#pragma unroll
-  for (int j = 0; j < E; ++j) e[j] = s2[j] < 0.0f ? -e[j] : e[j];
-  warp_fwht<E>(e, lane);
+  const float levels = (float)((1 << BITS) - 1);
+  const int lanes_per_group = p.value_group / E;  // power of two, >= 1
+  const int R = p.residual_len;
+  const int Tn = p.new_tokens;
+  const int S = p.block_size;
+  auto div_r = [&](int v) { return p.residual_shift >= 0 ? v >> p.residual_shift : v / R; };
+  auto div_s = [&](int v) { return p.block_shift >= 0 ? v >> p.block_shift : v / S; };
 
-  uint8_t* krow = chunk + p.layout.off_kcodes + tok * p.layout.key_bytes;
-  if constexpr (BITS == 4) {
-    uint64_t field = 0;
+  const int L = (int)p.old_lengths[b];
+  const int Lp = L + Tn;
+  if (p.new_lengths != nullptr && (blockIdx.x | blockIdx.y | threadIdx.x) == 0) p.new_lengths[b] = Lp;
+  const int Lq = L > R ? L - R : 0;
+  const int Lqp = Lp > R ? Lp - R : 0;
+  const int nq = Lqp - Lq;
+  const int wstart = L > Lqp ? L : Lqp;
+  const int nw = Lp - wstart;
+  const int64_t slot = p.window_slots[b];
+  T* ring_k = reinterpret_cast<T*>(p.window) + ((slot * 2 + 0) * p.kv_heads + h) * (int64_t)R * D + e0;
+  T* ring_v = reinterpret_cast<T*>(p.window) + ((slot * 2 + 1) * p.kv_heads + h) * (int64_t)R * D + e0;
+  // incoming token at position pos sits at in_k + (pos - L) * stride_t
+  const T* in_k = reinterpret_cast<const T*>(p.k_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h + e0;
+  const T* in_v = reinterpret_cast<const T*>(p.v_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h + e0;
+  const int32_t* table_row = p.block_table + (int64_t)b * p.table_stride;
+
+  for (int u = (int)blockIdx.x * kAppendWarps + (threadIdx.x >> 5); u < nq + nw; u += p.u_chunks * kAppendWarps) {
+    if (u >= nq) {
+      // window item: plain copy unless the slot's old occupant is quantized (and rewritten) by another warp
+      const int pw = wstart + (u - nq);
+      const int k = div_r(pw - L + R);  // smallest k >= 1 with pw - k*R < L
+      const int p_old = pw - k * R;
+      if (p_old >= Lq) continue;
+      const int rs = pw - div_r(pw) * R;
+      lane_copy<T, E>(in_k + (int64_t)(pw - L) * p.stride_t, ring_k + rs * D);
+      lane_copy<T, E>(in_v + (int64_t)(pw - L) * p.stride_t, ring_v + rs * D);
+      continue;
+    }
+
+    // ---- quantize item -----------------------------------------------------------------------------------------
+    const int pos = Lq + u;
+    float x[E], v[E];
+    if (pos < L) {
+      const int rs = pos - div_r(pos) * R;
+      lane_load<T, E>(ring_k + rs * D, x);
+      lane_load<T, E>(ring_v + rs * D, v);
+      const int k = div_r(wstart - pos + R - 1);
+      const int pw = pos + k * R;  // new occupant of this ring slot, if it arrives in this call
+      if (pw < Lp) {
+        lane_copy<T, E>(in_k + (int64_t)(pw - L) * p.stride_t, ring_k + rs * D);
+        lane_copy<T, E>(in_v + (int64_t)(pw - L) * p.stride_t, ring_v + rs * D);
+      }
+    } else {
+      lane_load<T, E>(in_k + (int64_t)(pos - L) * p.stride_t, x);
+      lane_load<T, E>(in_v + (int64_t)(pos - L) * p.stride_t, v);
+    }
+
+    const int blk = div_s(pos);
+    const int tok = pos - blk * S;
+    int32_t pid = -1;
+    if (blk < p.max_blocks) pid = table_row[blk];
+    if (pid < 0 || pid >= p.num_pages) {
+      if (lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
+      continue;
+    }
+    uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
+
+    // ---- keys: normalise, rotate, index, residual sign ----------------------------------------------------------
+    float t[E], w[E];
 #pragma unroll
-    for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 8u : 0u)) << (4 * j);
-    warp_pack_store<4 * E>(field, krow, lane);
-  } else if constexpr (BITS == 2) {
-    uint64_t field = 0;
+    for (int j = 0; j < E; ++j) t[j] = __fmul_rn(x[j], x[j]);
+    const float norm = __fsqrt_rn(warp_tree_sum<E>(t));
+    const float inv = __frcp_rn(fmaxf(norm, 1e-20f));
 #pragma unroll
-    for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 2u : 0u)) << (2 * j);
-    warp_pack_store<2 * E>(field, krow, lane);
-  } else {
-    uint64_t idx_field = 0, sign_field = 0;
+    for (int j = 0; j < E; ++j) w[j] = __uint_as_float(__float_as_uint(x[j]) ^ ((flips >> j) << 31));
+    warp_fwht<E>(w, lane);
+
+    uint32_t code[E];
+    float e[E];
 #pragma unroll
     for (int j = 0; j < E; ++j) {
-      idx_field |= (uint64_t)code[j] << (2 * j);
-      sign_field |= (uint64_t)(e[j] >= 0.0f ? 1u : 0u) << j;
+      const float scaled = __fmul_rn(w[j], inv);
+      uint32_t c = 0;
+#pragma unroll
+      for (int k = 0; k < NB; ++k) c += scaled > bnd[k] ? 1u : 0u;
+      code[j] = c;
+      e[j] = __fsub_rn(scaled, sm_cent[c]);
     }
-    warp_pack_store<2 * E>(idx_field, krow, lane);
-    warp_pack_store<E>(sign_field, krow + D / 4, lane);
-  }
-  if (lane == 0) {
-    reinterpret_cast<float*>(chunk + p.layout.off_knorm)[tok] = norm;
-    reinterpret_cast<float*>(chunk + p.layout.off_krnorm)[tok] = rnorm;
-  }
+#pragma unroll
+    for (int j = 0; j < E; ++j) t[j] = __fmul_rn(e[j], e[j]);
+    const float rnorm = __fmul_rn(__fsqrt_rn(warp_tree_sum<E>(t)), rsqrt_dim);
+#pragma unroll
+    for (int j = 0; j < E; ++j) e[j] = __uint_as_float(__float_as_uint(e[j]) ^ ((flips >> (8 + j)) << 31));
+    warp_fwht<E>(e, lane);
 
-  // ---- values: per-group min/max -> scale / zero in the cache dtype -> round-half-even codes ---------------------
-  const int lanes_per_group = p.value_group / E;  // power of two, >= 1
-  float lo = v[0], hi = v[0];
+    uint8_t* krow = chunk + p.layout.off_kcodes + tok * p.layout.key_bytes;
+    if constexpr (BITS == 4) {
+      uint64_t field = 0;
 #pragma unroll
-  for (int j = 1; j < E; ++j) {
-    lo = fminf(lo, v[j]);
-    hi = fmaxf(hi, v[j]);
-  }
-  for (int dl = 1; dl < lanes_per_group; dl <<= 1) {
-    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, dl));
-    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, dl));
-  }
-  const float levels = (float)((1 << BITS) - 1);
-  const float raw = __fdiv_rn(__fsub_rn(hi, lo), levels);
-  const float scale = round_to_elem<T>(raw < 1e-8f ? 1e-8f : raw);
-  const float zero = round_to_elem<T>(lo);
-  uint64_t vfield = 0;
+      for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 8u : 0u)) << (4 * j);
+      warp_pack_store<4 * E>(field, krow, lane);
+    } else if constexpr (BITS == 2) {
+      uint64_t field = 0;
 #pragma unroll
-  for (int j = 0; j < E; ++j) {
-    float q = rintf(__fdiv_rn(__fsub_rn(v[j], zero), scale));
-    if (!(q >= 0.0f)) q = 0.0f;
-    if (q > levels) q = levels;
-    vfield |= (uint64_t)(uint32_t)q << (VS * j);
-  }
-  warp_pack_store<VS * E>(vfield, chunk + p.layout.off_vdata + tok * p.layout.value_bytes, lane);
-  if (lane % lanes_per_group == 0) {
-    const int g = lane / lanes_per_group;
-    reinterpret_cast<T*>(chunk + p.layout.off_vscale)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(scale);
-    reinterpret_cast<T*>(chunk + p.layout.off_vzero)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(zero);
+      for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 2u : 0u)) << (2 * j);
+      warp_pack_store<2 * E>(field, krow, lane);
+    } else {
+      uint64_t idx_field = 0, sign_field = 0;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        idx_field |= (uint64_t)code[j] << (2 * j);
+        sign_field |= (uint64_t)(e[j] >= 0.0f ? 1u : 0u) << j;
+      }
+      warp_pack_store<2 * E>(idx_field, krow, lane);
+      warp_pack_store<E>(sign_field, krow + D / 4, lane);
+    }
+    if (lane == 0) {
+      reinterpret_cast<float*>(chunk + p.layout.off_knorm)[tok] = norm;
+      reinterpret_cast<float*>(chunk + p.layout.off_krnorm)[tok] = rnorm;
+    }
+
+    // ---- values: per-group min/max -> scale / zero in the cache dtype -> round-half-even codes -------------------
+    float lo = v[0], hi = v[0];
+#pragma unroll
+    for (int j = 1; j < E; ++j) {
+      lo = fminf(lo, v[j]);
+      hi = fmaxf(hi, v[j]);
+    }
+    for (int dl = 1; dl < lanes_per_group; dl <<= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, dl));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, dl));
+    }
+    const float raw = __fdiv_rn(__fsub_rn(hi, lo), levels);
+    const float scale = round_to_elem<T>(raw < 1e-8f ? 1e-8f : raw);
+    const float zero = round_to_elem<T>(lo);
+    uint64_t vfield = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      float q = rintf(__fdiv_rn(__fsub_rn(v[j], zero), scale));
+      if (!(q >= 0.0f)) q = 0.0f;
+      if (q > levels) q = levels;
+      vfield |= (uint64_t)(uint32_t)q << (VS * j);
+    }
+    warp_pack_store<VS * E>(vfield, chunk + p.layout.off_vdata + tok * p.layout.value_bytes, lane);
+    if (lane % lanes_per_group == 0) {
+      const int g = lane / lanes_per_group;
+      reinterpret_cast<T*>(chunk + p.layout.off_vscale)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(scale);
+      reinterpret_cast<T*>(chunk + p.layout.off_vzero)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(zero);
+    }
   }
 }
 
@@ -252,12 +261,38 @@ extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_s
   if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, &p.layout))
     return set_error(ANNA_ERR_INVALID, "anna_tq_append: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim, bits,
                      block_size, value_group);
-  const int64_t items = 2 * (int64_t)new_tokens;
-  dim3 grid((unsigned)((items + kAppendWarps - 1) / kAppendWarps), (unsigned)kv_heads, (unsigned)batch);
+  ANNA_REQUIRE((int64_t)new_tokens < ((int64_t)1 << 29) && max_blocks * (int64_t)block_size < ((int64_t)1 << 30),
+               "anna_tq_append: context too long for 32-bit positions");
+  p.block_shift = p.residual_shift = -1;
+  for (int sh = 0; sh < 30; ++sh) {
+    if ((1 << sh) == block_size) p.block_shift = sh;
+    if ((1 << sh) == residual_len) p.residual_shift = sh;
+  }
   return ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
     return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
       return ANNA_DISPATCH_TQ_BITS(bits, BITS, [&]() -> int {
-        tq_append_kernel<T, D, BITS><<<grid, kAppendWarps * 32, 0, (cudaStream_t)stream>>>(p);
+        auto kernel = tq_append_kernel<T, D, BITS>;
+        static int resident[64] = {};  // per device: CTAs of this kernel that fit the whole GPU at once
+        int device = 0;
+        ANNA_CUDA_CHECK(cudaGetDevice(&device));
+        int ctas = (device >= 0 && device < 64) ? resident[device] : 0;
+        if (ctas == 0) {
+          int sms = 0, per_sm = 0;
+          ANNA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+          ANNA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kAppendWarps * 32, 0));
+          ctas = sms * (per_sm > 0 ? per_sm : 1);
+          if (device >= 0 && device < 64) resident[device] = ctas;
+        }
+        // about two resident waves of CTAs, each (row, kv head) cut into u_chunks pieces along its items
+        const int64_t heads_total = (int64_t)kv_heads * batch;
+        const int64_t max_chunks = (2 * (int64_t)new_tokens + kAppendWarps - 1) / kAppendWarps;
+        int64_t chunks = (2 * (int64_t)ctas + heads_total - 1) / heads_total;
+        if (chunks > max_chunks) chunks = max_chunks;
+        if (chunks < 1) chunks = 1;
+        TqAppendParams q = p;
+        q.u_chunks = (int)chunks;
+        dim3 grid((unsigned)chunks, (unsigned)kv_heads, (unsigned)batch);
+        kernel<<<grid, kAppendWarps * 32, 0, (cudaStream_t)stream>>>(q);
         return check_launch("tq_append_kernel");
       });
     });

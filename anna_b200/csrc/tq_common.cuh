@@ -50,11 +50,12 @@ __device__ __forceinline__ void warp_fwht(float (&w)[E], int lane) {
   }
 #pragma unroll
   for (int dl = 1; dl < 32; dl <<= 1) {
-    const bool upper = (lane & dl) != 0;
+    // lower lane: w + other, upper lane: other - w.  One fused multiply-add by +-1 rounds exactly like the add / sub.
+    const float sgn = (lane & dl) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int j = 0; j < E; ++j) {
       const float other = __shfl_xor_sync(0xffffffffu, w[j], dl);
-      w[j] = upper ? __fsub_rn(other, w[j]) : __fadd_rn(w[j], other);
+      w[j] = __fmaf_rn(w[j], sgn, other);
     }
   }
 }
