@@ -117,7 +117,12 @@ static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_
       if (chunk_tokens_in <= 0) {
         rc = try_launch_paged_decode_tma(p, batch, head_dim, dtype, stream);
         if (rc != ANNA_ERR_UNSUPPORTED) return rc;
-        if (dense_balanced_mma_applicable(p, batch))
+        // Two schedules for the same tile body.  Few CTAs' worth of work: one resident wave with an even share per CTA
+        // (no tail, one pipeline start per CTA).  Many: fixed chunks handed out by the hardware block scheduler, which
+        // lets faster SMs take more chunks; measured 3-10 % ahead from about 6000 grid CTAs on (48+ rows of 1-8 K
+        // tokens, 32+ rows of 16-32 K), and up to 40 % behind below that.
+        const int64_t grid_ctas = (int64_t)num_chunks * p.kv_heads * ((p.groups + 7) / 8) * batch;
+        if (grid_ctas < 6000 && dense_balanced_mma_applicable(p, batch))
           return launch_dense_balanced_mma(p, batch, head_dim, dtype, stream);
       }
       return launch_dense_split_mma(p, batch, head_dim, dtype, stream);
