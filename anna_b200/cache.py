@@ -629,8 +629,9 @@ class Qwen3DynamicCache:
             picked = pages[index]  # [B, blocks, Hkv, S, D]
             dense = picked.permute(0, 2, 1, 3, 4).reshape(batch_size, pages.shape[1], blocks * self.block_size,
                                                           pages.shape[3])[:, :, :max_length, :]
-            mask = torch.arange(max_length, device=device)[None, :] < visible[:, None]
-            return dense * mask[:, None, :, None].to(dense.dtype)
+            # slots past a row's length hold whatever the page held before: select, do not multiply (NaN * 0 is NaN)
+            hidden = torch.arange(max_length, device=device)[None, :] >= visible[:, None]
+            return dense.masked_fill(hidden[:, None, :, None], 0)
 
         return gather(layer.key_pages), gather(layer.value_pages), visible
 
