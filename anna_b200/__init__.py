@@ -19,11 +19,11 @@ from .fused_ops import (
 )
 from .pools import Qwen3PagedLayerAllocator, TurboQuantLayerPool, resolve_value_group_size
 from .prefix_block_cache import PrefixBlockPool
-from .turboquant import VALID_KV_CACHE_QUANT_BITS, TurboQuantKVRow, turboquant_is_available
+from .turboquant import VALID_KV_CACHE_QUANT_BITS, TurboQuantKVRow, TurboQuantTensorRow, turboquant_is_available
 
 __all__ = [
     "KVCacheConfig", "Qwen3DynamicCache", "Qwen3PageAllocator", "Qwen3PagedLayerAllocator", "TurboQuantLayerPool",
-    "PrefixBlockPool", "TurboQuantKVRow", "VALID_KV_CACHE_QUANT_BITS", "resolve_value_group_size",
+    "PrefixBlockPool", "TurboQuantKVRow", "TurboQuantTensorRow", "VALID_KV_CACHE_QUANT_BITS", "resolve_value_group_size",
     "turboquant_is_available", "maybe_load_gated_delta_library", "gqa_decode_fused_is_available",
     "gqa_decode_splitkv_fused_is_available", "gqa_decode_splitkv_fused_out_is_available",
     "gqa_decode_splitkv_turboquant_fused_out_is_available", "paged_gqa_decode_fused_is_available",

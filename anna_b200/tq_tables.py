@@ -67,20 +67,24 @@ class KeyQuantizerTables:
         return math.sqrt(math.pi / 2.0) / math.sqrt(self.head_dim)
 
 
-_DEVICE_TABLES: dict[tuple[int, int, str], KeyQuantizerTables] = {}
+_DEVICE_TABLES: dict[tuple[int, int, str, str], KeyQuantizerTables] = {}
 
 
-def key_tables(*, head_dim: int, bits: int, device: torch.device | str) -> KeyQuantizerTables:
-    """Device-resident constants for the inner-product quantizer of (head_dim, bits)."""
+def key_tables(*, head_dim: int, bits: int, device: torch.device | str, variant: str = "ip") -> KeyQuantizerTables:
+    """Device-resident constants of the quantizer of (head_dim, bits): ``variant="ip"`` is the inner-product
+    quantizer of KV rows (``bits - 1`` index bits + QJL sign), ``"mse"`` the plain one of tensor rows (``bits`` index
+    bits, src/anna/model/turboquant.py:75-82)."""
+    if variant not in ("ip", "mse"):
+        raise ValueError(f"unknown TurboQuant variant {variant!r}")
     device = torch.device(device)
-    key = (int(head_dim), int(bits), str(device))
+    key = (int(head_dim), int(bits), str(device), variant)
     tables = _DEVICE_TABLES.get(key)
     if tables is not None:
         return tables
     with _LOCK:
         tables = _DEVICE_TABLES.get(key)
         if tables is None:
-            index_bits = int(bits) - 1
+            index_bits = int(bits) - (1 if variant == "ip" else 0)
             cent, bnd = codebook(int(head_dim), index_bits)
             tables = KeyQuantizerTables(
                 head_dim=int(head_dim),

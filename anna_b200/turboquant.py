@@ -131,6 +131,149 @@ def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, qu
             "anna_tq_materialize")
 
 
+class TurboQuantTensorRow:
+    """History of one tensor (the K or the V of one sequence) with MSE-only TurboQuant codes for everything older than
+    the newest ``residual_len`` tokens; mirrors ``TurboQuantTensorRow`` of the Gemma4 runtime
+    (src/anna/model/turboquant.py:335-477): ``append([heads, tokens, dim])``, ``materialize``, ``clone``, ``to``.
+
+    Codes live in growable device buffers (indices packed to ``bits`` / 4-bit fields, fp32 norms); the quantizer and
+    its inverse are CUDA kernels, nothing is computed on the host."""
+
+    def __init__(self, *, bits: int, residual_len: int) -> None:
+        self.bits = int(bits)
+        self.residual_len = max(1, int(residual_len))
+        self.device: torch.device | None = None
+        self.dtype: torch.dtype | None = None
+        self.head_dim: int | None = None
+        self._codes: torch.Tensor | None = None   # uint8 [heads, capacity, row_bytes]
+        self._norms: torch.Tensor | None = None   # float32 [heads, capacity]
+        self._quantized = 0
+        self._residual: torch.Tensor | None = None
+        self._length = 0
+
+    @property
+    def length(self) -> int:
+        return self._length
+
+    @property
+    def quantized_length(self) -> int:
+        return self._quantized
+
+    @property
+    def initialized(self) -> bool:
+        return self.device is not None and self.dtype is not None and self.head_dim is not None
+
+    def _ensure_capacity(self, heads: int, tokens: int) -> None:
+        assert self.device is not None and self.head_dim is not None
+        have = 0 if self._codes is None else int(self._codes.shape[1])
+        if tokens <= have:
+            return
+        capacity = max(tokens, 16, 2 * have)  # growth rule of the reference buffers (turboquant.py:576-581)
+        row_bytes = _lib.lib().anna_tq_tensor_row_bytes(self.head_dim, self.bits)
+        if row_bytes <= 0:
+            raise RuntimeError(f"unsupported TurboQuant tensor geometry: head_dim={self.head_dim}, bits={self.bits}")
+        codes = torch.empty((heads, capacity, row_bytes), dtype=torch.uint8, device=self.device)
+        norms = torch.empty((heads, capacity), dtype=torch.float32, device=self.device)
+        if self._codes is not None and self._quantized > 0:
+            codes[:, : self._quantized].copy_(self._codes[:, : self._quantized])
+            norms[:, : self._quantized].copy_(self._norms[:, : self._quantized])
+        self._codes, self._norms = codes, norms
+
+    def append(self, tensor: torch.Tensor) -> None:
+        if tensor.ndim != 3:
+            raise ValueError(f"TurboQuantTensorRow expects [heads, tokens, dim], got {tuple(tensor.shape)}")
+        if tensor.shape[1] <= 0:
+            return
+        if not self.initialized:
+            _require_cuda(tensor, "TurboQuantTensorRow.append")
+            self.device, self.dtype, self.head_dim = tensor.device, tensor.dtype, int(tensor.shape[-1])
+            self._residual = tensor.detach().contiguous()
+            self._length = int(tensor.shape[1])
+        else:
+            if tensor.device != self.device:
+                tensor = tensor.to(device=self.device)
+            if tensor.dtype != self.dtype:
+                tensor = tensor.to(dtype=self.dtype)
+            if int(tensor.shape[-1]) != self.head_dim:
+                raise ValueError(
+                    f"TurboQuantTensorRow head_dim mismatch: expected {self.head_dim}, got {int(tensor.shape[-1])}")
+            residual = self._residual
+            self._residual = (tensor.detach().contiguous() if residual is None
+                              else torch.cat((residual, tensor.detach()), dim=1).contiguous())
+            self._length += int(tensor.shape[1])
+        residual = self._residual
+        if residual is None or residual.shape[1] <= self.residual_len:
+            return
+        overflow = int(residual.shape[1] - self.residual_len)
+        heads = int(residual.shape[0])
+        self._ensure_capacity(heads, self._quantized + overflow)
+        assert self._codes is not None and self._norms is not None and self.device is not None
+        tables = key_tables(head_dim=self.head_dim, bits=self.bits, device=self.device, variant="mse")
+        with on_device(self.device):
+            _lib.check(_lib.lib().anna_tq_tensor_quantize(
+                ptr(residual), residual.stride(0), residual.stride(1), ptr(self._codes), ptr(self._norms),
+                int(self._codes.shape[1]), self._quantized, heads, overflow, self.head_dim, self.bits,
+                ptr(tables.signs1), ptr(tables.boundaries), dtype_code(residual.dtype), stream_ptr(self.device)),
+                "anna_tq_tensor_quantize")
+        self._quantized += overflow
+        self._residual = residual[:, overflow:, :].contiguous()
+
+    def materialize(self, *, device: torch.device | None = None, dtype: torch.dtype | None = None) -> torch.Tensor:
+        if not self.initialized:
+            raise RuntimeError("TurboQuantTensorRow is not initialized.")
+        assert self.device is not None and self.dtype is not None and self.head_dim is not None
+        residual = self._residual
+        window = 0 if residual is None else int(residual.shape[1])
+        if self._quantized == 0 and window == 0:
+            out = torch.empty((0, 0, self.head_dim), device=self.device, dtype=self.dtype)
+        else:
+            heads = int(self._codes.shape[0]) if self._quantized else int(residual.shape[0])
+            out = torch.empty((heads, self._quantized + window, self.head_dim), device=self.device, dtype=self.dtype)
+            if self._quantized:
+                tables = key_tables(head_dim=self.head_dim, bits=self.bits, device=self.device, variant="mse")
+                with on_device(self.device):
+                    _lib.check(_lib.lib().anna_tq_tensor_dequantize(
+                        ptr(self._codes), ptr(self._norms), int(self._codes.shape[1]), 0, ptr(out), out.stride(0),
+                        out.stride(1), heads, self._quantized, self.head_dim, self.bits, ptr(tables.signs1),
+                        ptr(tables.centroids), dtype_code(out.dtype), stream_ptr(self.device)),
+                        "anna_tq_tensor_dequantize")
+            if window:
+                out[:, self._quantized:].copy_(residual)
+        kwargs: dict[str, object] = {}
+        if device is not None:
+            kwargs["device"] = device
+        if dtype is not None:
+            kwargs["dtype"] = dtype
+        return out.to(**kwargs) if kwargs else out
+
+    def clone(self) -> "TurboQuantTensorRow":
+        cloned = TurboQuantTensorRow(bits=self.bits, residual_len=self.residual_len)
+        cloned.device, cloned.dtype, cloned.head_dim = self.device, self.dtype, self.head_dim
+        cloned._length, cloned._quantized = self._length, self._quantized
+        cloned._codes = None if self._codes is None else self._codes.clone()
+        cloned._norms = None if self._norms is None else self._norms.clone()
+        cloned._residual = None if self._residual is None else self._residual.clone()
+        return cloned
+
+    def to(self, *, device: torch.device | None = None, dtype: torch.dtype | None = None) -> "TurboQuantTensorRow":
+        if not self.initialized:
+            return self
+        if device is not None and torch.device(device).type != "cuda":
+            raise RuntimeError("TurboQuantTensorRow lives on a CUDA device; there is no CPU implementation.")
+        if device is not None:
+            if self._codes is not None:
+                self._codes = self._codes.to(device=device)
+                self._norms = self._norms.to(device=device)
+            if self._residual is not None:
+                self._residual = self._residual.to(device=device)
+            self.device = torch.device(device)
+        if dtype is not None:
+            if self._residual is not None:
+                self._residual = self._residual.to(dtype=dtype)
+            self.dtype = dtype
+        return self
+
+
 class TurboQuantKVRow:
     """One sequence of one TurboQuant layer: newest ``residual_len`` tokens in a ring, older tokens packed in pages."""
 

@@ -245,6 +245,25 @@ int anna_gqa_decode_turboquant_values(const void* q, int64_t q_stride_b, int64_t
                                       int64_t quantized_len, int64_t residual_len, int head_dim, int value_bits,
                                       int value_group, float scaling, int dtype, anna_stream_t stream);
 
+/*
+ * MSE-only TurboQuant codes for a plain tensor row: what TurboQuantTensorRow (src/anna/model/turboquant.py:335-477, the
+ * K / V history rows of the Gemma4 runtime) asks of TurboQuantMSE(dim, bits, seed=42).quantize / .dequantize
+ * (turboquant.py:392-395, :415-418).  Every [head_dim] vector becomes `bits`-bit Lloyd-Max indices of its normalised,
+ * rotated coordinates plus its fp32 norm.  head_dim 64 / 128 / 256 / 512; bits 2 / 3 / 4.
+ *   x / out   [heads, tokens, head_dim] with element strides (stride_h, stride_t), last dim contiguous
+ *   idx       uint8 [heads, capacity, anna_tq_tensor_row_bytes(head_dim, bits)]: 2-bit fields for bits == 2, else 4-bit
+ *             fields, low field first;   norms  float32 [heads, capacity]
+ *   offset    position of token 0 of this call inside the code buffers (offset + tokens <= capacity)
+ *   signs1 float32 [head_dim];  boundaries float32 [2^bits - 1];  centroids float32 [2^bits]
+ */
+int anna_tq_tensor_row_bytes(int head_dim, int bits);
+int anna_tq_tensor_quantize(const void* x, int64_t stride_h, int64_t stride_t, uint8_t* idx, float* norms,
+                            int64_t capacity, int64_t offset, int heads, int tokens, int head_dim, int bits,
+                            const float* signs1, const float* boundaries, int dtype, anna_stream_t stream);
+int anna_tq_tensor_dequantize(const uint8_t* idx, const float* norms, int64_t capacity, int64_t offset, void* out,
+                              int64_t stride_h, int64_t stride_t, int heads, int tokens, int head_dim, int bits,
+                              const float* signs1, const float* centroids, int dtype, anna_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
