@@ -59,7 +59,14 @@ class Qwen3PageAllocator:
             )
             for layer_idx in range(config.num_hidden_layers)
         ]
-        self.turboquant_layers = [TurboQuantLayerPool(self.block_size) for _ in range(config.num_hidden_layers)]
+        # packed pages of quantized layers are shared the same way, keyed by the whole prompt prefix up to the block
+        self.packed_prefix_block_pool = PrefixBlockPool()
+        self.turboquant_layers = [
+            TurboQuantLayerPool(
+                self.block_size,
+                on_page_freed=lambda pid, li=layer_idx: self.packed_prefix_block_pool.discard_page(li, pid))
+            for layer_idx in range(config.num_hidden_layers)
+        ]
         # The reference keeps a contiguous dense mirror of full-attention layers by default; this build gathers the
         # dense view from the pages on demand, so the switch is accepted and ignored.
         self.maintain_full_attention_mirror = False
@@ -99,6 +106,7 @@ class Qwen3PageAllocator:
         for pool in self.turboquant_layers:
             released += pool.clear()
         self.prefix_block_pool.clear()
+        self.packed_prefix_block_pool.clear()
         return released
 
     def to(self, *, device: torch.device | None = None, dtype: torch.dtype | None = None) -> "Qwen3PageAllocator":
@@ -199,6 +207,8 @@ class Qwen3DynamicCache:
         self._released = False
         self._prefill_input_ids: torch.Tensor | None = None
         self._prompt_token_ids: list[int] | None = None
+        self._prompt_prefix_keys: list[tuple] | None = None   # per full prompt block: key of the prefix ending there
+        self._packed_blocks_registered: list[int] = [0] * layers  # prompt blocks of row 0 already offered for sharing
         self._prefix_kv_share = os.environ.get("ANNA_PREFIX_KV_SHARE", "1") != "0"
 
     # -- small bookkeeping (ops.py:398-441, :859-889) ----------------------------------------------------------------
@@ -215,6 +225,7 @@ class Qwen3DynamicCache:
         if int(input_ids.shape[0]) != 1 or self.get_seq_length() != 0 or int(input_ids.shape[1]) <= 0:
             return
         self._prompt_token_ids = [int(t) for t in input_ids[0].tolist()]
+        self._prompt_prefix_keys = None
 
     def reserve_sequence_capacity(self, seq_length: int) -> None:
         self.reserved_seq_capacity = max(0, int(seq_length))
@@ -486,6 +497,52 @@ class Qwen3DynamicCache:
     def _tq_pool(self, layer_idx: int) -> TurboQuantLayerPool:
         return self.allocator.turboquant_layers[layer_idx]
 
+    def _prefix_keys(self) -> list[tuple]:
+        """One key per full block of the prompt: (block index, chained hash of all tokens up to its end, the block's
+        own tokens).  Packed codes depend on the whole prefix (keys and values come out of causal layers), so the
+        registry is keyed by the prefix, not by the block's tokens alone."""
+        if self._prompt_prefix_keys is None:
+            prompt, bs = self._prompt_token_ids or [], self.block_size
+            keys, chain = [], 0
+            for j in range(len(prompt) // bs):
+                block = tuple(prompt[j * bs:(j + 1) * bs])
+                chain = hash((chain, block))
+                keys.append((j, chain, block))
+            self._prompt_prefix_keys = keys
+        return self._prompt_prefix_keys
+
+    def _reserve_shared_packed_blocks(self, row: TurboQuantKVRow, pool: TurboQuantLayerPool, layer_idx: int,
+                                      new_length: int) -> list[int]:
+        """Single-row prompt path: like ``row._reserve_blocks`` but a block whose whole prompt prefix was packed by an
+        earlier sequence is mapped by reference.  Returns the indices of the blocks mapped that way in this call."""
+        quantized = max(0, int(new_length) - row.residual_len)
+        need = (quantized + pool.block_size - 1) // pool.block_size
+        keys = self._prefix_keys()
+        registry = self.allocator.packed_prefix_block_pool
+        shared: list[int] = []
+        table = row.block_table
+        while len(table) < need:
+            j = len(table)
+            hit = None
+            if j < len(keys) and (j + 1) * pool.block_size <= quantized:  # a full prompt block, packed by this call
+                hit = registry.lookup(layer_idx, keys[j])
+            if hit is not None:
+                pool.retain_page(hit)
+                table.append(hit)
+                shared.append(j)
+            else:
+                table.extend(pool.allocate(1))
+        return shared
+
+    def _register_packed_blocks(self, row: TurboQuantKVRow, pool: TurboQuantLayerPool, layer_idx: int) -> None:
+        """Offer every prompt block of the row that is completely packed by now to later sequences."""
+        keys = self._prefix_keys()
+        registry = self.allocator.packed_prefix_block_pool
+        done = min(row.quantized_length // pool.block_size, len(keys), len(row.block_table))
+        for j in range(self._packed_blocks_registered[layer_idx], done):
+            registry.register(layer_idx, keys[j], row.block_table[j])
+        self._packed_blocks_registered[layer_idx] = max(self._packed_blocks_registered[layer_idx], done)
+
     def _update_turboquant_layer(self, key_states, value_states, layer_idx: int, *, require_dense_cache: bool):
         batch_size, kv_heads, append_length, head_dim = (int(v) for v in key_states.shape)
         self._ensure_batch_size(batch_size)
@@ -498,13 +555,18 @@ class Qwen3DynamicCache:
         missing = sum(1 for row in rows if row is None)
         if missing:
             pool.ensure_slot_capacity(pool.slot_capacity() - len(pool.free_slots) + missing)
+        use_prefix_share = self._prefix_kv_share and batch_size == 1 and self._prompt_token_ids is not None
+        shared_blocks: list[int] = []
         for batch_idx in range(batch_size):
             row = rows[batch_idx]
             if row is None:
                 row = TurboQuantKVRow(bits=self.kv_cache_quant_bits, residual_len=self.kv_cache_residual_len)
                 row._bind(pool, kv_heads=kv_heads, head_dim=head_dim, dtype=key_states.dtype, device=device)
                 rows[batch_idx] = row
-            row._reserve_blocks(row.length + append_length)
+            if use_prefix_share:
+                shared_blocks = self._reserve_shared_packed_blocks(row, pool, layer_idx, row.length + append_length)
+            else:
+                row._reserve_blocks(row.length + append_length)
         slots = [row.slot for row in rows]
         lengths = self.layer_lengths[layer_idx]
         for batch_idx, row in enumerate(rows):
@@ -519,10 +581,19 @@ class Qwen3DynamicCache:
             past_lengths = torch.tensor(past, device=device, dtype=torch.long)
         if append_length > 0:
             table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
+            mask_dev = None
+            if shared_blocks and table_dev is not None:
+                words = np.zeros((1, (int(table_dev.shape[1]) + 31) // 32), dtype=np.uint32)
+                for j in shared_blocks:
+                    words[0, j >> 5] |= np.uint32(1 << (j & 31))
+                mask_dev = torch.from_numpy(words.view(np.int32)).to(device)
             launch_tq_append(pool, key_states, value_states, table_dev, slots, past, slots_dev=slots_dev,
-                             past_dev=past_lengths if state is not None else None, new_lengths_dev=new_lengths)
+                             past_dev=past_lengths if state is not None else None, new_lengths_dev=new_lengths,
+                             shared_blocks=mask_dev)
             if state is not None:
                 state.after_append(lengths)
+            if use_prefix_share:
+                self._register_packed_blocks(rows[0], pool, layer_idx)
         self.seen_tokens = max(self.seen_tokens, max(lengths, default=0))
         if not require_dense_cache:
             return None, None, past_lengths
@@ -758,6 +829,8 @@ class Qwen3DynamicCache:
         batch_size = self.get_batch_size()
         self._prefill_input_ids = None
         self._prompt_token_ids = None
+        self._prompt_prefix_keys = None
+        self._packed_blocks_registered = [0] * self.config.num_hidden_layers
         for layer_idx in range(self.config.num_hidden_layers):
             self.layer_lengths[layer_idx] = [0] * batch_size
             self.page_tables[layer_idx] = [[] for _ in range(batch_size)]

@@ -16,6 +16,8 @@ struct TqAppendParams {
   uint8_t* pages;
   const int32_t* block_table;
   int64_t table_stride;
+  const uint32_t* shared_blocks;  // optional bit mask [batch, mask_stride words]: block already holds these tokens
+  int64_t mask_stride;
   void* window;
   const int64_t* window_slots;
   const int64_t* old_lengths;
@@ -126,6 +128,8 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
       if (lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
       continue;
     }
+    // a block mapped from another sequence with the same prompt prefix already holds exactly these codes
+    if (p.shared_blocks != nullptr && ((p.shared_blocks[(int64_t)b * p.mask_stride + (blk >> 5)] >> (blk & 31)) & 1u)) continue;
     uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
 
     // ---- keys: normalise, rotate, index, residual sign ----------------------------------------------------------
@@ -229,7 +233,7 @@ extern "C" int anna_tq_page_layout(int head_dim, int bits, int block_size, int d
 
 extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                               int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table,
-                              int64_t table_stride, void* window, const int64_t* window_slots,
+                              int64_t table_stride, const uint32_t* shared_blocks, int64_t mask_stride, void* window, const int64_t* window_slots,
                               const int64_t* old_lengths, int64_t* new_lengths, const float* signs1,
                               const float* signs2, const float* centroids, const float* boundaries, int batch, int kv_heads,
                               int new_tokens, int head_dim, int block_size, int residual_len, int bits,
@@ -253,6 +257,10 @@ extern "C" int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_s
   p.k_new = k_new; p.v_new = v_new;
   p.stride_b = kn_stride_b; p.stride_h = kn_stride_h; p.stride_t = kn_stride_t;
   p.pages = packed_pages; p.block_table = block_table; p.table_stride = table_stride;
+  p.shared_blocks = shared_blocks; p.mask_stride = mask_stride;
+  ANNA_REQUIRE(shared_blocks == nullptr || mask_stride * 32 >= max_blocks,
+               "anna_tq_append: shared-block mask of %lld words per row does not cover %lld blocks", (long long)mask_stride,
+               (long long)max_blocks);
   p.window = window; p.window_slots = window_slots; p.old_lengths = old_lengths; p.new_lengths = new_lengths;
   p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids; p.boundaries = boundaries;
   p.batch = batch; p.kv_heads = kv_heads; p.new_tokens = new_tokens; p.block_size = block_size;

@@ -171,9 +171,9 @@ class Qwen3PagedLayerAllocator:
 class TurboQuantLayerPool:
     """Packed page pool + window rings of one TurboQuant layer (geometry fixed by the first append)."""
 
-    def __init__(self, block_size: int) -> None:
+    def __init__(self, block_size: int, *, on_page_freed: Callable[[int], None] | None = None) -> None:
         self.block_size = int(block_size)
-        self._book = _PageBook()
+        self._book = _PageBook(on_page_freed)
         self.packed_pages: torch.Tensor | None = None  # uint8 [P, Hkv, chunk_bytes]
         self.window: torch.Tensor | None = None        # dtype [slots, 2, Hkv, R, D]
         self.free_slots: list[int] = []
@@ -235,6 +235,12 @@ class TurboQuantLayerPool:
     def release_pages(self, page_ids: list[int]) -> None:
         for page_id in reversed(page_ids):
             self._book.release(page_id)
+
+    def retain_page(self, page_id: int) -> None:
+        """One more owner of a packed page (a sequence that maps it for a shared prompt prefix)."""
+        if page_id < 0 or page_id >= self.capacity() or self._book.refcount.get(page_id, 0) <= 0:
+            raise ValueError(f"retain_page: page {page_id} is not a live packed page (capacity {self.capacity()}).")
+        self._book.retain(page_id)
 
     def slot_capacity(self) -> int:
         return 0 if self.window is None else int(self.window.shape[0])

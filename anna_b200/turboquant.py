@@ -44,11 +44,13 @@ def _require_cuda(tensor: torch.Tensor, what: str) -> None:
 def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_states: torch.Tensor,
                      table_dev: torch.Tensor | None, slots: list[int], past: list[int], *,
                      slots_dev: torch.Tensor | None = None, past_dev: torch.Tensor | None = None,
-                     new_lengths_dev: torch.Tensor | None = None) -> None:
+                     new_lengths_dev: torch.Tensor | None = None, shared_blocks: torch.Tensor | None = None) -> None:
     """Append ``[B, Hkv, T, D]`` to B rows of one layer: ring update + quantize-on-overflow + page scatter.
 
     ``slots_dev`` / ``past_dev`` (optional, int64 ``[B]`` on the device) are copies of ``slots`` / ``past`` that the
-    caller already holds there; ``new_lengths_dev`` (optional) receives ``past + T`` from the kernel."""
+    caller already holds there; ``new_lengths_dev`` (optional) receives ``past + T`` from the kernel;
+    ``shared_blocks`` (optional, int32 ``[B, words]`` bit mask on the device) marks blocks whose pages already hold
+    their tokens' codes (mapped from a sequence with the same prompt prefix)."""
     _require_cuda(key_states, "TurboQuant append")
     key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
     if value_states.stride() != key_states.stride():
@@ -66,7 +68,8 @@ def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_
     with on_device(device):
         _lib.check(_lib.lib().anna_tq_append(
             ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
-            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(slots_dev), ptr(past_dev),
+            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(shared_blocks),
+            0 if shared_blocks is None else shared_blocks.stride(0), ptr(pool.window), ptr(slots_dev), ptr(past_dev),
             ptr(new_lengths_dev), ptr(tables.signs1), ptr(tables.signs2), ptr(tables.centroids), ptr(tables.boundaries), batch, kv_heads,
             tokens, dim, pool.block_size, pool.residual_len, pool.bits, pool.value_group, pool.capacity(), max_blocks,
             dtype_code(key_states.dtype), ptr(pool.status), stream_ptr(device)), "anna_tq_append")

@@ -172,12 +172,15 @@ int anna_tq_page_layout(int head_dim, int bits, int block_size, int dtype, int v
  *   k_new, v_new  [B, Hkv, T, D] element strides (kn_stride_b, kn_stride_h, kn_stride_t)
  *   old_lengths   int64 [B] (lengths before this call);  window_slots int64 [B] (ring index of each row)
  *   new_lengths   optional int64 [B] (may be NULL, must not alias old_lengths): receives old_lengths[b] + T
+ *   shared_blocks optional uint32 [B, mask_stride] bit mask (may be NULL): bit j of row b set = block j of that row is a
+ *                 page mapped from another sequence with the same prompt prefix and already holds these tokens' codes,
+ *                 so its tokens are not quantized again (extends the prefix sharing of ops.py:779-857 to packed pages)
  *   signs1, signs2  float32 [D] (+1 / -1): rotation and QJL sign vectors;  centroids float32 [2^(bits-1)];
  *   boundaries    float32 [2^(bits-1) - 1]
  */
 int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, int64_t kn_stride_h,
                    int64_t kn_stride_t, uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                   void* window, const int64_t* window_slots, const int64_t* old_lengths, int64_t* new_lengths,
+                   const uint32_t* shared_blocks, int64_t mask_stride, void* window, const int64_t* window_slots, const int64_t* old_lengths, int64_t* new_lengths,
                    const float* signs1, const float* signs2, const float* centroids, const float* boundaries,
                    int batch, int kv_heads, int new_tokens, int head_dim, int block_size, int residual_len, int bits,
                    int value_group, int64_t num_pages, int64_t max_blocks, int dtype, int32_t* status,

@@ -117,3 +117,53 @@ def test_turboquant_dense_view_and_lifecycle(cuda_device):
     pair.cache.release()
     assert pool.used_pages() == 0
     assert pair.cache.allocator.trim() > 0 and pool.packed_pages is None
+
+
+def test_packed_prefix_sharing_gives_identical_decode(cuda_device):
+    """A sequence that maps the packed pages of a shared prompt prefix decodes bit-identically to one that packed
+    everything itself, also after the sequence that first wrote those pages is gone."""
+    torch.manual_seed(8)
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=16)
+    heads, kv_heads, dim, residual = 8, 2, 128, 8
+    prompt = torch.arange(1000, 1100).view(1, -1)                     # 100 tokens: 92 packed = 5 full blocks + 12
+    k = torch.randn(1, kv_heads, 100, dim, device=cuda_device, dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    k_tail = torch.randn(1, kv_heads, 40, dim, device=cuda_device, dtype=torch.bfloat16)  # a different continuation
+    v_tail = torch.randn_like(k_tail)
+
+    def run(allocator, tokens, keys, values):
+        cache = Qwen3DynamicCache(config, allocator=allocator, kv_cache_quantization="turboquant",
+                                  kv_cache_quant_bits=4, kv_cache_residual_len=residual)
+        cache.set_prompt_token_ids(tokens)
+        cache.update(keys, values, 0, require_dense_cache=False)
+        return cache
+
+    shared_alloc = Qwen3PageAllocator(config)
+    writer = run(shared_alloc, prompt, k, v)
+    longer_prompt = torch.cat((prompt, torch.arange(5000, 5040).view(1, -1)), dim=1)
+    k_long, v_long = torch.cat((k, k_tail), dim=2), torch.cat((v, v_tail), dim=2)
+    reader = run(shared_alloc, longer_prompt, k_long, v_long)
+    table_w = writer.turboquant_rows[0][0].block_table
+    table_r = reader.turboquant_rows[0][0].block_table
+    assert table_r[:5] == table_w[:5] and not set(table_r[5:]) & set(table_w)
+    alone = run(Qwen3PageAllocator(config), longer_prompt, k_long, v_long)   # nothing to share with
+    query = torch.randn(1, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+
+    def decode(cache):
+        return cache.turboquant_single_token_decode_attention(0, query, scaling=dim ** -0.5,
+                                                              num_key_value_groups=heads // kv_heads)
+
+    want = decode(alone)
+    assert torch.equal(decode(reader), want)
+    dense_alone = alone._gather_layer_cache(0)
+    dense_reader = reader._gather_layer_cache(0)
+    assert torch.equal(dense_reader[0], dense_alone[0]) and torch.equal(dense_reader[1], dense_alone[1])
+    writer.release()
+    assert torch.equal(decode(reader), want)
+    step_k = torch.randn(1, kv_heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    for cache in (reader, alone):
+        cache.update(step_k, step_k, 0, require_dense_cache=False)
+    assert torch.equal(decode(reader), decode(alone))
+    reader.release()
+    assert shared_alloc.turboquant_layers[0].used_pages() == 0
+    assert not shared_alloc.packed_prefix_block_pool._page_of

@@ -272,3 +272,58 @@ def test_quantizer_tables_agree_with_oracle():
     root = Path(__file__).resolve().parent.parent
     assert (root / "oracle" / "tq_codebooks.json").read_text() == \
         (root / "anna_b200" / "data" / "tq_codebooks.json").read_text()
+
+
+def test_packed_prefix_blocks_are_shared_between_sequences(launches):
+    """Two single-row TurboQuant caches with the same prompt on one allocator: the second maps the packed pages of the
+    shared prefix by reference (and tells the append launch to leave them alone); pages live until their last owner
+    lets go and the registry forgets a page the moment it is freed."""
+    recorded = []
+    original = cache_module.launch_tq_append
+
+    def recording_append(pool, key_states, value_states, table_dev, slots, past, **device_copies):
+        recorded.append(device_copies.get("shared_blocks"))
+        return original(pool, key_states, value_states, table_dev, slots, past, **device_copies)
+
+    cache_module.launch_tq_append = recording_append
+    try:
+        config = _config(block=4)
+        allocator = Qwen3PageAllocator(config)
+        prompt = torch.arange(100, 130).view(1, -1)  # 30 tokens
+
+        def prefill(tokens):
+            cache = Qwen3DynamicCache(config, allocator=allocator, kv_cache_quantization="turboquant",
+                                      kv_cache_quant_bits=4, kv_cache_residual_len=6)
+            cache.set_prompt_token_ids(tokens)
+            states = torch.zeros(1, 2, int(tokens.shape[1]), 32, dtype=torch.bfloat16)
+            cache.update(states, states, 0, require_dense_cache=False)
+            return cache
+
+        first = prefill(prompt)
+        table_a = list(first.turboquant_rows[0][0].block_table)
+        assert len(table_a) == 6 and recorded[-1] is None             # 24 packed tokens = 6 blocks, nothing shared
+        second = prefill(prompt)
+        table_b = second.turboquant_rows[0][0].block_table
+        assert table_b == table_a                                      # all six full blocks mapped by reference
+        mask = recorded[-1]
+        assert mask is not None and int(mask.view(-1)[0]) == 0b111111
+        other = prefill(torch.cat((prompt[:, :9], prompt[:, 9:] + 1000), dim=1))
+        table_c = other.turboquant_rows[0][0].block_table
+        assert table_c[:2] == table_a[:2] and not set(table_c[2:]) & set(table_a)   # prefix of 8 tokens = 2 blocks
+        pool = allocator.turboquant_layers[0]
+        assert pool.used_pages() == 6 + 4
+        # growth of one sequence past the prompt never touches the shared pages
+        step = torch.zeros(1, 2, 1, 32, dtype=torch.bfloat16)
+        for _ in range(5):
+            second.update(step, step, 0, require_dense_cache=False)
+        assert second.turboquant_rows[0][0].block_table[:6] == table_a
+        first.release()
+        assert pool.used_pages() == 6 + 4 + 2          # second still owns the six, plus its two new blocks
+        third = prefill(prompt)
+        assert third.turboquant_rows[0][0].block_table == table_a
+        for cache in (second, third, other):
+            cache.release()
+        assert pool.used_pages() == 0
+        assert not allocator.packed_prefix_block_pool._page_of
+    finally:
+        cache_module.launch_tq_append = original
