@@ -66,6 +66,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                   c_i64, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32,
                                                   c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_i32, c_i32, c_f32,
                                                   c_i32, c_ptr]),
+    "anna_tq_gather_dense": (c_i32, [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64,
+                                     c_i64, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i64,
+                                     c_i32, c_ptr]),
     "anna_tq_tensor_row_bytes": (c_i32, [c_i32, c_i32]),
     "anna_tq_tensor_quantize": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i32, c_i32, c_i32, c_i32,
                                         c_ptr, c_ptr, c_i32, c_ptr]),

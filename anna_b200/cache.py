@@ -28,7 +28,8 @@ from . import _lib
 from .fused_ops import MetadataUploader, dtype_code, on_device, ptr, stream_ptr
 from .pools import Qwen3PagedLayerAllocator, TurboQuantLayerPool
 from .prefix_block_cache import PrefixBlockPool
-from .turboquant import VALID_KV_CACHE_QUANT_BITS, TurboQuantKVRow, launch_tq_append, launch_tq_decode
+from .turboquant import (VALID_KV_CACHE_QUANT_BITS, TurboQuantKVRow, launch_tq_append, launch_tq_decode,
+                         launch_tq_gather_dense)
 
 
 @dataclass
@@ -676,14 +677,12 @@ class Qwen3DynamicCache:
             rows = self.turboquant_rows[layer_idx]
             if any(row is None for row in rows):
                 raise RuntimeError(f"TurboQuant cache row for layer {layer_idx} is missing.")
-            parts = [row.materialize() for row in rows]
-            device, dtype = parts[0][0].device, parts[0][0].dtype
-            keys = torch.zeros((batch_size, parts[0][0].shape[0], max_length, parts[0][0].shape[2]), device=device,
-                               dtype=dtype)
-            values = torch.zeros_like(keys)
-            for idx, (row_k, row_v) in enumerate(parts):
-                keys[idx, :, : row_k.shape[1]].copy_(row_k)
-                values[idx, :, : row_v.shape[1]].copy_(row_v)
+            pool = self._tq_pool(layer_idx)
+            device = pool.device
+            assert device is not None
+            table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
+            keys, values = launch_tq_gather_dense(pool, table_dev, [row.slot for row in rows], list(lengths),
+                                                  max_length)
             return keys, values, visible.to(device)
         layer = self.allocator.layers[layer_idx]
         if layer.key_pages is None or layer.value_pages is None or max_length <= 0:

@@ -1,4 +1,6 @@
-// De-quantize packed TurboQuant pages into dense keys / values in the cache dtype (one warp per token-head).
+// De-quantize packed TurboQuant pages into dense keys / values in the cache dtype (one warp per token-head); with the
+// window ring given, the same launch also copies the un-quantized tail of every row and zero-pads up to max_len, i.e.
+// it produces the whole dense view of a batch of rows.
 #include "tq_common.cuh"
 
 namespace anna {
@@ -17,6 +19,11 @@ struct TqMaterializeParams {
   int kv_heads, block_size, value_group;
   int64_t num_pages, max_blocks, max_quantized_len;
   anna_tq_layout layout;
+  // optional dense tail: window ring [slots, 2, Hkv, R, D], ring slot and total length per row
+  const void* window;
+  const int64_t* window_slots;
+  const int64_t* lengths;
+  int residual_len;
 };
 
 constexpr int kMaterializeWarps = 4;
@@ -34,14 +41,50 @@ __global__ void __launch_bounds__(kMaterializeWarps * 32) tq_materialize_kernel(
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int64_t t = (int64_t)blockIdx.x * kMaterializeWarps + warp;
-  int64_t lq = p.quantized_lengths[b];
-  lq = min(lq, p.max_quantized_len);
-  if (t >= lq) return;
+  int64_t lq;
+  if (p.window != nullptr) {
+    // whole dense view: [0, len - R) from the pages, [len - R, len) from the ring, [len, max) zeros
+    if (t >= p.max_quantized_len) return;  // (max_quantized_len is the padded length in this mode)
+    const int64_t len = max((int64_t)0, min(p.lengths[b], p.max_quantized_len));
+    lq = len > p.residual_len ? len - p.residual_len : 0;
+    if (t >= lq) {
+      const int64_t off = (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h + t * p.out_stride_t + lane * E;
+      T* kdst = reinterpret_cast<T*>(p.key_out) + off;
+      T* vdst = reinterpret_cast<T*>(p.value_out) + off;
+      if (t < len) {
+        const int64_t slot = p.window_slots[b];
+        const int64_t rs = t % p.residual_len;
+        const T* ring = reinterpret_cast<const T*>(p.window);
+        lane_copy<T, E>(ring + (((slot * 2 + 0) * p.kv_heads + h) * p.residual_len + rs) * D + lane * E, kdst);
+        lane_copy<T, E>(ring + (((slot * 2 + 1) * p.kv_heads + h) * p.residual_len + rs) * D + lane * E, vdst);
+      } else {
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          kdst[j] = ElemTraits<T>::from_float(0.0f);
+          vdst[j] = ElemTraits<T>::from_float(0.0f);
+        }
+      }
+      return;
+    }
+  } else {
+    lq = min(p.quantized_lengths[b], p.max_quantized_len);
+    if (t >= lq) return;
+  }
   const int64_t blk = t / p.block_size;
   const int tok = (int)(t % p.block_size);
   int32_t pid = -1;
   if (blk < p.max_blocks) pid = p.block_table[(int64_t)b * p.table_stride + blk];
-  if (pid < 0 || pid >= p.num_pages) return;
+  if (pid < 0 || pid >= p.num_pages) {
+    if (p.window != nullptr) {  // the dense view has no holes: an unmapped block reads as zeros
+      const int64_t off = (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h + t * p.out_stride_t + lane * E;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        (reinterpret_cast<T*>(p.key_out) + off)[j] = ElemTraits<T>::from_float(0.0f);
+        (reinterpret_cast<T*>(p.value_out) + off)[j] = ElemTraits<T>::from_float(0.0f);
+      }
+    }
+    return;
+  }
   const uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
   const int e0 = lane * E;
 
@@ -107,6 +150,48 @@ __global__ void __launch_bounds__(kMaterializeWarps * 32) tq_materialize_kernel(
 
 using namespace anna;
 
+static int launch_materialize(TqMaterializeParams p, int batch, int kv_heads, int head_dim, int block_size, int bits,
+                              int value_group, int dtype, cudaStream_t stream) {
+  if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, &p.layout))
+    return set_error(ANNA_ERR_INVALID, "TurboQuant materialize: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim,
+                     bits, block_size, value_group);
+  dim3 grid((unsigned)((p.max_quantized_len + kMaterializeWarps - 1) / kMaterializeWarps), (unsigned)kv_heads,
+            (unsigned)batch);
+  return ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
+    return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
+      return ANNA_DISPATCH_TQ_BITS(bits, BITS, [&]() -> int {
+        tq_materialize_kernel<T, D, BITS><<<grid, kMaterializeWarps * 32, 0, stream>>>(p);
+        return check_launch("tq_materialize_kernel");
+      });
+    });
+  });
+}
+
+extern "C" int anna_tq_gather_dense(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                                    const void* window, const int64_t* window_slots, const int64_t* lengths,
+                                    const float* signs1, const float* signs2, const float* centroids, void* key_out,
+                                    void* value_out, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
+                                    int batch, int kv_heads, int head_dim, int block_size, int residual_len, int bits,
+                                    int value_group, int64_t num_pages, int64_t max_blocks, int64_t max_len, int dtype,
+                                    anna_stream_t stream) {
+  ANNA_REQUIRE(window && window_slots && lengths && signs1 && signs2 && centroids && key_out && value_out,
+               "anna_tq_gather_dense: null pointer argument");
+  ANNA_REQUIRE(packed_pages != nullptr || num_pages == 0, "anna_tq_gather_dense: null page pool with num_pages > 0");
+  ANNA_REQUIRE(block_table != nullptr || max_blocks == 0, "anna_tq_gather_dense: null block table with max_blocks > 0");
+  ANNA_REQUIRE(batch > 0 && kv_heads > 0 && block_size >= 1 && residual_len >= 1 && max_len >= 0,
+               "anna_tq_gather_dense: sizes must be positive");
+  if (max_len == 0) return ANNA_OK;
+  TqMaterializeParams p{};
+  p.pages = packed_pages; p.block_table = block_table; p.table_stride = table_stride;
+  p.signs1 = signs1; p.signs2 = signs2; p.centroids = centroids;
+  p.key_out = key_out; p.value_out = value_out;
+  p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_t = out_stride_t;
+  p.kv_heads = kv_heads; p.block_size = block_size; p.value_group = value_group;
+  p.num_pages = num_pages; p.max_blocks = max_blocks; p.max_quantized_len = max_len;
+  p.window = window; p.window_slots = window_slots; p.lengths = lengths; p.residual_len = residual_len;
+  return launch_materialize(p, batch, kv_heads, head_dim, block_size, bits, value_group, dtype, (cudaStream_t)stream);
+}
+
 extern "C" int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
                                    const int64_t* quantized_lengths, const float* signs1, const float* signs2,
                                    const float* centroids, void* key_out, void* value_out, int64_t out_stride_b,
@@ -125,17 +210,5 @@ extern "C" int anna_tq_materialize(const uint8_t* packed_pages, const int32_t* b
   p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_t = out_stride_t;
   p.kv_heads = kv_heads; p.block_size = block_size; p.value_group = value_group;
   p.num_pages = num_pages; p.max_blocks = max_blocks; p.max_quantized_len = max_quantized_len;
-  if (!tq_make_layout(head_dim, bits, block_size, dtype_bytes_of(dtype), value_group, &p.layout))
-    return set_error(ANNA_ERR_INVALID, "anna_tq_materialize: unsupported geometry D=%d bits=%d S=%d group=%d", head_dim,
-                     bits, block_size, value_group);
-  dim3 grid((unsigned)((max_quantized_len + kMaterializeWarps - 1) / kMaterializeWarps), (unsigned)kv_heads,
-            (unsigned)batch);
-  return ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
-    return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
-      return ANNA_DISPATCH_TQ_BITS(bits, BITS, [&]() -> int {
-        tq_materialize_kernel<T, D, BITS><<<grid, kMaterializeWarps * 32, 0, (cudaStream_t)stream>>>(p);
-        return check_launch("tq_materialize_kernel");
-      });
-    });
-  });
+  return launch_materialize(p, batch, kv_heads, head_dim, block_size, bits, value_group, dtype, (cudaStream_t)stream);
 }

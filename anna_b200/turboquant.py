@@ -134,6 +134,29 @@ def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, qu
             "anna_tq_materialize")
 
 
+def launch_tq_gather_dense(pool: TurboQuantLayerPool, table_dev: torch.Tensor | None, slots: list[int], lengths: list[int],
+                           max_len: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Dense ``[B, Hkv, max_len, D]`` keys and values of B rows of one layer in one launch: de-quantized prefix, window
+    tokens, zero padding."""
+    assert pool.window is not None and pool.device is not None and pool.dtype is not None
+    device = pool.device
+    batch = len(lengths)
+    tables = key_tables(head_dim=pool.head_dim, bits=pool.bits, device=device)
+    meta = MetadataUploader.for_device(device).upload([lengths, slots])
+    keys = torch.empty((batch, pool.kv_heads, max_len, pool.head_dim), dtype=pool.dtype, device=device)
+    values = torch.empty_like(keys)
+    table_stride = 0 if table_dev is None else table_dev.stride(0)
+    max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
+    with on_device(device):
+        _lib.check(_lib.lib().anna_tq_gather_dense(
+            ptr(pool.packed_pages), ptr(table_dev), table_stride, ptr(pool.window), ptr(meta[1]), ptr(meta[0]),
+            ptr(tables.signs1), ptr(tables.signs2), ptr(tables.centroids), ptr(keys), ptr(values), keys.stride(0),
+            keys.stride(1), keys.stride(2), batch, pool.kv_heads, pool.head_dim, pool.block_size, pool.residual_len,
+            pool.bits, pool.value_group, pool.capacity(), max_blocks, int(max_len), dtype_code(pool.dtype),
+            stream_ptr(device)), "anna_tq_gather_dense")
+    return keys, values
+
+
 class TurboQuantTensorRow:
     """History of one tensor (the K or the V of one sequence) with MSE-only TurboQuant codes for everything older than
     the newest ``residual_len`` tokens; mirrors ``TurboQuantTensorRow`` of the Gemma4 runtime

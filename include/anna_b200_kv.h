@@ -249,6 +249,20 @@ int anna_gqa_decode_turboquant_values(const void* q, int64_t q_stride_b, int64_t
                                       int value_group, float scaling, int dtype, anna_stream_t stream);
 
 /*
+ * Dense view of a batch of TurboQuant rows in one launch: keys / values [B, Hkv, max_len, D] in the cache dtype with
+ * the de-quantized prefix, then the un-quantized window tokens (read from the ring), then zeros up to max_len.
+ * Batched form of Qwen3DynamicCache._gather_layer_cache for quantized layers (src/anna/model/ops.py:931-1006, which
+ * calls TurboQuantKVRow.materialize row by row, turboquant.py:1142-1179, and pads).
+ *   lengths int64 [B] (total tokens per row);  window_slots int64 [B];  other arguments as anna_tq_paged_decode
+ */
+int anna_tq_gather_dense(const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                         const void* window, const int64_t* window_slots, const int64_t* lengths, const float* signs1,
+                         const float* signs2, const float* centroids, void* key_out, void* value_out,
+                         int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads,
+                         int head_dim, int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
+                         int64_t max_blocks, int64_t max_len, int dtype, anna_stream_t stream);
+
+/*
  * MSE-only TurboQuant codes for a plain tensor row: what TurboQuantTensorRow (src/anna/model/turboquant.py:335-477, the
  * K / V history rows of the Gemma4 runtime) asks of TurboQuantMSE(dim, bits, seed=42).quantize / .dequantize
  * (turboquant.py:392-395, :415-418).  Every [head_dim] vector becomes `bits`-bit Lloyd-Max indices of its normalised,
