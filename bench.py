@@ -320,7 +320,7 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
                    "per_rank_batch": batch, "parallelism": f"sequence-sharded x{dist.world}, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / args.steps * 1e3},
-        "gpu_launches": 3 * args.steps,
+        "gpu_launches": 2 * args.steps,  # per step: paged_kv_write_kernel + the decode kernel (merge fused in its tail)
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": int(algo_bytes * NCU_TRAFFIC_RATIO), "traffic_source": NCU_TRAFFIC_SOURCE,
@@ -424,6 +424,8 @@ def run_kvhead_variant(args, dist: Dist, device) -> dict:
                    "kv_heads_per_rank": local_kv, "q_heads_per_rank": local_q,
                    "parallelism": f"kv-head-sharded x{dist.world}, one all-gather of [B, Hq/N, D] per step",
                    "l2_policy": f"{per_rank_bytes / 1e6:.0f} MB of packed KV per rank and step exceed the 126 MB L2"},
+        # per step: tq_append, tq_prepare_queries, tq_window_split_mma, tq_decode_split_mma (+ NCCL's all-gather and
+        # one strided copy, which are library kernels and not counted)
         "gpu_launches": 4 * args.steps, "clocks": clocks,
         "self_check": {"max_abs_vs_unsharded": check_err, "rows": check_rows, "context": check_tokens},
         "roofline": {"bound": "hbm (issue-bound today)", "achieved": achieved, "peak": peak, "unit": "GB/s",
