@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
 
 One step = one pass of the hot path over one batch: append one token per sequence into the paged cache, then
-single-token GQA decode attention for every sequence.  The headline workload is the second BASELINE configuration
+single-token GQA decode attention for every sequence.  The headline workload is the second benchmark configuration
 (un-quantized paged bf16 GQA decode: 32 sequences, 32 query / 8 KV heads, head_dim 128, page size 16, contexts
 uniform in [1024, 8192], block tables a seeded random permutation of a shared page pool, N(0,1) data).  With N > 1
 (one process per GPU under torchrun) every rank runs its own batch of the same shape (weak scaling, no data-path

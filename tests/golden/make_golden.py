@@ -32,7 +32,7 @@ def digest(array: np.ndarray) -> str:
 
 
 def config1_inputs(seed: int = 1):
-    """BASELINE config 1: B=2, Hkv=2, D=128, K,V ~ N(0,1) with 4 outlier channels per head scaled x8."""
+    """Benchmark configuration 1: B=2, Hkv=2, D=128, K,V ~ N(0,1) with 4 outlier channels per head scaled x8."""
     from tests.helpers import outlier_kv
 
     gen = torch.Generator().manual_seed(seed)
@@ -47,7 +47,7 @@ def config1_inputs(seed: int = 1):
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of funkpopo/Anna to import from")
     args = parser.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
 

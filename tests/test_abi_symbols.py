@@ -94,7 +94,7 @@ def test_page_layout_matches_oracle_layout(library):
                     for field in ("key_bytes", "value_bytes", "groups", "off_kcodes", "off_knorm", "off_krnorm",
                                   "off_vdata", "off_vscale", "off_vzero", "chunk_bytes"):
                         assert got[field] == getattr(want, field), (dim, bits, block, field)
-    # algorithmic bytes per token-head of the BASELINE configs (D*b/8 + 8 for keys, D*sb/8 + 2*(D/32)*e for values)
+    # algorithmic bytes per token-head of the benchmark configurations (D*b/8 + 8 for keys, D*sb/8 + 2*(D/32)*e for values)
     assert oracle.PackedPageLayout(128, 4, 16, 2, 32).bytes_per_token() == 152
     assert oracle.PackedPageLayout(256, 2, 16, 2, 32).bytes_per_token() == 168
     assert oracle.PackedPageLayout(128, 3, 16, 2, 32).bytes_per_token() == 136

@@ -30,7 +30,7 @@ def test_append_is_bit_exact_small_window(cuda_device, dtype, bits, head_dim):
 
 
 def test_append_config1_prefill_and_decode_steps(cuda_device):
-    """BASELINE config 1: fp32, 8q/2kv heads, D=128, S=16, 4-bit, R=128; prefill 512 then 64 single-token appends."""
+    """Benchmark configuration 1: fp32, 8q/2kv heads, D=128, S=16, 4-bit, R=128; prefill 512 then 64 single-token appends."""
     pair = TqPair(device=cuda_device, batch=2, kv_heads=2, head_dim=128, bits=4, residual_len=128, block_size=16,
                   dtype=torch.float32)
     _run_schedule(pair, [512] + [1] * 64, seed=1)
