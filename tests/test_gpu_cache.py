@@ -167,3 +167,31 @@ def test_packed_prefix_sharing_gives_identical_decode(cuda_device):
     reader.release()
     assert shared_alloc.turboquant_layers[0].used_pages() == 0
     assert not shared_alloc.packed_prefix_block_pool._page_of
+
+
+def test_turboquant_batched_dense_view_matches_row_materialize(cuda_device):
+    """The one-launch dense view of a ragged batch (shorter than the window, exactly the window, many pages) equals each
+    row's own materialize() and is zero past the row's length, whatever the pages held before."""
+    torch.manual_seed(4)
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=16)
+    allocator = Qwen3PageAllocator(config)
+    lengths = [3, 8, 9, 70, 200]
+    kv_heads, dim, residual = 2, 128, 8
+    caches, inputs = [], []
+    for n in lengths:
+        cache = Qwen3DynamicCache(config, allocator=allocator, kv_cache_quantization="turboquant",
+                                  kv_cache_quant_bits=3, kv_cache_residual_len=residual)
+        k = torch.randn(1, kv_heads, n, dim, device=cuda_device, dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        cache.update(k, v, 0, require_dense_cache=False)
+        caches.append(cache)
+        inputs.append((k, v))
+    stacked = Qwen3DynamicCache.stack(caches, config)
+    keys, values, visible = stacked._gather_layer_cache(0)
+    assert keys.shape == (len(lengths), kv_heads, max(lengths), dim) and visible.tolist() == lengths
+    for b, n in enumerate(lengths):
+        row_k, row_v = stacked.turboquant_rows[0][b].materialize()
+        assert torch.equal(keys[b, :, :n], row_k) and torch.equal(values[b, :, :n], row_v)
+        assert torch.count_nonzero(keys[b, :, n:]) == 0 and torch.count_nonzero(values[b, :, n:]) == 0
+        tail = min(n, residual)
+        assert torch.equal(keys[b, :, n - tail:n], inputs[b][0][0, :, n - tail:]) and torch.isfinite(keys[b]).all()

@@ -160,3 +160,20 @@ def test_bf16_rounding_matches_torch():
     np.testing.assert_array_equal(oracle.round_bf16(x.numpy()), x.to(torch.bfloat16).float().numpy())
     for value in x[:64].tolist():
         assert oracle.lib().tqo_f32_to_f16(value) == int(torch.tensor(value).half().view(torch.int16).item()) & 0xFFFF
+
+
+@pytest.mark.parametrize("dim,bits", [(64, 2), (128, 3), (256, 4), (512, 4)])
+def test_mse_variant_round_trip_quality(dim, bits):
+    """The MSE-only quantizer of tensor rows (turboquant.py:75-82, :392-418): `bits` index bits, no sign plane; the
+    reconstruction error of unit-scale data stays under the reference's own bound for this row type (< 0.5,
+    tests/test_gemma4_text_runtime.py:339-340) and shrinks as bits grow."""
+    rng = np.random.default_rng(dim + bits)
+    x = rng.standard_normal((64, dim)).astype(np.float32)
+    idx, sign, norms, rnorms = oracle.quantize_keys(x, bits, "mse")
+    assert sign is None and rnorms is None and idx.max() < (1 << bits) and idx.dtype == np.uint8
+    np.testing.assert_allclose(norms, np.linalg.norm(x, axis=-1), rtol=1e-5)
+    recon = oracle.dequantize_keys(idx, None, norms, None, bits, "mse")
+    mse = float(((recon - x) ** 2).mean())
+    assert mse < 0.5
+    coarse = oracle.dequantize_keys(*(lambda r: (r[0], None, r[2], None))(oracle.quantize_keys(x, 2, "mse")), 2, "mse")
+    assert mse <= float(((coarse - x) ** 2).mean()) + 1e-6
