@@ -195,6 +195,7 @@ class Qwen3DynamicCache:
         self.turboquant_rows: list[list[TurboQuantKVRow | None]] = [[None] * batch_size for _ in range(layers)]
         self.page_table_caches: list[torch.Tensor | None] = [None] * layers
         self.page_table_capacities: list[int] = [0] * layers
+        self._table_host: list[torch.Tensor | None] = [None] * layers     # host mirror of page_table_caches
         self._table_rows_synced: list[list[int] | None] = [None] * layers  # blocks already on the device per row
         self._table_blocks_total: list[int] = [-1] * layers                # sum of table lengths at the last sync
         self._dev_lengths: list[_DeviceLengths | None] = [None] * layers  # device mirror of layer_lengths
@@ -303,6 +304,7 @@ class Qwen3DynamicCache:
             self.page_table_caches[layer_idx] = None
             self.page_table_capacities[layer_idx] = 0
             self._table_rows_synced[layer_idx] = None
+            self._table_host[layer_idx] = None
             self._table_blocks_total[layer_idx] = -1
             return None
         buffer = self.page_table_caches[layer_idx]
@@ -313,32 +315,38 @@ class Qwen3DynamicCache:
         if (buffer is None or buffer.shape[0] != batch_size or buffer.device != device
                 or buffer.shape[1] < required or synced is None):
             capacity = max(required, max(1, self.page_table_capacities[layer_idx] * 2))
-            host = np.full((batch_size, capacity), -1, dtype=np.int32)
+            # host mirror of the device table; pinned, so that patches go up as asynchronous copies
+            mirror = torch.full((batch_size, capacity), -1, dtype=torch.int32)
+            if device.type == "cuda":
+                mirror = mirror.pin_memory()
+            host = mirror.numpy()
             for row_idx, table in enumerate(tables):
                 if table:
                     host[row_idx, : len(table)] = table
-            buffer = torch.from_numpy(host).to(device)
+            buffer = torch.empty((batch_size, capacity), dtype=torch.int32, device=device)
+            buffer.copy_(mirror, non_blocking=True)
             self.page_table_caches[layer_idx] = buffer
             self.page_table_capacities[layer_idx] = capacity
+            self._table_host[layer_idx] = mirror
             self._table_rows_synced[layer_idx] = [len(t) for t in tables]
             self._table_blocks_total[layer_idx] = total
             return buffer[:, :required]
-        flat_index: list[int] = []
-        flat_value: list[int] = []
-        stride = int(buffer.shape[1])
+        # Patch: new entries go into the mirror row by row, then one strided copy moves the column range that changed.
+        # Entries are write-once while a row lives, so a copy that runs late can only carry values that a later patch
+        # would upload anyway.
+        mirror = self._table_host[layer_idx]
+        host = mirror.numpy()
+        lo, hi = None, 0
         for row_idx, table in enumerate(tables):
             have = synced[row_idx]
-            if len(table) > have:
-                flat_index.extend(range(row_idx * stride + have, row_idx * stride + len(table)))
-                flat_value.extend(table[have:])
-                synced[row_idx] = len(table)
-        if flat_index:
-            if device.type == "cuda":
-                patch = MetadataUploader.for_device(device).upload([flat_index, flat_value])
-                buffer.view(-1).index_copy_(0, patch[0], patch[1].to(torch.int32))
-            else:
-                index = torch.tensor(flat_index, dtype=torch.long, device=device)
-                buffer.view(-1).index_copy_(0, index, _i32(flat_value, device))
+            n = len(table)
+            if n > have:
+                host[row_idx, have:n] = table[have:]
+                synced[row_idx] = n
+                lo = have if lo is None or have < lo else lo
+                hi = n if n > hi else hi
+        if lo is not None:
+            buffer[:, lo:hi].copy_(mirror[:, lo:hi], non_blocking=True)
         self._table_blocks_total[layer_idx] = total
         return buffer[:, :required]
 
@@ -839,6 +847,7 @@ class Qwen3DynamicCache:
             self.page_table_caches[layer_idx] = None
             self.page_table_capacities[layer_idx] = 0
             self._table_rows_synced[layer_idx] = None
+            self._table_host[layer_idx] = None
             self._table_blocks_total[layer_idx] = -1
             self._dev_lengths[layer_idx] = None
             self._page_headroom[layer_idx] = None
