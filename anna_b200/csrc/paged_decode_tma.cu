@@ -22,7 +22,9 @@
 #include "balanced_schedule.cuh"
 #include "decode_core.cuh"
 #include "decode_params.cuh"
+#include "mbarrier_utils.cuh"
 #include "mma_utils.cuh"
+#include "tq_decode_params.cuh"
 
 #ifndef ANNA_TMA_STAGES
 #define ANNA_TMA_STAGES 2
@@ -38,8 +40,6 @@ constexpr int kTmaThreads = kTmaWarps * 32;
 constexpr int kTmaTile = 16;          // tokens per tile (the M of the MMA)
 constexpr int kBoxCols = 64;          // 16-bit elements per box row = 128 bytes = the swizzle span
 constexpr int kBoxBytes = kTmaTile * 128;
-constexpr uint32_t kWaitSpins = 1u << 16;      // bounded: at most this many suspended waits per tile
-constexpr uint32_t kWaitHintNs = 20000u;       // a waiting warp sleeps in hardware instead of polling
 
 __device__ int32_t g_tma_decode_faults;  // bumped when a bounded mbarrier wait expires
 
@@ -61,33 +61,7 @@ struct TmaCfg {
   static_assert(D % kBoxCols == 0, "head_dim must be a multiple of 64");
 };
 
-// ---- mbarrier / TMA primitives ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kWaitSpins; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
+// ---- tiled TMA load (mbarrier helpers: mbarrier_utils.cuh) --------------------------------------------------------------
 // One box: columns [x, x + 64) of rows [y, y + 16) -> shared `dst` (1024-byte aligned), completion bytes on `bar`.
 __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -260,7 +234,7 @@ paged_decode_tma_kernel(const DenseDecodeParams p, const int batch, const __grid
   if (threadIdx.x == 0) {
     const uint32_t bars = smem_u32(smem_raw + Cfg::kRingBytes);
     for (int i = 0; i < kTmaWarps * Cfg::kStages; ++i) mbar_init(bars + i * 8, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    mbar_init_fence();
   }
   const int group_tiles = (p.groups + 7) / 8;
   const int streams_per_row = p.kv_heads * group_tiles;
@@ -699,12 +673,15 @@ int try_launch_paged_decode_tma(const DenseDecodeParams& p, int batch, int head_
 
 }  // namespace anna
 
-// Number of bounded waits that expired in the TMA decode kernel on the current device since the library was loaded
+// Number of bounded waits that expired in the kernels that stage tiles with the copy engine, on the current device, since the library was loaded
 // (0 in a healthy run).  Synchronises the device.
 extern "C" int anna_kv_device_faults(int* count) {
   ANNA_REQUIRE(count != nullptr, "anna_kv_device_faults: null output pointer");
   int32_t value = 0;
   ANNA_CUDA_CHECK(cudaMemcpyFromSymbol(&value, anna::g_tma_decode_faults, sizeof(value)));
-  *count = (int)value;
+  int packed = 0;
+  const int rc = anna::tq_decode_mma_faults(&packed);
+  if (rc != ANNA_OK) return rc;
+  *count = (int)value + packed;
   return ANNA_OK;
 }

@@ -3,7 +3,8 @@
 // A CTA (4 warps) owns one (row, kv head, chunk).  Chunks that cover the un-quantized window ring run the dense
 // tensor-core body (dense_mma_body.cuh); chunks over the packed prefix run the path below.  Per warp and 16-token tile:
 //
-//   packed bytes of the tile --cp.async--> shared (2 stages per warp)
+//   packed bytes of the tile --bulk copy (cp.async.bulk, mbarrier)--> shared (2 stages per warp); a tile of a 16-token
+//              page is one linear copy issued by one lane, larger pages take six
 //   K codes -> fp16 A fragments in registers: byte-permute (PRMT) table lookups turn 4-bit / 2-bit fields into
 //              centroid values and +-1 signs, two tokens x D/4 coordinates per lane, no shared-memory round trip
 //   S1[16 tok x 8 heads] = centroid(K) . Q1^T      S2 = sign(K) . Q2^T        (2 x D/16 mma.sync m16n8k16, fp16)
@@ -16,12 +17,15 @@
 // The K-dimension slots of the two score products are free to permute, so each lane takes the coordinates whose
 // codes it can unpack with the fewest instructions; Q1 / Q2 fragments are gathered with the same permutation.
 #include "dense_mma_body.cuh"
+#include "mbarrier_utils.cuh"
 #include "tq_common.cuh"
 #include "tq_decode_params.cuh"
 
 #include <cstdlib>
 
 namespace anna {
+
+__device__ int32_t g_tq_mma_faults;  // bumped when a bounded wait on a tile copy expires
 
 // Byte permute and logic helpers are plain intrinsics / C so that the compiler can fold the constant selectors,
 // masks and magic numbers into immediates instead of keeping them in registers.
@@ -83,7 +87,12 @@ struct TqMmaCfg {
   static constexpr int kMergeSmem = (2 * kMmaWarps * 8 + kMmaWarps * 8 * (D + 4)) * 4;
   static constexpr int kTailSmem = 8 * kFusedMaxChunks * 4;
   static constexpr int kSmemBytes0 = kPackedSmem > kMergeSmem ? kPackedSmem : kMergeSmem;
-  static constexpr int kSmemBytes = kSmemBytes0 > kTailSmem ? kSmemBytes0 : kTailSmem;
+  static constexpr int kWorkSmem = ((kSmemBytes0 > kTailSmem ? kSmemBytes0 : kTailSmem) + 15) / 16 * 16;
+  // behind the working area (which the epilogue reuses): one mbarrier and one valid-token count per warp and stage
+  static constexpr int kBarrierBytes = kMmaWarps * kStages * 8;
+  static constexpr int kSmemBytes = kWorkSmem + kBarrierBytes + kMmaWarps * kStages * 4;
+  // bytes of one 16-token tile in the stage (= in a 16-token page chunk, padding excluded)
+  static constexpr int kTileDataBytes = kOffZero + 16 * kGroups * 2;
   // per-lane key code words per token (this lane's D/4 coordinates)
   static constexpr int kIdxWords = BITS == 4 ? D / 32 : D / 64;
   static constexpr int kSignWords = BITS == 3 ? D / 128 : 0;
@@ -236,6 +245,12 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
   const int t1 = min(Lq, t0 + p.chunk_tokens);
   const int out_slot = active_window + chunk;  // active slots stay contiguous: [window | packed]
   const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
+  if (threadIdx.x == 0) {
+    const uint32_t bars = smem_u32(smem_raw + Cfg::kWorkSmem);
+    for (int i = 0; i < kMmaWarps * Cfg::kStages; ++i) mbar_init(bars + i * 8, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -285,41 +300,41 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
   const uint32_t warp_smem_u32 = smem_u32(smem_raw + warp * Cfg::kWarpSmem);
   const uint8_t* warp_smem = smem_raw + warp * Cfg::kWarpSmem;
   const int32_t* table_row = p.block_table + (int64_t)b * p.table_stride;
-  // Issue the async copies of one 16-token tile: six contiguous runs of the page chunk (codes, norms, residual
-  // norms, value codes, scales, zeros), each landing at the same relative place of the stage.
+  // Start the copies of one 16-token tile into a stage.  The stage has the layout of a 16-token page chunk, so with
+  // 16-token pages the tile is one linear run; with larger pages it is six runs (codes, norms, residual norms, value
+  // codes, scales, zeros).  One lane issues them; their bytes complete the stage's mbarrier.
   const uint32_t block_size = (uint32_t)p.block_size;
   const int block_shift = p.block_shift;
+  const uint32_t bars_u32 = smem_u32(smem_raw + Cfg::kWorkSmem) + warp * Cfg::kStages * 8;
+  volatile int* stage_valid = reinterpret_cast<volatile int*>(smem_raw + Cfg::kWorkSmem + Cfg::kBarrierBytes) +
+                              warp * Cfg::kStages;
   auto issue_tile = [&](int tile, int stage) {
+    if (lane != 0) return;
     const int ts = t0 + tile * kTileTokens;
     const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
     const int s0 = ts - (int)(blk * block_size);          // first slot of the tile inside its page
     const int32_t pid = table_row[blk];
-    const bool ok = pid >= 0 && pid < p.num_pages;
-    const uint8_t* chunk_ptr = p.pages + ((int64_t)(ok ? pid : 0) * p.kv_heads + kvh) * p.layout.chunk_bytes + lane * 16;
-    const uint32_t dst = warp_smem_u32 + stage * Cfg::kStageBytes + lane * 16;
-    const int bytes = ok ? 16 : 0;
-    {
-      const uint8_t* src = chunk_ptr + p.layout.off_kcodes + s0 * Cfg::kKeyBytes;
-#pragma unroll
-      for (int i = 0; i < (Cfg::kKeyBytes + 31) / 32; ++i)
-        if (Cfg::kKeyBytes % 32 == 0 || lane + 32 * i < Cfg::kKeyBytes) cp_async16(dst + Cfg::kOffKey + i * 512, src + i * 512, bytes);
+    const uint32_t bar = bars_u32 + stage * 8;
+    if (pid < 0 || pid >= p.num_pages) {  // hole in the block table: nothing to copy, the phase completes at once
+      stage_valid[stage] = 0;
+      mbar_arrive(bar);
+      return;
     }
-    {
-      const uint8_t* src = chunk_ptr + p.layout.off_vdata + s0 * Cfg::kValBytes;
-#pragma unroll
-      for (int i = 0; i < (Cfg::kValBytes + 31) / 32; ++i)
-        if (Cfg::kValBytes % 32 == 0 || lane + 32 * i < Cfg::kValBytes) cp_async16(dst + Cfg::kOffVal + i * 512, src + i * 512, bytes);
-    }
-    {
-      constexpr int kMetaUnits = Cfg::kGroups * 2;  // 16-byte units per metadata array (scales, zeros)
-      static_assert(kMetaUnits <= 16, "metadata copy assumes at most 16 units per array");
-      // lanes 0-3: norms, 4-7: residual norms (same lane*16 offset trick: subtract the lane base for 4-7)
-      if (lane < 4) cp_async16(dst + Cfg::kOffNorm, chunk_ptr + p.layout.off_knorm + 4 * s0, bytes);
-      else if (lane < 8) cp_async16(dst + Cfg::kOffRnorm - 64, chunk_ptr + p.layout.off_krnorm + 4 * s0 - 64, bytes);
-      if (lane < kMetaUnits)
-        cp_async16(dst + Cfg::kOffScale, chunk_ptr + p.layout.off_vscale + s0 * Cfg::kGroups * 2, bytes);
-      else if (lane >= 16 && lane < 16 + kMetaUnits)
-        cp_async16(dst + Cfg::kOffZero - 256, chunk_ptr + p.layout.off_vzero + s0 * Cfg::kGroups * 2 - 256, bytes);
+    stage_valid[stage] = min(kTileTokens, t1 - ts);
+    const uint8_t* chunk_ptr = p.pages + ((int64_t)pid * p.kv_heads + kvh) * p.layout.chunk_bytes;
+    const uint32_t dst = warp_smem_u32 + stage * Cfg::kStageBytes;
+    mbar_expect_tx(bar, Cfg::kTileDataBytes);
+    if (block_size == (uint32_t)kTileTokens) {
+      bulk_copy_g2s(dst, chunk_ptr, Cfg::kTileDataBytes, bar);
+    } else {
+      bulk_copy_g2s(dst + Cfg::kOffKey, chunk_ptr + p.layout.off_kcodes + s0 * Cfg::kKeyBytes, 16 * Cfg::kKeyBytes, bar);
+      bulk_copy_g2s(dst + Cfg::kOffNorm, chunk_ptr + p.layout.off_knorm + 4 * s0, 64, bar);
+      bulk_copy_g2s(dst + Cfg::kOffRnorm, chunk_ptr + p.layout.off_krnorm + 4 * s0, 64, bar);
+      bulk_copy_g2s(dst + Cfg::kOffVal, chunk_ptr + p.layout.off_vdata + s0 * Cfg::kValBytes, 16 * Cfg::kValBytes, bar);
+      bulk_copy_g2s(dst + Cfg::kOffScale, chunk_ptr + p.layout.off_vscale + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
+                    bar);
+      bulk_copy_g2s(dst + Cfg::kOffZero, chunk_ptr + p.layout.off_vzero + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
+                    bar);
     }
   };
 
@@ -333,26 +348,20 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
 
   const int my_tiles = num_tiles > warp ? (num_tiles - warp + kMmaWarps - 1) / kMmaWarps : 0;
   if (my_tiles > 0) issue_tile(warp, 0);
-  cp_async_commit();
 
   // this lane's value dims: D/8 consecutive dims starting at gid * D/8, all inside value group (gid * D/8) / 32
   const int v_group = (gid * (D / 8)) / 32;
 
   for (int n = 0; n < my_tiles; ++n) {
-    __syncwarp();
+    __syncwarp();  // every lane is done with the stage that is re-armed next
     if (n + 1 < my_tiles) issue_tile(warp + (n + 1) * kMmaWarps, (n + 1) & 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncwarp();
-
-    const int tile = warp + n * kMmaWarps;
-    const int ts = t0 + tile * kTileTokens;
-    int valid = min(kTileTokens, t1 - ts);
-    {
-      const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
-      const int32_t pid = table_row[blk];
-      if (pid < 0 || pid >= p.num_pages) valid = 0;
+    if (!mbar_wait(bars_u32 + (n & 1) * 8, (uint32_t)(n >> 1) & 1u)) {
+      if (lane == 0) atomicAdd(&g_tq_mma_faults, 1);
+      if (n + 1 < my_tiles) (void)mbar_wait(bars_u32 + ((n + 1) & 1) * 8, (uint32_t)((n + 1) >> 1) & 1u);
+      break;  // give up on this chunk: the fault counter tells the host that the output is not valid
     }
+    const int valid = stage_valid[n & 1];
+    if (valid == 0) continue;  // hole: no token of this tile exists
     const uint8_t* st = warp_smem + (n & 1) * Cfg::kStageBytes;
 
     // ---- scores ------------------------------------------------------------------------------------------------------
@@ -570,8 +579,6 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
       }
     }
   }
-  cp_async_wait<0>();
-
   // ---- merge the four warps; m-tile j holds dims gid*D/8 + 2j (row gid) and + 2j + 1 (row gid + 8) --------------------------
 #pragma unroll
   for (int d = 4; d <= 16; d <<= 1) {
@@ -644,6 +651,13 @@ static int launch_tq_mma(const TqDecodeParams& p, int batch, cudaStream_t stream
                                          MmaCfg<D>::kSmemBytes));
     if (device >= 0 && device < 64) configured[device] = true;
   }
+  // with 16-token pages a tile is copied as one run, so the page chunk must have exactly the stage's layout
+  if (p.block_size == kTileTokens &&
+      (p.layout.off_kcodes != Cfg::kOffKey || p.layout.off_knorm != Cfg::kOffNorm ||
+       p.layout.off_krnorm != Cfg::kOffRnorm || p.layout.off_vdata != Cfg::kOffVal ||
+       p.layout.off_vscale != Cfg::kOffScale || p.layout.off_vzero != Cfg::kOffZero ||
+       p.layout.chunk_bytes < Cfg::kTileDataBytes))
+    return set_error(ANNA_ERR_INVALID, "packed page layout does not match the decode kernel's tile layout");
   const int group_tiles = (p.groups + 7) / 8;
   dim3 prep_grid((unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
   tq_prepare_queries_kernel<T, D, BITS><<<prep_grid, kMmaThreads, 0, stream>>>(p);
@@ -659,6 +673,13 @@ static int launch_tq_mma(const TqDecodeParams& p, int batch, cudaStream_t stream
     rc = check_launch("tq_decode_split_mma_kernel");
   }
   return rc;
+}
+
+int tq_decode_mma_faults(int* count) {
+  int32_t value = 0;
+  ANNA_CUDA_CHECK(cudaMemcpyFromSymbol(&value, g_tq_mma_faults, sizeof(value)));
+  *count = (int)value;
+  return ANNA_OK;
 }
 
 bool tq_split_mma_applicable(const TqDecodeParams& p, int head_dim, int dtype) {

@@ -36,4 +36,7 @@ struct TqDecodeParams {
 bool tq_split_mma_applicable(const TqDecodeParams& p, int head_dim, int dtype);
 int launch_tq_split_mma(const TqDecodeParams& p, int batch, int head_dim, int bits, int dtype, cudaStream_t stream);
 
+// bounded copy waits that expired in the tensor-core packed decode on the current device (tq_decode_mma.cu)
+int tq_decode_mma_faults(int* count);
+
 }  // namespace anna
