@@ -673,6 +673,43 @@ int try_launch_paged_decode_tma(const DenseDecodeParams& p, int batch, int head_
 
 }  // namespace anna
 
+// ---- self-test of the bounded wait -------------------------------------------------------------------------------------------
+namespace anna {
+__global__ void wait_expiry_selftest_kernel(int32_t* result) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_init_fence();
+  }
+  __syncwarp();
+  // nobody ever arrives on this barrier: the wait has to give up and say so
+  const bool landed = mbar_wait(bar, 0u);
+  if (threadIdx.x == 0) *result = landed ? 0 : 1;
+}
+}  // namespace anna
+
+// Launches one warp that waits on an mbarrier nothing completes and reports whether the bounded wait gave up
+// (*expired = 1) -- the path every copy wait of the library takes when its data does not arrive.  Takes about a second
+// (the full wait budget), synchronises the stream, and leaves the context usable.  No counterpart in the reference.
+extern "C" int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream) {
+  ANNA_REQUIRE(expired != nullptr, "anna_kv_selftest_wait_expiry: null output pointer");
+  int32_t* flag = nullptr;
+  ANNA_CUDA_CHECK(cudaMalloc(&flag, sizeof(int32_t)));
+  cudaError_t err = cudaMemsetAsync(flag, 0xff, sizeof(int32_t), (cudaStream_t)stream);
+  if (err == cudaSuccess) {
+    anna::wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flag);
+    err = cudaGetLastError();
+  }
+  int32_t value = -1;
+  if (err == cudaSuccess) err = cudaMemcpyAsync(&value, flag, sizeof(value), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
+  cudaFree(flag);
+  if (err != cudaSuccess) return anna::set_error(ANNA_ERR_CUDA, "wait-expiry self-test failed: %s", cudaGetErrorString(err));
+  *expired = (int)value;
+  return ANNA_OK;
+}
+
 // Number of bounded waits that expired in the kernels that stage tiles with the copy engine, on the current device, since the library was loaded
 // (0 in a healthy run).  Synchronises the device.
 extern "C" int anna_kv_device_faults(int* count) {

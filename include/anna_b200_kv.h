@@ -46,6 +46,13 @@ int anna_kv_abi_version(void);
  */
 int anna_kv_device_faults(int* count);
 
+/*
+ * Self-test of that mechanism: one warp waits on a barrier that nothing completes; *expired = 1 when the bounded wait
+ * gave up as designed (after its whole budget, about a second).  Synchronises the stream; the context stays usable.
+ * No counterpart in the reference.
+ */
+int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
  * (row, query head, chunk) leaves a partial in caller-owned float32 buffers

@@ -87,3 +87,19 @@ def test_noalloc_decode_rejects_problems_beyond_its_scratch(cuda_device):
         512, 64, 8, 256, 16, 1 << 20, 4096, 0.1, 2, stream)
     assert status == 4  # ANNA_ERR_WORKSPACE
     assert "built-in" in _lib.last_error()
+
+
+def test_bounded_copy_wait_gives_up_and_context_survives(cuda_device):
+    """A wait on a barrier nothing completes must expire (not hang), and the GPU keeps working afterwards."""
+    import ctypes
+
+    from anna_b200 import _lib
+
+    expired = ctypes.c_int(-1)
+    with torch.cuda.device(cuda_device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().anna_kv_selftest_wait_expiry(ctypes.byref(expired), stream or None),
+                   "anna_kv_selftest_wait_expiry")
+    assert expired.value == 1
+    probe = torch.arange(8, device=cuda_device).sum()
+    assert int(probe) == 28 and _lib.device_faults() == 0
