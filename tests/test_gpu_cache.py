@@ -195,3 +195,65 @@ def test_turboquant_batched_dense_view_matches_row_materialize(cuda_device):
         assert torch.count_nonzero(keys[b, :, n:]) == 0 and torch.count_nonzero(values[b, :, n:]) == 0
         tail = min(n, residual)
         assert torch.equal(keys[b, :, n - tail:n], inputs[b][0][0, :, n - tail:]) and torch.isfinite(keys[b]).all()
+
+
+def test_turboquant_churn_matches_oracle(cuda_device):
+    """Configuration-4-like churn at small scale: every step some sequences finish (pages and ring slots go back to the
+    pool) and new ones are admitted with a chunked prefill, the rest decode one token.  Block tables must follow the
+    oracle allocator exactly through the churn and every decode must match the oracle rows."""
+    import random
+
+    import oracle
+    from tests.helpers import DTYPE_CODE, TQ_ATOL
+
+    rng = random.Random(9)
+    gen = torch.Generator().manual_seed(9)
+    heads, kv_heads, dim, bits, residual, block = 8, 2, 128, 3, 8, 16
+    dtype = torch.bfloat16
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=block)
+    allocator = Qwen3PageAllocator(config)
+    oracle_allocator = oracle.OracleLayerAllocator()
+
+    def admit(tokens: int):
+        cache = Qwen3DynamicCache(config, allocator=allocator, kv_cache_quantization="turboquant",
+                                  kv_cache_quant_bits=bits, kv_cache_residual_len=residual)
+        row = oracle.OracleTurboQuantRow(bits=bits, residual_len=residual, dtype=DTYPE_CODE[dtype], block_size=block,
+                                         allocator=oracle_allocator)
+        done = 0
+        while done < tokens:  # chunked prefill
+            step = min(40, tokens - done)
+            k = torch.randn(1, kv_heads, step, dim, generator=gen).to(dtype)
+            v = torch.randn(1, kv_heads, step, dim, generator=gen).to(dtype)
+            cache.update(k.to(cuda_device), v.to(cuda_device), 0, require_dense_cache=False)
+            row.append(to_np(k[0]), to_np(v[0]))
+            done += step
+        return cache, row
+
+    live = [admit(rng.randint(5, 150)) for _ in range(6)]
+    for step in range(8):
+        # one or two sequences finish; their pages return in the reference's order, then new ones come in
+        for _ in range(rng.randint(1, 2)):
+            cache, row = live.pop(rng.randrange(len(live)))
+            cache.release()
+            oracle_allocator.release_pages(row.block_table)
+        while len(live) < 6:
+            live.append(admit(rng.randint(5, 150)))
+        # rows move into the batch and back out as handles (no page is copied or allocated)
+        batch = Qwen3DynamicCache.stack([cache for cache, _ in live], config, clone_turboquant_rows=False)
+        k1 = torch.randn(len(live), kv_heads, 1, dim, generator=gen).to(dtype)
+        v1 = torch.randn(len(live), kv_heads, 1, dim, generator=gen).to(dtype)
+        batch.update(k1.to(cuda_device), v1.to(cuda_device), 0, require_dense_cache=False)
+        query = torch.randn(len(live), heads, 1, dim, generator=gen).to(dtype)
+        out = batch.turboquant_single_token_decode_attention(0, query.to(cuda_device), scaling=dim ** -0.5,
+                                                             num_key_value_groups=heads // kv_heads)
+        for b, (_, row) in enumerate(live):
+            row.append(to_np(k1[b]), to_np(v1[b]))
+            assert batch.turboquant_rows[0][b].block_table == row.block_table, (step, b)
+            want = row.decode_attention(to_np(query[b, :, 0]), scaling=dim ** -0.5)
+            np.testing.assert_allclose(to_np(out[b, :, 0]), want, atol=TQ_ATOL[dtype], rtol=TQ_ATOL[dtype])
+        live = [(cache, row) for cache, (_, row) in zip(batch.split_batch(clone_turboquant_rows=False), live)]
+    pool = allocator.turboquant_layers[0]
+    assert pool.used_pages() == sum(len(row.block_table) for _, row in live)
+    for cache, _ in live:
+        cache.release()
+    assert pool.used_pages() == 0

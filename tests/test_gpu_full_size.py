@@ -1,0 +1,83 @@
+"""GPU: the benchmark configurations at full size, checked through properties that need no CPU oracle.
+
+The oracle finishes small cases in seconds but not 64 sequences of 32768 tokens, so at full size two independent kernel
+paths are played against each other: the paged / packed decode on one side, the dense decode over the gathered (or
+de-quantized) cache on the other.  They share no tile, schedule or merge code, so agreement within the tolerance of the
+small-size oracle tests carries those results to the full shapes.  A second property: sequences are independent, so a
+row decoded alone must give the output it gives inside the batch (up to rounding: the split points of the schedule
+depend on the batch)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from anna_b200 import KVCacheConfig, Qwen3DynamicCache, Qwen3PageAllocator, fused_ops
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config2_full_size_paged_decode_agrees_with_dense_decode(cuda_device):
+    """32 sequences, 32 q / 8 kv heads, D=128, page 16, contexts uniform in [1024, 8192], permuted block tables."""
+    torch.manual_seed(21)
+    batch, heads, kv_heads, dim, page = 32, 32, 8, 128, 16
+    lengths = torch.randint(1024, 8193, (batch,), generator=torch.Generator().manual_seed(5)).tolist()
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
+    allocator = Qwen3PageAllocator(config)
+    template = torch.empty(1, kv_heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    layer = allocator.layers[0]
+    layer.ensure_capacity(sum((n + page - 1) // page for n in lengths) + 8, key_template=template,
+                          value_template=template)
+    layer.free_pages[:] = torch.randperm(layer.capacity(), generator=torch.Generator().manual_seed(6)).tolist()
+    rows = []
+    for n in lengths:
+        row = Qwen3DynamicCache(config, allocator=allocator)
+        k = torch.randn(1, kv_heads, n, dim, device=cuda_device, dtype=torch.bfloat16)
+        row.update(k, torch.randn_like(k), 0, require_dense_cache=False)
+        rows.append(row)
+    cache = Qwen3DynamicCache.stack(rows, config)
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16)
+    key_pages, value_pages, table, visible = cache.paged_attention_state(0)
+    paged = fused_ops.run_paged_gqa_decode_fused(query=query, key_pages=key_pages, value_pages=value_pages,
+                                                 page_table=table, visible_lengths=visible, scaling=dim ** -0.5)
+    keys, values, dense_visible = cache._gather_layer_cache(0)
+    assert dense_visible.tolist() == lengths
+    dense = fused_ops.run_gqa_decode_fused(query=query, key=keys, value=values, visible_lengths=dense_visible,
+                                           scaling=dim ** -0.5)
+    assert torch.isfinite(paged).all()
+    torch.testing.assert_close(paged.float(), dense.float(), atol=2e-2, rtol=2e-2)
+    # independence of sequences: a row decoded alone gives what it gives inside the batch
+    for b in (0, 17, 31):
+        alone = fused_ops.run_paged_gqa_decode_fused(query=query[b:b + 1], key_pages=key_pages, value_pages=value_pages,
+                                                     page_table=table[b:b + 1], visible_lengths=visible[b:b + 1],
+                                                     scaling=dim ** -0.5)
+        torch.testing.assert_close(alone.float(), paged[b:b + 1].float(), atol=2e-2, rtol=2e-2)
+
+
+def test_config5_shard_full_size_packed_decode_agrees_with_dense_decode(cuda_device):
+    """The per-GPU share of configuration 5: 64 sequences x 32768 tokens, 4-bit, 32 q / 8 kv heads, D=128, window 128."""
+    torch.manual_seed(22)
+    batch, heads, kv_heads, dim, context = 64, 32, 8, 128, 32768
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=16)
+    cache = Qwen3DynamicCache(config, batch_size=batch, kv_cache_quantization="turboquant", kv_cache_quant_bits=4,
+                              kv_cache_residual_len=128)
+    cache.reserve_sequence_capacity(context)
+    gen = torch.Generator(device=cuda_device).manual_seed(7)
+    for _ in range(context // 4096):
+        k = torch.randn(batch, kv_heads, 4096, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+        v = torch.randn(batch, kv_heads, 4096, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+        cache.update(k, v, 0, require_dense_cache=False)
+        del k, v
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+    packed = cache.turboquant_single_token_decode_attention(0, query, scaling=dim ** -0.5,
+                                                            num_key_value_groups=heads // kv_heads)
+    keys, values, visible = cache._gather_layer_cache(0)       # de-quantized prefix + exact window, one launch
+    assert keys.shape == (batch, kv_heads, context, dim) and visible.tolist() == [context] * batch
+    dense = fused_ops.run_gqa_decode_fused(query=query, key=keys, value=values, visible_lengths=visible.to(cuda_device),
+                                           scaling=dim ** -0.5)
+    assert torch.isfinite(packed).all()
+    # same tolerance as the small TurboQuant cases against the oracle (the dense path rounds K-hat to bf16 first)
+    torch.testing.assert_close(packed.float(), dense.float(), atol=4e-2, rtol=4e-2)
+    pool = cache.allocator.turboquant_layers[0]
+    assert pool.used_pages() == batch * ((context - 128 + 15) // 16)
+    cache.release()
+    assert pool.used_pages() == 0
