@@ -41,6 +41,18 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// fp16 pair (+-1, +-1) from bits b and b + 16 of x (0 <= b <= 15): a set bit gives +1.  One shift and one logic op.
+__device__ __forceinline__ uint32_t pm_one_pair(uint32_t x, int b) {
+  return ((x << (15 - b)) & 0x80008000u) ^ 0xBC00BC00u;
+}
+// mma.sync m16n8k16 (fp16 in, fp32 accumulate) without the volatile qualifier: a pure function of its operands, so
+// the compiler may interleave the independent accumulation chains of this kernel
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 // N consecutive 32-bit words from shared memory with the widest aligned load (the address is N*4-byte aligned).
 template <int N>
 __device__ __forceinline__ void lds_words(const uint8_t* ptr, uint32_t (&dst)[N]) {
@@ -65,6 +77,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+#ifndef ANNA_TQ_CTAS128
+#define ANNA_TQ_CTAS128 4
+#endif
+#ifndef ANNA_TQ_CTAS256
+#define ANNA_TQ_CTAS256 3
+#endif
+#ifndef ANNA_TQ_TILES_PER_STEP
+#define ANNA_TQ_TILES_PER_STEP 2
+#endif
+#ifndef ANNA_TQ_RING_TILES
+#define ANNA_TQ_RING_TILES 4
+#endif
+constexpr float kLazyRescale = 8.0f;  // log2 units: probabilities stay below 2^8, well inside fp16
+
 template <typename T, int D, int BITS>
 struct TqMmaCfg {
   static constexpr int kSteps = D / 16;
@@ -81,16 +107,18 @@ struct TqMmaCfg {
   static constexpr int kOffScale = kOffVal + 16 * kValBytes;
   static constexpr int kOffZero = kOffScale + 16 * kGroups * 2;
   static constexpr int kStageBytes = (kOffZero + 16 * kGroups * 2 + 127) / 128 * 128;
-  static constexpr int kStages = 2;
-  static constexpr int kWarpSmem = kStages * kStageBytes;
+  static constexpr int kTilesPerStep = ANNA_TQ_TILES_PER_STEP;  // 16-token tiles a warp scores together (one softmax update)
+  static constexpr int kStages = ANNA_TQ_RING_TILES / kTilesPerStep;  // steps per warp ring; kStages - 1 are in flight
+  static constexpr int kMinBlocks = D >= 256 ? ANNA_TQ_CTAS256 : ANNA_TQ_CTAS128;
+  static constexpr int kWarpSmem = kStages * kTilesPerStep * kStageBytes;
   static constexpr int kPackedSmem = kMmaWarps * kWarpSmem;
   static constexpr int kMergeSmem = (2 * kMmaWarps * 8 + kMmaWarps * 8 * (D + 4)) * 4;
   static constexpr int kTailSmem = 8 * kFusedMaxChunks * 4;
   static constexpr int kSmemBytes0 = kPackedSmem > kMergeSmem ? kPackedSmem : kMergeSmem;
   static constexpr int kWorkSmem = ((kSmemBytes0 > kTailSmem ? kSmemBytes0 : kTailSmem) + 15) / 16 * 16;
-  // behind the working area (which the epilogue reuses): one mbarrier and one valid-token count per warp and stage
+  // behind the working area (which the epilogue reuses): one mbarrier per warp and stage, one valid-token count per tile
   static constexpr int kBarrierBytes = kMmaWarps * kStages * 8;
-  static constexpr int kSmemBytes = kWorkSmem + kBarrierBytes + kMmaWarps * kStages * 4;
+  static constexpr int kSmemBytes = kWorkSmem + kBarrierBytes + kMmaWarps * kStages * kTilesPerStep * 4;
   // bytes of one 16-token tile in the stage (= in a 16-token page chunk, padding excluded)
   static constexpr int kTileDataBytes = kOffZero + 16 * kGroups * 2;
   // per-lane key code words per token (this lane's D/4 coordinates)
@@ -106,12 +134,16 @@ __device__ __forceinline__ int idx_coord(int tig, int s, int k) {
   constexpr int kRun = D / 4;
   if constexpr (BITS == 4) return tig * kRun + 4 * s + k;
   if constexpr (BITS == 3) return tig * kRun + 8 * (s / 2) + 2 * k + (s % 2);
-  return tig * kRun + 16 * (s / 4) + 8 * ((s % 4) / 2) + 2 * k + (s % 2);
+  // 1-bit indices: bits 2c of a 16-coordinate word; a register pairs coordinates c and c + 8
+  return tig * kRun + 16 * (s / 4) + 2 * (s % 4) + (k >> 1) + 8 * (k & 1);
 }
 template <int D, int BITS>
 __device__ __forceinline__ int sign_coord(int tig, int s, int k) {
   constexpr int kRun = D / 4;
-  if constexpr (BITS == 3) return tig * kRun + 16 * (s / 4) + (s % 4) + 4 * k;
+  // the two halves of a register take sign bits 16 apart in their word: 4 coordinates (4-bit codes), 8 (2-bit codes)
+  // or 16 (the separate sign plane of 3-bit codes) apart
+  if constexpr (BITS == 4) return tig * kRun + 8 * (s / 2) + 2 * (s % 2) + (k >> 1) + 4 * (k & 1);
+  if constexpr (BITS == 3) return tig * kRun + 32 * (s / 8) + 2 * (s % 8) + (k >> 1) + 16 * (k & 1);
   return idx_coord<D, BITS>(tig, s, k);
 }
 
@@ -151,8 +183,13 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
     for (int j = 0; j < E; ++j) q_rot[1][g][lane * E + j] = w[j];
   }
   __syncthreads();
+  // score (log2 units) = norm * (S1 + rnorm * S2) with every constant folded into the fragments:
+  //   q.k_hat = norm/D * [Q1.c + sqrt(pi/2)/sqrt(D) * rnorm * Q2.sign],  Q1 = fwht(s1*q), Q2 = fwht(s2*Q1)
+  //   (1-bit indices: the centroids are +-c0 and the fragments carry +-1, so c0 goes into the factor)
   const float inv_sqrt_d = rsqrt_dim_const<D>();
-  const float inv_d = inv_sqrt_d * inv_sqrt_d;
+  const float log2e = 1.4426950408889634f;
+  const float f1 = (BITS == 2 ? __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d * inv_sqrt_d;
+  const float f2 = p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d * inv_sqrt_d * inv_sqrt_d;
   uint4* out = reinterpret_cast<uint4*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * 32 * kSteps;
   for (int item = threadIdx.x; item < 32 * kSteps; item += kMmaThreads) {
     const int ln = item / kSteps;
@@ -161,10 +198,10 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
     const float* r1 = q_rot[0][gid];
     const float* r2 = q_rot[1][gid];
     uint4 v;
-    v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * inv_sqrt_d, r1[idx_coord<D, BITS>(tig, s, 1)] * inv_sqrt_d);
-    v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * inv_sqrt_d, r1[idx_coord<D, BITS>(tig, s, 3)] * inv_sqrt_d);
-    v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * inv_d, r2[sign_coord<D, BITS>(tig, s, 1)] * inv_d);
-    v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * inv_d, r2[sign_coord<D, BITS>(tig, s, 3)] * inv_d);
+    v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * f1, r1[idx_coord<D, BITS>(tig, s, 1)] * f1);
+    v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * f1, r1[idx_coord<D, BITS>(tig, s, 3)] * f1);
+    v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * f2, r2[sign_coord<D, BITS>(tig, s, 1)] * f2);
+    v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * f2, r2[sign_coord<D, BITS>(tig, s, 3)] * f2);
     out[item] = v;
   }
 }
@@ -215,8 +252,10 @@ __global__ void __launch_bounds__(kMmaThreads, MmaCfg<D>::kMinBlocks) tq_window_
 }
 
 template <typename T, int D, int BITS>
-__global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split_mma_kernel(const TqDecodeParams p) {
+__global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
+    tq_decode_split_mma_kernel(const TqDecodeParams p) {
   using Cfg = TqMmaCfg<T, D, BITS>;
+  constexpr int U = Cfg::kTilesPerStep;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
 
   const int slot = blockIdx.x;
@@ -256,8 +295,8 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
   const int lane = threadIdx.x & 31;
   const int gid = lane >> 2;
   const int tig = lane & 3;
-  // Q fragments (fp16) were prepared by tq_prepare_queries_kernel in exactly this lane's register order:
-  //   [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]
+  // Q fragments (fp16, softmax scale and log2(e) folded in) were prepared by tq_prepare_queries_kernel in exactly this
+  // lane's register order: [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]
   uint32_t q1f[Cfg::kSteps][2], q2f[Cfg::kSteps][2];
   {
     const uint4* frag = reinterpret_cast<const uint4*>(p.query_frags) +
@@ -268,13 +307,6 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
       q1f[s][0] = v.x; q1f[s][1] = v.y; q2f[s][0] = v.z; q2f[s][1] = v.w;
     }
   }
-  // score (log2 units) = norm * (k1 * S1 + k2 * rnorm * S2) with S1 = Q1/sqrt(D) . c, S2 = Q2/D . sign:
-  //   q.k_hat = norm/D * [Q1.c + sqrt(pi/2)/sqrt(D) * rnorm * Q2.sign]
-  //           = norm * [ (1/sqrt(D)) * S1 + sqrt(pi/2)/sqrt(D) * rnorm * S2 ]
-  const float inv_sqrt_d = rsqrt_dim_const<D>();
-  const float log2e = 1.4426950408889634f;
-  const float k1 = (BITS == 2 ? __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d;
-  const float k2 = p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d;
 
   // centroid lookup tables for PRMT: low bytes and high bytes of the fp16 centroids (up to 8 entries)
   uint32_t lut_lo[2] = {0u, 0u}, lut_hi[2] = {0u, 0u};
@@ -292,49 +324,58 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
       lut_hi[1] = lut_hi[0];
     }
   }
-  constexpr uint32_t kSignLut = 0x00003CBCu;   // byte 0: high byte of fp16 -1.0, byte 1: high byte of +1.0
-  // 2-bit format: a nibble holds two fields [s1 i1 s0 i0]; after masking with 0x5 it is 0, 1, 4 or 5
-  constexpr uint32_t kEvenLut0 = 0x3CBC3CBCu, kEvenLut1 = 0x3CBC3CBCu;  // entry v: bit 0 set -> +1
-  constexpr uint32_t kOddLut0 = 0xBCBCBCBCu, kOddLut1 = 0x3C3C3C3Cu;    // entry v: bit 2 set -> +1
 
   const uint32_t warp_smem_u32 = smem_u32(smem_raw + warp * Cfg::kWarpSmem);
   const uint8_t* warp_smem = smem_raw + warp * Cfg::kWarpSmem;
   const int32_t* table_row = p.block_table + (int64_t)b * p.table_stride;
-  // Start the copies of one 16-token tile into a stage.  The stage has the layout of a 16-token page chunk, so with
-  // 16-token pages the tile is one linear run; with larger pages it is six runs (codes, norms, residual norms, value
-  // codes, scales, zeros).  One lane issues them; their bytes complete the stage's mbarrier.
   const uint32_t block_size = (uint32_t)p.block_size;
   const int block_shift = p.block_shift;
   const uint32_t bars_u32 = smem_u32(smem_raw + Cfg::kWorkSmem) + warp * Cfg::kStages * 8;
   volatile int* stage_valid = reinterpret_cast<volatile int*>(smem_raw + Cfg::kWorkSmem + Cfg::kBarrierBytes) +
-                              warp * Cfg::kStages;
-  auto issue_tile = [&](int tile, int stage) {
-    if (lane != 0) return;
-    const int ts = t0 + tile * kTileTokens;
-    const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
-    const int s0 = ts - (int)(blk * block_size);          // first slot of the tile inside its page
-    const int32_t pid = table_row[blk];
-    const uint32_t bar = bars_u32 + stage * 8;
-    if (pid < 0 || pid >= p.num_pages) {  // hole in the block table: nothing to copy, the phase completes at once
-      stage_valid[stage] = 0;
-      mbar_arrive(bar);
-      return;
+                              warp * Cfg::kStages * U;
+  // Start the copies of one step (U consecutive 16-token tiles) into a stage.  Each tile slot of the stage has the
+  // layout of a 16-token page chunk, so with 16-token pages a tile is one linear run; with larger pages it is six runs
+  // (codes, norms, residual norms, value codes, scales, zeros).  Lanes 0 .. U-1 look up and copy one tile each; lane 0
+  // arms the stage's mbarrier with the bytes of all of them first.  Called by the whole warp.
+  auto issue_step = [&](int step, int stage) {
+    int valid = 0;
+    const uint8_t* chunk_ptr = nullptr;
+    int s0 = 0;
+    if (lane < U) {
+      const int tile = (warp + step * kMmaWarps) * U + lane;
+      if (tile < num_tiles) {
+        const int ts = t0 + tile * kTileTokens;
+        const uint32_t blk = block_shift >= 0 ? ((uint32_t)ts >> block_shift) : ((uint32_t)ts / block_size);
+        s0 = ts - (int)(blk * block_size);  // first slot of the tile inside its page
+        const int32_t pid = table_row[blk];
+        if (pid >= 0 && pid < p.num_pages) {  // else a hole in the block table: nothing to copy
+          valid = min(kTileTokens, t1 - ts);
+          chunk_ptr = p.pages + ((int64_t)pid * p.kv_heads + kvh) * p.layout.chunk_bytes;
+        }
+      }
+      stage_valid[stage * U + lane] = valid;
     }
-    stage_valid[stage] = min(kTileTokens, t1 - ts);
-    const uint8_t* chunk_ptr = p.pages + ((int64_t)pid * p.kv_heads + kvh) * p.layout.chunk_bytes;
-    const uint32_t dst = warp_smem_u32 + stage * Cfg::kStageBytes;
-    mbar_expect_tx(bar, Cfg::kTileDataBytes);
-    if (block_size == (uint32_t)kTileTokens) {
-      bulk_copy_g2s(dst, chunk_ptr, Cfg::kTileDataBytes, bar);
-    } else {
-      bulk_copy_g2s(dst + Cfg::kOffKey, chunk_ptr + p.layout.off_kcodes + s0 * Cfg::kKeyBytes, 16 * Cfg::kKeyBytes, bar);
-      bulk_copy_g2s(dst + Cfg::kOffNorm, chunk_ptr + p.layout.off_knorm + 4 * s0, 64, bar);
-      bulk_copy_g2s(dst + Cfg::kOffRnorm, chunk_ptr + p.layout.off_krnorm + 4 * s0, 64, bar);
-      bulk_copy_g2s(dst + Cfg::kOffVal, chunk_ptr + p.layout.off_vdata + s0 * Cfg::kValBytes, 16 * Cfg::kValBytes, bar);
-      bulk_copy_g2s(dst + Cfg::kOffScale, chunk_ptr + p.layout.off_vscale + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
-                    bar);
-      bulk_copy_g2s(dst + Cfg::kOffZero, chunk_ptr + p.layout.off_vzero + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
-                    bar);
+    const uint32_t bar = bars_u32 + stage * 8;
+    const unsigned have = __ballot_sync(0xffffffffu, valid > 0);
+    if (lane == 0) {
+      if (have != 0u) mbar_expect_tx(bar, (uint32_t)__popc(have) * Cfg::kTileDataBytes);
+      else mbar_arrive(bar);  // the phase completes at once
+    }
+    __syncwarp();
+    if (valid > 0) {
+      const uint32_t dst = warp_smem_u32 + (stage * U + lane) * Cfg::kStageBytes;
+      if (block_size == (uint32_t)kTileTokens) {
+        bulk_copy_g2s(dst, chunk_ptr, Cfg::kTileDataBytes, bar);
+      } else {
+        bulk_copy_g2s(dst + Cfg::kOffKey, chunk_ptr + p.layout.off_kcodes + s0 * Cfg::kKeyBytes, 16 * Cfg::kKeyBytes, bar);
+        bulk_copy_g2s(dst + Cfg::kOffNorm, chunk_ptr + p.layout.off_knorm + 4 * s0, 64, bar);
+        bulk_copy_g2s(dst + Cfg::kOffRnorm, chunk_ptr + p.layout.off_krnorm + 4 * s0, 64, bar);
+        bulk_copy_g2s(dst + Cfg::kOffVal, chunk_ptr + p.layout.off_vdata + s0 * Cfg::kValBytes, 16 * Cfg::kValBytes, bar);
+        bulk_copy_g2s(dst + Cfg::kOffScale, chunk_ptr + p.layout.off_vscale + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
+                      bar);
+        bulk_copy_g2s(dst + Cfg::kOffZero, chunk_ptr + p.layout.off_vzero + s0 * Cfg::kGroups * 2, 16 * Cfg::kGroups * 2,
+                      bar);
+      }
     }
   };
 
@@ -346,148 +387,175 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
 #pragma unroll
     for (int r = 0; r < 4; ++r) o_acc[j][r] = 0.0f;
 
-  const int my_tiles = num_tiles > warp ? (num_tiles - warp + kMmaWarps - 1) / kMmaWarps : 0;
-  if (my_tiles > 0) issue_tile(warp, 0);
+  const int num_steps = (num_tiles + U - 1) / U;
+  const int my_steps = num_steps > warp ? (num_steps - warp + kMmaWarps - 1) / kMmaWarps : 0;
+#pragma unroll
+  for (int i = 0; i < Cfg::kStages - 1; ++i)
+    if (i < my_steps) issue_step(i, i);
 
+  // MMA row r of a tile holds token r ^ ((r >> 1) & 1): neighbouring token rows sit in different halves of the
+  // shared-memory banks, and with this order the four token rows one value load touches fall into both halves.
+  const int tok_lo = gid ^ ((gid >> 1) & 1);  // rows gid and gid + 8 of the score product
+  const int tok_hi = tok_lo + 8;
+  // k-slots 2tig, 2tig+1 (and +8) of the value product = the same rows
+  const int tok_a0 = (2 * tig) ^ (tig & 1), tok_a1 = (2 * tig + 1) ^ (tig & 1);
   // this lane's value dims: D/8 consecutive dims starting at gid * D/8, all inside value group (gid * D/8) / 32
   const int v_group = (gid * (D / 8)) / 32;
 
-  for (int n = 0; n < my_tiles; ++n) {
-    __syncwarp();  // every lane is done with the stage that is re-armed next
-    if (n + 1 < my_tiles) issue_tile(warp + (n + 1) * kMmaWarps, (n + 1) & 1);
-    if (!mbar_wait(bars_u32 + (n & 1) * 8, (uint32_t)(n >> 1) & 1u)) {
+  int stage = 0;        // stage of step n
+  uint32_t phase = 0;   // parity of the mbarrier phase that step n completes
+  for (int n = 0; n < my_steps; ++n) {
+    __syncwarp();  // every lane is done with the stage that is re-armed next (the one step n - 1 used)
+    {
+      const int ahead = n + Cfg::kStages - 1;
+      if (ahead < my_steps) issue_step(ahead, stage == 0 ? Cfg::kStages - 1 : stage - 1);
+    }
+    if (!mbar_wait(bars_u32 + stage * 8, phase)) {
       if (lane == 0) atomicAdd(&g_tq_mma_faults, 1);
-      if (n + 1 < my_tiles) (void)mbar_wait(bars_u32 + ((n + 1) & 1) * 8, (uint32_t)((n + 1) >> 1) & 1u);
+      // wait (bounded) for the copies still in flight before the epilogue reuses the stages
+      for (int k = 1; k < Cfg::kStages && n + k < my_steps; ++k) {
+        const int st_k = (stage + k) % Cfg::kStages;
+        (void)mbar_wait(bars_u32 + st_k * 8, (uint32_t)((n + k) / Cfg::kStages) & 1u);
+      }
       break;  // give up on this chunk: the fault counter tells the host that the output is not valid
     }
-    const int valid = stage_valid[n & 1];
-    if (valid == 0) continue;  // hole: no token of this tile exists
-    const uint8_t* st = warp_smem + (n & 1) * Cfg::kStageBytes;
+    const int cur = stage;
+    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+    int valid[U];
+    int valid_sum = 0;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      valid[u] = stage_valid[cur * U + u];
+      valid_sum += valid[u];
+    }
+    if (valid_sum == 0) continue;  // holes only: no token of this step exists
+    const bool full = valid_sum == U * kTileTokens;
+    const uint8_t* st0 = warp_smem + cur * U * Cfg::kStageBytes;
 
-    // ---- scores ------------------------------------------------------------------------------------------------------
-    float s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // ---- scores: U independent pairs of accumulation chains ------------------------------------------------------------
+    float s1[U][4], s2[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s1[u][r] = s2[u][r] = 0.0f;
     {
-      uint32_t iw_lo[Cfg::kIdxWords], iw_hi[Cfg::kIdxWords];  // rows gid and gid + 8
-      const uint8_t* row_lo = st + Cfg::kOffKey + gid * Cfg::kKeyBytes + tig * (Cfg::kIdxWords * 4);
-      const uint8_t* row_hi = row_lo + 8 * Cfg::kKeyBytes;
-      lds_words<Cfg::kIdxWords>(row_lo, iw_lo);
-      lds_words<Cfg::kIdxWords>(row_hi, iw_hi);
+      uint32_t iw_lo[U][Cfg::kIdxWords], iw_hi[U][Cfg::kIdxWords];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint8_t* keys = st0 + u * Cfg::kStageBytes + Cfg::kOffKey + tig * (Cfg::kIdxWords * 4);
+        lds_words<Cfg::kIdxWords>(keys + tok_lo * Cfg::kKeyBytes, iw_lo[u]);
+        lds_words<Cfg::kIdxWords>(keys + tok_hi * Cfg::kKeyBytes, iw_hi[u]);
+      }
       if constexpr (BITS == 4) {
 #pragma unroll
         for (int s = 0; s < Cfg::kSteps; ++s) {
-          const uint32_t wl = iw_lo[s / 2] >> (16 * (s % 2));
-          const uint32_t wh = iw_hi[s / 2] >> (16 * (s % 2));
-          uint32_t a[4];
-          {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t wl = iw_lo[u][s / 2] >> (16 * (s % 2));
+            const uint32_t wh = iw_hi[u][s / 2] >> (16 * (s % 2));
             const uint32_t sl = wl & 0x7777u, sh = wh & 0x7777u;
             const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
             const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
-            a[0] = prmt(lo_l, hi_l, 0x5140u);
-            a[1] = prmt(lo_h, hi_h, 0x5140u);
-            a[2] = prmt(lo_l, hi_l, 0x7362u);
-            a[3] = prmt(lo_h, hi_h, 0x7362u);
+            const uint32_t a[4] = {prmt(lo_l, hi_l, 0x5140u), prmt(lo_h, hi_h, 0x5140u), prmt(lo_l, hi_l, 0x7362u),
+                                   prmt(lo_h, hi_h, 0x7362u)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
-          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
-          {
-            const uint32_t gl = prmt(kSignLut, 0u, (wl >> 3) & 0x1111u);
-            const uint32_t gh = prmt(kSignLut, 0u, (wh >> 3) & 0x1111u);
-            a[0] = prmt(gl, 0u, 0x1404u);
-            a[1] = prmt(gh, 0u, 0x1404u);
-            a[2] = prmt(gl, 0u, 0x3424u);
-            a[3] = prmt(gh, 0u, 0x3424u);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            // sign bits 3 + 4i of the word: nibbles i and i + 4 land in the two halves of one register
+            const uint32_t xl = iw_lo[u][s / 2], xh = iw_hi[u][s / 2];
+            const int b0 = 3 + 8 * (s % 2), b1 = 7 + 8 * (s % 2);
+            const uint32_t a[4] = {pm_one_pair(xl, b0), pm_one_pair(xh, b0), pm_one_pair(xl, b1), pm_one_pair(xh, b1)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
-          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
         }
       } else if constexpr (BITS == 2) {
 #pragma unroll
         for (int s = 0; s < Cfg::kSteps; ++s) {
-          const uint32_t wl = iw_lo[s / 4] >> (16 * ((s % 4) / 2));
-          const uint32_t wh = iw_hi[s / 4] >> (16 * ((s % 4) / 2));
-          const uint32_t la = (s % 2) ? kOddLut0 : kEvenLut0;
-          const uint32_t lb = (s % 2) ? kOddLut1 : kEvenLut1;
-          uint32_t a[4];
-          {
-            const uint32_t gl = prmt(la, lb, wl & 0x5555u);
-            const uint32_t gh = prmt(la, lb, wh & 0x5555u);
-            a[0] = prmt(gl, 0u, 0x1404u);
-            a[1] = prmt(gh, 0u, 0x1404u);
-            a[2] = prmt(gl, 0u, 0x3424u);
-            a[3] = prmt(gh, 0u, 0x3424u);
+          const int h = s % 4;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h), pm_one_pair(xh, 4 * h), pm_one_pair(xl, 4 * h + 2),
+                                   pm_one_pair(xh, 4 * h + 2)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
-          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
-          {
-            const uint32_t gl = prmt(la, lb, (wl >> 1) & 0x5555u);
-            const uint32_t gh = prmt(la, lb, (wh >> 1) & 0x5555u);
-            a[0] = prmt(gl, 0u, 0x1404u);
-            a[1] = prmt(gh, 0u, 0x1404u);
-            a[2] = prmt(gl, 0u, 0x3424u);
-            a[3] = prmt(gh, 0u, 0x3424u);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h + 1), pm_one_pair(xh, 4 * h + 1), pm_one_pair(xl, 4 * h + 3),
+                                   pm_one_pair(xh, 4 * h + 3)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
-          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
         }
       } else {
-        uint32_t sw_lo[Cfg::kSignWords], sw_hi[Cfg::kSignWords];
-        const uint8_t* srow_lo = st + Cfg::kOffKey + gid * Cfg::kKeyBytes + Cfg::kIdxBytes + tig * (Cfg::kSignWords * 4);
-        const uint8_t* srow_hi = srow_lo + 8 * Cfg::kKeyBytes;
-        lds_words<Cfg::kSignWords>(srow_lo, sw_lo);
-        lds_words<Cfg::kSignWords>(srow_hi, sw_hi);
+        uint32_t sw_lo[U][Cfg::kSignWords], sw_hi[U][Cfg::kSignWords];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint8_t* signs = st0 + u * Cfg::kStageBytes + Cfg::kOffKey + Cfg::kIdxBytes + tig * (Cfg::kSignWords * 4);
+          lds_words<Cfg::kSignWords>(signs + tok_lo * Cfg::kKeyBytes, sw_lo[u]);
+          lds_words<Cfg::kSignWords>(signs + tok_hi * Cfg::kKeyBytes, sw_hi[u]);
+        }
 #pragma unroll
         for (int s = 0; s < Cfg::kSteps; ++s) {
-          // 2-bit indices: half-word s / 2 of the lane's run, even (s % 2 == 0) or odd fields
-          const uint32_t wl = iw_lo[s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
-          const uint32_t wh = iw_hi[s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
-          uint32_t a[4];
-          {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            // 2-bit indices: half-word s / 2 of the lane's run, even (s % 2 == 0) or odd fields
+            const uint32_t wl = iw_lo[u][s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
+            const uint32_t wh = iw_hi[u][s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
             const uint32_t sl = wl & 0x3333u, sh = wh & 0x3333u;
             const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
             const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
-            a[0] = prmt(lo_l, hi_l, 0x5140u);
-            a[1] = prmt(lo_h, hi_h, 0x5140u);
-            a[2] = prmt(lo_l, hi_l, 0x7362u);
-            a[3] = prmt(lo_h, hi_h, 0x7362u);
+            const uint32_t a[4] = {prmt(lo_l, hi_l, 0x5140u), prmt(lo_h, hi_h, 0x5140u), prmt(lo_l, hi_l, 0x7362u),
+                                   prmt(lo_h, hi_h, 0x7362u)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
-          mma_m16n8k16<__half>(s1, a, q1f[s][0], q1f[s][1]);
-          {
-            // sign plane: coordinates 16 * (s / 4) + (s % 4) + 4k of the lane's run
-            const uint32_t xl = sw_lo[s / 8] >> (16 * ((s / 4) % 2) + (s % 4));
-            const uint32_t xh = sw_hi[s / 8] >> (16 * ((s / 4) % 2) + (s % 4));
-            const uint32_t gl = prmt(kSignLut, 0u, xl & 0x1111u);
-            const uint32_t gh = prmt(kSignLut, 0u, xh & 0x1111u);
-            a[0] = prmt(gl, 0u, 0x1404u);
-            a[1] = prmt(gh, 0u, 0x1404u);
-            a[2] = prmt(gl, 0u, 0x3424u);
-            a[3] = prmt(gh, 0u, 0x3424u);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            // sign plane: bits 2h, 2h + 1 (and + 16) of word s / 8, h = s % 8
+            const uint32_t xl = sw_lo[u][s / 8], xh = sw_hi[u][s / 8];
+            const int h = s % 8;
+            const uint32_t a[4] = {pm_one_pair(xl, 2 * h), pm_one_pair(xh, 2 * h), pm_one_pair(xl, 2 * h + 1),
+                                   pm_one_pair(xh, 2 * h + 1)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
-          mma_m16n8k16<__half>(s2, a, q2f[s][0], q2f[s][1]);
         }
       }
     }
-    const float* norms = reinterpret_cast<const float*>(st + Cfg::kOffNorm);
-    const float* rnorms = reinterpret_cast<const float*>(st + Cfg::kOffRnorm);
-    const bool ok_lo = gid < valid, ok_hi = gid + 8 < valid;
-    float s[4];
-    {
-      const float n_lo = norms[gid], r_lo = rnorms[gid], n_hi = norms[gid + 8], r_hi = rnorms[gid + 8];
-      s[0] = ok_lo ? n_lo * fmaf(k2 * r_lo, s2[0], k1 * s1[0]) : -INFINITY;
-      s[1] = ok_lo ? n_lo * fmaf(k2 * r_lo, s2[1], k1 * s1[1]) : -INFINITY;
-      s[2] = ok_hi ? n_hi * fmaf(k2 * r_hi, s2[2], k1 * s1[2]) : -INFINITY;
-      s[3] = ok_hi ? n_hi * fmaf(k2 * r_hi, s2[3], k1 * s1[3]) : -INFINITY;
+    // score (log2 units) = norm * (S1 + rnorm * S2); the constant factors are folded into the query fragments
+    float sc[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float* norms = reinterpret_cast<const float*>(st0 + u * Cfg::kStageBytes + Cfg::kOffNorm);
+      const float* rnorms = reinterpret_cast<const float*>(st0 + u * Cfg::kStageBytes + Cfg::kOffRnorm);
+      const float n_lo = norms[tok_lo], r_lo = rnorms[tok_lo], n_hi = norms[tok_hi], r_hi = rnorms[tok_hi];
+      sc[u][0] = n_lo * fmaf(r_lo, s2[u][0], s1[u][0]);
+      sc[u][1] = n_lo * fmaf(r_lo, s2[u][1], s1[u][1]);
+      sc[u][2] = n_hi * fmaf(r_hi, s2[u][2], s1[u][2]);
+      sc[u][3] = n_hi * fmaf(r_hi, s2[u][3], s1[u][3]);
+      if (!full) {  // rows past the end of the prefix (their bytes may be anything)
+        if (tok_lo >= valid[u]) sc[u][0] = sc[u][1] = -INFINITY;
+        if (tok_hi >= valid[u]) sc[u][2] = sc[u][3] = -INFINITY;
+      }
     }
 
-    // ---- online softmax ---------------------------------------------------------------------------------------------------
-    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+    // ---- online softmax over the U * 16 tokens; the running maximum moves only when it would grow by more than 2^8 ----
+    float mx[2] = {fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[0][1], sc[0][3])};
+#pragma unroll
+    for (int u = 1; u < U; ++u) {
+      mx[0] = fmaxf(mx[0], fmaxf(sc[u][0], sc[u][2]));
+      mx[1] = fmaxf(mx[1], fmaxf(sc[u][1], sc[u][3]));
+    }
 #pragma unroll
     for (int d = 4; d <= 16; d <<= 1) {
       mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
       mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
     }
-    const float m_new[2] = {fmaxf(m_run[0], mx[0]), fmaxf(m_run[1], mx[1])};
-    const bool grew = (m_new[0] > m_run[0]) || (m_new[1] > m_run[1]);
-    const float m_safe[2] = {m_new[0] == -INFINITY ? 0.0f : m_new[0], m_new[1] == -INFINITY ? 0.0f : m_new[1]};
+    const bool grew = (mx[0] > m_run[0] + kLazyRescale) || (mx[1] > m_run[1] + kLazyRescale);
     if (__any_sync(0xffffffffu, grew)) {
-      const float a0 = fast_exp2(m_run[0] - m_safe[0]);
-      const float a1 = fast_exp2(m_run[1] - m_safe[1]);
+      const float m_new[2] = {fmaxf(m_run[0], mx[0]), fmaxf(m_run[1], mx[1])};
+      const float a0 = fast_exp2(m_run[0] - (m_new[0] == -INFINITY ? 0.0f : m_new[0]));
+      const float a1 = fast_exp2(m_run[1] - (m_new[1] == -INFINITY ? 0.0f : m_new[1]));
       l_run[0] *= a0;
       l_run[1] *= a1;
 #pragma unroll
@@ -500,56 +568,69 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
       m_run[0] = m_new[0];
       m_run[1] = m_new[1];
     }
-    const float p0 = fast_exp2(s[0] - m_safe[0]);
-    const float p1 = fast_exp2(s[1] - m_safe[1]);
-    const float p2 = fast_exp2(s[2] - m_safe[0]);
-    const float p3 = fast_exp2(s[3] - m_safe[1]);
-    l_run[0] += p0 + p2;
-    l_run[1] += p1 + p3;
-    const uint32_t pb0 = movmatrix_trans(pack2<__half>(p0, p1));  // tokens 2tig, 2tig+1 of head gid
-    const uint32_t pb1 = movmatrix_trans(pack2<__half>(p2, p3));  // tokens 2tig+8, 2tig+9
-
-    // ---- values: lane holds tokens {2tig, 2tig+1} and {2tig+8, 2tig+9}, dims gid*D/8 .. +D/8 ---------------------------------
-    const int tok_a = 2 * tig, tok_c = 2 * tig + 8;
-    uint32_t sc_pair[2], zp_pair[2];
-    {
-      const T* scales = reinterpret_cast<const T*>(st + Cfg::kOffScale);
-      const T* zeros = reinterpret_cast<const T*>(st + Cfg::kOffZero);
-      auto meta = [&](const T* arr, int tok) -> float {
-        return tok < valid ? ElemTraits<T>::to_float(arr[tok * Cfg::kGroups + v_group]) : 0.0f;
-      };
-      sc_pair[0] = pack2<__half>(meta(scales, tok_a), meta(scales, tok_a + 1));
-      sc_pair[1] = pack2<__half>(meta(scales, tok_c), meta(scales, tok_c + 1));
-      zp_pair[0] = pack2<__half>(meta(zeros, tok_a), meta(zeros, tok_a + 1));
-      zp_pair[1] = pack2<__half>(meta(zeros, tok_c), meta(zeros, tok_c + 1));
+    const float m_ref[2] = {m_run[0] == -INFINITY ? 0.0f : m_run[0], m_run[1] == -INFINITY ? 0.0f : m_run[1]};
+    uint32_t pb[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float p0 = fast_exp2(sc[u][0] - m_ref[0]);
+      const float p1 = fast_exp2(sc[u][1] - m_ref[1]);
+      const float p2 = fast_exp2(sc[u][2] - m_ref[0]);
+      const float p3 = fast_exp2(sc[u][3] - m_ref[1]);
+      l_run[0] += p0 + p2;
+      l_run[1] += p1 + p3;
+      pb[u][0] = movmatrix_trans(pack2<__half>(p0, p1));  // rows 2tig, 2tig+1 of head gid
+      pb[u][1] = movmatrix_trans(pack2<__half>(p2, p3));  // rows 2tig+8, 2tig+9
     }
-    const uint8_t* vbase = st + Cfg::kOffVal + gid * (Cfg::kValWords * 4);
-    uint32_t vw[4][Cfg::kValWords];  // tokens a, a+1, c, c+1
-    lds_words<Cfg::kValWords>(vbase + tok_a * Cfg::kValBytes, vw[0]);
-    lds_words<Cfg::kValWords>(vbase + (tok_a + 1) * Cfg::kValBytes, vw[1]);
-    lds_words<Cfg::kValWords>(vbase + tok_c * Cfg::kValBytes, vw[2]);
-    lds_words<Cfg::kValWords>(vbase + (tok_c + 1) * Cfg::kValBytes, vw[3]);
+
+    // ---- values: lane holds rows {2tig, 2tig+1} and {2tig+8, 2tig+9}, dims gid*D/8 .. +D/8 -----------------------------------
+    uint32_t sc_pair[U][2], zp_pair[U][2];
+    uint32_t vw[U][4][Cfg::kValWords];  // rows 2tig, 2tig+1, 2tig+8, 2tig+9
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint8_t* st = st0 + u * Cfg::kStageBytes;
+      const T* scales = reinterpret_cast<const T*>(st + Cfg::kOffScale) + v_group;
+      const T* zeros = reinterpret_cast<const T*>(st + Cfg::kOffZero) + v_group;
+      float sv[4], zv[4];
+      const int toks[4] = {tok_a0, tok_a1, tok_a0 + 8, tok_a1 + 8};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sv[i] = ElemTraits<T>::to_float(scales[toks[i] * Cfg::kGroups]);
+        zv[i] = ElemTraits<T>::to_float(zeros[toks[i] * Cfg::kGroups]);
+        if (!full && toks[i] >= valid[u]) sv[i] = zv[i] = 0.0f;
+      }
+      sc_pair[u][0] = pack2<__half>(sv[0], sv[1]);
+      sc_pair[u][1] = pack2<__half>(sv[2], sv[3]);
+      zp_pair[u][0] = pack2<__half>(zv[0], zv[1]);
+      zp_pair[u][1] = pack2<__half>(zv[2], zv[3]);
+      const uint8_t* vbase = st + Cfg::kOffVal + gid * (Cfg::kValWords * 4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) lds_words<Cfg::kValWords>(vbase + toks[i] * Cfg::kValBytes, vw[u][i]);
+    }
     if constexpr (BITS != 2) {
       // 4-bit codes: one 16-bit half-word = 4 dims; x packs the same 4 dims of two tokens (low / high half)
       constexpr uint32_t kMagicLo = 0x64006400u, kMagicHi = 0x54005400u;  // 1024 + n, 64 + n
 #pragma unroll
       for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
         const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
-        uint32_t r[2][4];
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-          const uint32_t x = prmt(vw[2 * pr][hw / 2], vw[2 * pr + 1][hw / 2], sel);
-          const uint32_t y = x >> 8;
-          r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000F000Fu, kMagicLo), kMagicLo), sc_pair[pr], zp_pair[pr]);
-          r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00F000F0u, kMagicHi), kMagicHi), sc_pair[pr], zp_pair[pr]);
-          r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000F000Fu, kMagicLo), kMagicLo), sc_pair[pr], zp_pair[pr]);
-          r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00F000F0u, kMagicHi), kMagicHi), sc_pair[pr], zp_pair[pr]);
+        for (int u = 0; u < U; ++u) {
+          uint32_t r[2][4];
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr) {
+            const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
+            const uint32_t y = x >> 8;
+            const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
+            r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000F000Fu, kMagicLo), kMagicLo), scl, zpt);
+            r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00F000F0u, kMagicHi), kMagicHi), scl, zpt);
+            r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000F000Fu, kMagicLo), kMagicLo), scl, zpt);
+            r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00F000F0u, kMagicHi), kMagicHi), scl, zpt);
+          }
+          // dims 4hw + {0,1} -> m-tile 2hw (rows gid, gid+8); dims 4hw + {2,3} -> m-tile 2hw + 1
+          const uint32_t a_even[4] = {r[0][0], r[0][1], r[1][0], r[1][1]};
+          const uint32_t a_odd[4] = {r[0][2], r[0][3], r[1][2], r[1][3]};
+          mma_f16(o_acc[2 * hw], a_even, pb[u][0], pb[u][1]);
+          mma_f16(o_acc[2 * hw + 1], a_odd, pb[u][0], pb[u][1]);
         }
-        // dims 4hw + {0,1} -> m-tile 2hw (rows gid, gid+8); dims 4hw + {2,3} -> m-tile 2hw + 1
-        const uint32_t a_even[4] = {r[0][0], r[0][1], r[1][0], r[1][1]};
-        const uint32_t a_odd[4] = {r[0][2], r[0][3], r[1][2], r[1][3]};
-        mma_m16n8k16<__half>(o_acc[2 * hw], a_even, pb0, pb1);
-        mma_m16n8k16<__half>(o_acc[2 * hw + 1], a_odd, pb0, pb1);
       }
     } else {
       // 2-bit codes: one 16-bit half-word = 8 dims
@@ -557,24 +638,28 @@ __global__ void __launch_bounds__(kMmaThreads, D >= 256 ? 2 : 3) tq_decode_split
 #pragma unroll
       for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
         const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
-        uint32_t r[2][8];
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-          const uint32_t x = prmt(vw[2 * pr][hw / 2], vw[2 * pr + 1][hw / 2], sel);
-          const uint32_t y = x >> 10;
-          r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00030003u, kM0), kM0), sc_pair[pr], zp_pair[pr]);
-          r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000C000Cu, kM1), kM1), sc_pair[pr], zp_pair[pr]);
-          r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00300030u, kM2), kM2), sc_pair[pr], zp_pair[pr]);
-          r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00C000C0u, kM3), kM3), sc_pair[pr], zp_pair[pr]);
-          r[pr][4] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x03000300u, kM4), kM4), sc_pair[pr], zp_pair[pr]);
-          r[pr][5] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00030003u, kM0), kM0), sc_pair[pr], zp_pair[pr]);
-          r[pr][6] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000C000Cu, kM1), kM1), sc_pair[pr], zp_pair[pr]);
-          r[pr][7] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00300030u, kM2), kM2), sc_pair[pr], zp_pair[pr]);
-        }
+        for (int u = 0; u < U; ++u) {
+          uint32_t r[2][8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {  // dims 8hw + {2q, 2q+1} -> m-tile 4hw + q
-          const uint32_t a[4] = {r[0][2 * q], r[0][2 * q + 1], r[1][2 * q], r[1][2 * q + 1]};
-          mma_m16n8k16<__half>(o_acc[4 * hw + q], a, pb0, pb1);
+          for (int pr = 0; pr < 2; ++pr) {
+            const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
+            const uint32_t y = x >> 10;
+            const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
+            r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00030003u, kM0), kM0), scl, zpt);
+            r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000C000Cu, kM1), kM1), scl, zpt);
+            r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00300030u, kM2), kM2), scl, zpt);
+            r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00C000C0u, kM3), kM3), scl, zpt);
+            r[pr][4] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x03000300u, kM4), kM4), scl, zpt);
+            r[pr][5] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00030003u, kM0), kM0), scl, zpt);
+            r[pr][6] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000C000Cu, kM1), kM1), scl, zpt);
+            r[pr][7] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00300030u, kM2), kM2), scl, zpt);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // dims 8hw + {2q, 2q+1} -> m-tile 4hw + q
+            const uint32_t a[4] = {r[0][2 * q], r[0][2 * q + 1], r[1][2 * q], r[1][2 * q + 1]};
+            mma_f16(o_acc[4 * hw + q], a, pb[u][0], pb[u][1]);
+          }
         }
       }
     }
