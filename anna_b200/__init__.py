@@ -3,6 +3,7 @@
 Everything computes through ``libanna_b200_kv.so`` (hand-written CUDA for sm_100a, C ABI in
 ``include/anna_b200_kv.h``); there is no CPU fallback.
 """
+from .attention import grouped_query_attention
 from .cache import KVCacheConfig, Qwen3DynamicCache, Qwen3PageAllocator
 from .fused_ops import (
     gqa_decode_fused_is_available,
@@ -28,5 +29,5 @@ __all__ = [
     "gqa_decode_splitkv_fused_is_available", "gqa_decode_splitkv_fused_out_is_available",
     "gqa_decode_splitkv_turboquant_fused_out_is_available", "paged_gqa_decode_fused_is_available",
     "run_gqa_decode_fused", "run_gqa_decode_splitkv_fused", "run_gqa_decode_splitkv_fused_out",
-    "run_gqa_decode_splitkv_turboquant_fused_out", "run_paged_gqa_decode_fused",
+    "run_gqa_decode_splitkv_turboquant_fused_out", "run_paged_gqa_decode_fused", "grouped_query_attention",
 ]

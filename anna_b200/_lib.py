@@ -53,6 +53,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64,
                                 c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i64,
                                 c_i32, c_f32, c_i32, c_ptr]),
+    "anna_gqa_prefill": (c_i32, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64,
+                                 c_i64, c_i64, c_i32, c_i32, c_i32, c_i32, c_i64, c_i32, c_f32, c_i32, c_i32, c_ptr]),
     "anna_tq_page_layout": (c_i32, [c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.POINTER(TqLayout)]),
     "anna_tq_append": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_ptr, c_ptr,
                                c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i64,

@@ -1,0 +1,287 @@
+// Multi-token (prefill / chunked-prefill) grouped-query attention over dense K/V, tensor cores, 16-bit dtypes.
+//
+// Semantics of grouped_query_attention (src/anna/model/ops.py:1552-1574) for the masks the model builds
+// (ops.py:1840-1852, :2008-2016): row r sees its first key_lengths[r] keys (visible_mask / key_padding_mask in prefix
+// form); with the causal flag, query t of the chunk sits at position key_lengths[r] - T + t and sees keys up to and
+// including its own position.  softmax in fp32, output in the query dtype, rows without any visible key give zeros.
+//
+// A CTA (4 warps) owns 64 query rows of one query head; a warp owns 16 of them.  Per 64-key tile:
+//   K / V tile --cp.async (2 stages, zero-filled past the row's keys)--> xor-swizzled shared memory
+//   S[16 x 64]  = Q . K^T          Q fragments by ldmatrix from the staged query tile, K by ldmatrix (8 n-tiles x D/16)
+//   mask, online softmax in fp32 on the C fragments (row reductions over the 4 lanes of a quad)
+//   O[16 x D]  += P . V            P re-packed from the C fragments (no shuffle), V by ldmatrix.trans
+// Key tiles above the causal diagonal of the CTA's last query row are never loaded.
+#include "mma_utils.cuh"
+
+namespace anna {
+
+constexpr int kPrefillWarps = 4;
+constexpr int kPrefillThreads = kPrefillWarps * 32;
+constexpr int kPrefillRows = kPrefillWarps * 16;  // query rows per CTA
+
+struct PrefillParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const int64_t* key_lengths;
+  int64_t q_stride_b, q_stride_h, q_stride_t;
+  int64_t kv_stride_b, kv_stride_h, kv_stride_t;
+  int64_t out_stride_b, out_stride_h, out_stride_t;
+  int q_len, groups, causal;
+  int64_t key_len;
+  float scale_log2;  // scaling * log2(e)
+};
+
+template <int D>
+struct PrefillCfg {
+  static constexpr int kKeys = D >= 256 ? 32 : 64;      // keys per tile
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kChunks = D / 8;                  // 16-byte chunks per row
+  static constexpr int kQBytes = kPrefillRows * kRowBytes;
+  static constexpr int kTileBytes = kKeys * kRowBytes;
+  static constexpr int kSmemBytes = kQBytes + 4 * kTileBytes;  // Q | K0 K1 | V0 V1
+  static constexpr int kSteps = D / 16;
+  static constexpr int kNTiles = kKeys / 8;
+};
+
+// rows [row0, row0 + rows) of a [*, D] matrix with token stride `stride` -> swizzled tile; rows >= limit are zero-filled
+template <typename T, int D>
+__device__ __forceinline__ void prefill_load_tile(uint32_t dst, const T* base, int64_t stride, int64_t row0, int rows,
+                                                  int64_t limit) {
+  constexpr int kChunks = D / 8;
+  for (int item = threadIdx.x; item < rows * kChunks; item += kPrefillThreads) {
+    const int r = item / kChunks;
+    const int c = item % kChunks;
+    const bool ok = row0 + r < limit;
+    const T* src = base + (ok ? (row0 + r) * stride + c * 8 : 0);
+    cp_async16(dst + swizzled_offset(r, c, D * 2), src, ok ? 16 : 0);
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrefillThreads) gqa_prefill_mma_kernel(const PrefillParams p) {
+  using Cfg = PrefillCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int m0 = blockIdx.x * kPrefillRows;
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int kvh = hq / p.groups;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int gid = lane >> 2;
+  const int tig = lane & 3;
+  const int mi = lane >> 3;  // ldmatrix: lanes 8i .. 8i+7 give the row addresses of matrix i
+  const int l8 = lane & 7;
+
+  int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
+  n_keys = max((int64_t)0, min(n_keys, p.key_len));
+  const int64_t past = n_keys - p.q_len;  // position of the chunk's first query (negative: the row is shorter than the chunk)
+  const int last_row = min(m0 + kPrefillRows, p.q_len) - 1;
+  int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
+  cta_limit = max(cta_limit, (int64_t)0);
+  const int n_tiles = (int)((cta_limit + Cfg::kKeys - 1) / Cfg::kKeys);
+
+  const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + hq * p.q_stride_h;
+  const T* k_base = reinterpret_cast<const T*>(p.k) + b * p.kv_stride_b + kvh * p.kv_stride_h;
+  const T* v_base = reinterpret_cast<const T*>(p.v) + b * p.kv_stride_b + kvh * p.kv_stride_h;
+  const uint32_t q_s = smem_u32(smem_raw);
+  const uint32_t k_s = q_s + Cfg::kQBytes;
+  const uint32_t v_s = k_s + 2 * Cfg::kTileBytes;
+
+  prefill_load_tile<T, D>(q_s, q_base, p.q_stride_t, m0, kPrefillRows, p.q_len);
+  if (n_tiles > 0) {
+    prefill_load_tile<T, D>(k_s, k_base, p.kv_stride_t, 0, Cfg::kKeys, n_keys);
+    prefill_load_tile<T, D>(v_s, v_base, p.kv_stride_t, 0, Cfg::kKeys, n_keys);
+  }
+  cp_async_commit();
+
+  const int row_lo = m0 + warp * 16 + gid;
+  const int row_hi = row_lo + 8;
+  const int64_t lim_lo = p.causal ? min(n_keys, past + row_lo + 1) : n_keys;
+  const int64_t lim_hi = p.causal ? min(n_keys, past + row_hi + 1) : n_keys;
+
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o[j][r] = 0.0f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) {
+      const int64_t key0 = (int64_t)(it + 1) * Cfg::kKeys;
+      prefill_load_tile<T, D>(k_s + (stage ^ 1) * Cfg::kTileBytes, k_base, p.kv_stride_t, key0, Cfg::kKeys, n_keys);
+      prefill_load_tile<T, D>(v_s + (stage ^ 1) * Cfg::kTileBytes, v_base, p.kv_stride_t, key0, Cfg::kKeys, n_keys);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t k_tile = k_s + stage * Cfg::kTileBytes;
+    const uint32_t v_tile = v_s + stage * Cfg::kTileBytes;
+
+    // ---- S = Q . K^T ---------------------------------------------------------------------------------------------------
+    float s[Cfg::kNTiles][4];
+#pragma unroll
+    for (int j = 0; j < Cfg::kNTiles; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s[j][r] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < Cfg::kSteps; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + swizzled_offset(warp * 16 + (mi & 1) * 8 + l8, 2 * ks + (mi >> 1), Cfg::kRowBytes));
+#pragma unroll
+      for (int jp = 0; jp < Cfg::kNTiles / 2; ++jp) {
+        uint32_t bk[4];
+        ldmatrix_x4(bk, k_tile + swizzled_offset(jp * 16 + (mi >> 1) * 8 + l8, 2 * ks + (mi & 1), Cfg::kRowBytes));
+        mma_m16n8k16<T>(s[2 * jp], a, bk[0], bk[1]);
+        mma_m16n8k16<T>(s[2 * jp + 1], a, bk[2], bk[3]);
+      }
+    }
+
+    // ---- mask + online softmax (log2 units) -----------------------------------------------------------------------------
+    const int64_t key_base = (int64_t)it * Cfg::kKeys + 2 * tig;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < Cfg::kNTiles; ++j) {
+      const int64_t key = key_base + 8 * j;
+      s[j][0] = key < lim_lo ? s[j][0] * p.scale_log2 : -INFINITY;
+      s[j][1] = key + 1 < lim_lo ? s[j][1] * p.scale_log2 : -INFINITY;
+      s[j][2] = key < lim_hi ? s[j][2] * p.scale_log2 : -INFINITY;
+      s[j][3] = key + 1 < lim_hi ? s[j][3] * p.scale_log2 : -INFINITY;
+      mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+    }
+#pragma unroll
+    for (int d = 1; d <= 2; d <<= 1) {
+      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+    }
+    float alpha[2], m_safe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_safe[r] = m_new == -INFINITY ? 0.0f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_safe[r]);  // 0 on the first visible tile (m_run = -inf)
+      m_run[r] = m_new;
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= alpha[0];
+      o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1];
+      o[j][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int j = 0; j < Cfg::kNTiles; ++j) {
+      s[j][0] = exp2f(s[j][0] - m_safe[0]);
+      s[j][1] = exp2f(s[j][1] - m_safe[0]);
+      s[j][2] = exp2f(s[j][2] - m_safe[1]);
+      s[j][3] = exp2f(s[j][3] - m_safe[1]);
+      l_run[0] += s[j][0] + s[j][1];
+      l_run[1] += s[j][2] + s[j][3];
+    }
+
+    // ---- O += P . V ------------------------------------------------------------------------------------------------------
+#pragma unroll
+    for (int kk = 0; kk < Cfg::kKeys / 16; ++kk) {
+      const uint32_t a[4] = {pack2<T>(s[2 * kk][0], s[2 * kk][1]), pack2<T>(s[2 * kk][2], s[2 * kk][3]),
+                             pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        uint32_t bv[4];
+        ldmatrix_x4_trans(bv, v_tile + swizzled_offset(kk * 16 + (mi & 1) * 8 + l8, 2 * dp + (mi >> 1), Cfg::kRowBytes));
+        mma_m16n8k16<T>(o[2 * dp], a, bv[0], bv[1]);
+        mma_m16n8k16<T>(o[2 * dp + 1], a, bv[2], bv[3]);
+      }
+    }
+    __syncthreads();  // the stage is refilled by the next iteration's loads
+  }
+  cp_async_wait<0>();
+
+  // ---- normalise and store -------------------------------------------------------------------------------------------------
+#pragma unroll
+  for (int d = 1; d <= 2; d <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+  }
+  const float inv_lo = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
+  const float inv_hi = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
+  T* out_base = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + hq * p.out_stride_h;
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    const int col = 8 * j + 2 * tig;
+    if (row_lo < p.q_len)
+      *reinterpret_cast<uint32_t*>(out_base + row_lo * p.out_stride_t + col) = pack2<T>(o[j][0] * inv_lo, o[j][1] * inv_lo);
+    if (row_hi < p.q_len)
+      *reinterpret_cast<uint32_t*>(out_base + row_hi * p.out_stride_t + col) = pack2<T>(o[j][2] * inv_hi, o[j][3] * inv_hi);
+  }
+}
+
+template <typename T, int D>
+static int launch_prefill(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
+  using Cfg = PrefillCfg<D>;
+  auto kernel = gqa_prefill_mma_kernel<T, D>;
+  static bool configured[64] = {};
+  int device = 0;
+  ANNA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !configured[device]) {
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  dim3 grid((unsigned)((p.q_len + kPrefillRows - 1) / kPrefillRows), (unsigned)q_heads, (unsigned)batch);
+  kernel<<<grid, kPrefillThreads, Cfg::kSmemBytes, stream>>>(p);
+  return check_launch("gqa_prefill_mma_kernel");
+}
+
+}  // namespace anna
+
+using namespace anna;
+
+extern "C" int anna_gqa_prefill(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                                const void* key, const void* value, int64_t kv_stride_b, int64_t kv_stride_h,
+                                int64_t kv_stride_t, const int64_t* key_lengths, void* out, int64_t out_stride_b,
+                                int64_t out_stride_h, int64_t out_stride_t, int batch, int q_heads, int kv_heads,
+                                int q_len, int64_t key_len, int head_dim, float scaling, int causal, int dtype,
+                                anna_stream_t stream) {
+  ANNA_REQUIRE(q && key && value && out, "anna_gqa_prefill: null pointer argument");
+  ANNA_REQUIRE(batch > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
+               "anna_gqa_prefill: query heads (%d) must be a positive multiple of kv heads (%d)", q_heads, kv_heads);
+  ANNA_REQUIRE(q_len > 0 && key_len >= 0, "anna_gqa_prefill: bad lengths (q_len %d, key_len %lld)", q_len,
+               (long long)key_len);
+  ANNA_REQUIRE(batch <= 65535 && q_heads <= 65535, "anna_gqa_prefill: batch and heads are limited to 65535");
+  if (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16)
+    return set_error(ANNA_ERR_UNSUPPORTED, "anna_gqa_prefill: 16-bit dtypes only (got dtype code %d)", dtype);
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+    return set_error(ANNA_ERR_UNSUPPORTED, "anna_gqa_prefill: head_dim %d (64, 128 and 256 are built)", head_dim);
+  // 16-byte copies: every row start has to be 16-byte aligned
+  const int64_t strides[] = {q_stride_b, q_stride_h, q_stride_t, kv_stride_b, kv_stride_h, kv_stride_t};
+  for (int64_t s : strides) ANNA_REQUIRE(s % 8 == 0, "anna_gqa_prefill: q / k / v strides must be multiples of 8 elements");
+  ANNA_REQUIRE(out_stride_b % 2 == 0 && out_stride_h % 2 == 0 && out_stride_t % 2 == 0,
+               "anna_gqa_prefill: output strides must be even");
+  ANNA_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)key % 16 == 0 && (uintptr_t)value % 16 == 0 && (uintptr_t)out % 4 == 0,
+               "anna_gqa_prefill: q / k / v must be 16-byte aligned");
+  PrefillParams p{};
+  p.q = q; p.k = key; p.v = value; p.out = out; p.key_lengths = key_lengths;
+  p.q_stride_b = q_stride_b; p.q_stride_h = q_stride_h; p.q_stride_t = q_stride_t;
+  p.kv_stride_b = kv_stride_b; p.kv_stride_h = kv_stride_h; p.kv_stride_t = kv_stride_t;
+  p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_t = out_stride_t;
+  p.q_len = q_len; p.groups = q_heads / kv_heads; p.causal = causal != 0;
+  p.key_len = key_len;
+  p.scale_log2 = scaling * 1.4426950408889634f;
+  cudaStream_t s = (cudaStream_t)stream;
+#define ANNA_PREFILL_CASE(TYPE, DIM) \
+  if (head_dim == DIM) return launch_prefill<TYPE, DIM>(p, batch, q_heads, s);
+  if (dtype == ANNA_DTYPE_BF16) {
+    ANNA_PREFILL_CASE(__nv_bfloat16, 64) ANNA_PREFILL_CASE(__nv_bfloat16, 128) ANNA_PREFILL_CASE(__nv_bfloat16, 256)
+  } else {
+    ANNA_PREFILL_CASE(__half, 64) ANNA_PREFILL_CASE(__half, 128) ANNA_PREFILL_CASE(__half, 256)
+  }
+#undef ANNA_PREFILL_CASE
+  return set_error(ANNA_ERR_UNSUPPORTED, "anna_gqa_prefill: unsupported head_dim %d", head_dim);
+}

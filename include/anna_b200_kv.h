@@ -148,6 +148,21 @@ int anna_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const
                     int chunk_tokens, int32_t* split_counters, int batch, int q_heads, int kv_heads, int64_t key_len,
                     int head_dim, float scaling, int dtype, anna_stream_t stream);
 
+/*
+ * Multi-token (prefill / chunked prefill) GQA over dense K/V: q [B, Hq, T, D], key / value [B, Hkv, L, D], out
+ * [B, Hq, T, D], element strides for batch / head / token, last dim contiguous.  Replaces grouped_query_attention
+ * (src/anna/model/ops.py:1552-1574) for the masks the model builds (ops.py:1840-1852, :2008-2016):
+ *   key_lengths int64 [B] (or NULL = L): row r sees its first key_lengths[r] keys (visible_mask / key_padding_mask in
+ *   prefix form); causal != 0: query t sits at position key_lengths[r] - T + t and sees keys up to its own position.
+ * softmax in fp32; a query without any visible key gives zeros.  16-bit dtypes, head_dim 64 / 128 / 256 (else
+ * ANNA_ERR_UNSUPPORTED); q / k / v 16-byte aligned with strides that are multiples of 8 elements.
+ */
+int anna_gqa_prefill(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t, const void* key,
+                     const void* value, int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t,
+                     const int64_t* key_lengths, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                     int64_t out_stride_t, int batch, int q_heads, int kv_heads, int q_len, int64_t key_len,
+                     int head_dim, float scaling, int causal, int dtype, anna_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * TurboQuant packed paged cache.
  *

@@ -283,6 +283,36 @@ def gqa_decode_blas(q, k, v, scaling: float, gate=None) -> np.ndarray:
     return out.astype(np.float32)
 
 
+def grouped_query_attention(q, k, v, scaling: float, *, causal_mask=None, visible_mask=None,
+                            key_padding_mask=None) -> np.ndarray:
+    """Multi-token attention with the reference's masks (ops.py:1552-1574), numpy fp32.
+
+    q [B, Hq, T, D], k/v [B, Hkv, L, D]; causal_mask bool [B, T, L] (True = hidden), visible_mask and
+    key_padding_mask bool [B, L] (True = visible).  softmax in fp32.  A query row with every key hidden gives NaN in
+    the reference (softmax of all -inf); this restatement returns zeros there and the tests avoid comparing such rows
+    with the reference itself."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    batch, hq, t, dim = q.shape
+    hkv = k.shape[1]
+    grouped = q.reshape(batch, hkv, hq // hkv, t, dim)
+    scores = np.matmul(grouped, k[:, :, None].transpose(0, 1, 2, 4, 3)) * np.float32(scaling)
+    hidden = np.zeros((batch, 1, 1, t, k.shape[2]), dtype=bool)
+    if causal_mask is not None:
+        hidden |= np.asarray(causal_mask, dtype=bool)[:, None, None, :, :]
+    if visible_mask is not None:
+        hidden |= ~np.asarray(visible_mask, dtype=bool)[:, None, None, None, :]
+    if key_padding_mask is not None:
+        hidden |= ~np.asarray(key_padding_mask, dtype=bool)[:, None, None, None, :]
+    scores = np.where(hidden, -np.inf, scores).astype(np.float32)
+    top = scores.max(axis=-1, keepdims=True)
+    top = np.where(np.isfinite(top), top, 0.0)
+    probs = np.exp(scores - top, dtype=np.float32)
+    denom = probs.sum(axis=-1, keepdims=True)
+    probs = np.divide(probs, denom, out=np.zeros_like(probs), where=denom > 0)
+    out = np.matmul(probs, v[:, :, None])
+    return out.reshape(batch, hq, t, dim).astype(np.float32)
+
+
 from .kv_state import (  # noqa: E402
     OracleLayerAllocator,
     OracleTurboQuantRow,

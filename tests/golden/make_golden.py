@@ -48,6 +48,7 @@ def config1_inputs(seed: int = 1):
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", required=True, help="checkout of funkpopo/Anna to import from")
+    parser.add_argument("--only", choices=("prefill",), default=None, help="write just this fixture")
     args = parser.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
 
@@ -56,6 +57,35 @@ def main() -> None:
     turboquant_core_shim.install()
     from anna.model import ops as ref_ops
     from anna.model import turboquant as ref_tq
+
+    # ---- 5. multi-token attention with the model's masks (ops.py:1552-1574, masks as in :1840-1852, :2008-2016) ------
+    prefill = {}
+    gen = torch.Generator().manual_seed(31)
+    cases = {"chunk": (2, 4, 2, 70, 160, 128, (160, 101), True), "full": (2, 4, 4, 33, 33, 64, (33, 20), True),
+             "padding_only": (3, 6, 2, 5, 90, 256, (90, 64, 7), False)}
+    for name, (batch, heads, kv_heads, q_len, key_len, dim, lengths, causal) in cases.items():
+        # inputs are fp16-representable so that the fixture stores them exactly in half the space
+        q = torch.randn(batch, heads, q_len, dim, generator=gen).half().float()
+        k = torch.randn(batch, kv_heads, key_len, dim, generator=gen).half().float()
+        v = torch.randn(batch, kv_heads, key_len, dim, generator=gen).half().float()
+        visible = torch.tensor(lengths, dtype=torch.long)
+        past = visible - q_len
+        positions = torch.arange(key_len)[None, :]
+        visible_mask = positions < visible[:, None]
+        causal_mask = None
+        if causal:
+            q_positions = past[:, None] + torch.arange(q_len)[None, :]
+            causal_mask = positions[:, None, :] > q_positions[:, :, None]
+        ref = ref_ops.grouped_query_attention(q, k, v, scaling=dim ** -0.5, causal_mask=causal_mask,
+                                              visible_mask=visible_mask)
+        prefill[f"{name}_q"], prefill[f"{name}_k"], prefill[f"{name}_v"] = (t.numpy().astype(np.float16) for t in (q, k, v))
+        prefill[f"{name}_lengths"] = visible.numpy()
+        prefill[f"{name}_causal"] = np.array(int(causal))
+        prefill[f"{name}_ref"] = ref.numpy()
+    np.savez_compressed(HERE / "prefill_attention.npz", **prefill)
+    if args.only == "prefill":
+        print("prefill fixture written to", HERE)
+        return
 
     # ---- 1. value quantizer (turboquant.py:199-252) --------------------------------------------------------------
     values = {}

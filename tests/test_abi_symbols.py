@@ -36,7 +36,7 @@ def library():
 def test_header_declares_the_expected_entry_points():
     names = set(_declarations())
     assert {"anna_kv_last_error", "anna_kv_abi_version", "anna_decode_plan", "anna_paged_kv_write",
-            "anna_paged_gqa_decode", "anna_gqa_decode", "anna_tq_page_layout", "anna_tq_append",
+            "anna_paged_gqa_decode", "anna_gqa_decode", "anna_gqa_prefill", "anna_tq_page_layout", "anna_tq_append",
             "anna_tq_paged_decode", "anna_tq_materialize", "anna_gqa_decode_turboquant_values",
             "anna_tq_decode_plan", "anna_kv_device_faults", "anna_tq_tensor_row_bytes",
             "anna_tq_tensor_quantize", "anna_tq_tensor_dequantize", "anna_tq_gather_dense", "anna_kv_selftest_wait_expiry"} <= names

@@ -1,0 +1,102 @@
+"""GPU parity of multi-token grouped-query attention (prefill / chunked prefill) against the CPU oracle and the
+fixture computed by the reference's own grouped_query_attention (src/anna/model/ops.py:1552-1574)."""
+from __future__ import annotations
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from anna_b200 import grouped_query_attention
+from anna_b200 import attention as attention_module
+from tests.helpers import ATOL, error_stats, to_np
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _model_masks(lengths: torch.Tensor, q_len: int, key_len: int, causal: bool):
+    """The masks Qwen3Attention builds (ops.py:1840-1852, :2008-2016) for a chunk that ends at each row's last key."""
+    positions = torch.arange(key_len, device=lengths.device)[None, :]
+    visible = positions < lengths[:, None]
+    causal_mask = None
+    if causal:
+        q_positions = (lengths - q_len)[:, None] + torch.arange(q_len, device=lengths.device)[None, :]
+        causal_mask = positions[:, None, :] > q_positions[:, :, None]
+    return causal_mask, visible
+
+
+def _oracle(q, k, v, lengths, causal):
+    causal_mask, visible = _model_masks(lengths.cpu(), q.shape[2], k.shape[2], causal)
+    return oracle.grouped_query_attention(to_np(q), to_np(k), to_np(v), q.shape[3] ** -0.5,
+                                          causal_mask=None if causal_mask is None else causal_mask.numpy(),
+                                          visible_mask=visible.numpy())
+
+
+@pytest.mark.parametrize("dtype,heads,kv_heads,dim,q_len,key_len,lengths,causal", [
+    (torch.bfloat16, 8, 2, 128, 70, 200, (200, 133), True),      # ragged chunk: 70 queries, not a multiple of 64
+    (torch.bfloat16, 32, 8, 128, 256, 1100, (1100, 777), True),  # several key tiles and query tiles
+    (torch.float16, 16, 2, 256, 48, 300, (300, 48, 129), True),  # head_dim 256 (32-key tiles), a row that is all chunk
+    (torch.float16, 4, 4, 64, 33, 33, (33, 20), True),           # a row shorter than the chunk: queries without keys
+    (torch.bfloat16, 6, 2, 128, 5, 90, (90, 64, 7), False),      # key padding only
+    (torch.float32, 8, 2, 128, 16, 48, (48, 30), True),          # fp32 cache: row-by-row path through the decode kernel
+])
+def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len, key_len, lengths, causal):
+    gen = torch.Generator().manual_seed(heads * 1000 + q_len)
+    batch = len(lengths)
+    q = torch.randn(batch, heads, q_len, dim, generator=gen).to(dtype).to(cuda_device)
+    k = torch.randn(batch, kv_heads, key_len, dim, generator=gen).to(dtype).to(cuda_device)
+    v = torch.randn(batch, kv_heads, key_len, dim, generator=gen).to(dtype).to(cuda_device)
+    n = torch.tensor(lengths, dtype=torch.long, device=cuda_device)
+    causal_mask, visible = _model_masks(n, q_len, key_len, causal)
+    out = grouped_query_attention(q, k, v, scaling=dim ** -0.5, causal_mask=causal_mask, visible_mask=visible,
+                                  check_masks=True)
+    assert out.shape == q.shape and out.dtype == dtype
+    expected = _oracle(q, k, v, n, causal)
+    max_abs, rel_l2 = error_stats(to_np(out), expected)
+    assert max_abs <= ATOL[dtype], (max_abs, rel_l2)
+    # the same call with the lengths given directly (no mask is read)
+    again = grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=n, causal=causal)
+    assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("case", ["chunk", "full", "padding_only"])
+def test_prefill_matches_reference_fixture(cuda_device, case):
+    data = np.load(GOLDEN / "prefill_attention.npz")
+    q, k, v = (torch.from_numpy(data[f"{case}_{name}"]).to(cuda_device) for name in ("q", "k", "v"))  # fp16, exact
+    n = torch.from_numpy(data[f"{case}_lengths"]).to(cuda_device)
+    out = grouped_query_attention(q, k, v, scaling=q.shape[3] ** -0.5, key_lengths=n,
+                                  causal=bool(data[f"{case}_causal"]))
+    ref = data[f"{case}_ref"]
+    hidden = ~np.isfinite(ref)
+    got = to_np(out)
+    assert float(np.abs(got[~hidden] - ref[~hidden]).max()) <= ATOL[torch.float16]
+    assert not got[hidden].any()
+
+
+def test_tensor_core_and_row_paths_agree_on_strided_views(cuda_device):
+    """Both kernels on the same operands, K/V being views of a longer cache buffer (token stride > head_dim rows)."""
+    gen = torch.Generator().manual_seed(5)
+    batch, heads, kv_heads, dim, q_len, key_len = 2, 8, 2, 128, 40, 150
+    q = torch.randn(batch, q_len, heads, dim, generator=gen).to(torch.bfloat16).to(cuda_device).transpose(1, 2)
+    cache = torch.randn(2, batch, kv_heads, 256, dim, generator=gen).to(torch.bfloat16).to(cuda_device)
+    k, v = cache[0, :, :, :key_len], cache[1, :, :, :key_len]
+    n = torch.tensor([150, 97], dtype=torch.long, device=cuda_device)
+    fast = attention_module._prefill_tensor_core(q, k, v, n, dim ** -0.5, True)
+    slow = attention_module._prefill_by_rows(q, k, v, n, dim ** -0.5, True)
+    assert float((fast.float() - slow.float()).abs().max()) <= ATOL[torch.bfloat16]
+
+
+def test_masks_of_another_shape_are_rejected(cuda_device):
+    q = torch.zeros(1, 2, 4, 64, dtype=torch.float16, device=cuda_device)
+    k = torch.zeros(1, 2, 8, 64, dtype=torch.float16, device=cuda_device)
+    holes = torch.tensor([[True, False, True, True, True, True, True, True]], device=cuda_device)
+    with pytest.raises(ValueError, match="suffix"):
+        grouped_query_attention(q, k, k, scaling=1.0, visible_mask=holes, check_masks=True)
+    band = torch.zeros(1, 4, 8, dtype=torch.bool, device=cuda_device)
+    with pytest.raises(ValueError, match="causal"):
+        grouped_query_attention(q, k, k, scaling=1.0, causal_mask=band, check_masks=True)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        grouped_query_attention(q.cpu(), k.cpu(), k.cpu(), scaling=1.0)

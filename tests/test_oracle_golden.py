@@ -177,3 +177,29 @@ def test_mse_variant_round_trip_quality(dim, bits):
     assert mse < 0.5
     coarse = oracle.dequantize_keys(*(lambda r: (r[0], None, r[2], None))(oracle.quantize_keys(x, 2, "mse")), 2, "mse")
     assert mse <= float(((coarse - x) ** 2).mean()) + 1e-6
+
+
+def _masks(lengths: np.ndarray, q_len: int, key_len: int, causal: bool):
+    positions = np.arange(key_len)[None, :]
+    visible = positions < lengths[:, None]
+    causal_mask = None
+    if causal:
+        q_positions = (lengths - q_len)[:, None] + np.arange(q_len)[None, :]
+        causal_mask = positions[:, None, :] > q_positions[:, :, None]
+    return causal_mask, visible
+
+
+@pytest.mark.parametrize("case", ["chunk", "full", "padding_only"])
+def test_grouped_query_attention_matches_reference(case):
+    """oracle.grouped_query_attention against outputs of the reference's own function (ops.py:1552-1574) run with the
+    masks the model builds."""
+    data = np.load(GOLDEN / "prefill_attention.npz")
+    q, k, v = (data[f"{case}_{n}"].astype(np.float32) for n in ("q", "k", "v"))
+    lengths = data[f"{case}_lengths"]
+    causal_mask, visible = _masks(lengths, q.shape[2], k.shape[2], bool(data[f"{case}_causal"]))
+    out = oracle.grouped_query_attention(q, k, v, q.shape[3] ** -0.5, causal_mask=causal_mask, visible_mask=visible)
+    ref = data[f"{case}_ref"]
+    hidden = ~np.isfinite(ref)  # queries without a visible key: NaN in the reference, zeros here
+    assert hidden.any() == (case == "full")
+    np.testing.assert_allclose(out[~hidden], ref[~hidden], atol=2e-5, rtol=1e-5)
+    assert not out[hidden].any()
