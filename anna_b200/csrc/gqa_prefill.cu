@@ -15,6 +15,28 @@
 
 namespace anna {
 
+// mma.sync m16n8k16 without the volatile qualifier (a pure function of its operands): the compiler may then move the
+// independent accumulations around the fragment loads, whose order is fixed by hand below.
+template <typename T>
+__device__ __forceinline__ void mma_pure(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_pure<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_pure<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int kPrefillWarps = 4;
 constexpr int kPrefillThreads = kPrefillWarps * 32;
 constexpr int kPrefillRows = kPrefillWarps * 16;  // query rows per CTA
@@ -35,7 +57,13 @@ struct PrefillParams {
 
 template <int D>
 struct PrefillCfg {
-  static constexpr int kKeys = D >= 256 ? 32 : 64;      // keys per tile
+#ifndef ANNA_PREFILL_KEYS128
+#define ANNA_PREFILL_KEYS128 64
+#endif
+#ifndef ANNA_PREFILL_CTAS
+#define ANNA_PREFILL_CTAS 2
+#endif
+  static constexpr int kKeys = D >= 256 ? 32 : ANNA_PREFILL_KEYS128;      // keys per tile
   static constexpr int kRowBytes = D * 2;
   static constexpr int kChunks = D / 8;                  // 16-byte chunks per row
   static constexpr int kQBytes = kPrefillRows * kRowBytes;
@@ -60,7 +88,7 @@ __device__ __forceinline__ void prefill_load_tile(uint32_t dst, const T* base, i
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kPrefillThreads) gqa_prefill_mma_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_CTAS) gqa_prefill_mma_kernel(const PrefillParams p) {
   using Cfg = PrefillCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int m0 = blockIdx.x * kPrefillRows;
@@ -130,16 +158,29 @@ __global__ void __launch_bounds__(kPrefillThreads) gqa_prefill_mma_kernel(const 
     for (int j = 0; j < Cfg::kNTiles; ++j)
 #pragma unroll
       for (int r = 0; r < 4; ++r) s[j][r] = 0.0f;
+    {
+      // fragment loads run one item ahead of the MMAs that consume them (item = one k-step of one pair of n-tiles)
+      constexpr int kPairs = Cfg::kNTiles / 2;
+      constexpr int kItems = Cfg::kSteps * kPairs;
+      uint32_t a[2][4], bk[2][4];
+      auto load_a = [&](int ks, uint32_t (&dst)[4]) {
+        ldmatrix_x4(dst, q_s + swizzled_offset(warp * 16 + (mi & 1) * 8 + l8, 2 * ks + (mi >> 1), Cfg::kRowBytes));
+      };
+      auto load_b = [&](int ks, int jp, uint32_t (&dst)[4]) {
+        ldmatrix_x4(dst, k_tile + swizzled_offset(jp * 16 + (mi >> 1) * 8 + l8, 2 * ks + (mi & 1), Cfg::kRowBytes));
+      };
+      load_a(0, a[0]);
+      load_b(0, 0, bk[0]);
 #pragma unroll
-    for (int ks = 0; ks < Cfg::kSteps; ++ks) {
-      uint32_t a[4];
-      ldmatrix_x4(a, q_s + swizzled_offset(warp * 16 + (mi & 1) * 8 + l8, 2 * ks + (mi >> 1), Cfg::kRowBytes));
-#pragma unroll
-      for (int jp = 0; jp < Cfg::kNTiles / 2; ++jp) {
-        uint32_t bk[4];
-        ldmatrix_x4(bk, k_tile + swizzled_offset(jp * 16 + (mi >> 1) * 8 + l8, 2 * ks + (mi & 1), Cfg::kRowBytes));
-        mma_m16n8k16<T>(s[2 * jp], a, bk[0], bk[1]);
-        mma_m16n8k16<T>(s[2 * jp + 1], a, bk[2], bk[3]);
+      for (int item = 0; item < kItems; ++item) {
+        const int ks = item / kPairs, jp = item % kPairs;
+        if (item + 1 < kItems) {
+          const int ks1 = (item + 1) / kPairs, jp1 = (item + 1) % kPairs;
+          if (jp1 == 0) load_a(ks1, a[ks1 & 1]);
+          load_b(ks1, jp1, bk[(item + 1) & 1]);
+        }
+        mma_pure<T>(s[2 * jp], a[ks & 1], bk[item & 1][0], bk[item & 1][1]);
+        mma_pure<T>(s[2 * jp + 1], a[ks & 1], bk[item & 1][2], bk[item & 1][3]);
       }
     }
 
@@ -166,7 +207,7 @@ __global__ void __launch_bounds__(kPrefillThreads) gqa_prefill_mma_kernel(const 
     for (int r = 0; r < 2; ++r) {
       const float m_new = fmaxf(m_run[r], mx[r]);
       m_safe[r] = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[r] = exp2f(m_run[r] - m_safe[r]);  // 0 on the first visible tile (m_run = -inf)
+      alpha[r] = ex2_fast(m_run[r] - m_safe[r]);  // 0 on the first visible tile (m_run = -inf)
       m_run[r] = m_new;
       l_run[r] *= alpha[r];
     }
@@ -179,25 +220,31 @@ __global__ void __launch_bounds__(kPrefillThreads) gqa_prefill_mma_kernel(const 
     }
 #pragma unroll
     for (int j = 0; j < Cfg::kNTiles; ++j) {
-      s[j][0] = exp2f(s[j][0] - m_safe[0]);
-      s[j][1] = exp2f(s[j][1] - m_safe[0]);
-      s[j][2] = exp2f(s[j][2] - m_safe[1]);
-      s[j][3] = exp2f(s[j][3] - m_safe[1]);
+      s[j][0] = ex2_fast(s[j][0] - m_safe[0]);
+      s[j][1] = ex2_fast(s[j][1] - m_safe[0]);
+      s[j][2] = ex2_fast(s[j][2] - m_safe[1]);
+      s[j][3] = ex2_fast(s[j][3] - m_safe[1]);
       l_run[0] += s[j][0] + s[j][1];
       l_run[1] += s[j][2] + s[j][3];
     }
 
     // ---- O += P . V ------------------------------------------------------------------------------------------------------
+    {
+      constexpr int kDPairs = D / 16;
+      constexpr int kItems = (Cfg::kKeys / 16) * kDPairs;
+      uint32_t bv[2][4];
+      auto load_v = [&](int kk, int dp, uint32_t (&dst)[4]) {
+        ldmatrix_x4_trans(dst, v_tile + swizzled_offset(kk * 16 + (mi & 1) * 8 + l8, 2 * dp + (mi >> 1), Cfg::kRowBytes));
+      };
+      load_v(0, 0, bv[0]);
 #pragma unroll
-    for (int kk = 0; kk < Cfg::kKeys / 16; ++kk) {
-      const uint32_t a[4] = {pack2<T>(s[2 * kk][0], s[2 * kk][1]), pack2<T>(s[2 * kk][2], s[2 * kk][3]),
-                             pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3])};
-#pragma unroll
-      for (int dp = 0; dp < D / 16; ++dp) {
-        uint32_t bv[4];
-        ldmatrix_x4_trans(bv, v_tile + swizzled_offset(kk * 16 + (mi & 1) * 8 + l8, 2 * dp + (mi >> 1), Cfg::kRowBytes));
-        mma_m16n8k16<T>(o[2 * dp], a, bv[0], bv[1]);
-        mma_m16n8k16<T>(o[2 * dp + 1], a, bv[2], bv[3]);
+      for (int item = 0; item < kItems; ++item) {
+        const int kk = item / kDPairs, dp = item % kDPairs;
+        if (item + 1 < kItems) load_v((item + 1) / kDPairs, (item + 1) % kDPairs, bv[(item + 1) & 1]);
+        const uint32_t a[4] = {pack2<T>(s[2 * kk][0], s[2 * kk][1]), pack2<T>(s[2 * kk][2], s[2 * kk][3]),
+                               pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+        mma_pure<T>(o[2 * dp], a, bv[item & 1][0], bv[item & 1][1]);
+        mma_pure<T>(o[2 * dp + 1], a, bv[item & 1][2], bv[item & 1][3]);
       }
     }
     __syncthreads();  // the stage is refilled by the next iteration's loads

@@ -606,6 +606,36 @@ def run_reference_arm(args, dist: Dist) -> dict | None:
 # small cases for profiler captures (inputs larger than L2, well under a GB on the device, a handful of launches)
 
 
+def run_prefill_extra(device, *, batch: int = 8, q_heads: int = 16, kv_heads: int = 4, dim: int = 128,
+                      chunk: int = 2048, past: int = 8192, iters: int = 10) -> dict:
+    """cfg4's prefill side: causal attention of a 2048-token chunk over (past + chunk) dense bf16 keys, the operands
+    `update(require_dense_cache=True)` hands to grouped_query_attention.  Tensor-bound: flops against the measured
+    bf16 GEMM peak."""
+    from anna_b200 import grouped_query_attention
+
+    gen = torch.Generator(device=device).manual_seed(11)
+    total = past + chunk
+    q = torch.randn(batch, q_heads, chunk, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    k = torch.randn(batch, kv_heads, total, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    v = torch.randn(batch, kv_heads, total, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    lengths = torch.full((batch,), total, dtype=torch.long, device=device)
+    fn = lambda: grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=lengths, causal=True)  # noqa: E731
+    ms = _time_device(fn, iters=iters, warmup=3)
+    visible_pairs = batch * q_heads * (chunk * past + chunk * (chunk + 1) // 2)
+    flops = 4.0 * visible_pairs * dim
+    peak_tflops = None
+    try:
+        peak_tflops = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        pass
+    tflops = flops / (ms / 1e3) / 1e12
+    return {"workload": f"cfg4-like prefill attention: {batch} seq x {chunk}-token chunk over {past} cached tokens, "
+                        f"{q_heads}q/{kv_heads}kv heads, D={dim}, bf16 dense K/V",
+            "prefill_ms": ms, "prefill_tokens_per_s": batch * chunk / (ms / 1e3), "algorithmic_flops": flops,
+            "TFLOPs": tflops, "frac_of_measured_bf16_peak": None if peak_tflops is None else tflops / peak_tflops,
+            "bound": "tensor"}
+
+
 def run_profile_case(case: str, device) -> dict:
     from anna_b200 import KVCacheConfig, Qwen3DynamicCache, Qwen3PageAllocator, fused_ops
 
@@ -635,6 +665,9 @@ def run_profile_case(case: str, device) -> dict:
             query=q, key_pages=key_pages, value_pages=value_pages, page_table=table, visible_lengths=visible,
             scaling=dim ** -0.5)
         algo = sum(lengths) * kv_heads * 2 * dim * 2
+    elif case == "prefill":
+        result = run_prefill_extra(device, batch=2, iters=3)
+        return {"profile_case": case, **result}
     elif case == "tqappend":
         # bulk append: 2048 new tokens on top of 2176 cached ones, all 2048 oldest window/incoming tokens get packed
         batch, kv_heads, dim, page, tokens = 16, 8, 128, 16, 2048
@@ -684,7 +717,7 @@ def main() -> None:
     parser.add_argument("--kvhead-context", type=int, default=32768)
     parser.add_argument("--no-clock-spin", action="store_true",
                         help="do not repeat the decode launch while waiting for clock samples (for profiler runs)")
-    parser.add_argument("--profile-case", choices=("paged", "tq4", "tq3", "tq2", "tqappend"), default=None,
+    parser.add_argument("--profile-case", choices=("paged", "tq4", "tq3", "tq2", "tqappend", "prefill"), default=None,
                         help="run one small decode case a few times and exit (meant to be wrapped by ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -741,6 +774,10 @@ def main() -> None:
                     extras.append(run_turboquant_extra(device, **kwargs))
                 except Exception as exc:  # noqa: BLE001 - extras never take the headline down
                     extras.append({"workload": kwargs["name"], "error": repr(exc)})
+            try:
+                extras.append(run_prefill_extra(device))
+            except Exception as exc:  # noqa: BLE001
+                extras.append({"workload": "cfg4-like prefill attention", "error": repr(exc)})
             result["extra"] = extras
     dist.barrier()
     if dist.rank == 0:

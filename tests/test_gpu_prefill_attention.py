@@ -100,3 +100,36 @@ def test_masks_of_another_shape_are_rejected(cuda_device):
         grouped_query_attention(q, k, k, scaling=1.0, causal_mask=band, check_masks=True)
     with pytest.raises(RuntimeError, match="CUDA"):
         grouped_query_attention(q.cpu(), k.cpu(), k.cpu(), scaling=1.0)
+
+
+def test_chunked_prefill_over_turboquant_cache_matches_oracle(cuda_device):
+    """The reference's prefill flow on a quantized cache (ops.py:2008-2025): update(require_dense_cache=True) hands back
+    the de-quantized prefix + window + chunk as dense K/V, the chunk's queries attend to it causally.  Rows of different
+    lengths, two chunks each; the expectation is the oracle row's materialize() followed by the oracle attention."""
+    from tests.helpers import DTYPE_CODE, TQ_ATOL, TqPair
+
+    dtype, heads, kv_heads, dim, bits, residual = torch.bfloat16, 8, 2, 128, 4, 16
+    pair = TqPair(device=cuda_device, batch=2, kv_heads=kv_heads, head_dim=dim, bits=bits, residual_len=residual,
+                  block_size=16, dtype=dtype)
+    gen = torch.Generator().manual_seed(9)
+    assert DTYPE_CODE[dtype] == oracle.DTYPE_BF16
+    for chunk in (70, 45):
+        k = torch.randn(2, kv_heads, chunk, dim, generator=gen).to(dtype)
+        v = torch.randn(2, kv_heads, chunk, dim, generator=gen).to(dtype)
+        q = torch.randn(2, heads, chunk, dim, generator=gen).to(dtype)
+        keys, values, past = pair.cache.update(k.to(cuda_device), v.to(cuda_device), 0, require_dense_cache=True)
+        for b, row in enumerate(pair.rows):
+            row.append(to_np(k[b]), to_np(v[b]))
+        visible = past + chunk
+        out = grouped_query_attention(q.to(cuda_device), keys, values, scaling=dim ** -0.5, key_lengths=visible,
+                                      causal=True)
+        for b, row in enumerate(pair.rows):
+            dense_k, dense_v = row.materialize()
+            n = dense_k.shape[1]
+            assert n == int(visible[b])
+            positions = np.arange(n)[None, None, :]
+            causal_mask = positions > (n - chunk + np.arange(chunk))[None, :, None]
+            expected = oracle.grouped_query_attention(to_np(q[b:b + 1]), dense_k[None], dense_v[None], dim ** -0.5,
+                                                      causal_mask=causal_mask)
+            max_abs, _ = error_stats(to_np(out[b:b + 1]), expected)
+            assert max_abs <= TQ_ATOL[dtype], (chunk, b, max_abs)
