@@ -5,9 +5,10 @@
 // form); with the causal flag, query t of the chunk sits at position key_lengths[r] - T + t and sees keys up to and
 // including its own position.  softmax in fp32, output in the query dtype, rows without any visible key give zeros.
 //
-// A CTA (4 warps) owns 64 query rows of one query head; a warp owns 16 of them.  Per 64-key tile:
+// A CTA (4 warps) owns 128 query rows of one query head, a warp two 16-row tiles of them (64 rows and one tile per
+// warp at head_dim 256), so every K / V fragment read from shared memory feeds four MMAs.  Per 32-key tile:
 //   K / V tile --cp.async (2 stages, zero-filled past the row's keys)--> xor-swizzled shared memory
-//   S[16 x 64]  = Q . K^T          Q fragments by ldmatrix from the staged query tile, K by ldmatrix (8 n-tiles x D/16)
+//   S[16 x 32]  = Q . K^T          Q fragments by ldmatrix from the staged query tile, K by ldmatrix (4 n-tiles x D/16)
 //   mask, online softmax in fp32 on the C fragments (row reductions over the 4 lanes of a quad)
 //   O[16 x D]  += P . V            P re-packed from the C fragments (no shuffle), V by ldmatrix.trans
 // Key tiles above the causal diagonal of the CTA's last query row are never loaded.
@@ -39,7 +40,6 @@ __device__ __forceinline__ float ex2_fast(float x) {
 
 constexpr int kPrefillWarps = 4;
 constexpr int kPrefillThreads = kPrefillWarps * 32;
-constexpr int kPrefillRows = kPrefillWarps * 16;  // query rows per CTA
 
 struct PrefillParams {
   const void* q;
@@ -55,19 +55,25 @@ struct PrefillParams {
   float scale_log2;  // scaling * log2(e)
 };
 
+#ifndef ANNA_PREFILL_MT
+#define ANNA_PREFILL_MT 2
+#endif
 template <int D>
 struct PrefillCfg {
-#ifndef ANNA_PREFILL_KEYS128
-#define ANNA_PREFILL_KEYS128 64
-#endif
-#ifndef ANNA_PREFILL_CTAS
-#define ANNA_PREFILL_CTAS 2
-#endif
-  static constexpr int kKeys = D >= 256 ? 32 : ANNA_PREFILL_KEYS128;      // keys per tile
+  // 16-row query tiles per warp: with two, every K / V fragment loaded from shared memory feeds four MMAs instead of two
+  static constexpr int kMT = D <= 128 ? ANNA_PREFILL_MT : 1;
+  static constexpr int kRows = kPrefillWarps * 16 * kMT;  // query rows per CTA
+  static constexpr int kKeys = (D >= 256 || kMT > 1) ? 32 : 64;  // keys per tile (bounded by the score registers)
   static constexpr int kRowBytes = D * 2;
   static constexpr int kChunks = D / 8;                  // 16-byte chunks per row
-  static constexpr int kQBytes = kPrefillRows * kRowBytes;
-  static constexpr int kTileBytes = kKeys * kRowBytes;
+  static constexpr int kQBytes = kRows * kRowBytes;
+#ifndef ANNA_PREFILL_SUBS
+#define ANNA_PREFILL_SUBS 1
+#endif
+  // a stage may hold kSubs key tiles (one CTA barrier pair per kStageKeys keys); two measured the same as one
+  static constexpr int kSubs = D <= 128 ? ANNA_PREFILL_SUBS : 1;
+  static constexpr int kStageKeys = kKeys * kSubs;
+  static constexpr int kTileBytes = kStageKeys * kRowBytes;
   static constexpr int kSmemBytes = kQBytes + 4 * kTileBytes;  // Q | K0 K1 | V0 V1
   static constexpr int kSteps = D / 16;
   static constexpr int kNTiles = kKeys / 8;
@@ -88,10 +94,11 @@ __device__ __forceinline__ void prefill_load_tile(uint32_t dst, const T* base, i
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_CTAS) gqa_prefill_mma_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kPrefillThreads, 2) gqa_prefill_mma_kernel(const PrefillParams p) {
   using Cfg = PrefillCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const int m0 = blockIdx.x * kPrefillRows;
+  constexpr int MT = Cfg::kMT;
+  const int m0 = blockIdx.x * Cfg::kRows;
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
   const int kvh = hq / p.groups;
@@ -105,10 +112,10 @@ __global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_C
   int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
   n_keys = max((int64_t)0, min(n_keys, p.key_len));
   const int64_t past = n_keys - p.q_len;  // position of the chunk's first query (negative: the row is shorter than the chunk)
-  const int last_row = min(m0 + kPrefillRows, p.q_len) - 1;
+  const int last_row = min(m0 + Cfg::kRows, p.q_len) - 1;
   int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
   cta_limit = max(cta_limit, (int64_t)0);
-  const int n_tiles = (int)((cta_limit + Cfg::kKeys - 1) / Cfg::kKeys);
+  const int n_tiles = (int)((cta_limit + Cfg::kStageKeys - 1) / Cfg::kStageKeys);
 
   const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + hq * p.q_stride_h;
   const T* k_base = reinterpret_cast<const T*>(p.k) + b * p.kv_stride_b + kvh * p.kv_stride_h;
@@ -117,54 +124,69 @@ __global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_C
   const uint32_t k_s = q_s + Cfg::kQBytes;
   const uint32_t v_s = k_s + 2 * Cfg::kTileBytes;
 
-  prefill_load_tile<T, D>(q_s, q_base, p.q_stride_t, m0, kPrefillRows, p.q_len);
+  prefill_load_tile<T, D>(q_s, q_base, p.q_stride_t, m0, Cfg::kRows, p.q_len);
   if (n_tiles > 0) {
-    prefill_load_tile<T, D>(k_s, k_base, p.kv_stride_t, 0, Cfg::kKeys, n_keys);
-    prefill_load_tile<T, D>(v_s, v_base, p.kv_stride_t, 0, Cfg::kKeys, n_keys);
+    prefill_load_tile<T, D>(k_s, k_base, p.kv_stride_t, 0, Cfg::kStageKeys, n_keys);
+    prefill_load_tile<T, D>(v_s, v_base, p.kv_stride_t, 0, Cfg::kStageKeys, n_keys);
   }
   cp_async_commit();
 
-  const int row_lo = m0 + warp * 16 + gid;
-  const int row_hi = row_lo + 8;
-  const int64_t lim_lo = p.causal ? min(n_keys, past + row_lo + 1) : n_keys;
-  const int64_t lim_hi = p.causal ? min(n_keys, past + row_hi + 1) : n_keys;
-
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.0f, 0.0f};
-  float o[D / 8][4];
+  // rows gid and gid + 8 of the warp's MT query tiles
+  int row[MT][2];
+  int64_t lim[MT][2];
+  float m_run[MT][2], l_run[MT][2];
+  float o[MT][D / 8][4];
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j)
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) o[j][r] = 0.0f;
+    for (int h = 0; h < 2; ++h) {
+      row[mt][h] = m0 + (warp * MT + mt) * 16 + gid + 8 * h;
+      lim[mt][h] = p.causal ? min(n_keys, past + row[mt][h] + 1) : n_keys;
+      m_run[mt][h] = -INFINITY;
+      l_run[mt][h] = 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) o[mt][j][r] = 0.0f;
+  }
 
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
-      const int64_t key0 = (int64_t)(it + 1) * Cfg::kKeys;
-      prefill_load_tile<T, D>(k_s + (stage ^ 1) * Cfg::kTileBytes, k_base, p.kv_stride_t, key0, Cfg::kKeys, n_keys);
-      prefill_load_tile<T, D>(v_s + (stage ^ 1) * Cfg::kTileBytes, v_base, p.kv_stride_t, key0, Cfg::kKeys, n_keys);
+      const int64_t key0 = (int64_t)(it + 1) * Cfg::kStageKeys;
+      prefill_load_tile<T, D>(k_s + (stage ^ 1) * Cfg::kTileBytes, k_base, p.kv_stride_t, key0, Cfg::kStageKeys, n_keys);
+      prefill_load_tile<T, D>(v_s + (stage ^ 1) * Cfg::kTileBytes, v_base, p.kv_stride_t, key0, Cfg::kStageKeys, n_keys);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const uint32_t k_tile = k_s + stage * Cfg::kTileBytes;
-    const uint32_t v_tile = v_s + stage * Cfg::kTileBytes;
+    for (int sub = 0; sub < Cfg::kSubs; ++sub) {
+    const int64_t sub_key0 = (int64_t)it * Cfg::kStageKeys + sub * Cfg::kKeys;
+    if (sub_key0 >= cta_limit) break;  // nothing visible to any row of the CTA (uniform)
+    const uint32_t k_tile = k_s + stage * Cfg::kTileBytes + sub * Cfg::kKeys * Cfg::kRowBytes;
+    const uint32_t v_tile = v_s + stage * Cfg::kTileBytes + sub * Cfg::kKeys * Cfg::kRowBytes;
 
     // ---- S = Q . K^T ---------------------------------------------------------------------------------------------------
-    float s[Cfg::kNTiles][4];
+    float s[MT][Cfg::kNTiles][4];
 #pragma unroll
-    for (int j = 0; j < Cfg::kNTiles; ++j)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int r = 0; r < 4; ++r) s[j][r] = 0.0f;
+      for (int j = 0; j < Cfg::kNTiles; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[mt][j][r] = 0.0f;
     {
       // fragment loads run one item ahead of the MMAs that consume them (item = one k-step of one pair of n-tiles)
       constexpr int kPairs = Cfg::kNTiles / 2;
       constexpr int kItems = Cfg::kSteps * kPairs;
-      uint32_t a[2][4], bk[2][4];
-      auto load_a = [&](int ks, uint32_t (&dst)[4]) {
-        ldmatrix_x4(dst, q_s + swizzled_offset(warp * 16 + (mi & 1) * 8 + l8, 2 * ks + (mi >> 1), Cfg::kRowBytes));
+      uint32_t a[2][MT][4], bk[2][4];
+      auto load_a = [&](int ks, uint32_t (&dst)[MT][4]) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          ldmatrix_x4(dst[mt], q_s + swizzled_offset((warp * MT + mt) * 16 + (mi & 1) * 8 + l8, 2 * ks + (mi >> 1),
+                                                     Cfg::kRowBytes));
       };
       auto load_b = [&](int ks, int jp, uint32_t (&dst)[4]) {
         ldmatrix_x4(dst, k_tile + swizzled_offset(jp * 16 + (mi >> 1) * 8 + l8, 2 * ks + (mi & 1), Cfg::kRowBytes));
@@ -179,53 +201,59 @@ __global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_C
           if (jp1 == 0) load_a(ks1, a[ks1 & 1]);
           load_b(ks1, jp1, bk[(item + 1) & 1]);
         }
-        mma_pure<T>(s[2 * jp], a[ks & 1], bk[item & 1][0], bk[item & 1][1]);
-        mma_pure<T>(s[2 * jp + 1], a[ks & 1], bk[item & 1][2], bk[item & 1][3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_pure<T>(s[mt][2 * jp], a[ks & 1][mt], bk[item & 1][0], bk[item & 1][1]);
+          mma_pure<T>(s[mt][2 * jp + 1], a[ks & 1][mt], bk[item & 1][2], bk[item & 1][3]);
+        }
       }
     }
 
     // ---- mask + online softmax (log2 units) -----------------------------------------------------------------------------
-    const int64_t key_base = (int64_t)it * Cfg::kKeys + 2 * tig;
-    float mx[2] = {-INFINITY, -INFINITY};
+    const int64_t key_base = sub_key0 + 2 * tig;
 #pragma unroll
-    for (int j = 0; j < Cfg::kNTiles; ++j) {
-      const int64_t key = key_base + 8 * j;
-      s[j][0] = key < lim_lo ? s[j][0] * p.scale_log2 : -INFINITY;
-      s[j][1] = key + 1 < lim_lo ? s[j][1] * p.scale_log2 : -INFINITY;
-      s[j][2] = key < lim_hi ? s[j][2] * p.scale_log2 : -INFINITY;
-      s[j][3] = key + 1 < lim_hi ? s[j][3] * p.scale_log2 : -INFINITY;
-      mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
-      mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
-    }
+    for (int mt = 0; mt < MT; ++mt) {
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int d = 1; d <= 2; d <<= 1) {
-      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
-      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
-    }
-    float alpha[2], m_safe[2];
+      for (int j = 0; j < Cfg::kNTiles; ++j) {
+        const int64_t key = key_base + 8 * j;
+        s[mt][j][0] = key < lim[mt][0] ? s[mt][j][0] * p.scale_log2 : -INFINITY;
+        s[mt][j][1] = key + 1 < lim[mt][0] ? s[mt][j][1] * p.scale_log2 : -INFINITY;
+        s[mt][j][2] = key < lim[mt][1] ? s[mt][j][2] * p.scale_log2 : -INFINITY;
+        s[mt][j][3] = key + 1 < lim[mt][1] ? s[mt][j][3] * p.scale_log2 : -INFINITY;
+        mx[0] = fmaxf(mx[0], fmaxf(s[mt][j][0], s[mt][j][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[mt][j][2], s[mt][j][3]));
+      }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const float m_new = fmaxf(m_run[r], mx[r]);
-      m_safe[r] = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[r] = ex2_fast(m_run[r] - m_safe[r]);  // 0 on the first visible tile (m_run = -inf)
-      m_run[r] = m_new;
-      l_run[r] *= alpha[r];
-    }
+      for (int d = 1; d <= 2; d <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+      }
+      float alpha[2], m_safe[2];
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      o[j][0] *= alpha[0];
-      o[j][1] *= alpha[0];
-      o[j][2] *= alpha[1];
-      o[j][3] *= alpha[1];
-    }
+      for (int r = 0; r < 2; ++r) {
+        const float m_new = fmaxf(m_run[mt][r], mx[r]);
+        m_safe[r] = m_new == -INFINITY ? 0.0f : m_new;
+        alpha[r] = ex2_fast(m_run[mt][r] - m_safe[r]);  // 0 on the first visible tile (m_run = -inf)
+        m_run[mt][r] = m_new;
+        l_run[mt][r] *= alpha[r];
+      }
 #pragma unroll
-    for (int j = 0; j < Cfg::kNTiles; ++j) {
-      s[j][0] = ex2_fast(s[j][0] - m_safe[0]);
-      s[j][1] = ex2_fast(s[j][1] - m_safe[0]);
-      s[j][2] = ex2_fast(s[j][2] - m_safe[1]);
-      s[j][3] = ex2_fast(s[j][3] - m_safe[1]);
-      l_run[0] += s[j][0] + s[j][1];
-      l_run[1] += s[j][2] + s[j][3];
+      for (int j = 0; j < D / 8; ++j) {
+        o[mt][j][0] *= alpha[0];
+        o[mt][j][1] *= alpha[0];
+        o[mt][j][2] *= alpha[1];
+        o[mt][j][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int j = 0; j < Cfg::kNTiles; ++j) {
+        s[mt][j][0] = ex2_fast(s[mt][j][0] - m_safe[0]);
+        s[mt][j][1] = ex2_fast(s[mt][j][1] - m_safe[0]);
+        s[mt][j][2] = ex2_fast(s[mt][j][2] - m_safe[1]);
+        s[mt][j][3] = ex2_fast(s[mt][j][3] - m_safe[1]);
+        l_run[mt][0] += s[mt][j][0] + s[mt][j][1];
+        l_run[mt][1] += s[mt][j][2] + s[mt][j][3];
+      }
     }
 
     // ---- O += P . V ------------------------------------------------------------------------------------------------------
@@ -236,37 +264,55 @@ __global__ void __launch_bounds__(kPrefillThreads, D >= 256 ? 2 : ANNA_PREFILL_C
       auto load_v = [&](int kk, int dp, uint32_t (&dst)[4]) {
         ldmatrix_x4_trans(dst, v_tile + swizzled_offset(kk * 16 + (mi & 1) * 8 + l8, 2 * dp + (mi >> 1), Cfg::kRowBytes));
       };
+      // P as A fragments: the C fragments of two neighbouring n-tiles are exactly the A fragment of one k-step
+      uint32_t pa[MT][Cfg::kKeys / 16][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int kk = 0; kk < Cfg::kKeys / 16; ++kk) {
+          pa[mt][kk][0] = pack2<T>(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+          pa[mt][kk][1] = pack2<T>(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+          pa[mt][kk][2] = pack2<T>(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+          pa[mt][kk][3] = pack2<T>(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+        }
       load_v(0, 0, bv[0]);
 #pragma unroll
       for (int item = 0; item < kItems; ++item) {
         const int kk = item / kDPairs, dp = item % kDPairs;
         if (item + 1 < kItems) load_v((item + 1) / kDPairs, (item + 1) % kDPairs, bv[(item + 1) & 1]);
-        const uint32_t a[4] = {pack2<T>(s[2 * kk][0], s[2 * kk][1]), pack2<T>(s[2 * kk][2], s[2 * kk][3]),
-                               pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3])};
-        mma_pure<T>(o[2 * dp], a, bv[item & 1][0], bv[item & 1][1]);
-        mma_pure<T>(o[2 * dp + 1], a, bv[item & 1][2], bv[item & 1][3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_pure<T>(o[mt][2 * dp], pa[mt][kk], bv[item & 1][0], bv[item & 1][1]);
+          mma_pure<T>(o[mt][2 * dp + 1], pa[mt][kk], bv[item & 1][2], bv[item & 1][3]);
+        }
       }
     }
+    }  // sub
     __syncthreads();  // the stage is refilled by the next iteration's loads
   }
   cp_async_wait<0>();
 
   // ---- normalise and store -------------------------------------------------------------------------------------------------
-#pragma unroll
-  for (int d = 1; d <= 2; d <<= 1) {
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
-  }
-  const float inv_lo = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
-  const float inv_hi = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
   T* out_base = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + hq * p.out_stride_h;
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j) {
-    const int col = 8 * j + 2 * tig;
-    if (row_lo < p.q_len)
-      *reinterpret_cast<uint32_t*>(out_base + row_lo * p.out_stride_t + col) = pack2<T>(o[j][0] * inv_lo, o[j][1] * inv_lo);
-    if (row_hi < p.q_len)
-      *reinterpret_cast<uint32_t*>(out_base + row_hi * p.out_stride_t + col) = pack2<T>(o[j][2] * inv_hi, o[j][3] * inv_hi);
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int d = 1; d <= 2; d <<= 1) {
+      l_run[mt][0] += __shfl_xor_sync(0xffffffffu, l_run[mt][0], d);
+      l_run[mt][1] += __shfl_xor_sync(0xffffffffu, l_run[mt][1], d);
+    }
+    const float inv_lo = l_run[mt][0] > 0.0f ? 1.0f / l_run[mt][0] : 0.0f;
+    const float inv_hi = l_run[mt][1] > 0.0f ? 1.0f / l_run[mt][1] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      const int col = 8 * j + 2 * tig;
+      if (row[mt][0] < p.q_len)
+        *reinterpret_cast<uint32_t*>(out_base + row[mt][0] * p.out_stride_t + col) =
+            pack2<T>(o[mt][j][0] * inv_lo, o[mt][j][1] * inv_lo);
+      if (row[mt][1] < p.q_len)
+        *reinterpret_cast<uint32_t*>(out_base + row[mt][1] * p.out_stride_t + col) =
+            pack2<T>(o[mt][j][2] * inv_hi, o[mt][j][3] * inv_hi);
+    }
   }
 }
 
@@ -281,7 +327,7 @@ static int launch_prefill(const PrefillParams& p, int batch, int q_heads, cudaSt
     ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  dim3 grid((unsigned)((p.q_len + kPrefillRows - 1) / kPrefillRows), (unsigned)q_heads, (unsigned)batch);
+  dim3 grid((unsigned)((p.q_len + Cfg::kRows - 1) / Cfg::kRows), (unsigned)q_heads, (unsigned)batch);
   kernel<<<grid, kPrefillThreads, Cfg::kSmemBytes, stream>>>(p);
   return check_launch("gqa_prefill_mma_kernel");
 }
