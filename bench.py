@@ -216,7 +216,7 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
 
     spec = cfg2_spec()
     batch, q_heads, kv_heads, dim = spec["batch"], spec["q_heads"], spec["kv_heads"], spec["head_dim"]
-    total_steps = 2 * (args.steps + args.warmup) + 8
+    total_steps = 3 * (args.steps + args.warmup) + 8  # device-resident, serial and pipelined host loops
     cache, lengths = build_cfg2_state(device, seed=1234 + dist.rank, headroom_tokens=total_steps)
     scaling = dim ** -0.5
     gen = torch.Generator(device=device).manual_seed(99 + dist.rank)
@@ -284,9 +284,18 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
     # the step's inputs (q, new k, new v) sit in one pinned host buffer and cross PCIe as one copy
     q_count, kv_count = q_dev.numel(), k_dev.numel()
     in_host = torch.cat([q_dev.reshape(-1), k_dev.reshape(-1), v_dev.reshape(-1)]).cpu().pin_memory()
-    out_host = torch.empty(batch, q_heads, 1, dim, dtype=torch.bfloat16).pin_memory()
+    out_hosts = [torch.empty(batch, q_heads, 1, dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    landed_events = [torch.cuda.Event(), torch.cuda.Event()]
+    landed: list = [None, None]
 
-    def step_e2e():
+    def step_e2e(index: int, pipelined: bool):
+        """One step from pinned host inputs to a pinned host result.  Serial: the host waits for the result of every
+        step before it prepares the next one.  Pipelined (depth 2): the result goes back asynchronously into one of
+        two pinned buffers and the host waits for a buffer only when it is about to be reused, so the host work of
+        step i+1 overlaps the kernels of step i, as a serving loop with asynchronous scheduling does."""
+        slot = index & 1
+        if pipelined and landed[slot] is not None:
+            landed[slot].synchronize()  # the result of step index - 2 is in host memory
         staged = in_host.to(device, non_blocking=True)
         q = staged[:q_count].view(batch, q_heads, 1, dim)
         k = staged[q_count:q_count + kv_count].view(batch, kv_heads, 1, dim)
@@ -295,20 +304,30 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
         key_pages, value_pages, table, visible = cache.paged_attention_state(0)
         out = fused_ops.run_paged_gqa_decode_fused(query=q, key_pages=key_pages, value_pages=value_pages,
                                                    page_table=table, visible_lengths=visible, scaling=scaling)
-        out_host.copy_(out, non_blocking=False)
+        if not pipelined:
+            out_hosts[slot].copy_(out, non_blocking=False)
+            return
+        out_hosts[slot].copy_(out, non_blocking=True)
+        landed[slot] = landed_events[slot]
+        landed[slot].record()
 
-    for _ in range(args.warmup):
-        step_e2e()
-    torch.cuda.synchronize(device)
-    dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_e2e()
-    torch.cuda.synchronize(device)
-    e2e_local = time.perf_counter() - t0
-    dist.barrier()
-    e2e_s = dist.max(e2e_local, device)
+    def timed_e2e(pipelined: bool) -> float:
+        for i in range(args.warmup):
+            step_e2e(i, pipelined)
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            step_e2e(i, pipelined)
+        torch.cuda.synchronize(device)  # every result has landed in host memory
+        local = time.perf_counter() - t0
+        dist.barrier()
+        return dist.max(local, device)
+
+    e2e_serial_s = timed_e2e(False)
+    e2e_s = timed_e2e(True)
     e2e_value = dist.world * batch * args.steps / e2e_s
+    out_host = out_hosts[0]
     h2d = in_host.numel() * 2
     d2h = out_host.numel() * 2
 
@@ -319,7 +338,10 @@ def run_cfg2_gpu(args, dist: Dist, device) -> dict:
         "config": {**spec, "l2_policy": "working set (705 MB of K/V per step) exceeds the 126 MB L2",
                    "per_rank_batch": batch, "parallelism": f"sequence-sharded x{dist.world}, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s / args.steps * 1e3},
+                "ms_per_step": e2e_s / args.steps * 1e3, "pipeline_depth": 2,
+                "serial_value": dist.world * batch * args.steps / e2e_serial_s,
+                "note": "value: results return asynchronously into two pinned buffers, the host waits for a buffer "
+                        "only before reusing it; serial_value: the host waits for every step's result before the next"},
         "gpu_launches": 2 * args.steps,  # per step: paged_kv_write_kernel + the decode kernel (merge fused in its tail)
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
