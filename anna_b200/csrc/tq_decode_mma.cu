@@ -89,6 +89,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifndef ANNA_TQ_RING_TILES
 #define ANNA_TQ_RING_TILES 4
 #endif
+#ifndef ANNA_TQ_OVERLAP_WINDOW
+#define ANNA_TQ_OVERLAP_WINDOW 1
+#endif
 constexpr float kLazyRescale = 8.0f;  // log2 units: probabilities stay below 2^8, well inside fp16
 
 template <typename T, int D, int BITS>
@@ -211,6 +214,11 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
 template <typename T, int D>
 __global__ void __launch_bounds__(kMmaThreads, MmaCfg<D>::kMinBlocks) tq_window_split_mma_kernel(const TqDecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+#if ANNA_TQ_OVERLAP_WINDOW
+  // The packed-chunk kernel that follows in the stream does not read anything this kernel writes before the
+  // arrival counters say so, so it may start as soon as every CTA here has been scheduled.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::);
+#endif
   const int slot = blockIdx.x;
   const int group_tiles = (p.groups + 7) / 8;
   const int kvh = blockIdx.y / group_tiles;
@@ -754,7 +762,23 @@ static int launch_tq_mma(const TqDecodeParams& p, int batch, cudaStream_t stream
   if (rc != ANNA_OK) return rc;
   if (p.num_chunks > p.num_window_chunks) {
     dim3 grid((unsigned)p.num_chunks, (unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
+#if ANNA_TQ_OVERLAP_WINDOW
+    // programmatic dependent launch: the packed chunks run beside the (small) window launch instead of after it; the
+    // query fragments they read come from the launch before that one, which has completed by then
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(kMmaThreads);
+    config.dynamicSmemBytes = Cfg::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    ANNA_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, p));
+#else
     kernel<<<grid, kMmaThreads, Cfg::kSmemBytes, stream>>>(p);
+#endif
     rc = check_launch("tq_decode_split_mma_kernel");
   }
   return rc;
