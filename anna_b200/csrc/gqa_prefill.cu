@@ -98,7 +98,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 2) gqa_prefill_mma_kernel(con
   using Cfg = PrefillCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int MT = Cfg::kMT;
-  const int m0 = blockIdx.x * Cfg::kRows;
+  // the query tiles with the most visible keys (the last ones of a causal chunk) are scheduled first
+#ifndef ANNA_PREFILL_HEAVY_FIRST
+#define ANNA_PREFILL_HEAVY_FIRST 1
+#endif
+  const int m0 = (ANNA_PREFILL_HEAVY_FIRST ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * Cfg::kRows;
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
   const int kvh = hq / p.groups;
