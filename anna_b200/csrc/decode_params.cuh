@@ -37,7 +37,5 @@ int launch_dense_split_mma(const DenseDecodeParams& p, int batch, int head_dim, 
 // one resident wave with an even share of tiles per CTA; needs the fused merge and the library's own split plan
 bool dense_balanced_mma_applicable(const DenseDecodeParams& p, int batch);
 int launch_dense_balanced_mma(const DenseDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream);
-// same schedule with TMA tile loads (paged_decode_tma.cu); ANNA_ERR_UNSUPPORTED = problem does not qualify, not launched
-int try_launch_paged_decode_tma(const DenseDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream);
 
 }  // namespace anna

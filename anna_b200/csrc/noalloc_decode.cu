@@ -16,7 +16,9 @@ constexpr size_t kNoAllocCounterBytes = 64u << 10;  // head of the array: arriva
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 // Device address of the array above, per device ordinal.  The array's name is only a handle on the host: the address
-// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.  The table is
+// filled without a lock: host threads that make their first call on one device at the same time may each do the
+// look-up, and all of them store the same address.
 static void* g_noalloc_scratch_ptr[64] = {};
 
 static int noalloc_scratch_base(unsigned char** base) {
@@ -60,7 +62,14 @@ extern "C" int anna_paged_gqa_decode_noalloc(const void* q, int64_t q_stride_b, 
   const size_t values_bytes = sizeof(float) * heads * num_chunks * head_dim;
   const size_t stats_offset = kNoAllocCounterBytes;
   const size_t values_offset = (stats_offset + stats_bytes + 255) / 256 * 256;
-  if (counter_bytes > kNoAllocCounterBytes || values_offset + values_bytes > kNoAllocScratchBytes)
+  if (counter_bytes > kNoAllocCounterBytes)
+    return set_error(ANNA_ERR_WORKSPACE,
+                     "anna_paged_gqa_decode_noalloc: batch * kv_heads * ceil(G / 8) = %zu (row, head-group) pairs need "
+                     "%zu bytes of merge counters but the built-in array reserves %zu (at most %zu pairs); use "
+                     "anna_paged_gqa_decode with caller-provided scratch",
+                     (size_t)batch * kv_heads * group_tiles, counter_bytes, (size_t)kNoAllocCounterBytes,
+                     (size_t)(kNoAllocCounterBytes / (2 * sizeof(int32_t))));
+  if (values_offset + values_bytes > kNoAllocScratchBytes)
     return set_error(ANNA_ERR_WORKSPACE,
                      "anna_paged_gqa_decode_noalloc: this problem needs %zu bytes of split-K scratch but the built-in "
                      "array holds %zu; use anna_paged_gqa_decode with caller-provided scratch",

@@ -115,8 +115,6 @@ static int run_dense_decode(DenseDecodeParams p, const void* gate, int64_t gate_
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
       p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
       if (chunk_tokens_in <= 0) {
-        rc = try_launch_paged_decode_tma(p, batch, head_dim, dtype, stream);
-        if (rc != ANNA_ERR_UNSUPPORTED) return rc;
         // Two schedules for the same tile body.  Few CTAs' worth of work: one resident wave with an even share per CTA
         // (no tail, one pipeline start per CTA).  Many: fixed chunks handed out by the hardware block scheduler, which
         // lets faster SMs take more chunks; measured 3-10 % ahead from about 6000 grid CTAs on (48+ rows of 1-8 K

@@ -50,8 +50,9 @@ dense_decode_balanced_mma_kernel(const DenseDecodeParams p, const int batch) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int group_tiles = (p.groups + 7) / 8;
   const int streams_per_row = p.kv_heads * group_tiles;
+  // the fused merge stages at most kFusedMaxChunks weights per head, however large the caller's scratch is
   balanced_for_each_segment<kMmaThreads>(
-      p.visible_lengths, p.max_len, batch, streams_per_row, p.chunk_capacity,
+      p.visible_lengths, p.max_len, batch, streams_per_row, min(p.chunk_capacity, kFusedMaxChunks),
       [&](int b) {
         for (int stream = 0; stream < streams_per_row; ++stream) {
           const int g0 = (stream % group_tiles) * 8;

@@ -334,8 +334,13 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   p.chunk_tokens = chunk_tokens; p.num_chunks = num_chunks; p.chunk_capacity = chunk_capacity;
   p.num_window_chunks = (residual_len + chunk_tokens - 1) / chunk_tokens;
   {
-    const size_t need = (size_t)batch * kv_heads * ((p.groups + 7) / 8) * 32 * (head_dim / 16) * 16;
-    p.query_frags = (query_scratch != nullptr && query_scratch_bytes >= need) ? query_scratch : nullptr;
+    const size_t need = tq_query_scratch_bytes(batch, q_heads, kv_heads, head_dim);
+    const bool fits = query_scratch != nullptr && query_scratch_bytes >= need &&
+                      (reinterpret_cast<uintptr_t>(query_scratch) & 15u) == 0;
+    p.query_frags = fits ? query_scratch : nullptr;
+    p.query_consts = fits ? reinterpret_cast<float*>(static_cast<uint8_t*>(query_scratch) + need -
+                                                     (size_t)batch * kv_heads * ((p.groups + 7) / 8) * 32 * sizeof(float))
+                          : nullptr;
   }
   if (tq_split_mma_applicable(p, head_dim, dtype)) {
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
@@ -362,6 +367,11 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   return launch_split_combine(ws, nullptr, p.lengths, -1, p.max_len, residual_len, gate, gate_stride_b, gate_stride_h,
                               out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,
                               dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t anna_tq_query_scratch_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
+  if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || q_heads % kv_heads != 0) return 0;
+  return tq_query_scratch_bytes(batch, q_heads, kv_heads, head_dim);
 }
 
 extern "C" int anna_tq_decode_plan(int batch, int kv_heads, int64_t max_blocks, int block_size, int residual_len,

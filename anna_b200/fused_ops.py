@@ -235,8 +235,8 @@ _SCRATCH = _Scratch()
 
 def query_scratch(device: torch.device, batch: int, heads: int, kv_heads: int, head_dim: int) -> torch.Tensor:
     """Scratch for the rotated query fragments of the packed tensor-core decode."""
-    group_tiles = (heads // kv_heads + 7) // 8
-    return _SCRATCH.bytes(device, batch * kv_heads * group_tiles * head_dim * 32)
+    need = int(_lib.lib().anna_tq_query_scratch_bytes(batch, heads, kv_heads, head_dim))
+    return _SCRATCH.bytes(device, need)
 
 
 _PLAN_CACHE: dict[tuple, int] = {}

@@ -121,9 +121,11 @@ int anna_paged_gqa_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * fixed 16 MiB array that is part of the library's device image, so every GPU that loads the library holds those
  * 16 MiB until the process exits.  The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - Problems whose plan needs more than the array (anna_noalloc_scratch_bytes()) are rejected with
- *     ANNA_ERR_WORKSPACE; batch * kv_heads * ceil(G / 8) must also stay within 16384.
+ *     ANNA_ERR_WORKSPACE; batch * kv_heads * ceil(G / 8) must also stay within 8192 (64 KiB of the array hold two
+ *     32-bit merge counters per (row, head-group) pair), which is reported with a message of its own.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
- *     current); make that first call outside of any stream capture.
+ *     current); make that first call outside of any stream capture.  Host threads whose first calls on one device
+ *     coincide may each do that look-up; they store the same address, so no lock is taken.
  *   - All calls share the one array.  Calls that can overlap on the GPU (different streams, no ordering between
  *     them) race on it; order them or use anna_paged_gqa_decode with separate scratch.
  */
@@ -216,14 +218,16 @@ int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, in
  * scored from their packed codes in the rotated basis (the identity of turboquant_key_attention_scores,
  * turboquant.py:290-332) instead of from a dense de-quantized copy.
  *   lengths   int64 [B]: total tokens per row (quantized = max(0, L - R), window = min(L, R)); L == 0 gives zeros
- *   query_scratch: optional device scratch of at least B * Hkv * ceil(G / 8) * head_dim * 32 bytes; the tensor-core
- *   path stores the rotated queries there (as fp16 MMA fragments) before the split pass.  Without it, or for fp32
- *   caches, head_dim 64, value groups other than 32 or page sizes that are not a multiple of 16, the CUDA-core path runs.
+ *   query_scratch: optional 16-byte aligned device scratch of at least anna_tq_query_scratch_bytes(B, Hq, Hkv, D)
+ *   bytes; the tensor-core path stores the rotated queries there (as 8-bit MMA fragments plus per-head constants)
+ *   before the split pass.  Without it, or for fp32 caches, head_dim 64, value groups other than 32 or page sizes that
+ *   are not a multiple of 16, the CUDA-core path runs.
  *   split-K slots: anna_tq_decode_plan gives the chunk length and the slot count (window chunks first, then the
  *   chunks of the packed prefix); scratch and counters as for the other decode entry points
  */
 int anna_tq_decode_plan(int batch, int kv_heads, int64_t max_blocks, int block_size, int residual_len,
                         int* chunk_tokens, int* num_chunks);
+size_t anna_tq_query_scratch_bytes(int batch, int q_heads, int kv_heads, int head_dim);  /* 0 for invalid sizes */
 
 int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* packed_pages,
                          const int32_t* block_table, int64_t table_stride, const void* window,

@@ -18,6 +18,7 @@ from __future__ import annotations
 import ctypes
 import json
 import math
+import os
 import struct
 import subprocess
 from pathlib import Path
@@ -73,6 +74,24 @@ def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
+def _for_row_ranges(count: int, call) -> int:
+    """Run ``call(first, rows) -> status`` over [0, count).  Vectors are independent, so large inputs are cut into one
+    range per host core and run on threads (ctypes drops the GIL during the C call); the results do not depend on the
+    cut.  Returns the first non-zero status."""
+    workers = min(os.cpu_count() or 1, count // 2048)
+    if workers <= 1:
+        return call(0, count)
+    from concurrent.futures import ThreadPoolExecutor
+
+    step = (count + workers - 1) // workers
+    ranges = [(first, min(step, count - first)) for first in range(0, count, step)]
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        for status in pool.map(lambda r: call(*r), ranges):
+            if status != 0:
+                return status
+    return 0
+
+
 def _p(a: np.ndarray, ctype):
     return a.ctypes.data_as(ctypes.POINTER(ctype))
 
@@ -83,10 +102,12 @@ def _p(a: np.ndarray, ctype):
 
 def round_bf16(a) -> np.ndarray:
     a = _f32(a)
-    bits = a.view(np.uint32).astype(np.uint64)
-    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
-    out = (rounded & 0xFFFFFFFF).astype(np.uint32).view(np.float32)
-    return np.where(np.isnan(a), a, out).astype(np.float32)
+    bits = a.view(np.uint32)
+    # round to nearest even on the 16 dropped bits; finite inputs cannot wrap (the largest finite float rounds to inf)
+    rounded = (bits + (np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1)))) & np.uint32(0xFFFF0000)
+    out = rounded.view(np.float32)
+    nan = np.isnan(a)
+    return np.where(nan, a, out) if nan.any() else out
 
 
 def round_dtype(a, dtype: int) -> np.ndarray:
@@ -153,14 +174,18 @@ def quantize_keys(x, bits: int, variant: str = "ip"):
     if variant == "ip":
         sign = np.zeros((n, dim), dtype=np.uint8)
         rnorms = np.zeros(n, dtype=np.float32)
-        sp, rp = _p(sign, ctypes.c_uint8), _p(rnorms, ctypes.c_float)
     else:
         sign = rnorms = None
-        sp = ctypes.POINTER(ctypes.c_uint8)()
-        rp = ctypes.POINTER(ctypes.c_float)()
-    rc = lib().tqo_quantize_keys(_p(flat, ctypes.c_float), n, dim, m, _p(s1, ctypes.c_float), _p(s2, ctypes.c_float),
-                                 _p(cent, ctypes.c_float), _p(bnd, ctypes.c_float), _p(idx, ctypes.c_uint8), sp,
-                                 _p(norms, ctypes.c_float), rp)
+    fn = lib().tqo_quantize_keys
+
+    def call(first: int, rows: int) -> int:
+        sp = _p(sign[first:], ctypes.c_uint8) if sign is not None else ctypes.POINTER(ctypes.c_uint8)()
+        rp = _p(rnorms[first:], ctypes.c_float) if rnorms is not None else ctypes.POINTER(ctypes.c_float)()
+        return fn(_p(flat[first:], ctypes.c_float), rows, dim, m, _p(s1, ctypes.c_float), _p(s2, ctypes.c_float),
+                  _p(cent, ctypes.c_float), _p(bnd, ctypes.c_float), _p(idx[first:], ctypes.c_uint8), sp,
+                  _p(norms[first:], ctypes.c_float), rp)
+
+    rc = _for_row_ranges(n, call)
     if rc != 0:
         raise ValueError(f"tqo_quantize_keys failed with status {rc} (dim={dim}, bits={bits})")
     lead = x.shape[:-1]
@@ -178,16 +203,20 @@ def dequantize_keys(idx, sign, norms, rnorms, bits: int, variant: str = "ip") ->
     s1, s2 = signs(dim, 0), signs(dim, 1)
     norms = _f32(norms).reshape(-1)
     out = np.zeros((n, dim), dtype=np.float32)
-    if sign is not None and rnorms is not None:
+    with_sign = sign is not None and rnorms is not None
+    if with_sign:
         sign = np.ascontiguousarray(sign, dtype=np.uint8).reshape(-1, dim)
         rnorms = _f32(rnorms).reshape(-1)
-        sp, rp = _p(sign, ctypes.c_uint8), _p(rnorms, ctypes.c_float)
-    else:
-        sp = ctypes.POINTER(ctypes.c_uint8)()
-        rp = ctypes.POINTER(ctypes.c_float)()
-    rc = lib().tqo_dequantize_keys(_p(flat, ctypes.c_uint8), sp, _p(norms, ctypes.c_float), rp, n, dim,
-                                   _p(s1, ctypes.c_float), _p(s2, ctypes.c_float), _p(cent, ctypes.c_float),
-                                   _p(out, ctypes.c_float))
+    fn = lib().tqo_dequantize_keys
+
+    def call(first: int, rows: int) -> int:
+        sp = _p(sign[first:], ctypes.c_uint8) if with_sign else ctypes.POINTER(ctypes.c_uint8)()
+        rp = _p(rnorms[first:], ctypes.c_float) if with_sign else ctypes.POINTER(ctypes.c_float)()
+        return fn(_p(flat[first:], ctypes.c_uint8), sp, _p(norms[first:], ctypes.c_float), rp, rows, dim,
+                  _p(s1, ctypes.c_float), _p(s2, ctypes.c_float), _p(cent, ctypes.c_float),
+                  _p(out[first:], ctypes.c_float))
+
+    rc = _for_row_ranges(n, call)
     if rc != 0:
         raise ValueError(f"tqo_dequantize_keys failed with status {rc}")
     return out.reshape(idx.shape)
@@ -266,8 +295,9 @@ def gqa_decode(q, k, v, scaling: float, gate=None) -> np.ndarray:
 
 
 def gqa_decode_blas(q, k, v, scaling: float, gate=None) -> np.ndarray:
-    """Same math through numpy matmul (multi-threaded BLAS); used for the timed CPU baseline."""
-    q, k, v = _f32(q), _f32(k), _f32(v)
+    """Same math through numpy matmul (multi-threaded BLAS); used for the timed CPU baseline.  k / v may be views of
+    larger buffers (a decode cache with spare capacity): they are not copied."""
+    q, k, v = _f32(q), np.asarray(k, dtype=np.float32), np.asarray(v, dtype=np.float32)
     hq, dim = q.shape
     hkv = k.shape[0]
     if k.shape[1] == 0:

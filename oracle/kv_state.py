@@ -208,7 +208,13 @@ class OracleLayerAllocator:
 
 class OracleTurboQuantRow:
     def __init__(self, *, bits: int, residual_len: int, dtype: int, block_size: int = 16,
-                 allocator: OracleLayerAllocator | None = None) -> None:
+                 allocator: OracleLayerAllocator | None = None, keep_decode_cache: bool = False) -> None:
+        # keep_decode_cache: hold the dense [Hkv, L, D] keys / values that decode_attention multiplies with and extend
+        # them in place at every append, as the reference does with _KEEP_DECODE_CACHE (turboquant.py:15, :742-782,
+        # :889-923, :1089-1140).  Off: every decode_attention call de-quantizes the whole prefix again.
+        self.keep_decode_cache = bool(keep_decode_cache)
+        self._full_keys: np.ndarray | None = None
+        self._full_values: np.ndarray | None = None
         self.bits = int(bits)
         self.residual_len = max(1, int(residual_len))
         self.dtype = int(dtype)
@@ -219,14 +225,41 @@ class OracleTurboQuantRow:
         self.num_heads: int | None = None
         self.head_dim: int | None = None
         self.group: int | None = None
-        self.idx = self.sign = self.norms = self.rnorms = None
-        self.vdata = self.vscales = self.vzeros = None
+        # quantized state: buffers that double when they run full (turboquant.py:576-581, :583-689), of which the first
+        # `quantized_length` tokens are in use; idx / sign / norms / rnorms / vdata / vscales / vzeros are views of them
+        self._state: dict[str, np.ndarray] = {}
+        self._quantized = 0
         self.residual_keys: np.ndarray | None = None
         self.residual_values: np.ndarray | None = None
 
     @property
     def quantized_length(self) -> int:
-        return 0 if self.idx is None else int(self.idx.shape[1])
+        return self._quantized
+
+    def _view(self, name: str) -> np.ndarray | None:
+        return None if self._quantized == 0 else self._state[name][:, :self._quantized]
+
+    idx = property(lambda self: self._view("idx"))
+    sign = property(lambda self: self._view("sign"))
+    norms = property(lambda self: self._view("norms"))
+    rnorms = property(lambda self: self._view("rnorms"))
+    vdata = property(lambda self: self._view("vdata"))
+    vscales = property(lambda self: self._view("vscales"))
+    vzeros = property(lambda self: self._view("vzeros"))
+
+    def _append_quantized_state(self, parts: dict[str, np.ndarray]) -> None:
+        count = next(iter(parts.values())).shape[1]
+        need = self._quantized + count
+        for name, part in parts.items():
+            current = self._state.get(name)
+            capacity = 0 if current is None else current.shape[1]
+            if need > capacity:
+                grown = np.empty((part.shape[0], max(need, 16, 2 * capacity)) + part.shape[2:], dtype=part.dtype)
+                if current is not None and self._quantized > 0:
+                    grown[:, :self._quantized] = current[:, :self._quantized]
+                self._state[name] = current = grown
+            current[:, self._quantized:need] = part
+        self._quantized = need
 
     @property
     def residual_length(self) -> int:
@@ -250,26 +283,51 @@ class OracleTurboQuantRow:
             self.residual_keys = np.concatenate([self.residual_keys, keys], axis=1)
             self.residual_values = np.concatenate([self.residual_values, values], axis=1)
         self.length += keys.shape[1]
+        if self.keep_decode_cache:
+            self._extend_full_cache(keys, values)
         overflow = self.residual_keys.shape[1] - self.residual_len
         if overflow <= 0:
             return
         old_k, old_v = self.residual_keys[:, :overflow], self.residual_values[:, :overflow]
         idx, sign, norms, rnorms = quantize_keys(old_k, self.bits, "ip")
         vdata, vscales, vzeros = quantize_values(old_v, self.bits, self.group, self.dtype)
-        parts = (idx, sign, norms, rnorms, vdata, vscales, vzeros)
-        names = ("idx", "sign", "norms", "rnorms", "vdata", "vscales", "vzeros")
-        for name, part in zip(names, parts):
-            current = getattr(self, name)
-            setattr(self, name, part if current is None else np.concatenate([current, part], axis=1))
+        self._append_quantized_state({"idx": idx, "sign": sign, "norms": norms, "rnorms": rnorms, "vdata": vdata,
+                                      "vscales": vscales, "vzeros": vzeros})
         self.residual_keys = np.ascontiguousarray(self.residual_keys[:, overflow:])
         self.residual_values = np.ascontiguousarray(self.residual_values[:, overflow:])
+        if self.keep_decode_cache:
+            # the tokens that just left the window are now seen through their codes (turboquant.py:1104-1111, :1134-1140)
+            from . import dequantize_keys, dequantize_values, round_dtype
+
+            first = self.quantized_length - overflow
+            self._full_keys[:, first:first + overflow] = round_dtype(
+                dequantize_keys(idx, sign, norms, rnorms, self.bits), self.dtype)
+            self._full_values[:, first:first + overflow] = round_dtype(
+                dequantize_values(vdata, vscales, vzeros, self.bits, self.group), self.dtype)
         if self.allocator is not None:
             need = paged_blocks_needed(self.quantized_length, self.block_size)
             if need > len(self.block_table):
                 self.block_table.extend(self.allocator.allocate(need - len(self.block_table)))
 
+    def _extend_full_cache(self, keys: np.ndarray, values: np.ndarray) -> None:
+        """Write the new tokens behind the cached ones; capacity doubles (min 16) like turboquant.py:576-581."""
+        have = self.length - keys.shape[1]
+        capacity = 0 if self._full_keys is None else self._full_keys.shape[1]
+        if self.length > capacity:
+            capacity = max(self.length, 16, 2 * capacity)
+            grown_k = np.empty((keys.shape[0], capacity, keys.shape[2]), dtype=np.float32)
+            grown_v = np.empty_like(grown_k)
+            if have > 0:
+                grown_k[:, :have] = self._full_keys[:, :have]
+                grown_v[:, :have] = self._full_values[:, :have]
+            self._full_keys, self._full_values = grown_k, grown_v
+        self._full_keys[:, have:self.length] = keys
+        self._full_values[:, have:self.length] = values
+
     def materialize(self) -> tuple[np.ndarray, np.ndarray]:
         """Dense [Hkv, L, D] keys / values in the cache dtype (turboquant.py:1142-1179)."""
+        if self.keep_decode_cache and self._full_keys is not None:
+            return self._full_keys[:, :self.length], self._full_values[:, :self.length]
         from . import dequantize_keys, dequantize_values, round_dtype
 
         if self.num_heads is None:

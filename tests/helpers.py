@@ -53,6 +53,51 @@ def oracle_layout(pool) -> "oracle.PackedPageLayout":
                                    dtype_bytes=4 if pool.dtype == torch.float32 else 2, group=pool.value_group)
 
 
+def packed_row_fields(pool, row, first_token: int = 0, last_token: int | None = None) -> dict[str, np.ndarray]:
+    """Per-token fields of quantized tokens [first_token, last_token) of one GPU row, read back from its packed pages
+    and laid out like the oracle's arrays: kcodes / vdata uint8 [Hkv, n, bytes], norms / rnorms float32 [Hkv, n],
+    vscales / vzeros float32 [Hkv, n, groups] (cache-dtype values widened to float32)."""
+    layout = oracle_layout(pool)
+    lq = row.quantized_length
+    last_token = lq if last_token is None else min(int(last_token), lq)
+    first_token = max(0, int(first_token))
+    heads, s = pool.kv_heads, pool.block_size
+    count = max(0, last_token - first_token)
+    out = {
+        "kcodes": np.zeros((heads, count, layout.key_bytes), np.uint8),
+        "norms": np.zeros((heads, count), np.float32), "rnorms": np.zeros((heads, count), np.float32),
+        "vdata": np.zeros((heads, count, layout.value_bytes), np.uint8),
+        "vscales": np.zeros((heads, count, layout.groups), np.float32),
+        "vzeros": np.zeros((heads, count, layout.groups), np.float32),
+    }
+    if count == 0:
+        return out
+    blk0, blk1 = first_token // s, (last_token + s - 1) // s
+    ids = torch.tensor(row.block_table[blk0:blk1], device=pool.packed_pages.device)
+    pages = pool.packed_pages[ids].cpu().numpy()  # [blocks, heads, chunk_bytes]
+    blocks = pages.shape[0]
+    lo, hi = first_token - blk0 * s, last_token - blk0 * s
+
+    def tokens(offset: int, width: int) -> np.ndarray:
+        """[heads, blocks * S, width] bytes of one per-token sub-array, cut to the asked token range."""
+        sub = pages[:, :, offset:offset + s * width].reshape(blocks, heads, s, width)
+        return np.ascontiguousarray(sub.transpose(1, 0, 2, 3).reshape(heads, blocks * s, width)[:, lo:hi])
+
+    out["kcodes"] = tokens(layout.off_kcodes, layout.key_bytes)
+    out["norms"] = tokens(layout.off_knorm, 4).view(np.float32)[..., 0]
+    out["rnorms"] = tokens(layout.off_krnorm, 4).view(np.float32)[..., 0]
+    out["vdata"] = tokens(layout.off_vdata, layout.value_bytes)
+    for name, base in (("vscales", layout.off_vscale), ("vzeros", layout.off_vzero)):
+        raw = tokens(base, layout.groups * layout.dtype_bytes)
+        if pool.dtype == torch.float32:
+            out[name] = raw.view(np.float32)
+        elif pool.dtype == torch.float16:
+            out[name] = raw.view(np.float16).astype(np.float32)
+        else:  # bfloat16
+            out[name] = (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    return out
+
+
 class TqPair:
     """A GPU Qwen3DynamicCache (one TurboQuant layer) driven in lock-step with per-row oracle rows."""
 
@@ -81,39 +126,7 @@ class TqPair:
 
     def gpu_fields(self, b: int) -> dict[str, np.ndarray]:
         """Per-token fields of row b read back from the packed pages, in the oracle's array shapes."""
-        pool, row = self.pool, self.cache.turboquant_rows[0][b]
-        layout = oracle_layout(pool)
-        lq = row.quantized_length
-        heads, dim, s = pool.kv_heads, pool.head_dim, pool.block_size
-        out = {
-            "kcodes": np.zeros((heads, lq, layout.key_bytes), np.uint8),
-            "norms": np.zeros((heads, lq), np.float32), "rnorms": np.zeros((heads, lq), np.float32),
-            "vdata": np.zeros((heads, lq, layout.value_bytes), np.uint8),
-            "vscales": np.zeros((heads, lq, layout.groups), np.float32),
-            "vzeros": np.zeros((heads, lq, layout.groups), np.float32),
-        }
-        if lq == 0:
-            return out
-        pages = pool.packed_pages[torch.tensor(row.block_table, device=pool.packed_pages.device)].cpu().numpy()
-        meta_dtype = {torch.float32: np.float32, torch.float16: np.float16}.get(pool.dtype)
-        for j in range(lq):
-            blk, slot = divmod(j, s)
-            for h in range(heads):
-                chunk = pages[blk, h]
-                o = layout.off_kcodes + slot * layout.key_bytes
-                out["kcodes"][h, j] = chunk[o:o + layout.key_bytes]
-                out["norms"][h, j] = chunk[layout.off_knorm + 4 * slot:layout.off_knorm + 4 * slot + 4].view(np.float32)[0]
-                out["rnorms"][h, j] = chunk[layout.off_krnorm + 4 * slot:layout.off_krnorm + 4 * slot + 4].view(np.float32)[0]
-                o = layout.off_vdata + slot * layout.value_bytes
-                out["vdata"][h, j] = chunk[o:o + layout.value_bytes]
-                for name, base in (("vscales", layout.off_vscale), ("vzeros", layout.off_vzero)):
-                    o = base + slot * layout.groups * layout.dtype_bytes
-                    raw = chunk[o:o + layout.groups * layout.dtype_bytes]
-                    if meta_dtype is not None:
-                        out[name][h, j] = raw.view(meta_dtype).astype(np.float32)
-                    else:  # bfloat16
-                        out[name][h, j] = (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
-        return out
+        return packed_row_fields(self.pool, self.cache.turboquant_rows[0][b])
 
     def assert_bit_exact(self) -> None:
         for b, orc in enumerate(self.rows):

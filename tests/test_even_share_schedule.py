@@ -80,3 +80,18 @@ def test_even_share_covers_every_tile_once_with_dense_slots(seed):
         for unit, *_rest in pieces:
             work[unit] = work.get(unit, 0) + _rest[3]
         assert max(work.values()) <= share
+
+
+FUSED_MAX_CHUNKS = 512  # kFusedMaxChunks: weights per head that the fused merge stages in shared memory
+
+
+@pytest.mark.parametrize("capacity", [600, 4096])
+def test_even_share_never_exceeds_the_fused_merge_limit(capacity):
+    """A caller may hand in a scratch larger than the fused merge can stage; the kernel clamps the capacity it gives
+    to the schedule to 512, so one very long row beside short ones still gets at most 512 partials."""
+    lengths = [512 * 1024] + [1] * 7           # ~586 partials with an unclamped capacity and 592 units
+    pieces, _ = segments(lengths, 1, 592, min(capacity, FUSED_MAX_CHUNKS), 4)
+    assert pieces
+    assert max(partials for *_head, partials in pieces) <= FUSED_MAX_CHUNKS
+    unclamped, _ = segments(lengths, 1, 592, capacity, 4)
+    assert max(partials for *_head, partials in unclamped) > FUSED_MAX_CHUNKS  # the case the clamp is for

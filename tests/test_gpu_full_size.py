@@ -81,3 +81,114 @@ def test_config5_shard_full_size_packed_decode_agrees_with_dense_decode(cuda_dev
     assert pool.used_pages() == batch * ((context - 128 + 15) // 16)
     cache.release()
     assert pool.used_pages() == 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# full shapes against the CPU oracle on a sample of rows (the oracle handles one row of 32768 tokens in seconds)
+
+
+def _check_rows_against_oracle(cache, host_kv, sample_rows, query, *, bits, residual, heads, kv_heads, dim, page):
+    """For each sampled row: feed the very K / V the GPU row received to an oracle row, compare the packed codes and
+    metadata of three 16-token pages (first, middle, last) bit for bit, the block count, and the decode output."""
+    import numpy as np
+
+    import oracle
+    from tests.helpers import TQ_ATOL, error_stats, packed_row_fields, to_np
+
+    pool = cache.allocator.turboquant_layers[0]
+    out = cache.turboquant_single_token_decode_attention(0, query, scaling=dim ** -0.5,
+                                                         num_key_value_groups=heads // kv_heads)
+    assert torch.isfinite(out).all()
+    for b in sample_rows:
+        keys, values = host_kv[b]
+        orc = oracle.OracleTurboQuantRow(bits=bits, residual_len=residual, dtype=oracle.DTYPE_BF16, block_size=page,
+                                         allocator=oracle.OracleLayerAllocator(), keep_decode_cache=True)
+        orc.append(keys, values)
+        row = cache.turboquant_rows[0][b]
+        assert (row.length, row.quantized_length) == (orc.length, orc.quantized_length)
+        assert len(row.block_table) == len(orc.block_table)
+        lq = orc.quantized_length
+        want_codes = oracle.pack_key_codes(orc.idx, orc.sign, bits)
+        for first in sorted({0, (lq // 2) // page * page, max(0, (lq - 1) // page * page)}):
+            last = min(lq, first + page)
+            got = packed_row_fields(pool, row, first, last)
+            np.testing.assert_array_equal(got["kcodes"], want_codes[:, first:last])
+            np.testing.assert_array_equal(got["norms"].view(np.uint32), orc.norms[:, first:last].view(np.uint32))
+            np.testing.assert_array_equal(got["rnorms"].view(np.uint32), orc.rnorms[:, first:last].view(np.uint32))
+            np.testing.assert_array_equal(got["vdata"], orc.vdata[:, first:last])
+            np.testing.assert_array_equal(got["vscales"].view(np.uint32), orc.vscales[:, first:last].view(np.uint32))
+            np.testing.assert_array_equal(got["vzeros"].view(np.uint32), orc.vzeros[:, first:last].view(np.uint32))
+        want = orc.decode_attention(to_np(query[b, :, 0]), scaling=dim ** -0.5, blas=True)
+        max_abs, rel = error_stats(to_np(out[b, :, 0]), want)
+        # 16-bit TurboQuant tolerance of the small-size tests (the reference's own, tests/test_fused_op_xpu.py:703)
+        assert max_abs <= TQ_ATOL[torch.bfloat16] and rel <= TQ_ATOL[torch.bfloat16], (b, max_abs, rel)
+
+
+def test_config5_shard_full_size_sampled_rows_match_oracle(cuda_device):
+    """64 sequences x 32768 tokens, 4-bit, 32 q / 8 kv heads, D=128: two rows checked against the oracle."""
+    from tests.helpers import to_np
+
+    batch, heads, kv_heads, dim, context, page, bits, residual = 64, 32, 8, 128, 32768, 16, 4, 128
+    sample_rows = (3, 61)
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
+    cache = Qwen3DynamicCache(config, batch_size=batch, kv_cache_quantization="turboquant", kv_cache_quant_bits=bits,
+                              kv_cache_residual_len=residual)
+    cache.reserve_sequence_capacity(context)
+    gen = torch.Generator(device=cuda_device).manual_seed(31)
+    host = {b: ([], []) for b in sample_rows}
+    for _ in range(context // 4096):
+        k = torch.randn(batch, kv_heads, 4096, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+        v = torch.randn(batch, kv_heads, 4096, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+        cache.update(k, v, 0, require_dense_cache=False)
+        for b in sample_rows:
+            host[b][0].append(to_np(k[b]))
+            host[b][1].append(to_np(v[b]))
+        del k, v
+    import numpy as np
+
+    host_kv = {b: (np.concatenate(ks, axis=1), np.concatenate(vs, axis=1)) for b, (ks, vs) in host.items()}
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+    _check_rows_against_oracle(cache, host_kv, sample_rows, query, bits=bits, residual=residual, heads=heads,
+                               kv_heads=kv_heads, dim=dim, page=page)
+    cache.release()
+
+
+def test_config3_full_size_ragged_rows_match_oracle(cuda_device):
+    """64 sequences, contexts uniform in [4096, 32768], 2-bit, 16 q / 2 kv heads, D=256, window 128, per-channel
+    log-normal scales (sigma 0.5): the shortest, the longest and one more row checked against the oracle."""
+    import numpy as np
+
+    from tests.helpers import to_np
+
+    batch, heads, kv_heads, dim, page, bits, residual = 64, 16, 2, 256, 16, 2, 128
+    lengths = torch.randint(4096, 32769, (batch,), generator=torch.Generator().manual_seed(41)).tolist()
+    sample_rows = sorted({lengths.index(min(lengths)), lengths.index(max(lengths)), 29})
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=page)
+    allocator = Qwen3PageAllocator(config)
+    gen = torch.Generator(device=cuda_device).manual_seed(42)
+    channel_scale = torch.exp(0.5 * torch.randn(kv_heads, 1, dim, device=cuda_device, generator=gen))
+    rows, host_kv = [], {}
+    for b, n in enumerate(lengths):
+        row = Qwen3DynamicCache(config, allocator=allocator, batch_size=1, kv_cache_quantization="turboquant",
+                                kv_cache_quant_bits=bits, kv_cache_residual_len=residual)
+        k = (torch.randn(1, kv_heads, n, dim, device=cuda_device, generator=gen) * channel_scale).to(torch.bfloat16)
+        v = (torch.randn(1, kv_heads, n, dim, device=cuda_device, generator=gen) * channel_scale).to(torch.bfloat16)
+        row.update(k, v, 0, require_dense_cache=False)
+        if b in sample_rows:
+            host_kv[b] = (to_np(k[0]), to_np(v[0]))
+        rows.append(row)
+        del k, v
+    cache = Qwen3DynamicCache.stack(rows, config, clone_turboquant_rows=False)
+    assert cache.layer_lengths[0] == lengths
+    query = torch.randn(batch, heads, 1, dim, device=cuda_device, dtype=torch.bfloat16, generator=gen)
+    _check_rows_against_oracle(cache, host_kv, sample_rows, query, bits=bits, residual=residual, heads=heads,
+                               kv_heads=kv_heads, dim=dim, page=page)
+    # one more decode step on top: append a token per row, decode again, the sampled rows still agree
+    k1 = (torch.randn(batch, kv_heads, 1, dim, device=cuda_device, generator=gen) * channel_scale).to(torch.bfloat16)
+    v1 = (torch.randn(batch, kv_heads, 1, dim, device=cuda_device, generator=gen) * channel_scale).to(torch.bfloat16)
+    cache.update(k1, v1, 0, require_dense_cache=False)
+    host_kv = {b: (np.concatenate([kv[0], to_np(k1[b])], axis=1), np.concatenate([kv[1], to_np(v1[b])], axis=1))
+               for b, kv in host_kv.items()}
+    _check_rows_against_oracle(cache, host_kv, sample_rows, query, bits=bits, residual=residual, heads=heads,
+                               kv_heads=kv_heads, dim=dim, page=page)
+    cache.release()

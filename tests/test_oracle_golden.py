@@ -203,3 +203,24 @@ def test_grouped_query_attention_matches_reference(case):
     assert hidden.any() == (case == "full")
     np.testing.assert_allclose(out[~hidden], ref[~hidden], atol=2e-5, rtol=1e-5)
     assert not out[hidden].any()
+
+
+def test_incremental_decode_cache_equals_full_rematerialisation():
+    """The oracle row that extends its dense decode cache in place at every append (the reference's
+    _KEEP_DECODE_CACHE, src/anna/model/turboquant.py:742-782, :1089-1140) sees exactly the keys and values of the row
+    that de-quantizes its whole prefix at every call, across prefill, decode steps and a second chunk."""
+    rng = np.random.default_rng(5)
+    plain = oracle.OracleTurboQuantRow(bits=3, residual_len=8, dtype=oracle.DTYPE_BF16)
+    cached = oracle.OracleTurboQuantRow(bits=3, residual_len=8, dtype=oracle.DTYPE_BF16, keep_decode_cache=True)
+    for tokens in (5, 7, 1, 1, 40, 1):
+        k = oracle.round_bf16(rng.standard_normal((2, tokens, 64), dtype=np.float32))
+        v = oracle.round_bf16(rng.standard_normal((2, tokens, 64), dtype=np.float32))
+        plain.append(k, v)
+        cached.append(k, v)
+        for got, want in zip(cached.materialize(), plain.materialize()):
+            np.testing.assert_array_equal(got, want)
+        for name in ("idx", "sign", "norms", "rnorms", "vdata", "vscales", "vzeros"):
+            np.testing.assert_array_equal(getattr(cached, name), getattr(plain, name))
+    q = rng.standard_normal((4, 64), dtype=np.float32)
+    np.testing.assert_allclose(cached.decode_attention(q, scaling=0.125, blas=True),
+                               plain.decode_attention(q, scaling=0.125), atol=1e-5, rtol=1e-5)

@@ -8,10 +8,13 @@ from __future__ import annotations
 
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
+import oracle
 from anna_b200 import _lib
+from tests.helpers import to_np
 
 pytestmark = pytest.mark.gpu
 
@@ -56,7 +59,25 @@ def _decode_both(device, seed, batch, heads, kv_heads, dim, block, max_blocks, d
         "anna_paged_gqa_decode_noalloc")
     torch.cuda.synchronize(device)
     grew = free_before - torch.cuda.mem_get_info(device)[0]
-    return got, want, grew
+    # the same rows through the CPU oracle: gather each row's pages (holes dropped), dense fp32 attention
+    ref = np.zeros((batch, heads, 1, dim), dtype=np.float32)
+    table_host, lengths_host = table.cpu().tolist(), lengths.cpu().tolist()
+    kp, vp = to_np(key_pages), to_np(value_pages)
+    for b in range(batch):
+        n = int(lengths_host[b])
+        if n == 0:
+            continue
+        keys, vals = [], []
+        for blk in range((n + block - 1) // block):
+            pid, take = table_host[b][blk], min(block, n - blk * block)
+            if pid >= 0:
+                keys.append(kp[pid][:, :take])
+                vals.append(vp[pid][:, :take])
+        if not keys:
+            continue
+        ref[b, :, 0] = oracle.gqa_decode(to_np(query[b, :, 0]), np.concatenate(keys, axis=1),
+                                         np.concatenate(vals, axis=1), dim ** -0.5, to_np(gate[b, :, 0]))
+    return got, want, grew, torch.from_numpy(ref)
 
 
 def test_noalloc_decode_matches_regular_entry_point_twice(cuda_device):
@@ -64,16 +85,19 @@ def test_noalloc_decode_matches_regular_entry_point_twice(cuda_device):
     first = _decode_both(cuda_device, 1, batch=5, heads=32, kv_heads=8, dim=128, block=16, max_blocks=40,
                          dtype=torch.bfloat16)
     torch.testing.assert_close(first[0].float(), first[1].float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(first[0].float().cpu(), first[3], atol=2e-2, rtol=2e-2)  # and against the CPU oracle
     assert torch.count_nonzero(first[0][-1]) == 0
     # The first call on a device may load the library's device image (which contains the 16 MiB array); later calls
     # must not take any device memory at all.
     second = _decode_both(cuda_device, 2, batch=3, heads=8, kv_heads=2, dim=64, block=32, max_blocks=9,
                           dtype=torch.float32)
     torch.testing.assert_close(second[0], second[1], atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(second[0].cpu(), second[3], atol=2e-4, rtol=2e-4)
     assert second[2] <= 0
     third = _decode_both(cuda_device, 3, batch=5, heads=32, kv_heads=8, dim=128, block=16, max_blocks=40,
                          dtype=torch.bfloat16)
     torch.testing.assert_close(third[0].float(), third[1].float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(third[0].float().cpu(), third[3], atol=2e-2, rtol=2e-2)
     assert third[2] <= 0
 
 
@@ -86,7 +110,13 @@ def test_noalloc_decode_rejects_problems_beyond_its_scratch(cuda_device):
         _ptr(dummy), 0, 0, _ptr(dummy), _ptr(dummy), _ptr(dummy), 0, _ptr(dummy), None, 0, 0, _ptr(dummy), 0, 0,
         512, 64, 8, 256, 16, 1 << 20, 4096, 0.1, 2, stream)
     assert status == 4  # ANNA_ERR_WORKSPACE
-    assert "built-in" in _lib.last_error()
+    assert "built-in" in _lib.last_error() and "split-K scratch" in _lib.last_error()
+    # a short context whose partials would fit, but with more (row, head-group) pairs than the counter region holds
+    status = lib.anna_paged_gqa_decode_noalloc(
+        _ptr(dummy), 0, 0, _ptr(dummy), _ptr(dummy), _ptr(dummy), 0, _ptr(dummy), None, 0, 0, _ptr(dummy), 0, 0,
+        8200, 1, 1, 64, 16, 1 << 20, 1, 0.1, 2, stream)
+    assert status == 4
+    assert "merge counters" in _lib.last_error() and "8192" in _lib.last_error()
 
 
 def test_bounded_copy_wait_gives_up_and_context_survives(cuda_device):
