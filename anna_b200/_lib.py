@@ -40,6 +40,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_kv_abi_version": (c_i32, []),
     "anna_kv_device_faults": (c_i32, [ctypes.POINTER(c_i32)]),
     "anna_kv_selftest_wait_expiry": (c_i32, [ctypes.POINTER(c_i32), c_ptr]),
+    "anna_kv_selftest_umma": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, ctypes.POINTER(c_i32), c_ptr]),
     "anna_decode_plan": (c_i32, [c_i32, c_i32, c_i64, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
     "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i32,
                                     c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),

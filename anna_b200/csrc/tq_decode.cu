@@ -338,9 +338,6 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
     const bool fits = query_scratch != nullptr && query_scratch_bytes >= need &&
                       (reinterpret_cast<uintptr_t>(query_scratch) & 15u) == 0;
     p.query_frags = fits ? query_scratch : nullptr;
-    p.query_consts = fits ? reinterpret_cast<float*>(static_cast<uint8_t*>(query_scratch) + need -
-                                                     (size_t)batch * kv_heads * ((p.groups + 7) / 8) * 32 * sizeof(float))
-                          : nullptr;
   }
   if (tq_split_mma_applicable(p, head_dim, dtype)) {
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {

@@ -5,18 +5,14 @@
 //
 //   packed bytes of the tile --bulk copy (cp.async.bulk, mbarrier)--> shared (2 stages per warp); a tile of a 16-token
 //              page is one linear copy issued by one lane, larger pages take six
-//   K codes -> 8-bit (e4m3) A fragments in registers, four codes per byte-permute (PRMT): the code nibbles / 2-bit
-//              fields are the selectors of a centroid byte table; sign bits sit in the selector bit that makes PRMT
-//              replicate the top bit of the chosen byte, which turns a table of 1.0 bytes into {1.0, 0.0}
-//   S1[16 tok x 8 heads] = centroid(K) . Q1^T      S2 = sign(K) . Q2^T     (mma.sync m16n8k32, e4m3 x e4m3 -> fp32)
-//              centroids and rotated queries go in as a rounded byte plus the byte of the rounding residual
-//              (A_hi.Q_hi + A_hi.Q_lo + A_lo.Q_hi), so products carry about 8 significant bits like a 16-bit cache
-//   score = norm * (S1 + rnorm * S2) / qs[head]   with Q1 = fwht(s1*q) * scaling / sqrt(D)  (times c0 for 1-bit indices)
-//                                                      Q2 = fwht(s2*fwht(s1*q)) * scaling * sqrt(pi/2) / D^1.5
-//              and qs the per-head factor that brings the query fragments into the e4m3 range
+//   K codes -> fp16 A fragments in registers: byte-permute (PRMT) table lookups turn 4-bit / 2-bit fields into
+//              centroid values and +-1 signs, two tokens x D/4 coordinates per lane, no shared-memory round trip
+//   S1[16 tok x 8 heads] = centroid(K) . Q1^T      S2 = sign(K) . Q2^T        (2 x D/16 mma.sync m16n8k16, fp16)
+//   score = norm * (S1 + rnorm * S2)   with Q1 = fwht(s1*q) * scaling / sqrt(D)  (times c0 for 1-bit indices)
+//                                           Q2 = fwht(s2*fwht(s1*q)) * scaling * sqrt(pi/2) / D^1.5
 //   online softmax in fp32 on the C fragments; P packed to fp16 and transposed with movmatrix
 //   V codes -> fp16 (magic-number trick) -> (code * scale + zero) in fp16 pairs -> A fragments of V^T
-//   O^T[D x 8 heads] += V^T . P^T                                              (D/16 mma.sync m16n8k16, fp16)
+//   O^T[D x 8 heads] += V^T . P^T                                              (D/16 mma.sync)
 //
 // The K-dimension slots of the two score products are free to permute, so each lane takes the coordinates whose
 // codes it can unpack with the fewest instructions; Q1 / Q2 fragments are gathered with the same permutation.
@@ -25,22 +21,15 @@
 #include "tq_common.cuh"
 #include "tq_decode_params.cuh"
 
-#include <cuda_fp8.h>
-
 #include <cstdlib>
 
 namespace anna {
 
 __device__ int32_t g_tq_mma_faults;  // bumped when a bounded wait on a tile copy expires
 
-// Byte permute in PTX's default mode: result byte i is the byte of {a (0-3), b (4-7)} that bits 0-2 of nibble i of
-// `sel` name, or, when bit 3 of that nibble is set, eight copies of that byte's top bit.  Written as PTX because the
-// sign planes rely on the bit-3 behaviour; not volatile, so the compiler schedules it like any other arithmetic.
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
-}
+// Byte permute and logic helpers are plain intrinsics / C so that the compiler can fold the constant selectors,
+// masks and magic numbers into immediates instead of keeping them in registers.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) { return (x & mask) | bits; }
 __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
   const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
@@ -52,22 +41,9 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// float <-> e4m3 byte (round to nearest even, saturating)
-__device__ __forceinline__ uint32_t f32_to_e4m3(float x) {
-  return (uint32_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
-}
-__device__ __forceinline__ float e4m3_to_f32(uint32_t byte) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, __NV_E4M3);
-  return __half2float(__half(h));
-}
-// Four bytes picked from an all-1.0 table (0x38 is 1.0 in e4m3) by the low four nibbles of `sel`: PRMT replicates the
-// top bit of the chosen byte (0) when bit 3 of a nibble is set, so byte j = 1.0 - (bit 4j + 3 of sel).
-__device__ __forceinline__ uint32_t one_minus_bit3(uint32_t sel) { return prmt(0x38383838u, 0x38383838u, sel); }
-// mma.sync m16n8k32 (e4m3 in, fp32 accumulate); not volatile, like mma_f16 below
-__device__ __forceinline__ void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// fp16 pair (+-1, +-1) from bits b and b + 16 of x (0 <= b <= 15): a set bit gives +1.  One shift and one logic op.
+__device__ __forceinline__ uint32_t pm_one_pair(uint32_t x, int b) {
+  return ((x << (15 - b)) & 0x80008000u) ^ 0xBC00BC00u;
 }
 // mma.sync m16n8k16 (fp16 in, fp32 accumulate) without the volatile qualifier: a pure function of its operands, so
 // the compiler may interleave the independent accumulation chains of this kernel
@@ -125,8 +101,7 @@ constexpr float kLazyRescale = 8.0f;  // log2 units: probabilities stay below 2^
 
 template <typename T, int D, int BITS>
 struct TqMmaCfg {
-  static constexpr int kSteps = D / 16;                        // m-tiles of the value product (mma m16n8k16)
-  static constexpr int kKSteps = D / 32;                       // k-steps of the score products (mma m16n8k32)
+  static constexpr int kSteps = D / 16;
   static constexpr int kGroups = D / 32;                       // value group size is 32 on this path
   static constexpr int kKeyBytes = D * BITS / 8;               // packed key bytes per token
   static constexpr int kIdxBytes = BITS == 3 ? D / 4 : kKeyBytes;  // first plane (all of it unless BITS == 3)
@@ -161,44 +136,32 @@ struct TqMmaCfg {
   static_assert(D == 128 || D == 256, "tensor-core TurboQuant decode is built for head_dim 128 and 256");
 };
 
-// Coordinate whose code lane `tig` turns into byte j (0..3) of half h of k-step s of the score products.  Half 0 is
-// the register pair a0 / a1 (k-slots 4tig .. 4tig+3), half 1 the pair a2 / a3 (k-slots 16 + 4tig ..); lane tig owns the
-// run of D/4 consecutive coordinates starting at tig * D/4.
+// Coordinate that lane `tig` feeds into slot k (0..3 = 2tig, 2tig+1, 2tig+8, 2tig+9) of k-step s.
 template <int D, int BITS>
-__device__ __forceinline__ int idx_coord(int tig, int s, int h, int j) {
+__device__ __forceinline__ int idx_coord(int tig, int s, int k) {
   constexpr int kRun = D / 4;
-  // 4-bit codes: word s of the run holds 8 nibbles; its low half-word is half 0
-  if constexpr (BITS == 4) return tig * kRun + 8 * s + 4 * h + j;
-  // 2-bit index fields, 16 per word: even fields (k-step 2w) and odd fields (k-step 2w + 1) of each half-word
-  if constexpr (BITS == 3) return tig * kRun + 16 * (s / 2) + 8 * h + 2 * j + (s % 2);
-  // 2-bit codes (index bit | sign bit << 1), 16 per word: odd coordinates first (their sign bits need no shift)
-  return tig * kRun + 16 * (s / 2) + 8 * h + 2 * j + ((s % 2) == 0 ? 1 : 0);
+  if constexpr (BITS == 4) return tig * kRun + 4 * s + k;
+  if constexpr (BITS == 3) return tig * kRun + 8 * (s / 2) + 2 * k + (s % 2);
+  // 1-bit indices: bits 2c of a 16-coordinate word; a register pairs coordinates c and c + 8
+  return tig * kRun + 16 * (s / 4) + 2 * (s % 4) + (k >> 1) + 8 * (k & 1);
 }
 template <int D, int BITS>
-__device__ __forceinline__ int sign_coord(int tig, int s, int h, int j) {
+__device__ __forceinline__ int sign_coord(int tig, int s, int k) {
   constexpr int kRun = D / 4;
-  // separate 1-bit sign plane, 32 per word: k-step 4w + k takes bits 3 - k + 4j of each half-word
-  if constexpr (BITS == 3) return tig * kRun + 32 * (s / 4) + 16 * h + 4 * j + 3 - (s % 4);
-  return idx_coord<D, BITS>(tig, s, h, j);
+  // the two halves of a register take sign bits 16 apart in their word: 4 coordinates (4-bit codes), 8 (2-bit codes)
+  // or 16 (the separate sign plane of 3-bit codes) apart
+  if constexpr (BITS == 4) return tig * kRun + 8 * (s / 2) + 2 * (s % 2) + (k >> 1) + 4 * (k & 1);
+  if constexpr (BITS == 3) return tig * kRun + 32 * (s / 8) + 2 * (s % 8) + (k >> 1) + 16 * (k & 1);
+  return idx_coord<D, BITS>(tig, s, k);
 }
 
-constexpr float kFp8Top = 224.0f;   // largest magnitude of a scaled query entry (e4m3 holds up to 448)
-constexpr int kQueryConstFloats = 32;  // per (row, head group): 1 / qs, start value of S1, start value of S2 for 8 heads
-
-// Rotates the queries of one (row, kv-head group) and stores them as e4m3 B fragments in the register order of the
-// split kernel: [row][group][lane][k-step][two uint4: {Q1 hi b0, Q1 hi b1, Q1 lo b0, Q1 lo b1}, {Q2 hi b0, Q2 hi b1,
-// 0, 0}], where "lo" is the e4m3 rounding of what the "hi" byte left over.  Q2 multiplies the QJL correction, a few
-// per cent of the score, and goes in as one byte: its rounding (2^-4 relative per entry, about 4 % of S2 r.m.s.) moves
-// a logit by less than the 16-bit rounding of a de-quantized key does.  Q1 = fwht(s1*q) * f1 * qs, Q2 = fwht(s2*fwht(s1*q)) * f2 * qs
-// with qs chosen per head so that the largest entry is kFp8Top.
-// A plane whose A fragments are {1.0, 0.0} bytes for bit {0, 1} (every sign plane; the index plane of 1-bit indices)
-// scores sum_d q_d * (2 * bit_d - 1) = sum_d q_d - 2 * sum_d q_d * a_d: its fragments carry -2 * q and the accumulator
-// starts at -1/2 of the sum of the rounded fragment values, which the kernel writes next to 1 / qs.
+// Rotates the queries of one (row, kv-head group) and stores them as fp16 B fragments in the register order of the
+// split kernel: [row][group][lane][step][q1 b0, q1 b1, q2 b0, q2 b1].  Q1 = fwht(s1*q) / sqrt(D), Q2 = fwht(s2*fwht(s1*q)) / D.
 template <typename T, int D, int BITS>
 __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const TqDecodeParams p) {
   constexpr int E = D / 32;
-  constexpr int kKSteps = D / 32;
-  __shared__ uint8_t q_byte[2][2][8][D];  // [plane][hi, lo][head][coordinate]
+  constexpr int kSteps = D / 16;
+  __shared__ float q_rot[2][8][D];
   const int group_tiles = (p.groups + 7) / 8;
   const int kvh = blockIdx.x / group_tiles;
   const int g0 = (blockIdx.x % group_tiles) * 8;
@@ -208,16 +171,8 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const T* q_ptr = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b;
-  // score (log2 units) = norm * (S1 + rnorm * S2) with every constant folded into the fragments:
-  //   q.k_hat = norm/D * [Q1.c + sqrt(pi/2)/sqrt(D) * rnorm * Q2.sign],  Q1 = fwht(s1*q), Q2 = fwht(s2*Q1)
-  //   (1-bit indices: the centroids are +-c0, so the index plane is a sign plane scaled by c0)
-  const float inv_sqrt_d = rsqrt_dim_const<D>();
-  const float log2e = 1.4426950408889634f;
-  const float f1 = (BITS == 2 ? -2.0f * __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d * inv_sqrt_d;
-  const float f2 = -2.0f * p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d * inv_sqrt_d * inv_sqrt_d;
-  float* consts = p.query_consts + ((int64_t)b * gridDim.x + blockIdx.x) * kQueryConstFloats;
   for (int g = warp; g < 8; g += kMmaWarps) {
-    float w[E], w2[E];
+    float w[E];
 #pragma unroll
     for (int j = 0; j < E; ++j) {
       const int d = lane * E + j;
@@ -227,68 +182,35 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
     warp_fwht<E>(w, lane);
 #pragma unroll
     for (int j = 0; j < E; ++j) {
-      w2[j] = w[j];
-      if (p.signs2[lane * E + j] < 0.0f) w2[j] = -w2[j];
-    }
-    warp_fwht<E>(w2, lane);
-    float top = 0.0f;
-#pragma unroll
-    for (int j = 0; j < E; ++j) {
-      w[j] *= f1;
-      w2[j] *= f2;
-      top = fmaxf(top, fmaxf(fabsf(w[j]), fabsf(w2[j])));
-    }
-#pragma unroll
-    for (int dl = 1; dl < 32; dl <<= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, dl));
-    const float qs = (top > 1e-30f && top < 1e30f) ? kFp8Top / top : 1.0f;
-    float sum1 = 0.0f, sum2 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < E; ++j) {
       const int d = lane * E + j;
-      const float v1 = w[j] * qs, v2 = w2[j] * qs;
-      const uint32_t h1 = f32_to_e4m3(v1), h2 = f32_to_e4m3(v2);
-      const float r1 = e4m3_to_f32(h1), r2 = e4m3_to_f32(h2);
-      const uint32_t l1 = f32_to_e4m3(v1 - r1);
-      q_byte[0][0][g][d] = (uint8_t)h1; q_byte[0][1][g][d] = (uint8_t)l1;
-      q_byte[1][0][g][d] = (uint8_t)h2; q_byte[1][1][g][d] = 0;
-      sum1 += r1 + e4m3_to_f32(l1);
-      sum2 += r2;
+      q_rot[0][g][d] = w[j];
+      if (p.signs2[d] < 0.0f) w[j] = -w[j];
     }
+    warp_fwht<E>(w, lane);
 #pragma unroll
-    for (int dl = 1; dl < 32; dl <<= 1) {
-      sum1 += __shfl_xor_sync(0xffffffffu, sum1, dl);
-      sum2 += __shfl_xor_sync(0xffffffffu, sum2, dl);
-    }
-    if (lane == 0) {
-      consts[g] = 1.0f / qs;
-      consts[8 + g] = BITS == 2 ? -0.5f * sum1 : 0.0f;
-      consts[16 + g] = -0.5f * sum2;
-      consts[24 + g] = 0.0f;
-    }
+    for (int j = 0; j < E; ++j) q_rot[1][g][lane * E + j] = w[j];
   }
   __syncthreads();
-  uint4* out = reinterpret_cast<uint4*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * 32 * kKSteps * 2;
-  for (int item = threadIdx.x; item < 32 * kKSteps; item += kMmaThreads) {
-    const int ln = item / kKSteps;
-    const int s = item % kKSteps;
+  // score (log2 units) = norm * (S1 + rnorm * S2) with every constant folded into the fragments:
+  //   q.k_hat = norm/D * [Q1.c + sqrt(pi/2)/sqrt(D) * rnorm * Q2.sign],  Q1 = fwht(s1*q), Q2 = fwht(s2*Q1)
+  //   (1-bit indices: the centroids are +-c0 and the fragments carry +-1, so c0 goes into the factor)
+  const float inv_sqrt_d = rsqrt_dim_const<D>();
+  const float log2e = 1.4426950408889634f;
+  const float f1 = (BITS == 2 ? __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d * inv_sqrt_d;
+  const float f2 = p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d * inv_sqrt_d * inv_sqrt_d;
+  uint4* out = reinterpret_cast<uint4*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * 32 * kSteps;
+  for (int item = threadIdx.x; item < 32 * kSteps; item += kMmaThreads) {
+    const int ln = item / kSteps;
+    const int s = item % kSteps;
     const int gid = ln >> 2, tig = ln & 3;
-    uint32_t word[2][2][2];  // [plane][hi, lo][half]
-#pragma unroll
-    for (int pl = 0; pl < 2; ++pl)
-#pragma unroll
-      for (int hl = 0; hl < 2; ++hl)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t v = 0u;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = pl == 0 ? idx_coord<D, BITS>(tig, s, h, j) : sign_coord<D, BITS>(tig, s, h, j);
-            v |= (uint32_t)q_byte[pl][hl][gid][c] << (8 * j);
-          }
-          word[pl][hl][h] = v;
-        }
-    out[2 * item] = make_uint4(word[0][0][0], word[0][0][1], word[0][1][0], word[0][1][1]);
-    out[2 * item + 1] = make_uint4(word[1][0][0], word[1][0][1], word[1][1][0], word[1][1][1]);
+    const float* r1 = q_rot[0][gid];
+    const float* r2 = q_rot[1][gid];
+    uint4 v;
+    v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * f1, r1[idx_coord<D, BITS>(tig, s, 1)] * f1);
+    v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * f1, r1[idx_coord<D, BITS>(tig, s, 3)] * f1);
+    v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * f2, r2[sign_coord<D, BITS>(tig, s, 1)] * f2);
+    v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * f2, r2[sign_coord<D, BITS>(tig, s, 3)] * f2);
+    out[item] = v;
   }
 }
 
@@ -393,42 +315,33 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
   const int lane = threadIdx.x & 31;
   const int gid = lane >> 2;
   const int tig = lane & 3;
-  // Q fragments (e4m3 hi / lo bytes; softmax scale, log2(e) and the per-head range factor qs folded in) were prepared
-  // by tq_prepare_queries_kernel in exactly this lane's register order
-  uint32_t q1h[Cfg::kKSteps][2], q1l[Cfg::kKSteps][2], q2h[Cfg::kKSteps][2];
+  // Q fragments (fp16, softmax scale and log2(e) folded in) were prepared by tq_prepare_queries_kernel in exactly this
+  // lane's register order: [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]
+  uint32_t q1f[Cfg::kSteps][2], q2f[Cfg::kSteps][2];
   {
     const uint4* frag = reinterpret_cast<const uint4*>(p.query_frags) +
-                        (((int64_t)b * gridDim.y + blockIdx.y) * 32 + lane) * Cfg::kKSteps * 2;
+                        (((int64_t)b * gridDim.y + blockIdx.y) * 32 + lane) * Cfg::kSteps;
 #pragma unroll
-    for (int s = 0; s < Cfg::kKSteps; ++s) {
-      const uint4 v = __ldg(frag + 2 * s);
-      const uint2 w = __ldg(reinterpret_cast<const uint2*>(frag + 2 * s + 1));
-      q1h[s][0] = v.x; q1h[s][1] = v.y; q1l[s][0] = v.z; q1l[s][1] = v.w;
-      q2h[s][0] = w.x; q2h[s][1] = w.y;
+    for (int s = 0; s < Cfg::kSteps; ++s) {
+      const uint4 v = __ldg(frag + s);
+      q1f[s][0] = v.x; q1f[s][1] = v.y; q2f[s][0] = v.z; q2f[s][1] = v.w;
     }
   }
-  // per head of this lane's two score columns (heads 2tig, 2tig + 1): 1 / qs and the start values of S1 and S2
-  const float* qconst = p.query_consts + ((int64_t)b * gridDim.y + blockIdx.y) * kQueryConstFloats;
-  const float kq[2] = {__ldg(qconst + 2 * tig), __ldg(qconst + 2 * tig + 1)};
-  // (only 1-bit indices have a sign-type index plane and with it a non-zero start value of S1)
-  const float s1_init[2] = {BITS == 2 ? __ldg(qconst + 8 + 2 * tig) : 0.0f, BITS == 2 ? __ldg(qconst + 8 + 2 * tig + 1) : 0.0f};
-  const float s2_init[2] = {__ldg(qconst + 16 + 2 * tig), __ldg(qconst + 16 + 2 * tig + 1)};
 
-  // centroid byte tables for PRMT (up to 8 entries): e4m3 rounding of each centroid and of what the rounding left over
-  uint32_t lut_hi[2] = {0u, 0u}, lut_lo[2] = {0u, 0u};
+  // centroid lookup tables for PRMT: low bytes and high bytes of the fp16 centroids (up to 8 entries)
+  uint32_t lut_lo[2] = {0u, 0u}, lut_hi[2] = {0u, 0u};
   if constexpr (BITS != 2) {
     constexpr int kEntries = 1 << (BITS - 1);
 #pragma unroll
     for (int e = 0; e < kEntries; ++e) {
-      const float c = __ldg(p.centroids + e);
-      const uint32_t hi = f32_to_e4m3(c);
-      const uint32_t lo = f32_to_e4m3(c - e4m3_to_f32(hi));
-      lut_hi[e / 4] |= hi << (8 * (e % 4));
-      lut_lo[e / 4] |= lo << (8 * (e % 4));
+      const __half h = __float2half_rn(__ldg(p.centroids + e));
+      const uint32_t bits = (uint32_t)__half_as_ushort(h);
+      lut_lo[e / 4] |= (bits & 0xffu) << (8 * (e % 4));
+      lut_hi[e / 4] |= (bits >> 8) << (8 * (e % 4));
     }
     if constexpr (BITS == 3) {  // 4 entries: mirror them so that PRMT may pick from either operand
-      lut_hi[1] = lut_hi[0];
       lut_lo[1] = lut_lo[0];
+      lut_hi[1] = lut_hi[0];
     }
   }
 
@@ -542,10 +455,9 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
     // ---- scores: U independent pairs of accumulation chains ------------------------------------------------------------
     float s1[U][4], s2[U][4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      s1[u][0] = s1[u][2] = s1_init[0]; s1[u][1] = s1[u][3] = s1_init[1];
-      s2[u][0] = s2[u][2] = s2_init[0]; s2[u][1] = s2[u][3] = s2_init[1];
-    }
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s1[u][r] = s2[u][r] = 0.0f;
     {
       uint32_t iw_lo[U][Cfg::kIdxWords], iw_hi[U][Cfg::kIdxWords];
 #pragma unroll
@@ -555,51 +467,45 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
         lds_words<Cfg::kIdxWords>(keys + tok_hi * Cfg::kKeyBytes, iw_hi[u]);
       }
       if constexpr (BITS == 4) {
-        // nibble = index | sign << 3: the masked nibbles select centroid bytes, the raw ones (bit 3) the sign bytes
 #pragma unroll
-        for (int s = 0; s < Cfg::kKSteps; ++s) {
+        for (int s = 0; s < Cfg::kSteps; ++s) {
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const uint32_t xl = iw_lo[u][s], xh = iw_hi[u][s];
-            const uint32_t tl = xl & 0x77777777u, th = xh & 0x77777777u;
-            const uint32_t tl2 = tl >> 16, th2 = th >> 16;
-            const uint32_t a_hi[4] = {prmt(lut_hi[0], lut_hi[1], tl), prmt(lut_hi[0], lut_hi[1], th),
-                                      prmt(lut_hi[0], lut_hi[1], tl2), prmt(lut_hi[0], lut_hi[1], th2)};
-            const uint32_t a_lo[4] = {prmt(lut_lo[0], lut_lo[1], tl), prmt(lut_lo[0], lut_lo[1], th),
-                                      prmt(lut_lo[0], lut_lo[1], tl2), prmt(lut_lo[0], lut_lo[1], th2)};
-            mma_e4m3(s1[u], a_hi, q1h[s][0], q1h[s][1]);
-            mma_e4m3(s1[u], a_hi, q1l[s][0], q1l[s][1]);
-            mma_e4m3(s1[u], a_lo, q1h[s][0], q1h[s][1]);
+            const uint32_t wl = iw_lo[u][s / 2] >> (16 * (s % 2));
+            const uint32_t wh = iw_hi[u][s / 2] >> (16 * (s % 2));
+            const uint32_t sl = wl & 0x7777u, sh = wh & 0x7777u;
+            const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
+            const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
+            const uint32_t a[4] = {prmt(lo_l, hi_l, 0x5140u), prmt(lo_h, hi_h, 0x5140u), prmt(lo_l, hi_l, 0x7362u),
+                                   prmt(lo_h, hi_h, 0x7362u)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const uint32_t xl = iw_lo[u][s], xh = iw_hi[u][s];
-            const uint32_t a[4] = {one_minus_bit3(xl), one_minus_bit3(xh), one_minus_bit3(xl >> 16),
-                                   one_minus_bit3(xh >> 16)};
-            mma_e4m3(s2[u], a, q2h[s][0], q2h[s][1]);
+            // sign bits 3 + 4i of the word: nibbles i and i + 4 land in the two halves of one register
+            const uint32_t xl = iw_lo[u][s / 2], xh = iw_hi[u][s / 2];
+            const int b0 = 3 + 8 * (s % 2), b1 = 7 + 8 * (s % 2);
+            const uint32_t a[4] = {pm_one_pair(xl, b0), pm_one_pair(xh, b0), pm_one_pair(xl, b1), pm_one_pair(xh, b1)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
         }
       } else if constexpr (BITS == 2) {
-        // field = index bit | sign bit << 1: a left shift by 0 .. 3 puts the wanted bit of every second coordinate into
-        // bit 3 of a selector nibble
 #pragma unroll
-        for (int s = 0; s < Cfg::kKSteps; ++s) {
-          const int ls = (s % 2) == 0 ? 0 : 2;  // sign bits of the odd / even coordinates
-          const int li = ls + 1;                // their index bits
+        for (int s = 0; s < Cfg::kSteps; ++s) {
+          const int h = s % 4;
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const uint32_t xl = iw_lo[u][s / 2], xh = iw_hi[u][s / 2];
-            const uint32_t a[4] = {one_minus_bit3(xl << li), one_minus_bit3(xh << li), one_minus_bit3(xl >> (16 - li)),
-                                   one_minus_bit3(xh >> (16 - li))};
-            mma_e4m3(s1[u], a, q1h[s][0], q1h[s][1]);
-            mma_e4m3(s1[u], a, q1l[s][0], q1l[s][1]);
+            const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h), pm_one_pair(xh, 4 * h), pm_one_pair(xl, 4 * h + 2),
+                                   pm_one_pair(xh, 4 * h + 2)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const uint32_t xl = iw_lo[u][s / 2], xh = iw_hi[u][s / 2];
-            const uint32_t a[4] = {one_minus_bit3(xl << ls), one_minus_bit3(xh << ls), one_minus_bit3(xl >> (16 - ls)),
-                                   one_minus_bit3(xh >> (16 - ls))};
-            mma_e4m3(s2[u], a, q2h[s][0], q2h[s][1]);
+            const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h + 1), pm_one_pair(xh, 4 * h + 1), pm_one_pair(xl, 4 * h + 3),
+                                   pm_one_pair(xh, 4 * h + 3)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
         }
       } else {
@@ -611,34 +517,32 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
           lds_words<Cfg::kSignWords>(signs + tok_hi * Cfg::kKeyBytes, sw_hi[u]);
         }
 #pragma unroll
-        for (int s = 0; s < Cfg::kKSteps; ++s) {
+        for (int s = 0; s < Cfg::kSteps; ++s) {
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            // 2-bit index fields: even fields of word s / 2 (s even) or odd ones (s odd) as selector nibbles
-            const uint32_t tl = (iw_lo[u][s / 2] >> (2 * (s % 2))) & 0x33333333u;
-            const uint32_t th = (iw_hi[u][s / 2] >> (2 * (s % 2))) & 0x33333333u;
-            const uint32_t tl2 = tl >> 16, th2 = th >> 16;
-            const uint32_t a_hi[4] = {prmt(lut_hi[0], lut_hi[1], tl), prmt(lut_hi[0], lut_hi[1], th),
-                                      prmt(lut_hi[0], lut_hi[1], tl2), prmt(lut_hi[0], lut_hi[1], th2)};
-            const uint32_t a_lo[4] = {prmt(lut_lo[0], lut_lo[1], tl), prmt(lut_lo[0], lut_lo[1], th),
-                                      prmt(lut_lo[0], lut_lo[1], tl2), prmt(lut_lo[0], lut_lo[1], th2)};
-            mma_e4m3(s1[u], a_hi, q1h[s][0], q1h[s][1]);
-            mma_e4m3(s1[u], a_hi, q1l[s][0], q1l[s][1]);
-            mma_e4m3(s1[u], a_lo, q1h[s][0], q1h[s][1]);
+            // 2-bit indices: half-word s / 2 of the lane's run, even (s % 2 == 0) or odd fields
+            const uint32_t wl = iw_lo[u][s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
+            const uint32_t wh = iw_hi[u][s / 4] >> (16 * ((s / 2) % 2) + 2 * (s % 2));
+            const uint32_t sl = wl & 0x3333u, sh = wh & 0x3333u;
+            const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
+            const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
+            const uint32_t a[4] = {prmt(lo_l, hi_l, 0x5140u), prmt(lo_h, hi_h, 0x5140u), prmt(lo_l, hi_l, 0x7362u),
+                                   prmt(lo_h, hi_h, 0x7362u)};
+            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            // sign plane: bits 3 - k + 4j of both half-words of word s / 4, k = s % 4
-            const uint32_t xl = sw_lo[u][s / 4], xh = sw_hi[u][s / 4];
-            const int k = s % 4;
-            const uint32_t a[4] = {one_minus_bit3(xl << k), one_minus_bit3(xh << k), one_minus_bit3(xl >> (16 - k)),
-                                   one_minus_bit3(xh >> (16 - k))};
-            mma_e4m3(s2[u], a, q2h[s][0], q2h[s][1]);
+            // sign plane: bits 2h, 2h + 1 (and + 16) of word s / 8, h = s % 8
+            const uint32_t xl = sw_lo[u][s / 8], xh = sw_hi[u][s / 8];
+            const int h = s % 8;
+            const uint32_t a[4] = {pm_one_pair(xl, 2 * h), pm_one_pair(xh, 2 * h), pm_one_pair(xl, 2 * h + 1),
+                                   pm_one_pair(xh, 2 * h + 1)};
+            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
         }
       }
     }
-    // score = norm * (S1 + rnorm * S2) in the fragments' units: true log2 score = kq[head] * sc
+    // score (log2 units) = norm * (S1 + rnorm * S2); the constant factors are folded into the query fragments
     float sc[U][4];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -667,12 +571,11 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
       mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
     }
-    // scores are in the fragments' units (true log2 score = kq * sc): the running maximum may lag by 2^8 true units
-    const bool grew = ((mx[0] - m_run[0]) * kq[0] > kLazyRescale) || ((mx[1] - m_run[1]) * kq[1] > kLazyRescale);
+    const bool grew = (mx[0] > m_run[0] + kLazyRescale) || (mx[1] > m_run[1] + kLazyRescale);
     if (__any_sync(0xffffffffu, grew)) {
       const float m_new[2] = {fmaxf(m_run[0], mx[0]), fmaxf(m_run[1], mx[1])};
-      const float a0 = fast_exp2(kq[0] * (m_run[0] - (m_new[0] == -INFINITY ? 0.0f : m_new[0])));
-      const float a1 = fast_exp2(kq[1] * (m_run[1] - (m_new[1] == -INFINITY ? 0.0f : m_new[1])));
+      const float a0 = fast_exp2(m_run[0] - (m_new[0] == -INFINITY ? 0.0f : m_new[0]));
+      const float a1 = fast_exp2(m_run[1] - (m_new[1] == -INFINITY ? 0.0f : m_new[1]));
       l_run[0] *= a0;
       l_run[1] *= a1;
 #pragma unroll
@@ -685,16 +588,14 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       m_run[0] = m_new[0];
       m_run[1] = m_new[1];
     }
-    // p = 2^(kq * (sc - m)) as one multiply-add and one exponential
-    const float nm[2] = {m_run[0] == -INFINITY ? 0.0f : -kq[0] * m_run[0],
-                         m_run[1] == -INFINITY ? 0.0f : -kq[1] * m_run[1]};
+    const float m_ref[2] = {m_run[0] == -INFINITY ? 0.0f : m_run[0], m_run[1] == -INFINITY ? 0.0f : m_run[1]};
     uint32_t pb[U][2];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const float p0 = fast_exp2(fmaf(sc[u][0], kq[0], nm[0]));
-      const float p1 = fast_exp2(fmaf(sc[u][1], kq[1], nm[1]));
-      const float p2 = fast_exp2(fmaf(sc[u][2], kq[0], nm[0]));
-      const float p3 = fast_exp2(fmaf(sc[u][3], kq[1], nm[1]));
+      const float p0 = fast_exp2(sc[u][0] - m_ref[0]);
+      const float p1 = fast_exp2(sc[u][1] - m_ref[1]);
+      const float p2 = fast_exp2(sc[u][2] - m_ref[0]);
+      const float p3 = fast_exp2(sc[u][3] - m_ref[1]);
       l_run[0] += p0 + p2;
       l_run[1] += p1 + p3;
       pb[u][0] = movmatrix_trans(pack2<__half>(p0, p1));  // rows 2tig, 2tig+1 of head gid
@@ -736,7 +637,7 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
           uint32_t r[2][4];
 #pragma unroll
           for (int pr = 0; pr < 2; ++pr) {
-            const uint32_t x = __byte_perm(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
+            const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
             const uint32_t y = x >> 8;
             const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
             r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000F000Fu, kMagicLo), kMagicLo), scl, zpt);
@@ -762,7 +663,7 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
           uint32_t r[2][8];
 #pragma unroll
           for (int pr = 0; pr < 2; ++pr) {
-            const uint32_t x = __byte_perm(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
+            const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
             const uint32_t y = x >> 10;
             const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
             r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00030003u, kM0), kM0), scl, zpt);
@@ -816,7 +717,6 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
   for (int item = threadIdx.x; item < g_count * D; item += kMmaThreads) {
     const int g = item / D;
     const int d = item % D;
-    const float kq_g = __ldg(qconst + g);  // the warps' maxima are in the fragments' units: true log2 = kq * m
     float m_all = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kMmaWarps; ++w) m_all = fmaxf(m_all, sm_m[w * 8 + g]);
@@ -824,13 +724,13 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
     float l_all = 0.0f, o_all = 0.0f;
 #pragma unroll
     for (int w = 0; w < kMmaWarps; ++w) {
-      const float wgt = exp2f(kq_g * (sm_m[w * 8 + g] - m_ref));
+      const float wgt = exp2f(sm_m[w * 8 + g] - m_ref);
       l_all += sm_l[w * 8 + g] * wgt;
       o_all += sm_o[(w * 8 + g) * kPad + d] * wgt;
     }
     values_out[(int64_t)g * p.chunk_capacity * D + d] = o_all;
     if (d == 0) {
-      stats_out[(int64_t)g * p.chunk_capacity * 2 + 0] = m_all * kq_g * 0.6931471805599453f;
+      stats_out[(int64_t)g * p.chunk_capacity * 2 + 0] = m_all * 0.6931471805599453f;
       stats_out[(int64_t)g * p.chunk_capacity * 2 + 1] = l_all;
     }
   }

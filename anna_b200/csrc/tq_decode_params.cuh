@@ -29,15 +29,12 @@ struct TqDecodeParams {
   float scaling;
   anna_tq_layout layout;
   FusedCombine fused;
-  void* query_frags;    // scratch for the rotated 8-bit query fragments (tensor-core path), or nullptr
-  float* query_consts;  // behind the fragments: 32 floats per (row, kv head, group of 8 query heads)
+  void* query_frags;  // scratch for the rotated fp16 query fragments (tensor-core path), or nullptr
 };
 
-// Bytes of query scratch the tensor-core path needs: fragments (32 * head_dim per (row, kv head, group of 8 query
-// heads)) followed by that group's 32 per-head constants.
+// Bytes of query scratch the tensor-core path needs: 32 * head_dim per (row, kv head, group of 8 query heads).
 inline size_t tq_query_scratch_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
-  const size_t units = (size_t)batch * kv_heads * ((q_heads / kv_heads + 7) / 8);
-  return units * ((size_t)32 * head_dim + 32 * sizeof(float));
+  return (size_t)batch * kv_heads * ((q_heads / kv_heads + 7) / 8) * 32 * head_dim;
 }
 
 // Tensor-core split pass (tq_decode_mma.cu): 16-bit cache dtypes, head_dim 128 / 256, value group 32, page size % 16 == 0.

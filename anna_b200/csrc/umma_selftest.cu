@@ -1,0 +1,116 @@
+// Self-test of the tensor-memory matrix-multiply primitives (umma_utils.cuh) in the two operand arrangements the packed
+// decode uses:
+//   D1[128 x 16] = A1[128 x 128] . B1[16 x 128]^T    e4m3 operands, both K-major          (scores: tokens x heads)
+//   D2[128 x 16] = A2[128 x 128]^T . B2[128 x 16]    f16 operands, both MN-major          (values: dims x heads)
+// Operands arrive as plain row-major device arrays, the kernel re-tiles them into the canonical shared-memory layouts
+// with the padded strides of the real kernel, multiplies, and returns the accumulators.  No counterpart in the reference.
+#include "umma_utils.cuh"
+
+namespace anna {
+
+constexpr int kSelfM = 128, kSelfN = 16, kSelfK = 128;
+// strides of the canonical layouts (bytes); the odd multiples of 16 spread a warp's 16-byte stores over all banks
+constexpr uint32_t kA1Sbo = 128, kA1Lbo = 128 * 16 + 16;   // K-major A: 8-row groups back to back, K chunks padded
+constexpr uint32_t kB1Sbo = 128, kB1Lbo = 256;             // K-major B: 16 rows = two groups per K chunk
+constexpr uint32_t kA2Sbo = 144, kA2Lbo = 16 * 144;        // MN-major A: 16 groups of 8 rows per 8 K indices, padded
+constexpr uint32_t kB2Sbo = 128, kB2Lbo = 256;             // MN-major B: two groups of 8 columns per 8 K indices
+constexpr uint32_t kA1Bytes = 8 * kA1Lbo, kB1Bytes = 8 * kB1Lbo, kA2Bytes = 16 * kA2Lbo, kB2Bytes = 16 * kB2Lbo;
+constexpr uint32_t kSelfSmem = kA1Bytes + kB1Bytes + kA2Bytes + kB2Bytes;
+
+__global__ void __launch_bounds__(128) umma_selftest_kernel(const uint8_t* a1, const uint8_t* b1, const __half* a2,
+                                                            const __half* b2, float* d1, float* d2, int32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* s_a1 = smem;
+  uint8_t* s_b1 = s_a1 + kA1Bytes;
+  uint8_t* s_a2 = s_b1 + kB1Bytes;
+  uint8_t* s_b2 = s_a2 + kA2Bytes;
+  const uint32_t bar = smem_u32(&bar_storage);
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 32);
+  // re-tile the operands
+  for (int i = threadIdx.x; i < kSelfM * kSelfK; i += blockDim.x) {  // A1[r][k], one byte each
+    const int r = i / kSelfK, k = i % kSelfK;
+    s_a1[(r / 8) * kA1Sbo + (k / 16) * kA1Lbo + (r % 8) * 16 + k % 16] = a1[i];
+  }
+  for (int i = threadIdx.x; i < kSelfN * kSelfK; i += blockDim.x) {  // B1[n][k]
+    const int r = i / kSelfK, k = i % kSelfK;
+    s_b1[(r / 8) * kB1Sbo + (k / 16) * kB1Lbo + (r % 8) * 16 + k % 16] = b1[i];
+  }
+  for (int i = threadIdx.x; i < kSelfK * kSelfM; i += blockDim.x) {  // A2[k][m]: K index k, row m (2 bytes each)
+    const int k = i / kSelfM, m = i % kSelfM;
+    *reinterpret_cast<__half*>(s_a2 + (m / 8) * kA2Sbo + (k / 8) * kA2Lbo + (k % 8) * 16 + (m % 8) * 2) = a2[i];
+  }
+  for (int i = threadIdx.x; i < kSelfK * kSelfN; i += blockDim.x) {  // B2[k][n]
+    const int k = i / kSelfN, n = i % kSelfN;
+    *reinterpret_cast<__half*>(s_b2 + (n / 8) * kB2Sbo + (k / 8) * kB2Lbo + (k % 8) * 16 + (n % 8) * 2) = b2[i];
+  }
+  fence_async_smem();
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc1 = umma_idesc(kUmmaE4M3, kUmmaE4M3, false, false, kSelfM, kSelfN);
+    constexpr uint32_t idesc2 = umma_idesc(kUmmaF16, kUmmaF16, true, true, kSelfM, kSelfN);
+    for (int k = 0; k < kSelfK / 32; ++k)  // 32 e4m3 values of K per instruction = two 16-byte chunks
+      umma_f8(tmem, umma_smem_desc(smem_u32(s_a1) + 2 * k * kA1Lbo, kA1Lbo, kA1Sbo),
+              umma_smem_desc(smem_u32(s_b1) + 2 * k * kB1Lbo, kB1Lbo, kB1Sbo), idesc1, k > 0);
+    for (int k = 0; k < kSelfK / 16; ++k)  // 16 f16 values of K per instruction = two groups of 8 K indices
+      umma_f16(tmem + 16, umma_smem_desc(smem_u32(s_a2) + 2 * k * kA2Lbo, kA2Lbo, kA2Sbo),
+               umma_smem_desc(smem_u32(s_b2) + 2 * k * kB2Lbo, kB2Lbo, kB2Sbo), idesc2, k > 0);
+    umma_commit(bar);
+  }
+  const bool landed = mbar_wait(bar, 0u);
+  tcgen05_fence_after_sync();
+  if (landed) {
+    uint32_t r1[16], r2[16];
+    tmem_ld16(tmem_addr(tmem, 32 * warp, 0), r1);
+    tmem_ld16(tmem_addr(tmem, 32 * warp, 16), r2);
+    tmem_wait_ld();
+    for (int j = 0; j < 16; ++j) {
+      d1[threadIdx.x * 16 + j] = __uint_as_float(r1[j]);
+      d2[threadIdx.x * 16 + j] = __uint_as_float(r2[j]);
+    }
+  } else if (threadIdx.x == 0) {
+    *status = 1;  // the multiply never reported completion
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 32);
+}
+
+}  // namespace anna
+
+// a1 uint8 [128][128] (e4m3 bytes), b1 uint8 [16][128], a2 f16 [128 (K)][128 (rows)], b2 f16 [128 (K)][16]:
+// d1 float [128][16] = a1 . b1^T, d2 float [128][16] = a2^T . b2.  *status = 1 when the tensor core did not report back
+// within the bounded wait.  Synchronises the stream.
+extern "C" int anna_kv_selftest_umma(const void* a1, const void* b1, const void* a2, const void* b2, float* d1,
+                                     float* d2, int* status, anna_stream_t stream) {
+  using namespace anna;
+  ANNA_REQUIRE(a1 && b1 && a2 && b2 && d1 && d2 && status, "anna_kv_selftest_umma: null pointer argument");
+  int32_t* flag = nullptr;
+  ANNA_CUDA_CHECK(cudaMalloc(&flag, sizeof(int32_t)));
+  cudaError_t err = cudaMemsetAsync(flag, 0, sizeof(int32_t), (cudaStream_t)stream);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSelfSmem);
+  if (err == cudaSuccess) {
+    umma_selftest_kernel<<<1, 128, kSelfSmem, (cudaStream_t)stream>>>(
+        static_cast<const uint8_t*>(a1), static_cast<const uint8_t*>(b1), static_cast<const __half*>(a2),
+        static_cast<const __half*>(b2), d1, d2, flag);
+    err = cudaGetLastError();
+  }
+  int32_t value = -1;
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(&value, flag, sizeof(value), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
+  cudaFree(flag);
+  if (err != cudaSuccess) return set_error(ANNA_ERR_CUDA, "tensor-memory self-test failed: %s", cudaGetErrorString(err));
+  *status = (int)value;
+  return ANNA_OK;
+}

@@ -1,0 +1,119 @@
+// 5th-generation tensor-core primitives (tcgen05 / tensor memory) as inline PTX, for kernels whose operands are
+// produced in shared memory by the CTA itself.
+//
+// Conventions used by every caller:
+//   * one CTA = one tcgen05 "cta_group::1" participant; M = 128 rows, so accumulator row i lives in tensor-memory lane i
+//     and accumulator column j in column base + j (32-bit cells); warp w may touch lanes [32 * (w % 4), +32) only
+//   * operands sit in shared memory in the un-swizzled canonical layouts, cut into "core matrices" of 8 x 16 bytes:
+//       K-major  (K contiguous):   element (row r, K-byte k) at (r / 8) * SBO + (k / 16) * LBO + (r % 8) * 16 + k % 16
+//       MN-major (rows contiguous): element (row-byte m, K index k) at (m / 16) * SBO + (k / 8) * LBO + (k % 8) * 16 + m % 16
+//     one instruction consumes 32 bytes of K per row (32 e4m3 or 16 f16 values), i.e. two core matrices along K, and
+//     finds the second one LBO bytes (K-major) / the next 8 K indices LBO bytes (MN-major) behind the first
+//   * shared-memory writes of ordinary threads become visible to the tensor core through fence_async_smem() + a CTA
+//     barrier; completion comes back through tcgen05.commit on an mbarrier, waited for with the bounded mbar_wait
+#pragma once
+
+#include "mbarrier_utils.cuh"
+
+namespace anna {
+
+// 64-bit shared-memory matrix descriptor: start address, leading / stride byte offsets (all in 16-byte units, 14 bits
+// each), descriptor version 1, no swizzle.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
+}
+
+enum UmmaFormat : uint32_t { kUmmaF16 = 0, kUmmaBF16 = 1, kUmmaE4M3 = 0, kUmmaE5M2 = 1 };
+
+// 32-bit instruction descriptor: fp32 accumulate, dense, A / B formats and majors, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_format, uint32_t b_format, bool a_mn_major, bool b_mn_major, int m, int n) {
+  return (1u << 4) | (a_format << 7) | (b_format << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- tensor memory --------------------------------------------------------------------------------------------------
+// Called by one whole warp; `columns` is a power of two >= 32.  The address lands in *smem_slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_slot)),
+               "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+// Called by the warp that allocated.
+__device__ __forceinline__ void tmem_free(uint32_t tmem_addr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_addr), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+// Orders this thread's earlier shared-memory writes before later reads of the asynchronous proxy (tensor core, copy
+// engine).
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// ---- matrix multiply-accumulate, both operands in shared memory; issued by ONE thread -------------------------------
+// D[tmem] (+)= A[smem] * B[smem]; accumulate == 0 overwrites D.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier gets one arrival once every multiply-accumulate this thread issued before has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// ---- tensor memory <-> registers: each lane of the warp moves N consecutive 32-bit columns of its own lane ---------
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Address of (lane, column) relative to an allocation base.
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t column) {
+  return base + (lane << 16) + column;
+}
+
+}  // namespace anna

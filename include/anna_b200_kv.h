@@ -53,6 +53,17 @@ int anna_kv_device_faults(int* count);
  */
 int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream);
 
+/*
+ * Self-test of the tensor-memory matrix multiply (tcgen05) in the two operand arrangements of the packed decode:
+ *   d1 float [128][16] = a1 . b1^T   a1 uint8 [128][128], b1 uint8 [16][128]: e4m3 bytes, K contiguous
+ *   d2 float [128][16] = a2^T . b2   a2 f16 [128 (K)][128 (rows)], b2 f16 [128 (K)][16 (columns)]
+ * The kernel re-tiles the row-major inputs into the shared-memory layouts of the real kernel, multiplies with fp32
+ * accumulation in tensor memory and returns the accumulators.  *status = 1 when the tensor core did not report back
+ * within the bounded wait.  Synchronises the stream.  No counterpart in the reference.
+ */
+int anna_kv_selftest_umma(const void* a1, const void* b1, const void* a2, const void* b2, float* d1, float* d2,
+                          int* status, anna_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
  * (row, query head, chunk) leaves a partial in caller-owned float32 buffers
@@ -219,7 +230,7 @@ int anna_tq_append(const void* k_new, const void* v_new, int64_t kn_stride_b, in
  * turboquant.py:290-332) instead of from a dense de-quantized copy.
  *   lengths   int64 [B]: total tokens per row (quantized = max(0, L - R), window = min(L, R)); L == 0 gives zeros
  *   query_scratch: optional 16-byte aligned device scratch of at least anna_tq_query_scratch_bytes(B, Hq, Hkv, D)
- *   bytes; the tensor-core path stores the rotated queries there (as 8-bit MMA fragments plus per-head constants)
+ *   bytes; the tensor-core path stores the rotated queries there (as fp16 MMA fragments)
  *   before the split pass.  Without it, or for fp32 caches, head_dim 64, value groups other than 32 or page sizes that
  *   are not a multiple of 16, the CUDA-core path runs.
  *   split-K slots: anna_tq_decode_plan gives the chunk length and the slot count (window chunks first, then the

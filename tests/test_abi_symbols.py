@@ -39,7 +39,8 @@ def test_header_declares_the_expected_entry_points():
             "anna_paged_gqa_decode", "anna_gqa_decode", "anna_gqa_prefill", "anna_tq_page_layout", "anna_tq_append",
             "anna_tq_paged_decode", "anna_tq_materialize", "anna_gqa_decode_turboquant_values",
             "anna_tq_decode_plan", "anna_kv_device_faults", "anna_tq_tensor_row_bytes",
-            "anna_tq_tensor_quantize", "anna_tq_tensor_dequantize", "anna_tq_gather_dense", "anna_kv_selftest_wait_expiry"} <= names
+            "anna_tq_tensor_quantize", "anna_tq_tensor_dequantize", "anna_tq_gather_dense", "anna_kv_selftest_wait_expiry", "anna_kv_selftest_umma",
+            "anna_tq_query_scratch_bytes"} <= names
 
 
 def test_library_exports_every_declared_symbol(library):
