@@ -8,6 +8,8 @@
 #include "tq_common.cuh"
 #include "tq_decode_params.cuh"
 
+#include <cstdlib>
+
 namespace anna {
 
 // Bits of COUNT consecutive coordinates starting at `first` in a row packed with WIDTH bits per coordinate.
@@ -340,11 +342,14 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
     p.query_frags = fits ? query_scratch : nullptr;
   }
   if (tq_split_mma_applicable(p, head_dim, dtype)) {
+    const bool umma = tq_split_umma_applicable(p, head_dim, bits, dtype);
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
       p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
-      return launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
+      return umma ? launch_tq_split_umma(p, batch, bits, dtype, (cudaStream_t)stream)
+                  : launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
     }
-    rc = launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
+    rc = umma ? launch_tq_split_umma(p, batch, bits, dtype, (cudaStream_t)stream)
+              : launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
     if (rc != ANNA_OK) return rc;
     return launch_split_combine(ws, nullptr, p.lengths, -1, p.max_len, residual_len, gate, gate_stride_b, gate_stride_h,
                                 out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,

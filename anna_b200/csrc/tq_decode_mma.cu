@@ -799,6 +799,29 @@ static int launch_tq_mma(const TqDecodeParams& p, int batch, cudaStream_t stream
   return rc;
 }
 
+template <typename T, int D>
+static int launch_window(const TqDecodeParams& p, int batch, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int device = 0;
+  ANNA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !configured[device]) {
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(tq_window_split_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         MmaCfg<D>::kSmemBytes));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  const int group_tiles = (p.groups + 7) / 8;
+  dim3 window_grid((unsigned)p.num_window_chunks, (unsigned)(p.kv_heads * group_tiles), (unsigned)batch);
+  tq_window_split_mma_kernel<T, D><<<window_grid, kMmaThreads, MmaCfg<D>::kSmemBytes, stream>>>(p);
+  return check_launch("tq_window_split_mma_kernel");
+}
+
+int launch_tq_window_split(const TqDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream) {
+  if (dtype == ANNA_DTYPE_BF16)
+    return head_dim == 128 ? launch_window<__nv_bfloat16, 128>(p, batch, stream)
+                           : launch_window<__nv_bfloat16, 256>(p, batch, stream);
+  return head_dim == 128 ? launch_window<__half, 128>(p, batch, stream) : launch_window<__half, 256>(p, batch, stream);
+}
+
 int tq_decode_mma_faults(int* count) {
   int32_t value = 0;
   ANNA_CUDA_CHECK(cudaMemcpyFromSymbol(&value, g_tq_mma_faults, sizeof(value)));
@@ -875,5 +898,10 @@ extern "C" int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream) 
 // since the library was loaded (0 in a healthy run).  Synchronises the device.
 extern "C" int anna_kv_device_faults(int* count) {
   ANNA_REQUIRE(count != nullptr, "anna_kv_device_faults: null output pointer");
-  return anna::tq_decode_mma_faults(count);
+  int mma = 0, umma = 0;
+  int rc = anna::tq_decode_mma_faults(&mma);
+  if (rc == ANNA_OK) rc = anna::tq_decode_umma_faults(&umma);
+  if (rc != ANNA_OK) return rc;
+  *count = mma + umma;
+  return ANNA_OK;
 }

@@ -32,9 +32,22 @@ struct TqDecodeParams {
   void* query_frags;  // scratch for the rotated fp16 query fragments (tensor-core path), or nullptr
 };
 
-// Bytes of query scratch the tensor-core path needs: 32 * head_dim per (row, kv head, group of 8 query heads).
+// Tensor-memory split pass (tq_decode_umma.cu): 16-bit cache dtypes, head_dim 128, 3- / 4-bit codes, 16-token pages,
+// value group 32, at most 4 query heads per kv head.
+bool tq_split_umma_applicable(const TqDecodeParams& p, int head_dim, int bits, int dtype);
+int launch_tq_split_umma(const TqDecodeParams& p, int batch, int bits, int dtype, cudaStream_t stream);
+int tq_decode_umma_faults(int* count);
+size_t tq_umma_query_bytes();  // query operand image per (row, kv head) of that path
+// the window-ring launch of the tensor-core paths (tq_decode_mma.cu)
+int launch_tq_window_split(const TqDecodeParams& p, int batch, int head_dim, int dtype, cudaStream_t stream);
+
+// Bytes of query scratch the tensor-core paths need per call: 32 * head_dim fragment bytes per (row, kv head, group of
+// 8 query heads) for the mma.sync path, one query operand image per (row, kv head) for the tensor-memory path.
 inline size_t tq_query_scratch_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
-  return (size_t)batch * kv_heads * ((q_heads / kv_heads + 7) / 8) * 32 * head_dim;
+  const size_t units = (size_t)batch * kv_heads * ((q_heads / kv_heads + 7) / 8);
+  const size_t frag = (size_t)32 * head_dim;
+  const size_t image = tq_umma_query_bytes();
+  return units * (frag > image ? frag : image);
 }
 
 // Tensor-core split pass (tq_decode_mma.cu): 16-bit cache dtypes, head_dim 128 / 256, value group 32, page size % 16 == 0.

@@ -1055,12 +1055,14 @@ def run_profile_case(case: str, device) -> dict:
     else:
         # tq4 / tq3 / tq2: contexts of 8 K tokens; tq4long / tq2long: few rows with the full 32 K context, so that a
         # CTA walks a 4096-token chunk as it does in the headline workload
-        bits = {"tq4": 4, "tq3": 3, "tq2": 2, "tq4long": 4, "tq2long": 2}[case]
-        long_case = case.endswith("long")
+        bits = {"tq4": 4, "tq3": 3, "tq2": 2, "tq4long": 4, "tq2long": 2, "tq4shard": 4}[case]
+        long_case = case.endswith("long") or case.endswith("shard")
         if bits == 2:
             batch, q_heads, kv_heads, dim = (16, 16, 2, 256) if long_case else (32, 16, 2, 256)
         else:
             batch, q_heads, kv_heads, dim = (8, 32, 8, 128) if long_case else (16, 32, 8, 128)
+        if case == "tq4shard":  # the per-GPU share of the headline workload at 8 GPUs (2.6 GB of packed pages)
+            batch = 64
         page, context = 16, (32768 if long_case else 8320)
         cache = build_tq_cache_uniform(device, rows=batch, context=context, q_heads=q_heads, kv_heads=kv_heads,
                                        dim=dim, bits=bits, residual=128, page=page, headroom=64, seed=3)
@@ -1107,7 +1109,7 @@ def main() -> None:
     parser.add_argument("--spin-steps", type=int, default=40,
                         help="at most this many untimed steps while waiting for nvidia-smi samples under load")
     parser.add_argument("--profile-case", default=None,
-                        choices=("paged", "tq4", "tq3", "tq2", "tq4long", "tq2long", "tqappend", "prefill"),
+                        choices=("paged", "tq4", "tq3", "tq2", "tq4long", "tq2long", "tq4shard", "tqappend", "prefill"),
                         help="run one small case a few times and exit (meant to be wrapped by ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -103,3 +103,43 @@ def test_row_handle_matches_batched_cache(cuda_device):
     out2 = clone.decode_attention(query.to(cuda_device), scaling=128 ** -0.5, num_key_value_groups=4)
     assert torch.equal(out, out2)
     assert clone.block_table != row.block_table
+
+
+def test_tensor_memory_decode_kernel_matches_oracle(cuda_device, tmp_path):
+    """The opt-in tcgen05 kernel (ANNA_B200_TQ_UMMA=1, read once per process; head_dim 128, 3- / 4-bit, 4 query heads
+    per kv head) against the oracle, in a child process: several 128-token steps, a ragged last step, a hole-free
+    table, a gate, and a window-only row beside them; no bounded wait may have expired."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    script = r"""
+import sys
+import numpy as np, torch
+from anna_b200 import _lib
+from tests.helpers import TQ_ATOL, TqPair, outlier_kv, to_np
+dev = torch.device("cuda:0")
+for bits in (3, 4):
+    pair = TqPair(device=dev, batch=3, kv_heads=2, head_dim=128, bits=bits, residual_len=16, block_size=16,
+                  dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(50 + bits)
+    for tokens in (700, 1, 37):
+        shape = (3, 2, tokens, 128)
+        pair.append(outlier_kv(gen, shape, torch.bfloat16), outlier_kv(gen, shape, torch.bfloat16))
+    pair.assert_bit_exact()
+    query = torch.randn(3, 8, 1, 128, generator=gen).to(torch.bfloat16)
+    gate = torch.randn(3, 8, 1, 128, generator=gen).to(torch.bfloat16)
+    out = pair.cache.turboquant_single_token_decode_attention(0, query.to(dev), scaling=128 ** -0.5,
+                                                              num_key_value_groups=4, gate=gate.to(dev))
+    want = np.stack([row.decode_attention(to_np(query[b, :, 0]), scaling=128 ** -0.5, gate=to_np(gate[b, :, 0]))
+                     for b, row in enumerate(pair.rows)])[:, :, None, :]
+    np.testing.assert_allclose(to_np(out), want, atol=TQ_ATOL[torch.bfloat16], rtol=TQ_ATOL[torch.bfloat16])
+assert _lib.device_faults() == 0
+print("ok")
+"""
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, ANNA_B200_TQ_UMMA="1", PYTHONPATH=str(root))
+    done = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=600,
+                          cwd=str(root))
+    assert done.returncode == 0 and "ok" in done.stdout, done.stderr[-3000:]

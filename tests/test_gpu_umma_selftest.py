@@ -20,6 +20,10 @@ def test_umma_products_match_fp32_reference(cuda_device):
     a1 = (torch.randn(128, 128, device=cuda_device, generator=gen) * 2).to(torch.float8_e4m3fn)
     b1 = (torch.randn(16, 128, device=cuda_device, generator=gen) * 2).to(torch.float8_e4m3fn)
     a2 = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.float16)   # [K][rows]
+    # the decode kernel feeds value codes as f16 subnormals (code * 2^-24, code * 2^-20): they must not be flushed
+    codes = torch.randint(0, 16, (128, 64), device=cuda_device, generator=gen).to(torch.float32)
+    a2[:, 0::4] = (codes[:, :32] * 2.0 ** -24).to(torch.float16)
+    a2[:, 1::4] = (codes[:, 32:] * 2.0 ** -20).to(torch.float16)
     b2 = torch.randn(128, 16, device=cuda_device, generator=gen).to(torch.float16)    # [K][columns]
     d1 = torch.zeros(128, 16, device=cuda_device, dtype=torch.float32)
     d2 = torch.zeros(128, 16, device=cuda_device, dtype=torch.float32)
@@ -35,3 +39,7 @@ def test_umma_products_match_fp32_reference(cuda_device):
     want2 = a2.float().t() @ b2.float()
     torch.testing.assert_close(d1, want1, atol=1e-3, rtol=1e-4)
     torch.testing.assert_close(d2, want2, atol=1e-3, rtol=1e-4)
+    # rows fed with subnormals only come out exactly (products of f16 values are exact, sums are small integers * 2^-k)
+    sub_rows = a2.float().t()[0::4] @ b2.float()
+    torch.testing.assert_close(d2[0::4], sub_rows, atol=0.0, rtol=2e-3)
+    assert float(d2[0::4].abs().max()) > 0.0
