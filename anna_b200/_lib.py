@@ -44,6 +44,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "anna_decode_plan": (c_i32, [c_i32, c_i32, c_i64, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
     "anna_paged_kv_write": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i32,
                                     c_i32, c_i32, c_i32, c_i32, c_i64, c_i64, c_i32, c_ptr, c_ptr]),
+    "anna_block_table_patch": (c_i32, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i32, c_ptr]),
+    "anna_paged_kv_gather": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_i32, c_i32,
+                                     c_i32, c_i32, c_i64, c_i64, c_i64, c_i32, c_ptr]),
     "anna_paged_gqa_decode": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_i64,
                                       c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32, c_ptr, c_i32, c_i32, c_i32, c_i32,
                                       c_i32, c_i64, c_i64, c_f32, c_i32, c_ptr]),

@@ -195,7 +195,7 @@ class Qwen3DynamicCache:
         self.turboquant_rows: list[list[TurboQuantKVRow | None]] = [[None] * batch_size for _ in range(layers)]
         self.page_table_caches: list[torch.Tensor | None] = [None] * layers
         self.page_table_capacities: list[int] = [0] * layers
-        self._table_host: list[torch.Tensor | None] = [None] * layers     # host mirror of page_table_caches
+        self._table_host: list[np.ndarray | None] = [None] * layers       # host mirror of page_table_caches
         self._table_rows_synced: list[list[int] | None] = [None] * layers  # blocks already on the device per row
         self._table_blocks_total: list[int] = [-1] * layers                # sum of table lengths at the last sync
         self._dev_lengths: list[_DeviceLengths | None] = [None] * layers  # device mirror of layer_lengths
@@ -315,44 +315,45 @@ class Qwen3DynamicCache:
         if (buffer is None or buffer.shape[0] != batch_size or buffer.device != device
                 or buffer.shape[1] < required or synced is None):
             capacity = max(required, max(1, self.page_table_capacities[layer_idx] * 2))
-            # host mirror of the device table; pinned, so that patches go up as asynchronous copies
-            mirror = torch.full((batch_size, capacity), -1, dtype=torch.int32)
-            if device.type == "cuda":
-                mirror = mirror.pin_memory()
-            host = mirror.numpy()
+            # host mirror of the device table; a full build goes up through the pinned staging ring in one copy
+            host = np.full((batch_size, capacity), -1, dtype=np.int32)
             for row_idx, table in enumerate(tables):
                 if table:
                     host[row_idx, : len(table)] = table
-            buffer = torch.empty((batch_size, capacity), dtype=torch.int32, device=device)
-            buffer.copy_(mirror, non_blocking=True)
+            if device.type == "cuda":
+                buffer = MetadataUploader.for_device(device).upload_i32(host.reshape(-1)).view(batch_size, capacity)
+            else:  # host-side bookkeeping of a cache that holds no device memory
+                buffer = torch.from_numpy(host.copy())
             self.page_table_caches[layer_idx] = buffer
             self.page_table_capacities[layer_idx] = capacity
-            self._table_host[layer_idx] = mirror
+            self._table_host[layer_idx] = host
             self._table_rows_synced[layer_idx] = [len(t) for t in tables]
             self._table_blocks_total[layer_idx] = total
             return buffer[:, :required]
-        # Patch: new entries go into the mirror row by row, then one strided copy moves the column range that changed.
-        # Entries are write-once while a row lives, so a copy that runs late can only carry values that a later patch
-        # would upload anyway.
-        mirror = self._table_host[layer_idx]
-        host = mirror.numpy()
-        lo, hi = None, 0
+        # Patch: the new entries go up as (row, column, page id) triples through a pinned staging buffer and a small
+        # scatter kernel writes them into the device table, so a step in which a few rows of a ragged batch take a page
+        # moves a few dozen bytes and never waits for the GPU.  Entries are write-once while a row lives.
+        host = self._table_host[layer_idx]
+        triples: list[int] = []
         for row_idx, table in enumerate(tables):
             have = synced[row_idx]
             n = len(table)
             if n > have:
                 host[row_idx, have:n] = table[have:]
                 synced[row_idx] = n
-                lo = have if lo is None or have < lo else lo
-                hi = n if n > hi else hi
-        if lo is not None:
-            buffer[:, lo:hi].copy_(mirror[:, lo:hi], non_blocking=True)
+                for col in range(have, n):
+                    triples.extend((row_idx, col, table[col]))
+        if triples and device.type != "cuda":  # host-side bookkeeping of a cache that holds no device memory
+            patch = np.asarray(triples, dtype=np.int64).reshape(-1, 3)
+            buffer[patch[:, 0], patch[:, 1]] = torch.from_numpy(patch[:, 2]).to(torch.int32)
+        elif triples:
+            entries = MetadataUploader.for_device(device).upload_i32(np.asarray(triples, dtype=np.int32))
+            with on_device(device):
+                _lib.check(_lib.lib().anna_block_table_patch(
+                    ptr(buffer), buffer.stride(0), int(buffer.shape[0]), int(buffer.shape[1]), ptr(entries),
+                    len(triples) // 3, stream_ptr(device)), "anna_block_table_patch")
         self._table_blocks_total[layer_idx] = total
         return buffer[:, :required]
-
-    def _lengths_on_device(self, layer_idx: int, lengths: list[int], device: torch.device,
-                           dtype: torch.dtype) -> torch.Tensor:
-        return torch.tensor(lengths, dtype=dtype, device=device)
 
     # -- append ------------------------------------------------------------------------------------------------------
 
@@ -389,6 +390,8 @@ class Qwen3DynamicCache:
             for batch_idx in range(batch_size):
                 required = past[batch_idx] + append_length
                 table = self.page_tables[layer_idx][batch_idx]
+                if append_length > 0:
+                    self._privatize_last_block(layer_idx, batch_idx, key_states, value_states)
                 if use_prefix_share:
                     segments = self._map_prefix_shared_blocks(key_states, value_states, layer_idx, batch_idx,
                                                               append_length)
@@ -433,6 +436,37 @@ class Qwen3DynamicCache:
             return None, None, past_lengths
         gathered_key, gathered_value, _ = self._gather_layer_cache(layer_idx)
         return gathered_key, gathered_value, past_lengths
+
+    def _resync_row_from(self, layer_idx: int, batch_idx: int, block: int) -> None:
+        """Entries of row `batch_idx` from column `block` on go to the device again at the next table sync."""
+        synced = self._table_rows_synced[layer_idx]
+        if synced is not None and batch_idx < len(synced) and synced[batch_idx] > block:
+            synced[batch_idx] = block
+            self._table_blocks_total[layer_idx] = -1
+        self._table_view[layer_idx] = None
+
+    def _privatize_last_block(self, layer_idx: int, batch_idx: int, key_states: torch.Tensor,
+                              value_states: torch.Tensor) -> None:
+        """Copy on first write for un-quantized pages: a cache made by ``clone`` maps the pages of its source.  Full
+        blocks are never written again; the partly filled last block is, so the first append of either cache copies
+        that one page and maps the copy."""
+        length = self.layer_lengths[layer_idx][batch_idx]
+        if length % self.block_size == 0:
+            return
+        table = self.page_tables[layer_idx][batch_idx]
+        blk = length // self.block_size
+        layer = self.allocator.layers[layer_idx]
+        if blk >= len(table) or layer.page_owners(table[blk]) <= 1:
+            return
+        shared = table[blk]
+        private = self.allocator.allocate(layer_idx, 1, key_template=key_states, value_template=value_states)[0]
+        layer = self.allocator.layers[layer_idx]
+        assert layer.key_pages is not None and layer.value_pages is not None
+        layer.key_pages[private].copy_(layer.key_pages[shared])
+        layer.value_pages[private].copy_(layer.value_pages[shared])
+        table[blk] = private
+        self.allocator.release_pages(layer_idx, [shared])
+        self._resync_row_from(layer_idx, batch_idx, blk)
 
     def _device_lengths_of(self, layer_idx: int, batch_size: int, device: torch.device) -> _DeviceLengths:
         state = self._dev_lengths[layer_idx]
@@ -524,6 +558,7 @@ class Qwen3DynamicCache:
                                       new_length: int) -> list[int]:
         """Single-row prompt path: like ``row._reserve_blocks`` but a block whose whole prompt prefix was packed by an
         earlier sequence is mapped by reference.  Returns the indices of the blocks mapped that way in this call."""
+        row._privatize_partial_block(new_length)
         quantized = max(0, int(new_length) - row.residual_len)
         need = (quantized + pool.block_size - 1) // pool.block_size
         keys = self._prefix_keys()
@@ -576,6 +611,9 @@ class Qwen3DynamicCache:
                 shared_blocks = self._reserve_shared_packed_blocks(row, pool, layer_idx, row.length + append_length)
             else:
                 row._reserve_blocks(row.length + append_length)
+            if row._privatized_block is not None:  # copy on write replaced a page id: upload that entry again
+                self._resync_row_from(layer_idx, batch_idx, row._privatized_block)
+                row._privatized_block = None
         slots = [row.slot for row in rows]
         lengths = self.layer_lengths[layer_idx]
         for batch_idx, row in enumerate(rows):
@@ -700,18 +738,16 @@ class Qwen3DynamicCache:
         visible = torch.tensor(lengths, dtype=torch.long, device=device)
         if table is None:
             return None, None, visible
-        blocks = (max_length + self.block_size - 1) // self.block_size
-        index = table[:, :blocks].clamp(min=0).long()
-
-        def gather(pages: torch.Tensor) -> torch.Tensor:
-            picked = pages[index]  # [B, blocks, Hkv, S, D]
-            dense = picked.permute(0, 2, 1, 3, 4).reshape(batch_size, pages.shape[1], blocks * self.block_size,
-                                                          pages.shape[3])[:, :, :max_length, :]
-            # slots past a row's length hold whatever the page held before: select, do not multiply (NaN * 0 is NaN)
-            hidden = torch.arange(max_length, device=device)[None, :] >= visible[:, None]
-            return dense.masked_fill(hidden[:, None, :, None], 0)
-
-        return gather(layer.key_pages), gather(layer.value_pages), visible
+        keys = torch.empty((batch_size, int(layer.key_pages.shape[1]), max_length, int(layer.key_pages.shape[3])),
+                           dtype=layer.key_pages.dtype, device=device)
+        values = torch.empty_like(keys)
+        with on_device(device):
+            _lib.check(_lib.lib().anna_paged_kv_gather(
+                ptr(layer.key_pages), ptr(layer.value_pages), ptr(table), table.stride(0), ptr(visible), ptr(keys),
+                ptr(values), keys.stride(0), keys.stride(1), keys.stride(2), batch_size, int(keys.shape[1]),
+                int(keys.shape[3]), self.block_size, layer.capacity(), int(table.shape[1]), max_length,
+                dtype_code(keys.dtype), stream_ptr(device)), "anna_paged_kv_gather")
+        return keys, values, visible
 
     def visible_key_cache(self, layer_idx: int):
         return self._gather_layer_cache(layer_idx)[0]
@@ -858,7 +894,9 @@ class Qwen3DynamicCache:
         self._released = True
 
     def clone(self) -> "Qwen3DynamicCache":
-        """Deep copy: un-quantized pages and packed pages / window rings are duplicated (ops.py:1323-1381)."""
+        """An independent copy of the cache state (ops.py:1323-1381) that copies no page: un-quantized and packed pages
+        get one more owner each and are mapped by both caches; only window rings are duplicated.  The first append of
+        either cache into a partly filled last block copies that one page (copy on first write)."""
         batch_size = self.get_batch_size()
         cloned = self._new_like(batch_size)
         for layer_idx in range(self.config.num_hidden_layers):
@@ -877,20 +915,12 @@ class Qwen3DynamicCache:
                     cloned.turboquant_rows[layer_idx][batch_idx] = row.clone()
             if self.uses_turboquant_for_layer(layer_idx):
                 continue
-            layer = self.allocator.layers[layer_idx]
-            if layer.key_pages is None or layer.value_pages is None:
-                continue
             for batch_idx, page_ids in enumerate(self.page_tables[layer_idx]):
-                if not page_ids:
-                    continue
-                new_ids = self.allocator.allocate(layer_idx, len(page_ids), key_template=layer.key_pages[:1],
-                                                  value_template=layer.value_pages[:1])
-                layer = self.allocator.layers[layer_idx]
-                src = torch.tensor(page_ids, dtype=torch.long, device=layer.key_pages.device)
-                dst = torch.tensor(new_ids, dtype=torch.long, device=layer.key_pages.device)
-                layer.key_pages.index_copy_(0, dst, layer.key_pages.index_select(0, src))
-                layer.value_pages.index_copy_(0, dst, layer.value_pages.index_select(0, src))
-                cloned.page_tables[layer_idx][batch_idx] = list(new_ids)
+                for page_id in page_ids:
+                    self.allocator.retain_shared_page(layer_idx, page_id)
+                cloned.page_tables[layer_idx][batch_idx] = list(page_ids)
+            # both caches now have to look at their last blocks before the next append
+            self._page_headroom[layer_idx] = None
         if self._prompt_token_ids is not None:
             cloned._prompt_token_ids = list(self._prompt_token_ids)
         return cloned

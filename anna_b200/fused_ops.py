@@ -137,6 +137,24 @@ class MetadataUploader:
         event.record()
         return out
 
+    def upload_i32(self, values) -> torch.Tensor:
+        """int32 copy of a flat numpy int32 array on the device, through the same pinned ring."""
+        count = int(values.size)
+        self._ensure((count + 1) // 2)
+        slot = self.next
+        self.next = (slot + 1) % self.slots
+        event = self.events[slot]
+        if event is not None:
+            event.synchronize()
+        staging = self.buffers[slot].view(torch.int32)
+        staging.numpy()[:count] = values
+        out = torch.empty(count, dtype=torch.int32, device=self.device)
+        out.copy_(staging[:count], non_blocking=True)
+        if event is None:
+            event = self.events[slot] = torch.cuda.Event()
+        event.record()
+        return out
+
 
 def _require_cuda(name: str, **tensors: torch.Tensor | None) -> torch.device:
     device = None

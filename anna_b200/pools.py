@@ -135,6 +135,10 @@ class Qwen3PagedLayerAllocator:
             raise ValueError(f"retain_page: invalid page_id={page_id} capacity={cap}.")
         self._book.retain(page_id)
 
+    def page_owners(self, page_id: int) -> int:
+        """How many block tables map this page (0 for a free page)."""
+        return self._book.refcount.get(page_id, 0)
+
     def release_page(self, page_id: int) -> None:
         self._book.release(page_id)
 
@@ -236,8 +240,12 @@ class TurboQuantLayerPool:
         for page_id in reversed(page_ids):
             self._book.release(page_id)
 
+    def page_owners(self, page_id: int) -> int:
+        """How many rows map this packed page (0 for a free page)."""
+        return self._book.refcount.get(page_id, 0)
+
     def retain_page(self, page_id: int) -> None:
-        """One more owner of a packed page (a sequence that maps it for a shared prompt prefix)."""
+        """One more owner of a packed page (a sequence that maps it for a shared prompt prefix, or a clone)."""
         if page_id < 0 or page_id >= self.capacity() or self._book.refcount.get(page_id, 0) <= 0:
             raise ValueError(f"retain_page: page {page_id} is not a live packed page (capacity {self.capacity()}).")
         self._book.retain(page_id)

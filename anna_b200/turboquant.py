@@ -315,6 +315,7 @@ class TurboQuantKVRow:
         self.slot = -1
         self.block_table: list[int] = []
         self._length = 0
+        self._privatized_block: int | None = None  # block whose page id changed by copy on write (see _reserve_blocks)
 
     # -- state ----------------------------------------------------------------------------------------------------------
 
@@ -344,9 +345,31 @@ class TurboQuantKVRow:
         self.value_group_size = pool.value_group
         self.slot = pool.allocate_slot()
 
+    def _privatize_partial_block(self, new_length: int) -> None:
+        """Copy on first write: a clone shares its packed pages with the row it was cloned from.  Full blocks are never
+        written again, but the last, partly filled block is: before an append that reaches it, a row that is not the
+        only owner of that page copies it, maps the copy and leaves the block index in ``_privatized_block`` so that
+        the owner of the device block table uploads the new id."""
+        assert self.pool is not None
+        pool = self.pool
+        quantized_now = self.quantized_length
+        if max(0, int(new_length) - self.residual_len) <= quantized_now or quantized_now % pool.block_size == 0:
+            return
+        blk = quantized_now // pool.block_size
+        if blk >= len(self.block_table) or pool.page_owners(self.block_table[blk]) <= 1:
+            return
+        shared = self.block_table[blk]
+        private = pool.allocate(1)[0]
+        assert pool.packed_pages is not None
+        pool.packed_pages[private].copy_(pool.packed_pages[shared])
+        self.block_table[blk] = private
+        pool.release_pages([shared])
+        self._privatized_block = blk
+
     def _reserve_blocks(self, new_length: int) -> None:
         """Take pages for every block the quantized prefix will reach once the row holds new_length tokens."""
         assert self.pool is not None
+        self._privatize_partial_block(new_length)
         quantized = max(0, int(new_length) - self.residual_len)
         need = (quantized + self.pool.block_size - 1) // self.pool.block_size
         if need > len(self.block_table):
@@ -430,7 +453,9 @@ class TurboQuantKVRow:
         return keys, values
 
     def clone(self) -> "TurboQuantKVRow":
-        """Deep copy inside the same pool: fresh pages and a fresh ring slot (turboquant.py:1348-1377)."""
+        """An independent copy of the row's state (turboquant.py:1348-1377) that copies no packed page: the clone maps
+        the same pages (one more owner each) and gets a window ring of its own; whichever of the two rows appends into
+        the partly filled last block first copies that one page (``_reserve_blocks``)."""
         cloned = TurboQuantKVRow(bits=self.bits, residual_len=self.residual_len,
                                  value_group_size=self.value_group_size)
         if not self.initialized:
@@ -438,11 +463,9 @@ class TurboQuantKVRow:
         assert self.pool is not None and self.device is not None and self.dtype is not None
         cloned._bind(self.pool, kv_heads=self.num_heads, head_dim=self.head_dim, dtype=self.dtype, device=self.device)
         cloned._length = self._length
-        if self.block_table:
-            cloned.block_table = self.pool.allocate(len(self.block_table))
-            src = torch.tensor(self.block_table, dtype=torch.long, device=self.device)
-            dst = torch.tensor(cloned.block_table, dtype=torch.long, device=self.device)
-            self.pool.packed_pages.index_copy_(0, dst, self.pool.packed_pages.index_select(0, src))
+        for page_id in self.block_table:
+            self.pool.retain_page(page_id)
+        cloned.block_table = list(self.block_table)
         self.pool.window[cloned.slot].copy_(self.pool.window[self.slot])
         return cloned
 

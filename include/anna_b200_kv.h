@@ -106,6 +106,26 @@ int anna_paged_kv_write(const void* k_new, const void* v_new, int64_t kn_stride_
                         int64_t max_blocks, int dtype, int32_t* status, anna_stream_t stream);
 
 /*
+ * Patch a device block table in place: entry i of `entries` is the int32 triple (row, column, page id); triples outside
+ * [0, rows) x [0, cols) are ignored.  Replaces the per-row rebuild-and-upload of the table in
+ * Qwen3DynamicCache._sync_page_table_layer_buffer (src/anna/model/ops.py:532-588) for the rows that took pages.
+ */
+int anna_block_table_patch(int32_t* table, int64_t table_stride, int64_t rows, int64_t cols, const int32_t* entries,
+                           int count, anna_stream_t stream);
+
+/*
+ * Dense view of un-quantized paged K/V: key_out / value_out [B, Hkv, max_len, D] (element strides out_stride_b / _h /
+ * _t, last dim contiguous) from the pages named by the block table; positions at or past a row's length and tokens
+ * of unmapped blocks come out as zeros.  Stands in for Qwen3DynamicCache._gather_layer_cache
+ * (src/anna/model/ops.py:931-1006).
+ */
+int anna_paged_kv_gather(const void* key_pages, const void* value_pages, const int32_t* page_table,
+                         int64_t table_stride, const int64_t* lengths, void* key_out, void* value_out,
+                         int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int kv_heads,
+                         int head_dim, int block_size, int64_t num_pages, int64_t max_blocks, int64_t max_len, int dtype,
+                         anna_stream_t stream);
+
+/*
  * Single-token GQA decode over paged K/V.  Stands in for torch.ops.anna.paged_gqa_decode_fused
  * (gated_delta_fused_op.sycl:5206-5360, schema :7670-7679): same masking (entries < 0 or >= P are skipped,
  * visible length clamped to [0, max_blocks * S]), fp32 online softmax, optional sigmoid(gate) epilogue, rows with

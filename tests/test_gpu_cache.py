@@ -110,7 +110,8 @@ def test_turboquant_dense_view_and_lifecycle(cuda_device):
     pair.assert_bit_exact()
     pool = pair.pool
     clone = pair.cache.clone()
-    assert pool.used_pages() == 8 and clone.turboquant_rows[0][0].block_table != pair.cache.turboquant_rows[0][0].block_table
+    # the clone maps the same packed pages (copy on write): no page is taken until one of the two appends
+    assert pool.used_pages() == 4 and clone.turboquant_rows[0][0].block_table == pair.cache.turboquant_rows[0][0].block_table
     ck, cv, _ = clone._gather_layer_cache(0)
     assert torch.equal(ck, dense_k) and torch.equal(cv, dense_v)
     clone.release()
@@ -257,3 +258,75 @@ def test_turboquant_churn_matches_oracle(cuda_device):
     for cache, _ in live:
         cache.release()
     assert pool.used_pages() == 0
+
+
+def test_clone_is_copy_on_write_for_packed_and_unquantized_pages(cuda_device):
+    """clone() maps pages by reference; after the clone and its source append different tokens, each decodes like an
+    oracle row that saw its own history, and the pages they still share were not disturbed (ops.py:1323-1381 copies
+    every page instead)."""
+    import copy
+
+    gen = torch.Generator().manual_seed(12)
+    # -- TurboQuant rows: 70 tokens, window 6 -> 64 quantized = 4 full blocks; +5 tokens -> a partly filled block ------
+    pair = TqPair(device=cuda_device, batch=2, kv_heads=2, head_dim=128, bits=4, residual_len=6, block_size=16,
+                  dtype=torch.bfloat16)
+    for tokens in (70, 5):
+        pair.append(outlier_kv(gen, (2, 2, tokens, 128), torch.bfloat16),
+                    outlier_kv(gen, (2, 2, tokens, 128), torch.bfloat16))
+    pool = pair.pool
+    used = pool.used_pages()
+    clone = pair.cache.clone()
+    clone_rows = [copy.deepcopy(row) for row in pair.rows]
+    assert pool.used_pages() == used
+    k_a, v_a = outlier_kv(gen, (2, 2, 3, 128), torch.bfloat16), outlier_kv(gen, (2, 2, 3, 128), torch.bfloat16)
+    k_b, v_b = outlier_kv(gen, (2, 2, 20, 128), torch.bfloat16), outlier_kv(gen, (2, 2, 20, 128), torch.bfloat16)
+    clone.update(k_b.to(cuda_device), v_b.to(cuda_device), 0, require_dense_cache=False)
+    for b, row in enumerate(clone_rows):
+        row.append(to_np(k_b[b]), to_np(v_b[b]))
+    pair.append(k_a, v_a)               # the source goes on with other tokens
+    pair.assert_bit_exact()             # ... and its codes are still exactly its own
+    query = torch.randn(2, 8, 1, 128, generator=gen).to(torch.bfloat16)
+    for cache, rows in ((pair.cache, pair.rows), (clone, clone_rows)):
+        out = cache.turboquant_single_token_decode_attention(0, query.to(cuda_device), scaling=128 ** -0.5,
+                                                             num_key_value_groups=4)
+        want = np.stack([row.decode_attention(to_np(query[b, :, 0]), scaling=128 ** -0.5)
+                         for b, row in enumerate(rows)])[:, :, None, :]
+        np.testing.assert_allclose(to_np(out), want, atol=4e-2, rtol=4e-2)
+    shared = set(pair.cache.turboquant_rows[0][0].block_table) & set(clone.turboquant_rows[0][0].block_table)
+    assert len(shared) == 4             # the four full blocks are still one copy
+    clone.release()
+    pair.cache.release()
+    assert pool.used_pages() == 0
+
+    # -- un-quantized pages ---------------------------------------------------------------------------------------------
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=16)
+    source = Qwen3DynamicCache(config, batch_size=2)
+    k0 = torch.randn(2, 2, 37, 128, generator=gen).to(torch.bfloat16)
+    v0 = torch.randn(2, 2, 37, 128, generator=gen).to(torch.bfloat16)
+    source.update(k0.to(cuda_device), v0.to(cuda_device), 0, require_dense_cache=False)
+    layer = source.allocator.layers[0]
+    used = layer.used_pages()
+    other = source.clone()
+    assert layer.used_pages() == used
+    k1 = torch.randn(2, 2, 4, 128, generator=gen).to(torch.bfloat16)
+    v1 = torch.randn(2, 2, 4, 128, generator=gen).to(torch.bfloat16)
+    k2 = torch.randn(2, 2, 30, 128, generator=gen).to(torch.bfloat16)
+    v2 = torch.randn(2, 2, 30, 128, generator=gen).to(torch.bfloat16)
+    source.update(k1.to(cuda_device), v1.to(cuda_device), 0, require_dense_cache=False)
+    other.update(k2.to(cuda_device), v2.to(cuda_device), 0, require_dense_cache=False)
+    histories = {id(source): (torch.cat([k0, k1], 2), torch.cat([v0, v1], 2)),
+                 id(other): (torch.cat([k0, k2], 2), torch.cat([v0, v2], 2))}
+    for cache in (source, other):
+        keys, values = histories[id(cache)]
+        key_pages, value_pages, table, visible = cache.paged_attention_state(0)
+        out = fused_ops.run_paged_gqa_decode_fused(query=query.to(cuda_device), key_pages=key_pages,
+                                                   value_pages=value_pages, page_table=table, visible_lengths=visible,
+                                                   scaling=128 ** -0.5)
+        for b in range(2):
+            want = oracle.gqa_decode(to_np(query[b, :, 0]), to_np(keys[b]), to_np(values[b]), 128 ** -0.5)
+            np.testing.assert_allclose(to_np(out[b, :, 0]), want, atol=2e-2, rtol=2e-2)
+        dense_k, dense_v, _ = cache._gather_layer_cache(0)     # the gather kernel sees the same history
+        assert torch.equal(dense_k.cpu(), keys) and torch.equal(dense_v.cpu(), values)
+    other.release()
+    source.release()
+    assert layer.used_pages() == 0

@@ -327,3 +327,58 @@ def test_packed_prefix_blocks_are_shared_between_sequences(launches):
         assert not allocator.packed_prefix_block_pool._page_of
     finally:
         cache_module.launch_tq_append = original
+
+
+def test_clone_maps_pages_by_reference_and_copies_the_last_block_on_first_write(launches):
+    """clone() (ops.py:1323-1381) takes no page: both caches map the same pages with two owners each.  The first
+    append into the partly filled last block copies that one page; full blocks stay shared until release."""
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=4)
+    source = Qwen3DynamicCache(config, batch_size=1)
+    k = torch.arange(1 * 2 * 10 * 8, dtype=torch.float32).reshape(1, 2, 10, 8)
+    source.update(k, k + 0.5, 0, require_dense_cache=False)
+    layer = source.allocator.layers[0]
+    pages_before = list(source.page_tables[0][0])
+    assert len(pages_before) == 3 and layer.used_pages() == 3
+    # the launches are recorders here, so put recognisable bytes into the last page by hand
+    layer.key_pages[pages_before[2]].fill_(7.0)
+    clone = source.clone()
+    assert clone.page_tables[0][0] == pages_before and layer.used_pages() == 3
+    assert [layer.page_owners(pid) for pid in pages_before] == [2, 2, 2]
+    one = torch.zeros(1, 2, 1, 8)
+    clone.update(one, one, 0, require_dense_cache=False)            # token 10 lands in the partly filled block 2
+    assert clone.page_tables[0][0][:2] == pages_before[:2] and clone.page_tables[0][0][2] != pages_before[2]
+    assert source.page_tables[0][0] == pages_before
+    assert [layer.page_owners(pid) for pid in pages_before] == [2, 2, 1] and layer.used_pages() == 4
+    assert torch.equal(layer.key_pages[clone.page_tables[0][0][2]], layer.key_pages[pages_before[2]])
+    # the device table of the clone carries the new page id
+    assert launches["page_write"][-1]["table"][0].tolist()[:3] == clone.page_tables[0][0]
+    source.update(one, one, 0, require_dense_cache=False)           # the source is the only owner of its last page now
+    assert source.page_tables[0][0] == pages_before and layer.used_pages() == 4
+    clone.release()
+    assert [layer.page_owners(pid) for pid in pages_before] == [1, 1, 1] and layer.used_pages() == 3
+    source.release()
+    assert layer.used_pages() == 0
+
+
+def test_turboquant_clone_shares_packed_pages_until_the_partial_block_is_written(launches):
+    config = KVCacheConfig(num_hidden_layers=1, cache_block_size=4)
+    source = Qwen3DynamicCache(config, batch_size=2, kv_cache_quantization="turboquant", kv_cache_quant_bits=4,
+                               kv_cache_residual_len=3)
+    k = torch.zeros(2, 2, 9, 64, dtype=torch.bfloat16)
+    source.update(k, k, 0, require_dense_cache=False)               # 6 quantized tokens: blocks 0 (full) and 1 (half)
+    pool = source.allocator.turboquant_layers[0]
+    tables = [list(row.block_table) for row in source.turboquant_rows[0]]
+    assert all(len(t) == 2 for t in tables) and pool.used_pages() == 4
+    clone = source.clone()
+    assert [list(row.block_table) for row in clone.turboquant_rows[0]] == tables and pool.used_pages() == 4
+    assert {row.slot for row in clone.turboquant_rows[0]}.isdisjoint({row.slot for row in source.turboquant_rows[0]})
+    one = torch.zeros(2, 2, 1, 64, dtype=torch.bfloat16)
+    clone.update(one, one, 0, require_dense_cache=False)            # quantizes token 6 into the shared half block
+    for row, before in zip(clone.turboquant_rows[0], tables):
+        assert row.block_table[0] == before[0] and row.block_table[1] != before[1]
+    assert pool.used_pages() == 6
+    sent = launches["tq_append"][-1]["table"]
+    assert [sent[i].tolist()[:2] for i in range(2)] == [row.block_table for row in clone.turboquant_rows[0]]
+    assert [list(row.block_table) for row in source.turboquant_rows[0]] == tables
+    clone.release()
+    assert pool.used_pages() == 4 and all(pool.page_owners(pid) == 1 for t in tables for pid in t)
