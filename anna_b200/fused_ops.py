@@ -41,6 +41,23 @@ SCHEMAS = {
         "float scaling, Tensor? gate=None) -> Tensor",
 }
 
+# Ops for the steps that are Python loops in the reference and kernels here: the page write of un-quantized layers
+# (Qwen3DynamicCache._write_pages, src/anna/model/ops.py:748-777), the fused TurboQuant append (TurboQuantKVRow.append,
+# src/anna/model/turboquant.py:1027-1140) and the decode over packed pages (turboquant.py:1181-1293).  They sit in the
+# same namespace as the five schemas above, which stay what the reference registers (gated_delta_fused_op.sycl:7621-7679).
+NEW_SCHEMAS = {
+    "paged_kv_write":
+        "(Tensor key_states, Tensor value_states, Tensor(a!) key_pages, Tensor(b!) value_pages, Tensor page_table, "
+        "Tensor past_lengths) -> ()",
+    "tq_append":
+        "(Tensor key_states, Tensor value_states, Tensor(a!) packed_pages, Tensor page_table, Tensor(b!) window, "
+        "Tensor window_slots, Tensor past_lengths, int bits, int residual_len, int block_size, int value_group_size) "
+        "-> ()",
+    "tq_paged_decode":
+        "(Tensor query, Tensor packed_pages, Tensor page_table, Tensor window, Tensor window_slots, Tensor lengths, "
+        "float scaling, int bits, int residual_len, int block_size, int value_group_size, Tensor? gate=None) -> Tensor",
+}
+
 
 def dtype_code(dtype: torch.dtype) -> int:
     try:
@@ -518,7 +535,134 @@ def _op_paged_gqa_decode_fused(query, key_pages, value_pages, page_table, visibl
     return out
 
 
+def _op_paged_kv_write(key_states, value_states, key_pages, value_pages, page_table, past_lengths):
+    """key_states / value_states [B, Hkv, T, D] -> pages [P, Hkv, S, D] at positions past_lengths[b] .. + T."""
+    name = "paged_kv_write"
+    if key_states.dim() != 4 or key_states.shape != value_states.shape:
+        raise RuntimeError(f"{name}: key_states and value_states must be matching [batch, kv_heads, tokens, head_dim]")
+    if key_pages.dim() != 4 or key_pages.shape != value_pages.shape:
+        raise RuntimeError(f"{name}: key_pages and value_pages must be matching [pages, kv_heads, block_size, head_dim]")
+    if key_pages.shape[1] != key_states.shape[1] or key_pages.shape[3] != key_states.shape[3]:
+        raise RuntimeError(f"{name}: pages and states disagree on kv_heads / head_dim")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.shape[0] != key_states.shape[0]:
+        raise RuntimeError(f"{name}: page_table must be int32 [batch, max_blocks]")
+    if past_lengths.dtype != torch.long or past_lengths.shape != (key_states.shape[0],):
+        raise RuntimeError(f"{name}: past_lengths must be int64 [batch]")
+    if not (key_states.dtype == value_states.dtype == key_pages.dtype == value_pages.dtype):
+        raise RuntimeError(f"{name}: states and pages must share the same dtype")
+    device = _require_cuda(name, key_states=key_states, value_states=value_states, key_pages=key_pages,
+                           value_pages=value_pages, page_table=page_table, past_lengths=past_lengths)
+    if not key_pages.is_contiguous() or not value_pages.is_contiguous():
+        raise RuntimeError(f"{name}: page pools must be contiguous")
+    key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
+    if value_states.stride() != key_states.stride():
+        key_states, value_states = key_states.contiguous(), value_states.contiguous()
+    if page_table.stride(1) != 1:
+        page_table = page_table.contiguous()
+    batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
+    if tokens == 0 or batch == 0:
+        return
+    with on_device(device):
+        _lib.check(_lib.lib().anna_paged_kv_write(
+            ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
+            ptr(key_pages), ptr(value_pages), ptr(page_table), page_table.stride(0), ptr(past_lengths.contiguous()),
+            None, batch, kv_heads, tokens, dim, int(key_pages.shape[2]), int(key_pages.shape[0]),
+            int(page_table.shape[1]), dtype_code(key_states.dtype), None, stream_ptr(device)), name)
+
+
+def _check_tq_geometry(name, packed_pages, page_table, window, window_slots, lengths, batch, head_dim, bits,
+                       residual_len, block_size, value_group_size, dtype):
+    if bits not in (2, 3, 4):
+        raise RuntimeError(f"{name}: bits must be 2, 3 or 4")
+    if packed_pages.dtype != torch.uint8 or packed_pages.dim() != 3 or not packed_pages.is_contiguous():
+        raise RuntimeError(f"{name}: packed_pages must be contiguous uint8 [pages, kv_heads, chunk_bytes]")
+    layout = _lib.tq_page_layout(head_dim, bits, block_size, dtype_code(dtype), value_group_size)
+    if int(packed_pages.shape[2]) != layout["chunk_bytes"]:
+        raise RuntimeError(f"{name}: packed page chunks are {int(packed_pages.shape[2])} bytes, the layout for "
+                           f"head_dim={head_dim} bits={bits} block_size={block_size} needs {layout['chunk_bytes']}")
+    if window.dim() != 5 or window.shape[1] != 2 or window.shape[3] != residual_len or window.shape[4] != head_dim:
+        raise RuntimeError(f"{name}: window must be [slots, 2, kv_heads, residual_len, head_dim]")
+    if window.dtype != dtype or not window.is_contiguous():
+        raise RuntimeError(f"{name}: window must be contiguous and share the dtype of the states")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.shape[0] != batch:
+        raise RuntimeError(f"{name}: page_table must be int32 [batch, max_blocks]")
+    for label, tensor in (("window_slots", window_slots), ("lengths", lengths)):
+        if tensor.dtype != torch.long or tensor.shape != (batch,):
+            raise RuntimeError(f"{name}: {label} must be int64 [batch]")
+
+
+def _op_tq_append(key_states, value_states, packed_pages, page_table, window, window_slots, past_lengths, bits,
+                  residual_len, block_size, value_group_size):
+    """Ring update + quantize-on-overflow + bit packing + page scatter for B rows in one launch."""
+    from .tq_tables import key_tables
+
+    name = "tq_append"
+    if key_states.dim() != 4 or key_states.shape != value_states.shape or key_states.dtype != value_states.dtype:
+        raise RuntimeError(f"{name}: key_states and value_states must be matching [batch, kv_heads, tokens, head_dim]")
+    batch, kv_heads, tokens, dim = (int(v) for v in key_states.shape)
+    _check_tq_geometry(name, packed_pages, page_table, window, window_slots, past_lengths, batch, dim, bits,
+                       residual_len, block_size, value_group_size, key_states.dtype)
+    device = _require_cuda(name, key_states=key_states, value_states=value_states, packed_pages=packed_pages,
+                           page_table=page_table, window=window, window_slots=window_slots, past_lengths=past_lengths)
+    if tokens == 0 or batch == 0:
+        return
+    key_states = key_states if key_states.stride(3) == 1 else key_states.contiguous()
+    if value_states.stride() != key_states.stride():
+        key_states, value_states = key_states.contiguous(), value_states.contiguous()
+    if page_table.stride(1) != 1:
+        page_table = page_table.contiguous()
+    tables = key_tables(head_dim=dim, bits=bits, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    with on_device(device):
+        _lib.check(_lib.lib().anna_tq_append(
+            ptr(key_states), ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
+            ptr(packed_pages), ptr(page_table), page_table.stride(0), None, 0, ptr(window),
+            ptr(window_slots.contiguous()), ptr(past_lengths.contiguous()), None, ptr(tables.signs1),
+            ptr(tables.signs2), ptr(tables.centroids), ptr(tables.boundaries), batch, kv_heads, tokens, dim,
+            block_size, residual_len, bits, value_group_size, int(packed_pages.shape[0]), int(page_table.shape[1]),
+            dtype_code(key_states.dtype), ptr(status), stream_ptr(device)), name)
+
+
+def _op_tq_paged_decode(query, packed_pages, page_table, window, window_slots, lengths, scaling, bits, residual_len,
+                        block_size, value_group_size, gate=None):
+    """Single-token GQA decode over [packed prefix | window ring] of B rows."""
+    from .tq_tables import key_tables
+
+    name = "tq_paged_decode"
+    query = _check_query(name, query)
+    batch, heads, _, dim = (int(v) for v in query.shape)
+    _check_tq_geometry(name, packed_pages, page_table, window, window_slots, lengths, batch, dim, bits, residual_len,
+                       block_size, value_group_size, query.dtype)
+    kv_heads = int(packed_pages.shape[1])
+    if heads % kv_heads != 0 or int(window.shape[2]) != kv_heads:
+        raise RuntimeError(f"{name}: query heads must be a multiple of the kv heads of the pages and the window")
+    device = _require_cuda(name, query=query, packed_pages=packed_pages, page_table=page_table, window=window,
+                           window_slots=window_slots, lengths=lengths, gate=gate)
+    gate, gate_sb, gate_sh = _check_gate(name, query, gate)
+    if page_table.stride(1) != 1:
+        page_table = page_table.contiguous()
+    out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    max_blocks = int(page_table.shape[1])
+    tables = key_tables(head_dim=dim, bits=bits, device=device)
+    stats, values, capacity, counters = split_scratch(device, batch, heads, dim, kv_heads,
+                                                      max_blocks * block_size + residual_len,
+                                                      turboquant=(max_blocks, block_size, residual_len))
+    frags = query_scratch(device, batch, heads, kv_heads, dim)
+    with on_device(device):
+        _lib.check(_lib.lib().anna_tq_paged_decode(
+            ptr(query), query.stride(0), query.stride(1), ptr(packed_pages), ptr(page_table), page_table.stride(0),
+            ptr(window), ptr(window_slots.contiguous()), ptr(lengths.contiguous()), ptr(tables.signs1),
+            ptr(tables.signs2), ptr(tables.centroids), ptr(gate), gate_sb, gate_sh, ptr(out), out.stride(0),
+            out.stride(1), ptr(stats), ptr(values), capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads,
+            kv_heads, dim, block_size, residual_len, bits, value_group_size, int(packed_pages.shape[0]), max_blocks,
+            float(scaling), dtype_code(query.dtype), stream_ptr(device)), name)
+    return out
+
+
 _IMPLS = {
+    "paged_kv_write": _op_paged_kv_write,
+    "tq_append": _op_tq_append,
+    "tq_paged_decode": _op_tq_paged_decode,
     "gqa_decode_fused": _op_gqa_decode_fused,
     "gqa_decode_splitkv_fused": _op_gqa_decode_splitkv_fused,
     "gqa_decode_splitkv_fused_out": _op_gqa_decode_splitkv_fused_out,
@@ -531,16 +675,43 @@ def _meta_like_query(query, *args, **kwargs):
     return torch.empty_like(query)
 
 
+def _meta_splitkv_out(query, key, value, output, *args, **kwargs):
+    return output  # the op returns its `output` argument (Tensor(a!))
+
+
+def _meta_turboquant_out(query, quantized_key, value_data, value_scales, value_zeros, residual_key, residual_value,
+                         output, *args, **kwargs):
+    return output
+
+
+def _meta_none(*args, **kwargs):
+    return None
+
+
+_META = {
+    "gqa_decode_fused": _meta_like_query,
+    "gqa_decode_splitkv_fused": _meta_like_query,
+    "gqa_decode_splitkv_fused_out": _meta_splitkv_out,
+    "gqa_decode_splitkv_turboquant_fused_out": _meta_turboquant_out,
+    "paged_gqa_decode_fused": _meta_like_query,
+    "paged_kv_write": _meta_none,
+    "tq_append": _meta_none,
+    "tq_paged_decode": _meta_like_query,
+}
+
+
 def _register_ops() -> None:
+    """CUDA kernels, Meta (shape-only) kernels and an autograd fall-through for every op, like the reference's
+    registration (gated_delta_fused_op.sycl:7916-7983)."""
     global _REGISTERED, _LIBRARY
     if _REGISTERED:
         return
     library = torch.library.Library("anna", "FRAGMENT")
-    for name, schema in SCHEMAS.items():
+    for name, schema in {**SCHEMAS, **NEW_SCHEMAS}.items():
         library.define(name + schema)
         library.impl(name, _IMPLS[name], "CUDA")
-        if not name.endswith("_out"):
-            library.impl(name, _meta_like_query, "Meta")
+        library.impl(name, _META[name], "Meta")
+        library.impl(name, torch.library.fallthrough_kernel, "Autograd")
     _LIBRARY = library
     _REGISTERED = True
 
