@@ -78,6 +78,23 @@ class _PageBook:
         else:
             self.refcount[page_id] = rc - 1
 
+    def release_many(self, page_ids) -> None:
+        """release() for every id of `page_ids`, in the given order, in one pass."""
+        refcount = self.refcount
+        freed: list[int] = []
+        for page_id in page_ids:
+            rc = refcount.get(page_id, 0)
+            if rc == 1:
+                del refcount[page_id]
+                freed.append(page_id)
+            elif rc > 1:
+                refcount[page_id] = rc - 1
+        if freed:
+            self.free_pages.extend(freed)
+            if self._on_page_freed is not None:
+                for page_id in freed:
+                    self._on_page_freed(page_id)
+
     def clear(self) -> None:
         self.free_pages.clear()
         self.refcount.clear()
@@ -143,8 +160,7 @@ class Qwen3PagedLayerAllocator:
         self._book.release(page_id)
 
     def release_pages(self, page_ids: list[int]) -> None:
-        for page_id in reversed(page_ids):
-            self._book.release(page_id)
+        self._book.release_many(reversed(page_ids))
 
     def free(self, page_ids: list[int]) -> None:
         self.release_pages(page_ids)
@@ -237,8 +253,7 @@ class TurboQuantLayerPool:
         return self.capacity()
 
     def release_pages(self, page_ids: list[int]) -> None:
-        for page_id in reversed(page_ids):
-            self._book.release(page_id)
+        self._book.release_many(reversed(page_ids))
 
     def page_owners(self, page_id: int) -> int:
         """How many rows map this packed page (0 for a free page)."""

@@ -31,6 +31,8 @@ class PrefixBlockPool:
             self._keys_of.setdefault((layer_idx, page_id), set()).add(key)
 
     def discard_page(self, layer_idx: int, page_id: int) -> None:
+        if not self._keys_of:  # nothing registered: the common case when no prompt prefix is shared
+            return
         for key in self._keys_of.pop((layer_idx, page_id), ()):
             self._page_of.pop(key, None)
 
