@@ -764,10 +764,7 @@ def run_cfg4_extra(args, device) -> dict:
     decode_gbps = statistics.mean(nbytes / (a.elapsed_time(b) / 1e3) / 1e9 for a, b, nbytes in decode_ev)
     decode_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in decode_ev)
     append_ms = statistics.mean(a.elapsed_time(b) for a, b in append_ev)
-    # per appended token and kv head: K and V read once; the first 128 tokens of a sequence stay in the window
-    # (written as they are), every later token pushes one token out of the window into packed form
-    append_bytes = new_rows * kv_heads * chunk * (2 * dim * 2 + 2 * dim * 2) \
-        + new_rows * kv_heads * chunk * (key_bytes + value_bytes)
+    append_bytes = append_algorithmic_bytes(new_rows * kv_heads, chunk, 128, dim, 2, key_bytes + value_bytes)
     state["decode"].release()
     state["prefill"].release()
     allocator.clear()
@@ -783,6 +780,16 @@ def run_cfg4_extra(args, device) -> dict:
             "quant_append_frac_of_measured_peak": append_bytes / (append_ms / 1e3) / 1e9 / peak,
             "note": "quant_append_ms brackets the update() call of the chunk (host bookkeeping + tq_append_kernel); the "
                     "kernel is bound by instruction issue, not by HBM"}
+
+
+def append_algorithmic_bytes(row_heads: int, new_tokens: int, residual: int, dim: int, elem_bytes: int,
+                              packed_token_bytes_kv: int) -> int:
+    """Bytes one fused quantize-append must move for ``row_heads`` (row, kv head) pairs whose window is already full:
+    the new K and V are read once, every new token pushes one token into packed form (codes, norms, scales written),
+    and the window ring has min(T, R) old tokens read out of it and min(T, R) new tokens written into it."""
+    vec = 2 * dim * elem_bytes
+    ring = 2 * min(new_tokens, residual) * vec
+    return row_heads * (new_tokens * (vec + packed_token_bytes_kv) + ring)
 
 
 def run_bulk_append_extra(device) -> dict:
@@ -824,7 +831,7 @@ def run_bulk_append_extra(device) -> dict:
             torch.cuda.synchronize()
             api_ms.append((time.perf_counter() - t0) * 1e3)
     key_bytes, value_bytes = packed_token_bytes(dim, bits)
-    nbytes = batch * kv_heads * chunk * (2 * dim * 2 + 2 * dim * 2 + key_bytes + value_bytes)
+    nbytes = append_algorithmic_bytes(batch * kv_heads, chunk, residual, dim, 2, key_bytes + value_bytes)
     peak, _ = measured_peak_gbs()
     ms = statistics.median(kernel_ms)
     cache.release()

@@ -102,7 +102,12 @@ def test_row_handle_matches_batched_cache(cuda_device):
     clone = row.clone()
     out2 = clone.decode_attention(query.to(cuda_device), scaling=128 ** -0.5, num_key_value_groups=4)
     assert torch.equal(out, out2)
-    assert clone.block_table != row.block_table
+    # copy-on-write: the clone maps the same packed pages until it writes into the partly filled last one
+    assert clone.block_table == row.block_table
+    keys = outlier_kv(gen, (2, 1, 128), torch.bfloat16)
+    clone.append(keys.to(cuda_device), keys.to(cuda_device))
+    assert clone.block_table[0] == row.block_table[0] and clone.block_table[1] != row.block_table[1]
+    assert torch.equal(row.decode_attention(query.to(cuda_device), scaling=128 ** -0.5, num_key_value_groups=4), out)
 
 
 def test_tensor_memory_decode_kernel_matches_oracle(cuda_device, tmp_path):
