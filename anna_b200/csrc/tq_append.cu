@@ -36,6 +36,33 @@ struct TqAppendParams {
 
 constexpr int kAppendWarps = 8;
 
+// Number of boundaries below `s` (= index of the nearest centroid) by bisection over the sorted boundaries: three
+// compares for 7 boundaries instead of seven.  Same result as counting `s > bnd[k]` over all k, NaN included (0).
+template <int NB>
+__device__ __forceinline__ uint32_t codebook_index(float s, const float (&bnd)[NB]) {
+  if constexpr (NB == 1) {
+    return s > bnd[0] ? 1u : 0u;
+  } else if constexpr (NB == 3) {
+    const bool p0 = s > bnd[1];
+    const bool p1 = s > (p0 ? bnd[2] : bnd[0]);
+    return (p0 ? 2u : 0u) + (p1 ? 1u : 0u);
+  } else {
+    static_assert(NB == 7, "codebooks have 2, 4 or 8 entries");
+    const bool p0 = s > bnd[3];
+    const bool p1 = s > (p0 ? bnd[5] : bnd[1]);
+    const float upper = p1 ? bnd[6] : bnd[4], lower = p1 ? bnd[2] : bnd[0];
+    const bool p2 = s > (p0 ? upper : lower);
+    return (p0 ? 4u : 0u) + (p1 ? 2u : 0u) + (p2 ? 1u : 0u);
+  }
+}
+
+// a / s, correctly rounded, from y = RN(1 / s): one multiply and two fused multiply-adds.  Exact (Markstein) while
+// nothing over- or underflows and the significand of s is not all ones; callers fall back to the division otherwise.
+__device__ __forceinline__ float div_by_shared(float a, float s, float y) {
+  const float q0 = __fmul_rn(a, y);
+  return __fmaf_rn(__fmaf_rn(-q0, s, a), y, q0);
+}
+
 // A CTA belongs to one (row, kv head); its warps stride over that head's 2 * new_tokens items, so everything that does
 // not depend on the item -- sign vectors, boundaries, centroids, lengths, ring and pool bases -- is set up once per
 // warp.  Positions are 32-bit (the host rejects longer contexts) and divisions by the window length and the page size
@@ -66,6 +93,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
   for (int k = 0; k < NB; ++k) bnd[k] = p.boundaries[k];
   constexpr float rsqrt_dim = rsqrt_dim_const<D>();
   const float levels = (float)((1 << BITS) - 1);
+  const float inv_levels = __frcp_rn(levels);
   const int lanes_per_group = p.value_group / E;  // power of two, >= 1
   const int R = p.residual_len;
   const int Tn = p.new_tokens;
@@ -89,21 +117,25 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
   const T* in_v = reinterpret_cast<const T*>(p.v_new) + (int64_t)b * p.stride_b + (int64_t)h * p.stride_h + e0;
   const int32_t* table_row = p.block_table + (int64_t)b * p.table_stride;
 
-  for (int u = (int)blockIdx.x * kAppendWarps + (threadIdx.x >> 5); u < nq + nw; u += p.u_chunks * kAppendWarps) {
-    if (u >= nq) {
-      // window item: plain copy unless the slot's old occupant is quantized (and rewritten) by another warp
-      const int pw = wstart + (u - nq);
-      const int k = div_r(pw - L + R);  // smallest k >= 1 with pw - k*R < L
-      const int p_old = pw - k * R;
-      if (p_old >= Lq) continue;
-      const int rs = pw - div_r(pw) * R;
-      lane_copy<T, E>(in_k + (int64_t)(pw - L) * p.stride_t, ring_k + rs * D);
-      lane_copy<T, E>(in_v + (int64_t)(pw - L) * p.stride_t, ring_v + rs * D);
-      continue;
-    }
+  const int warp = threadIdx.x >> 5;
+  const int u_stride = p.u_chunks * kAppendWarps;
 
-    // ---- quantize item -----------------------------------------------------------------------------------------
-    const int pos = Lq + u;
+  // ---- window items: plain copies, unless the slot's old occupant is quantized (and rewritten) by a quantize item ----
+  for (int u = (int)blockIdx.x * kAppendWarps + warp; u < nw; u += u_stride) {
+    const int pw = wstart + u;
+    const int k = div_r(pw - L + R);  // smallest k >= 1 with pw - k*R < L
+    const int p_old = pw - k * R;
+    if (p_old >= Lq) continue;
+    const int rs = pw - div_r(pw) * R;
+    lane_copy<T, E>(in_k + (int64_t)(pw - L) * p.stride_t, ring_k + rs * D);
+    lane_copy<T, E>(in_v + (int64_t)(pw - L) * p.stride_t, ring_v + rs * D);
+  }
+
+  // ---- quantize items.  The trip count depends on the CTA alone, so every warp stays converged through the warp
+  // exchanges of the body; a warp past the end repeats the last item and stores nothing. ------------------------------
+  for (int base = (int)blockIdx.x * kAppendWarps; base < nq; base += u_stride) {
+    const bool active = base + warp < nq;
+    const int pos = Lq + (active ? base + warp : nq - 1);
     float x[E], v[E];
     if (pos < L) {
       const int rs = pos - div_r(pos) * R;
@@ -111,7 +143,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
       lane_load<T, E>(ring_v + rs * D, v);
       const int k = div_r(wstart - pos + R - 1);
       const int pw = pos + k * R;  // new occupant of this ring slot, if it arrives in this call
-      if (pw < Lp) {
+      if (active && pw < Lp) {
         lane_copy<T, E>(in_k + (int64_t)(pw - L) * p.stride_t, ring_k + rs * D);
         lane_copy<T, E>(in_v + (int64_t)(pw - L) * p.stride_t, ring_v + rs * D);
       }
@@ -124,12 +156,15 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
     const int tok = pos - blk * S;
     int32_t pid = -1;
     if (blk < p.max_blocks) pid = table_row[blk];
+    bool store = active;
     if (pid < 0 || pid >= p.num_pages) {
-      if (lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
-      continue;
+      if (active && lane == 0 && p.status) atomicOr(p.status, (int)ANNA_DEV_BAD_PAGE);
+      store = false;
+      pid = 0;
     }
     // a block mapped from another sequence with the same prompt prefix already holds exactly these codes
-    if (p.shared_blocks != nullptr && ((p.shared_blocks[(int64_t)b * p.mask_stride + (blk >> 5)] >> (blk & 31)) & 1u)) continue;
+    if (p.shared_blocks != nullptr && ((p.shared_blocks[(int64_t)b * p.mask_stride + (blk >> 5)] >> (blk & 31)) & 1u))
+      store = false;
     uint8_t* chunk = p.pages + ((int64_t)pid * p.kv_heads + h) * p.layout.chunk_bytes;
 
     // ---- keys: normalise, rotate, index, residual sign ----------------------------------------------------------
@@ -147,9 +182,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
 #pragma unroll
     for (int j = 0; j < E; ++j) {
       const float scaled = __fmul_rn(w[j], inv);
-      uint32_t c = 0;
-#pragma unroll
-      for (int k = 0; k < NB; ++k) c += scaled > bnd[k] ? 1u : 0u;
+      const uint32_t c = codebook_index<NB>(scaled, bnd);
       code[j] = c;
       e[j] = __fsub_rn(scaled, sm_cent[c]);
     }
@@ -165,12 +198,12 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
       uint64_t field = 0;
 #pragma unroll
       for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 8u : 0u)) << (4 * j);
-      warp_pack_store<4 * E>(field, krow, lane);
+      warp_pack_store<4 * E>(field, krow, lane, store);
     } else if constexpr (BITS == 2) {
       uint64_t field = 0;
 #pragma unroll
       for (int j = 0; j < E; ++j) field |= (uint64_t)(code[j] | (e[j] >= 0.0f ? 2u : 0u)) << (2 * j);
-      warp_pack_store<2 * E>(field, krow, lane);
+      warp_pack_store<2 * E>(field, krow, lane, store);
     } else {
       uint64_t idx_field = 0, sign_field = 0;
 #pragma unroll
@@ -178,10 +211,10 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
         idx_field |= (uint64_t)code[j] << (2 * j);
         sign_field |= (uint64_t)(e[j] >= 0.0f ? 1u : 0u) << j;
       }
-      warp_pack_store<2 * E>(idx_field, krow, lane);
-      warp_pack_store<E>(sign_field, krow + D / 4, lane);
+      warp_pack_store<2 * E>(idx_field, krow, lane, store);
+      warp_pack_store<E>(sign_field, krow + D / 4, lane, store);
     }
-    if (lane == 0) {
+    if (store && lane == 0) {
       reinterpret_cast<float*>(chunk + p.layout.off_knorm)[tok] = norm;
       reinterpret_cast<float*>(chunk + p.layout.off_krnorm)[tok] = rnorm;
     }
@@ -193,23 +226,48 @@ __global__ void __launch_bounds__(kAppendWarps * 32) tq_append_kernel(const TqAp
       lo = fminf(lo, v[j]);
       hi = fmaxf(hi, v[j]);
     }
-    for (int dl = 1; dl < lanes_per_group; dl <<= 1) {
-      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, dl));
-      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, dl));
+#pragma unroll
+    for (int dl = 1; dl < 32; dl <<= 1) {
+      if (dl < lanes_per_group) {  // uniform over the grid
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, dl));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, dl));
+      }
     }
-    const float raw = __fdiv_rn(__fsub_rn(hi, lo), levels);
+    // The divisions below share their divisor inside a group (the scale) or over the whole launch (the level count),
+    // so each is a reciprocal taken once and a three-instruction correction per quotient; operands outside the safe
+    // range (an infinite or NaN range, a scale that rounds to zero in the cache dtype, fp32 caches whose scale can
+    // have any significand) take the plain correctly rounded division.
+    const float range = __fsub_rn(hi, lo);
+    const bool tame = sizeof(T) == 2 && range < 1e30f;
+    const float raw = tame ? div_by_shared(range, levels, inv_levels) : __fdiv_rn(range, levels);
     const float scale = round_to_elem<T>(raw < 1e-8f ? 1e-8f : raw);
     const float zero = round_to_elem<T>(lo);
     uint64_t vfield = 0;
+    if (tame && scale >= 1e-9f) {
+      const float inv_scale = __frcp_rn(scale);
 #pragma unroll
-    for (int j = 0; j < E; ++j) {
-      float q = rintf(__fdiv_rn(__fsub_rn(v[j], zero), scale));
-      if (!(q >= 0.0f)) q = 0.0f;
-      if (q > levels) q = levels;
-      vfield |= (uint64_t)(uint32_t)q << (VS * j);
+      for (int j0 = 0; j0 < E; j0 += 4) {
+        // four codes (at most 16 bits) are packed as an exact fp32 sum before the one conversion to integer
+        float packed = 0.0f;
+#pragma unroll
+        for (int j = j0; j < j0 + 4 && j < E; ++j) {
+          float q = rintf(div_by_shared(__fsub_rn(v[j], zero), scale, inv_scale));
+          q = fminf(fmaxf(q, 0.0f), levels);  // a NaN becomes 0, as in `if (!(q >= 0)) q = 0`
+          packed = __fmaf_rn(q, (float)(1u << (VS * (j - j0))), packed);
+        }
+        vfield |= (uint64_t)(uint32_t)packed << (VS * j0);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        float q = rintf(__fdiv_rn(__fsub_rn(v[j], zero), scale));
+        if (!(q >= 0.0f)) q = 0.0f;
+        if (q > levels) q = levels;
+        vfield |= (uint64_t)(uint32_t)q << (VS * j);
+      }
     }
-    warp_pack_store<VS * E>(vfield, chunk + p.layout.off_vdata + tok * p.layout.value_bytes, lane);
-    if (lane % lanes_per_group == 0) {
+    warp_pack_store<VS * E>(vfield, chunk + p.layout.off_vdata + tok * p.layout.value_bytes, lane, store);
+    if (store && lane % lanes_per_group == 0) {
       const int g = lane / lanes_per_group;
       reinterpret_cast<T*>(chunk + p.layout.off_vscale)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(scale);
       reinterpret_cast<T*>(chunk + p.layout.off_vzero)[tok * p.layout.groups + g] = ElemTraits<T>::from_float(zero);

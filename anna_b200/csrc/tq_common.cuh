@@ -75,21 +75,23 @@ __device__ __forceinline__ float warp_tree_sum(float (&t)[E]) {
 }
 
 // Store one packed row: lane l contributes the W-bit field `field` for bit positions [l*W, (l+1)*W).
-// dst must be 4-byte aligned.
+// dst must be 4-byte aligned.  With `enabled` false (warp-uniform) the warp takes part in the exchange but stores nothing.
 template <int W>
-__device__ __forceinline__ void warp_pack_store(uint64_t field, uint8_t* __restrict__ dst, int lane) {
+__device__ __forceinline__ void warp_pack_store(uint64_t field, uint8_t* __restrict__ dst, int lane, bool enabled = true) {
   if constexpr (W == 64) {
     uint32_t* out = reinterpret_cast<uint32_t*>(dst) + lane * 2;
-    out[0] = (uint32_t)field;
-    out[1] = (uint32_t)(field >> 32);
+    if (enabled) {
+      out[0] = (uint32_t)field;
+      out[1] = (uint32_t)(field >> 32);
+    }
   } else if constexpr (W == 32) {
-    reinterpret_cast<uint32_t*>(dst)[lane] = (uint32_t)field;
+    if (enabled) reinterpret_cast<uint32_t*>(dst)[lane] = (uint32_t)field;
   } else {
     constexpr int kLanesPerWord = 32 / W;
     uint32_t word = (uint32_t)field << ((lane % kLanesPerWord) * W);
 #pragma unroll
     for (int dl = 1; dl < kLanesPerWord; dl <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, dl);
-    if (lane % kLanesPerWord == 0) reinterpret_cast<uint32_t*>(dst)[lane / kLanesPerWord] = word;
+    if (enabled && lane % kLanesPerWord == 0) reinterpret_cast<uint32_t*>(dst)[lane / kLanesPerWord] = word;
   }
 }
 
