@@ -27,18 +27,38 @@ namespace anna {
 
 __device__ int32_t g_tq_mma_faults;  // bumped when a bounded wait on a tile copy expires
 
-// Byte permute and logic helpers are plain intrinsics / C so that the compiler can fold the constant selectors,
-// masks and magic numbers into immediates instead of keeping them in registers.
+// Byte permute and logic helpers are plain intrinsics / C so that the compiler can fold the constant selectors and
+// masks into immediates; the packed fp16 arithmetic goes through PTX on raw registers.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) { return (x & mask) | bits; }
 __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
-  return *reinterpret_cast<const uint32_t*>(&r);
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
+// Packed fp16 fused multiply-add on raw registers.  (Going through __half2 objects costs a logic operation per call to
+// put the two halves back together.)
 __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
-                            *reinterpret_cast<const __half2*>(&c));
-  return *reinterpret_cast<const uint32_t*>(&r);
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
+// A value the compiler cannot see through: `lane` rides along as an unused operand so that the result counts as
+// different in every lane and stays in an ordinary register.  (A value known to be the same in all lanes is moved to a
+// uniform register when registers are short and copied back, one instruction each time, in front of every use that
+// cannot read it from there.)
+__device__ __forceinline__ uint32_t pinned_u32(uint32_t value, int lane) {
+  uint32_t r;
+  asm volatile("{\n .reg .b32 t;\n mov.b32 t, %2;\n mov.b32 %0, %1;\n}\n" : "=r"(r) : "r"(value), "r"(lane));
+  return r;
+}
+// (x & mask) | bits as one three-input logic operation on registers (written out in C with two register constants it
+// becomes two instructions).
+__device__ __forceinline__ uint32_t and_or_regs(uint32_t x, uint32_t mask, uint32_t bits) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(x), "r"(mask), "r"(bits));
+  return r;
 }
 
 // fp16 pair (+-1, +-1) from bits b and b + 16 of x (0 <= b <= 15): a set bit gives +1.  One shift and one logic op.
@@ -51,6 +71,20 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
   asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// mma.sync m16n8k32 (signed 8-bit in, 32-bit integer accumulate); same C fragment layout as the fp16 shape above
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Byte permute in PTX's default mode: result byte i is the byte of {a (0-3), b (4-7)} that bits 0-2 of nibble i of
+// the low half of `sel` name, or, when bit 3 of that nibble is set, eight copies of that byte's top bit.
+__device__ __forceinline__ uint32_t prmt_ptx(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
 }
 
 // N consecutive 32-bit words from shared memory with the widest aligned load (the address is N*4-byte aligned).
@@ -94,6 +128,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifndef ANNA_TQ_RING_TILES
 #define ANNA_TQ_RING_TILES 4
 #endif
+#ifndef ANNA_TQ_FINE_QUERY
+#define ANNA_TQ_FINE_QUERY 1
+#endif
 #ifndef ANNA_TQ_OVERLAP_WINDOW
 #define ANNA_TQ_OVERLAP_WINDOW 1
 #endif
@@ -102,6 +139,15 @@ constexpr float kLazyRescale = 8.0f;  // log2 units: probabilities stay below 2^
 template <typename T, int D, int BITS>
 struct TqMmaCfg {
   static constexpr int kSteps = D / 16;
+  // 4-bit key codes are scored as 8-bit integers: one byte permute turns four codes into four centroid bytes, another
+  // into four sign bytes, and the rotated queries are rounded to 8 bits per head (127 steps up to their largest
+  // coordinate) -- about a third of the instructions of the fp16 expansion the 2- and 3-bit formats use
+  static constexpr bool kInt8Keys = BITS == 4;
+  static constexpr int kSteps8 = D / 32;                       // k-steps of the 8-bit score products
+  static constexpr int kFragBytes = kInt8Keys ? 32 * kSteps8 * 16 : 32 * kSteps * 16;  // query fragments of one unit
+  static constexpr int kFragLoBytes = kInt8Keys ? 32 * kSteps8 * 8 : 0;  // second (fine) byte of the rotated queries
+  static constexpr int kConstOffset = kFragBytes + kFragLoBytes;         // per-head factors and the centroid bytes
+  static_assert(!kInt8Keys || kConstOffset + 128 <= 32 * D, "the query scratch of a unit is 32 * D bytes");
   static constexpr int kGroups = D / 32;                       // value group size is 32 on this path
   static constexpr int kKeyBytes = D * BITS / 8;               // packed key bytes per token
   static constexpr int kIdxBytes = BITS == 3 ? D / 4 : kKeyBytes;  // first plane (all of it unless BITS == 3)
@@ -126,7 +172,10 @@ struct TqMmaCfg {
   static constexpr int kWorkSmem = ((kSmemBytes0 > kTailSmem ? kSmemBytes0 : kTailSmem) + 15) / 16 * 16;
   // behind the working area (which the epilogue reuses): one mbarrier per warp and stage, one valid-token count per tile
   static constexpr int kBarrierBytes = kMmaWarps * kStages * 8;
-  static constexpr int kSmemBytes = kWorkSmem + kBarrierBytes + kMmaWarps * kStages * kTilesPerStep * 4;
+  static constexpr int kQueryOffset = (kWorkSmem + kBarrierBytes + kMmaWarps * kStages * kTilesPerStep * 4 + 15) / 16 * 16;
+  // 8-bit scoring keeps the query fragments of the CTA in shared memory (a 16-byte and an 8-byte load per k-step
+  // and step) instead of 24 registers per lane
+  static constexpr int kSmemBytes = kQueryOffset + (kInt8Keys ? kFragBytes + kFragLoBytes : 0);
   // bytes of one 16-token tile in the stage (= in a 16-token page chunk, padding excluded)
   static constexpr int kTileDataBytes = kOffZero + 16 * kGroups * 2;
   // per-lane key code words per token (this lane's D/4 coordinates)
@@ -159,9 +208,11 @@ __device__ __forceinline__ int sign_coord(int tig, int s, int k) {
 // split kernel: [row][group][lane][step][q1 b0, q1 b1, q2 b0, q2 b1].  Q1 = fwht(s1*q) / sqrt(D), Q2 = fwht(s2*fwht(s1*q)) / D.
 template <typename T, int D, int BITS>
 __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const TqDecodeParams p) {
+  using Cfg = TqMmaCfg<T, D, BITS>;
   constexpr int E = D / 32;
   constexpr int kSteps = D / 16;
   __shared__ float q_rot[2][8][D];
+  __shared__ float q_amax[2][8];
   const int group_tiles = (p.groups + 7) / 8;
   const int kvh = blockIdx.x / group_tiles;
   const int g0 = (blockIdx.x % group_tiles) * 8;
@@ -180,15 +231,29 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
       if (p.signs1[d] < 0.0f) w[j] = -w[j];
     }
     warp_fwht<E>(w, lane);
+    float amax1 = 0.0f, amax2 = 0.0f;
 #pragma unroll
     for (int j = 0; j < E; ++j) {
       const int d = lane * E + j;
       q_rot[0][g][d] = w[j];
+      amax1 = fmaxf(amax1, fabsf(w[j]));
       if (p.signs2[d] < 0.0f) w[j] = -w[j];
     }
     warp_fwht<E>(w, lane);
 #pragma unroll
-    for (int j = 0; j < E; ++j) q_rot[1][g][lane * E + j] = w[j];
+    for (int j = 0; j < E; ++j) {
+      q_rot[1][g][lane * E + j] = w[j];
+      amax2 = fmaxf(amax2, fabsf(w[j]));
+    }
+#pragma unroll
+    for (int dl = 1; dl < 32; dl <<= 1) {
+      amax1 = fmaxf(amax1, __shfl_xor_sync(0xffffffffu, amax1, dl));
+      amax2 = fmaxf(amax2, __shfl_xor_sync(0xffffffffu, amax2, dl));
+    }
+    if (lane == 0) {
+      q_amax[0][g] = amax1;
+      q_amax[1][g] = amax2;
+    }
   }
   __syncthreads();
   // score (log2 units) = norm * (S1 + rnorm * S2) with every constant folded into the fragments:
@@ -198,19 +263,111 @@ __global__ void __launch_bounds__(kMmaThreads) tq_prepare_queries_kernel(const T
   const float log2e = 1.4426950408889634f;
   const float f1 = (BITS == 2 ? __ldg(p.centroids + 1) : 1.0f) * p.scaling * log2e * inv_sqrt_d * inv_sqrt_d;
   const float f2 = p.scaling * log2e * 1.2533141373155001f * inv_sqrt_d * inv_sqrt_d * inv_sqrt_d;
-  uint4* out = reinterpret_cast<uint4*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * 32 * kSteps;
-  for (int item = threadIdx.x; item < 32 * kSteps; item += kMmaThreads) {
-    const int ln = item / kSteps;
-    const int s = item % kSteps;
-    const int gid = ln >> 2, tig = ln & 3;
-    const float* r1 = q_rot[0][gid];
-    const float* r2 = q_rot[1][gid];
-    uint4 v;
-    v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * f1, r1[idx_coord<D, BITS>(tig, s, 1)] * f1);
-    v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * f1, r1[idx_coord<D, BITS>(tig, s, 3)] * f1);
-    v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * f2, r2[sign_coord<D, BITS>(tig, s, 1)] * f2);
-    v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * f2, r2[sign_coord<D, BITS>(tig, s, 3)] * f2);
-    out[item] = v;
+  // every unit owns 32 * D bytes of the scratch
+  uint8_t* unit = reinterpret_cast<uint8_t*>(p.query_frags) + ((int64_t)b * gridDim.x + blockIdx.x) * (32 * D);
+  if constexpr (Cfg::kInt8Keys) {
+    // 8-bit B fragments of m16n8k32: lane (gid, tig) feeds head gid with the coordinates of its code word s,
+    // tig * D/4 + 8s + {0..3} in the first register and + {4..7} in the second.  The rotated query is split into a
+    // coarse byte (127 steps up to the head's largest coordinate) and a fine byte (the rounding remainder in 1/254
+    // steps), so the centroid product sees about 15 bits of it; the sign product uses a coarse byte only.
+    //   [s][lane][q1 b0, q1 b1, q2 b0, q2 b1]   then   [s][lane][q1 fine b0, q1 fine b1]
+    // Behind them, per head: the factor of the centroid product, the factor of the sign product and the integer the
+    // sign accumulators start from (sign bytes are 2 for a clear bit and 0 for a set one: 2 * sum over clear bits
+    // minus the sum over all coordinates is minus the +-1 product); then the centroids as signed bytes.
+    constexpr int kSteps8 = Cfg::kSteps8;
+    constexpr int kEntries = 1 << (BITS - 1);
+    __shared__ float cent_scale;
+    if (warp == 0) {
+      // The byte scale of the centroids is the one, among 256 candidates from 127 down to 63 steps for the largest
+      // centroid, that leaves the smallest squared rounding error over the codebook.
+      float cent[kEntries], cmax = 0.0f;
+#pragma unroll
+      for (int e = 0; e < kEntries; ++e) {
+        cent[e] = __ldg(p.centroids + e);
+        cmax = fmaxf(cmax, fabsf(cent[e]));
+      }
+      float best_err = INFINITY, best_k = 0.0f;
+      if (cmax > 0.0f) {
+        for (int j = lane; j < 256; j += 32) {
+          const float k = (127.0f - 0.25f * (float)j) / cmax;
+          float err = 0.0f;
+#pragma unroll
+          for (int e = 0; e < kEntries; ++e) {
+            const float d = (cent[e] * k - rintf(cent[e] * k)) / k;
+            err += d * d;
+          }
+          if (err < best_err) { best_err = err; best_k = k; }
+        }
+      }
+#pragma unroll
+      for (int dl = 1; dl < 32; dl <<= 1) {
+        const float other_err = __shfl_xor_sync(0xffffffffu, best_err, dl);
+        const float other_k = __shfl_xor_sync(0xffffffffu, best_k, dl);
+        if (other_err < best_err || (other_err == best_err && other_k > best_k)) { best_err = other_err; best_k = other_k; }
+      }
+      if (lane == 0) {
+        cent_scale = best_k;
+        uint32_t lut[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < kEntries; ++e)
+          lut[e / 4] |= ((uint32_t)__float2int_rn(cent[e] * best_k) & 0xffu) << (8 * (e % 4));
+        uint32_t* consts = reinterpret_cast<uint32_t*>(unit + Cfg::kConstOffset);
+        consts[24] = lut[0];
+        consts[25] = lut[1];
+      }
+    }
+    __syncthreads();
+    auto coarse = [](float v, float k) { return max(-127, min(127, __float2int_rn(v * k))); };
+    auto fine = [](float v, float k, int c) { return max(-127, min(127, __float2int_rn((v * k - (float)c) * 254.0f))); };
+    uint4* out = reinterpret_cast<uint4*>(unit);
+    uint2* out_lo = reinterpret_cast<uint2*>(unit + Cfg::kFragBytes);
+    for (int item = threadIdx.x; item < 32 * kSteps8; item += kMmaThreads) {
+      const int ln = item / kSteps8;
+      const int s = item % kSteps8;
+      const int gid = ln >> 2, tig = ln & 3;
+      const float k1 = q_amax[0][gid] > 0.0f ? 127.0f / q_amax[0][gid] : 0.0f;
+      const float k2 = q_amax[1][gid] > 0.0f ? 127.0f / q_amax[1][gid] : 0.0f;
+      const float* r1 = q_rot[0][gid] + tig * (D / 4) + 8 * s;
+      const float* r2 = q_rot[1][gid] + tig * (D / 4) + 8 * s;
+      uint32_t w[4] = {0u, 0u, 0u, 0u}, wl[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c0 = coarse(r1[i], k1), c1 = coarse(r1[4 + i], k1);
+        w[0] |= ((uint32_t)c0 & 0xffu) << (8 * i);
+        w[1] |= ((uint32_t)c1 & 0xffu) << (8 * i);
+        wl[0] |= ((uint32_t)fine(r1[i], k1, c0) & 0xffu) << (8 * i);
+        wl[1] |= ((uint32_t)fine(r1[4 + i], k1, c1) & 0xffu) << (8 * i);
+        w[2] |= ((uint32_t)coarse(r2[i], k2) & 0xffu) << (8 * i);
+        w[3] |= ((uint32_t)coarse(r2[4 + i], k2) & 0xffu) << (8 * i);
+      }
+      out[s * 32 + ln] = make_uint4(w[0], w[1], w[2], w[3]);
+      out_lo[s * 32 + ln] = make_uint2(wl[0], wl[1]);
+    }
+    if (threadIdx.x < 8) {
+      const int g = threadIdx.x;
+      const float k2 = q_amax[1][g] > 0.0f ? 127.0f / q_amax[1][g] : 0.0f;
+      int total = 0;
+      for (int d = 0; d < D; ++d) total += coarse(q_rot[1][g][d], k2);
+      float* consts = reinterpret_cast<float*>(unit + Cfg::kConstOffset);
+      consts[g] = cent_scale > 0.0f ? (q_amax[0][g] * f1 / 127.0f) / cent_scale / (ANNA_TQ_FINE_QUERY ? 254.0f : 1.0f) : 0.0f;
+      consts[8 + g] = -(q_amax[1][g] * f2 / 127.0f);
+      reinterpret_cast<int*>(consts)[16 + g] = -total;
+    }
+  } else {
+    uint4* out = reinterpret_cast<uint4*>(unit);
+    for (int item = threadIdx.x; item < 32 * kSteps; item += kMmaThreads) {
+      const int ln = item / kSteps;
+      const int s = item % kSteps;
+      const int gid = ln >> 2, tig = ln & 3;
+      const float* r1 = q_rot[0][gid];
+      const float* r2 = q_rot[1][gid];
+      uint4 v;
+      v.x = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 0)] * f1, r1[idx_coord<D, BITS>(tig, s, 1)] * f1);
+      v.y = pack2<__half>(r1[idx_coord<D, BITS>(tig, s, 2)] * f1, r1[idx_coord<D, BITS>(tig, s, 3)] * f1);
+      v.z = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 0)] * f2, r2[sign_coord<D, BITS>(tig, s, 1)] * f2);
+      v.w = pack2<__half>(r2[sign_coord<D, BITS>(tig, s, 2)] * f2, r2[sign_coord<D, BITS>(tig, s, 3)] * f2);
+      out[item] = v;
+    }
   }
 }
 
@@ -315,22 +472,50 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
   const int lane = threadIdx.x & 31;
   const int gid = lane >> 2;
   const int tig = lane & 3;
-  // Q fragments (fp16, softmax scale and log2(e) folded in) were prepared by tq_prepare_queries_kernel in exactly this
-  // lane's register order: [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]
-  uint32_t q1f[Cfg::kSteps][2], q2f[Cfg::kSteps][2];
+  // Q fragments (softmax scale and log2(e) folded in) were prepared by tq_prepare_queries_kernel in exactly this
+  // lane's register order: [row b][blockIdx.y][lane][step][q1 b0, q1 b1, q2 b0, q2 b1]; fp16 pairs, or bytes with the
+  // per-head factors behind them when the key codes are scored as 8-bit integers
+  constexpr int kQSteps = Cfg::kInt8Keys ? 1 : Cfg::kSteps;
+  uint32_t q1f[kQSteps][2], q2f[kQSteps][2];
+  float beta1[2] = {0.0f, 0.0f}, beta2[2] = {0.0f, 0.0f};  // this lane's two heads (columns 2tig, 2tig + 1)
+  int s2_start[2] = {0, 0};
+  uint32_t cent_bytes[2] = {0u, 0u};
+  const uint4* q_coarse = reinterpret_cast<const uint4*>(smem_raw + Cfg::kQueryOffset) + lane;          // [s][lane]
+  const uint2* q_fine = reinterpret_cast<const uint2*>(smem_raw + Cfg::kQueryOffset + Cfg::kFragBytes) + lane;
   {
-    const uint4* frag = reinterpret_cast<const uint4*>(p.query_frags) +
-                        (((int64_t)b * gridDim.y + blockIdx.y) * 32 + lane) * Cfg::kSteps;
+    const uint8_t* unit = reinterpret_cast<const uint8_t*>(p.query_frags) + ((int64_t)b * gridDim.y + blockIdx.y) * (32 * D);
+    if constexpr (Cfg::kInt8Keys) {
+      // the CTA's query fragments go to shared memory once; every warp reads them after the barrier below
+      const uint4* src = reinterpret_cast<const uint4*>(unit);
+      uint4* dst = reinterpret_cast<uint4*>(smem_raw + Cfg::kQueryOffset);
+      for (int i = threadIdx.x; i < (Cfg::kFragBytes + Cfg::kFragLoBytes) / 16; i += kMmaThreads) dst[i] = __ldg(src + i);
+      const float* consts = reinterpret_cast<const float*>(unit + Cfg::kConstOffset);
 #pragma unroll
-    for (int s = 0; s < Cfg::kSteps; ++s) {
-      const uint4 v = __ldg(frag + s);
-      q1f[s][0] = v.x; q1f[s][1] = v.y; q2f[s][0] = v.z; q2f[s][1] = v.w;
+      for (int c = 0; c < 2; ++c) {
+        beta1[c] = __ldg(consts + 2 * tig + c);
+        beta2[c] = __ldg(consts + 8 + 2 * tig + c);
+        s2_start[c] = __ldg(reinterpret_cast<const int*>(consts) + 16 + 2 * tig + c);
+      }
+      cent_bytes[0] = __ldg(reinterpret_cast<const uint32_t*>(consts) + 24);
+      cent_bytes[1] = __ldg(reinterpret_cast<const uint32_t*>(consts) + 25);
+      __syncthreads();
+    } else {
+      const uint4* frag = reinterpret_cast<const uint4*>(unit) + lane * kQSteps;
+#pragma unroll
+      for (int s = 0; s < kQSteps; ++s) {
+        const uint4 v = __ldg(frag + s);
+        q1f[s][0] = v.x; q1f[s][1] = v.y; q2f[s][0] = v.z; q2f[s][1] = v.w;
+      }
     }
   }
 
-  // centroid lookup tables for PRMT: low bytes and high bytes of the fp16 centroids (up to 8 entries)
+  // centroid lookup tables for PRMT (up to 8 entries): low bytes and high bytes of the fp16 centroids, or -- 4-bit
+  // codes -- the centroids as signed bytes in lut_lo, as the query preparation rounded them
   uint32_t lut_lo[2] = {0u, 0u}, lut_hi[2] = {0u, 0u};
-  if constexpr (BITS != 2) {
+  if constexpr (Cfg::kInt8Keys) {
+    lut_lo[0] = pinned_u32(cent_bytes[0], lane);
+    lut_lo[1] = pinned_u32(cent_bytes[1], lane);
+  } else if constexpr (BITS != 2) {
     constexpr int kEntries = 1 << (BITS - 1);
 #pragma unroll
     for (int e = 0; e < kEntries; ++e) {
@@ -344,6 +529,11 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       lut_hi[1] = lut_hi[0];
     }
   }
+
+  // loop constants held in registers
+  const uint32_t nib_mask = pinned_u32(0x03C003C0u, lane), magic16 = pinned_u32(0x4C004C00u, lane);
+  const uint32_t kTwo = pinned_u32(0x02020202u, lane), kIdxMask = pinned_u32(0x77777777u, lane);
+  (void)nib_mask; (void)magic16; (void)kTwo; (void)kIdxMask;
 
   const uint32_t warp_smem_u32 = smem_u32(smem_raw + warp * Cfg::kWarpSmem);
   const uint8_t* warp_smem = smem_raw + warp * Cfg::kWarpSmem;
@@ -467,28 +657,47 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
         lds_words<Cfg::kIdxWords>(keys + tok_hi * Cfg::kKeyBytes, iw_hi[u]);
       }
       if constexpr (BITS == 4) {
+        // one code word = 8 coordinates of a token = one k-step: its low half-word selects four centroid bytes (and,
+        // unmasked, four sign bytes: bit 3 of a selector nibble asks for the top bit of the byte 0x02, i.e. 0), its high
+        // half-word the next four
+        int i1[U][4], i1l[U][4], i2[U][4];
 #pragma unroll
-        for (int s = 0; s < Cfg::kSteps; ++s) {
+        for (int u = 0; u < U; ++u) {
+          i1[u][0] = i1[u][1] = i1[u][2] = i1[u][3] = 0;
+          i1l[u][0] = i1l[u][1] = i1l[u][2] = i1l[u][3] = 0;
+          i2[u][0] = i2[u][2] = s2_start[0];
+          i2[u][1] = i2[u][3] = s2_start[1];
+        }
+#pragma unroll
+        for (int s = 0; s < Cfg::kSteps8; ++s) {
+          const uint4 qc = q_coarse[s * 32];  // q1 b0, q1 b1, q2 b0, q2 b1
+          const uint2 qf = q_fine[s * 32];
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const uint32_t wl = iw_lo[u][s / 2] >> (16 * (s % 2));
-            const uint32_t wh = iw_hi[u][s / 2] >> (16 * (s % 2));
-            const uint32_t sl = wl & 0x7777u, sh = wh & 0x7777u;
-            const uint32_t lo_l = prmt(lut_lo[0], lut_lo[1], sl), hi_l = prmt(lut_hi[0], lut_hi[1], sl);
-            const uint32_t lo_h = prmt(lut_lo[0], lut_lo[1], sh), hi_h = prmt(lut_hi[0], lut_hi[1], sh);
-            const uint32_t a[4] = {prmt(lo_l, hi_l, 0x5140u), prmt(lo_h, hi_h, 0x5140u), prmt(lo_l, hi_l, 0x7362u),
-                                   prmt(lo_h, hi_h, 0x7362u)};
-            mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
+            const uint32_t xl = iw_lo[u][s], xh = iw_hi[u][s];
+            const uint32_t ml = xl & kIdxMask, mh = xh & kIdxMask;
+            const uint32_t a[4] = {prmt_ptx(lut_lo[0], lut_lo[1], ml), prmt_ptx(lut_lo[0], lut_lo[1], mh),
+                                   prmt_ptx(lut_lo[0], lut_lo[1], ml >> 16),
+                                   prmt_ptx(lut_lo[0], lut_lo[1], mh >> 16)};
+            mma_s8(i1[u], a, qc.x, qc.y);
+            if (ANNA_TQ_FINE_QUERY) mma_s8(i1l[u], a, qf.x, qf.y);
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            // sign bits 3 + 4i of the word: nibbles i and i + 4 land in the two halves of one register
-            const uint32_t xl = iw_lo[u][s / 2], xh = iw_hi[u][s / 2];
-            const int b0 = 3 + 8 * (s % 2), b1 = 7 + 8 * (s % 2);
-            const uint32_t a[4] = {pm_one_pair(xl, b0), pm_one_pair(xh, b0), pm_one_pair(xl, b1), pm_one_pair(xh, b1)};
-            mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
+            const uint32_t xl = iw_lo[u][s], xh = iw_hi[u][s];
+            const uint32_t a[4] = {prmt_ptx(kTwo, kTwo, xl), prmt_ptx(kTwo, kTwo, xh),
+                                   prmt_ptx(kTwo, kTwo, xl >> 16), prmt_ptx(kTwo, kTwo, xh >> 16)};
+            mma_s8(i2[u], a, qc.z, qc.w);
           }
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            // 254 * coarse + fine stays below 2^31 (|coarse| <= 127 * 127 * D); beta1 carries the 1 / 254
+            s1[u][r] = (float)(ANNA_TQ_FINE_QUERY ? i1[u][r] * 254 + i1l[u][r] : i1[u][r]) * beta1[r & 1];
+            s2[u][r] = (float)i2[u][r] * beta2[r & 1];
+          }
       } else if constexpr (BITS == 2) {
 #pragma unroll
         for (int s = 0; s < Cfg::kSteps; ++s) {
@@ -554,6 +763,7 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       sc[u][2] = n_hi * fmaf(r_hi, s2[u][2], s1[u][2]);
       sc[u][3] = n_hi * fmaf(r_hi, s2[u][3], s1[u][3]);
       if (!full) {  // rows past the end of the prefix (their bytes may be anything)
+        asm volatile("" ::: "memory");  // a real (warp-uniform) branch: full steps pay nothing for the masking
         if (tok_lo >= valid[u]) sc[u][0] = sc[u][1] = -INFINITY;
         if (tok_hi >= valid[u]) sc[u][2] = sc[u][3] = -INFINITY;
       }
@@ -616,7 +826,12 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       for (int i = 0; i < 4; ++i) {
         sv[i] = ElemTraits<T>::to_float(scales[toks[i] * Cfg::kGroups]);
         zv[i] = ElemTraits<T>::to_float(zeros[toks[i] * Cfg::kGroups]);
-        if (!full && toks[i] >= valid[u]) sv[i] = zv[i] = 0.0f;
+      }
+      if (!full) {
+        asm volatile("" ::: "memory");  // a real (warp-uniform) branch, as above
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (toks[i] >= valid[u]) sv[i] = zv[i] = 0.0f;
       }
       sc_pair[u][0] = pack2<__half>(sv[0], sv[1]);
       sc_pair[u][1] = pack2<__half>(sv[2], sv[3]);
@@ -627,8 +842,14 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
       for (int i = 0; i < 4; ++i) lds_words<Cfg::kValWords>(vbase + toks[i] * Cfg::kValBytes, vw[u][i]);
     }
     if constexpr (BITS != 2) {
-      // 4-bit codes: one 16-bit half-word = 4 dims; x packs the same 4 dims of two tokens (low / high half)
-      constexpr uint32_t kMagicLo = 0x64006400u, kMagicHi = 0x54005400u;  // 1024 + n, 64 + n
+      // 4-bit codes: one 16-bit half-word = 4 dims; x packs the same 4 dims of two tokens (low / high half).  A code
+      // moved to bits 6..9 under the exponent of 16 reads as the fp16 number 16 + code, so one fused multiply-add
+      // de-quantises a pair: (16 + code) * scale + (zero - 16 * scale).  The shifted zero point is rounded to fp16 once
+      // per token and group; it is no larger than the values themselves, so this costs what their own rounding costs.
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) zp_pair[u][pr] = hfma2_u32(sc_pair[u][pr], 0xCC00CC00u, zp_pair[u][pr]);
 #pragma unroll
       for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
         const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
@@ -638,12 +859,11 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
 #pragma unroll
           for (int pr = 0; pr < 2; ++pr) {
             const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
-            const uint32_t y = x >> 8;
             const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
-            r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000F000Fu, kMagicLo), kMagicLo), scl, zpt);
-            r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00F000F0u, kMagicHi), kMagicHi), scl, zpt);
-            r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000F000Fu, kMagicLo), kMagicLo), scl, zpt);
-            r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00F000F0u, kMagicHi), kMagicHi), scl, zpt);
+            r[pr][0] = hfma2_u32(and_or_regs(x << 6, nib_mask, magic16), scl, zpt);
+            r[pr][1] = hfma2_u32(and_or_regs(x << 2, nib_mask, magic16), scl, zpt);
+            r[pr][2] = hfma2_u32(and_or_regs(x >> 2, nib_mask, magic16), scl, zpt);
+            r[pr][3] = hfma2_u32(and_or_regs(x >> 6, nib_mask, magic16), scl, zpt);
           }
           // dims 4hw + {0,1} -> m-tile 2hw (rows gid, gid+8); dims 4hw + {2,3} -> m-tile 2hw + 1
           const uint32_t a_even[4] = {r[0][0], r[0][1], r[1][0], r[1][1]};
