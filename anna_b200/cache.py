@@ -648,8 +648,11 @@ class Qwen3DynamicCache:
         return keys, values, past_lengths
 
     def turboquant_single_token_decode_attention(self, layer_idx: int, query_states: torch.Tensor, *, scaling: float,
-                                                 num_key_value_groups: int, gate: torch.Tensor | None = None):
-        """One launch pair for the whole batch (ops.py:1024-1070 loops over rows)."""
+                                                 num_key_value_groups: int, gate: torch.Tensor | None = None,
+                                                 output: torch.Tensor | None = None,
+                                                 peer_outputs: tuple[int, ...] = ()):
+        """One launch pair for the whole batch (ops.py:1024-1070 loops over rows).  ``output`` / ``peer_outputs``: see
+        ``launch_tq_decode`` (not part of the reference's signature; used by the KV-head-sharded layout)."""
         if not self.uses_turboquant_for_layer(layer_idx):
             raise ValueError(f"Layer {layer_idx} does not use TurboQuant-backed KV storage.")
         if query_states.ndim != 4 or query_states.shape[2] != 1:
@@ -663,6 +666,8 @@ class Qwen3DynamicCache:
             raise ValueError(f"Cache batch size mismatch: expected {len(rows)}, got {batch}")
         pool = self._tq_pool(layer_idx)
         if not pool.configured or all(row is None or row.length <= 0 for row in rows):
+            if output is not None or peer_outputs:
+                raise RuntimeError("an empty TurboQuant cache cannot decode into caller-provided outputs")
             return query_states.new_zeros(query_states.shape)
         if int(query_states.shape[1]) != pool.kv_heads * num_key_value_groups:
             raise ValueError(
@@ -677,7 +682,7 @@ class Qwen3DynamicCache:
             lengths_dev = state.current(lengths)
             slots_dev = state.slots(slots)
         return launch_tq_decode(pool, query_states, table_dev, slots, lengths, scaling, gate, slots_dev=slots_dev,
-                                lengths_dev=lengths_dev)
+                                lengths_dev=lengths_dev, output=output, peer_outputs=peer_outputs)
 
     # -- dense views -------------------------------------------------------------------------------------------------------
 

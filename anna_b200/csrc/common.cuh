@@ -30,6 +30,8 @@ int set_error(int code, const char* fmt, ...);  // formats into the thread-local
       return ::anna::set_error(ANNA_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));    \
   } while (0)
 
+constexpr int kMaxPeerOutputs = 7;  // the other GPUs of an 8-GPU box
+
 inline int check_launch(const char* what) {
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return set_error(ANNA_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(err));

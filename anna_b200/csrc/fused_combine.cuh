@@ -16,6 +16,10 @@ struct FusedCombine {
   int64_t out_stride_b, out_stride_h;
   const void* gate;
   int64_t gate_stride_b, gate_stride_h;
+  // KV-head-sharded decode: the same rows of the output tensors of the other ranks (peer memory mapped into this
+  // process).  Every merged output row is stored to all of them at the offset it has in `out`.
+  void* peers[kMaxPeerOutputs];
+  int num_peers;
 };
 
 constexpr int kFusedMaxChunks = 512;  // weights of one head are staged in shared memory
@@ -76,9 +80,13 @@ __device__ __forceinline__ void fused_combine_tail(const FusedCombine& fc, int b
                       (int64_t)(hq0 + g) * fc.gate_stride_h;
       acc *= sigmoidf_fast(ElemTraits<T>::to_float(gate[d]));
     }
-    T* out = reinterpret_cast<T*>(fc.out) + (int64_t)b * fc.out_stride_b + (int64_t)(hq0 + g) * fc.out_stride_h;
-    out[d] = ElemTraits<T>::from_float(acc);
+    const int64_t offset = (int64_t)b * fc.out_stride_b + (int64_t)(hq0 + g) * fc.out_stride_h + d;
+    const T result = ElemTraits<T>::from_float(acc);
+    reinterpret_cast<T*>(fc.out)[offset] = result;
+    for (int peer = 0; peer < fc.num_peers; ++peer) reinterpret_cast<T*>(fc.peers[peer])[offset] = result;
   }
+  // stores to other GPUs are ordered before whatever this stream signals to them after the kernel
+  if (fc.num_peers > 0) __threadfence_system();
 }
 
 // A row with no visible key has no contributing CTA; the CTA of chunk 0 writes its zeros.
@@ -87,9 +95,12 @@ __device__ __forceinline__ void fused_write_zero_row(const FusedCombine& fc, int
   for (int item = threadIdx.x; item < g_count * D; item += THREADS) {
     const int g = item / D;
     const int d = item % D;
-    T* out = reinterpret_cast<T*>(fc.out) + (int64_t)b * fc.out_stride_b + (int64_t)(hq0 + g) * fc.out_stride_h;
-    out[d] = ElemTraits<T>::from_float(0.0f);
+    const int64_t offset = (int64_t)b * fc.out_stride_b + (int64_t)(hq0 + g) * fc.out_stride_h + d;
+    reinterpret_cast<T*>(fc.out)[offset] = ElemTraits<T>::from_float(0.0f);
+    for (int peer = 0; peer < fc.num_peers; ++peer)
+      reinterpret_cast<T*>(fc.peers[peer])[offset] = ElemTraits<T>::from_float(0.0f);
   }
+  if (fc.num_peers > 0) __threadfence_system();
 }
 
 }  // namespace anna

@@ -281,17 +281,22 @@ static int launch_tq_split(const TqDecodeParams& p, int batch, cudaStream_t stre
 
 using namespace anna;
 
-extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
-                                    const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
-                                    const void* window, const int64_t* window_slots, const int64_t* lengths,
-                                    const float* signs1, const float* signs2, const float* centroids,
-                                    const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out,
-                                    int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
-                                    float* partial_values, int chunk_capacity, int chunk_tokens_in,
-                                    int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes,
-                                    int batch, int q_heads, int kv_heads, int head_dim,
-                                    int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
-                                    int64_t max_blocks, float scaling, int dtype, anna_stream_t stream) {
+static int tq_paged_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                                const void* window, const int64_t* window_slots, const int64_t* lengths,
+                                const float* signs1, const float* signs2, const float* centroids,
+                                const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out,
+                                int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
+                                float* partial_values, int chunk_capacity, int chunk_tokens_in,
+                                int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes,
+                                int batch, int q_heads, int kv_heads, int head_dim,
+                                int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
+                                int64_t max_blocks, float scaling, int dtype, void* const* peer_outputs, int num_peers,
+                                anna_stream_t stream) {
+  ANNA_REQUIRE(num_peers >= 0 && num_peers <= kMaxPeerOutputs && (num_peers == 0 || peer_outputs != nullptr),
+               "anna_tq_paged_decode: between 0 and %d peer outputs", kMaxPeerOutputs);
+  for (int i = 0; i < num_peers; ++i)
+    ANNA_REQUIRE(peer_outputs[i] != nullptr, "anna_tq_paged_decode: null peer output %d", i);
   ANNA_REQUIRE(q && window && window_slots && lengths && signs1 && signs2 && centroids && out,
                "anna_tq_paged_decode: null pointer argument");
   ANNA_REQUIRE(packed_pages != nullptr || num_pages == 0, "anna_tq_paged_decode: null page pool with num_pages > 0");
@@ -345,9 +350,14 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
     const bool umma = tq_split_umma_applicable(p, head_dim, bits, dtype);
     if (split_counters != nullptr && num_chunks <= kFusedMaxChunks) {
       p.fused = FusedCombine{split_counters, out, out_stride_b, out_stride_h, gate, gate_stride_b, gate_stride_h};
+      for (int i = 0; i < num_peers; ++i) p.fused.peers[i] = peer_outputs[i];
+      p.fused.num_peers = num_peers;
       return umma ? launch_tq_split_umma(p, batch, bits, dtype, (cudaStream_t)stream)
                   : launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
     }
+    if (num_peers > 0)
+      return set_error(ANNA_ERR_UNSUPPORTED, "peer outputs need the fused merge (split counters, at most %d chunks)",
+                       kFusedMaxChunks);
     rc = umma ? launch_tq_split_umma(p, batch, bits, dtype, (cudaStream_t)stream)
               : launch_tq_split_mma(p, batch, head_dim, bits, dtype, (cudaStream_t)stream);
     if (rc != ANNA_OK) return rc;
@@ -355,6 +365,8 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
                                 out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,
                                 dtype, (cudaStream_t)stream);
   }
+  if (num_peers > 0)
+    return set_error(ANNA_ERR_UNSUPPORTED, "peer outputs need the tensor-core decode path (16-bit cache, head_dim 128/256)");
   const int gpad = padded_group(p.groups);
   rc = ANNA_DISPATCH_DTYPE(dtype, T, [&]() -> int {
     return ANNA_DISPATCH_TQ_DIM(head_dim, D, [&]() -> int {
@@ -369,6 +381,45 @@ extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q
   return launch_split_combine(ws, nullptr, p.lengths, -1, p.max_len, residual_len, gate, gate_stride_b, gate_stride_h,
                               out, out_stride_b, out_stride_h, batch, q_heads, head_dim, chunk_tokens, num_chunks,
                               dtype, (cudaStream_t)stream);
+}
+
+extern "C" int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                    const uint8_t* packed_pages, const int32_t* block_table, int64_t table_stride,
+                                    const void* window, const int64_t* window_slots, const int64_t* lengths,
+                                    const float* signs1, const float* signs2, const float* centroids,
+                                    const void* gate, int64_t gate_stride_b, int64_t gate_stride_h, void* out,
+                                    int64_t out_stride_b, int64_t out_stride_h, float* partial_stats,
+                                    float* partial_values, int chunk_capacity, int chunk_tokens_in,
+                                    int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes,
+                                    int batch, int q_heads, int kv_heads, int head_dim,
+                                    int block_size, int residual_len, int bits, int value_group, int64_t num_pages,
+                                    int64_t max_blocks, float scaling, int dtype, anna_stream_t stream) {
+  return tq_paged_decode_impl(q, q_stride_b, q_stride_h, packed_pages, block_table, table_stride, window, window_slots,
+                              lengths, signs1, signs2, centroids, gate, gate_stride_b, gate_stride_h, out, out_stride_b,
+                              out_stride_h, partial_stats, partial_values, chunk_capacity, chunk_tokens_in,
+                              split_counters, query_scratch, query_scratch_bytes, batch, q_heads, kv_heads, head_dim,
+                              block_size, residual_len, bits, value_group, num_pages, max_blocks, scaling, dtype,
+                              nullptr, 0, stream);
+}
+
+extern "C" int anna_tq_paged_decode_peers(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                          const uint8_t* packed_pages, const int32_t* block_table,
+                                          int64_t table_stride, const void* window, const int64_t* window_slots,
+                                          const int64_t* lengths, const float* signs1, const float* signs2,
+                                          const float* centroids, const void* gate, int64_t gate_stride_b,
+                                          int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                                          float* partial_stats, float* partial_values, int chunk_capacity,
+                                          int chunk_tokens_in, int32_t* split_counters, void* query_scratch,
+                                          size_t query_scratch_bytes, int batch, int q_heads, int kv_heads,
+                                          int head_dim, int block_size, int residual_len, int bits, int value_group,
+                                          int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                                          void* const* peer_outputs, int num_peers, anna_stream_t stream) {
+  return tq_paged_decode_impl(q, q_stride_b, q_stride_h, packed_pages, block_table, table_stride, window, window_slots,
+                              lengths, signs1, signs2, centroids, gate, gate_stride_b, gate_stride_h, out, out_stride_b,
+                              out_stride_h, partial_stats, partial_values, chunk_capacity, chunk_tokens_in,
+                              split_counters, query_scratch, query_scratch_bytes, batch, q_heads, kv_heads, head_dim,
+                              block_size, residual_len, bits, value_group, num_pages, max_blocks, scaling, dtype,
+                              peer_outputs, num_peers, stream);
 }
 
 extern "C" size_t anna_tq_query_scratch_bytes(int batch, int q_heads, int kv_heads, int head_dim) {

@@ -133,3 +133,95 @@ class HeadGather:
         assert self._full is not None
         self._full.view(batch, world, heads, dim).copy_(self._staging.permute(1, 0, 2, 3))
         return self._full
+
+
+class PeerHeadGather:
+    """KV-head-sharded decode without a collective: every rank's decode kernel stores its output rows straight into
+    the ``[B, Hq, 1, D]`` output tensors of all ranks (peer stores over NVLink from the kernel's merge epilogue), then
+    one warp per rank publishes an arrival flag to the peers and waits, with a time limit, for theirs.
+
+    The tensors live in memory that all ranks of the group map (``torch.distributed._symmetric_memory``): two output
+    tensors, used in turn, so that a rank that is one step ahead writes where no peer still reads, and one array of
+    arrival flags.  Use::
+
+        gather = PeerHeadGather(shard, batch=B, q_heads=Hq, head_dim=D, dtype=torch.bfloat16, device=device)
+        local_out, peers = gather.begin()                      # this rank's head slice of the step's tensor
+        cache.turboquant_single_token_decode_attention(0, q_local, ..., output=local_out, peer_outputs=peers)
+        full = gather.finish()                                 # [B, Hq, 1, D], valid on the current stream
+
+    ``check()`` synchronises and raises if a wait ran out.  The reference is single-device: no counterpart."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, shard: KvHeadShard, *, batch: int, q_heads: int, head_dim: int, dtype: torch.dtype,
+                 device: torch.device, group=None, timeout_ms: int = 2000) -> None:
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        if device.type != "cuda":
+            raise RuntimeError("PeerHeadGather needs CUDA devices with peer access; use HeadGather on other backends")
+        # plain peer loads / stores only: nothing here needs an NVLink multicast binding of the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self._lib = _lib
+        self.shard = shard
+        self.group = dist.group.WORLD if group is None else group
+        self.world_size = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world_size != shard.world_size or self.rank != shard.rank:
+            raise ValueError("the shard does not describe this rank of the group")
+        if self.world_size > 8:
+            raise ValueError("PeerHeadGather serves the GPUs of one box (at most 8 ranks)")
+        self.shape = (batch, q_heads, 1, head_dim)
+        self.dtype = dtype
+        self.device = device
+        self.timeout_ms = int(timeout_ms)
+        elems = batch * q_heads * head_dim
+        self._out_bytes = (elems * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        self._buffer = symm_mem.empty(self.FLAG_BYTES + 2 * self._out_bytes, dtype=torch.uint8, device=device)
+        self._buffer.zero_()
+        self._handle = symm_mem.rendezvous(self._buffer, self.group)
+        self._bases = [int(p) for p in self._handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every rank's flags are zero before anybody publishes a step
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._step = 0
+        self._head_offset = shard.q_start * head_dim * torch.empty((), dtype=dtype).element_size()
+
+    def _tensor(self, parity: int) -> torch.Tensor:
+        start = self.FLAG_BYTES + parity * self._out_bytes
+        count = self.shape[0] * self.shape[1] * self.shape[3]
+        flat = self._buffer[start:start + self._out_bytes].view(self.dtype)[:count]
+        return flat.view(self.shape)
+
+    def begin(self) -> tuple[torch.Tensor, tuple[int, ...]]:
+        """This rank's ``[B, Hq / N, 1, D]`` slice of the next step's output tensor and the addresses of the same slice
+        in the other ranks' tensors."""
+        parity = (self._step + 1) & 1
+        local = self._tensor(parity)[:, self.shard.q_start:self.shard.q_stop]
+        offset = self.FLAG_BYTES + parity * self._out_bytes + self._head_offset
+        peers = tuple(base + offset for r, base in enumerate(self._bases) if r != self.rank)
+        return local, peers
+
+    def finish(self) -> torch.Tensor:
+        """Publishes this rank's arrival for the step begun last and waits (on the device, bounded) for the peers;
+        returns the full ``[B, Hq, 1, D]`` tensor of the step."""
+        import ctypes
+
+        from .fused_ops import on_device, ptr, stream_ptr
+
+        self._step += 1
+        flags = (ctypes.c_void_p * self.world_size)(*self._bases)
+        with on_device(self.device):
+            self._lib.check(self._lib.lib().anna_peer_signal_wait(
+                flags, self.rank, self.world_size, self._step, self.timeout_ms, ptr(self._status),
+                stream_ptr(self.device)), "anna_peer_signal_wait")
+        return self._tensor(self._step & 1)
+
+    def check(self) -> None:
+        status = int(self._status.item())
+        if status != 0:
+            raise RuntimeError(f"a peer did not arrive within {self.timeout_ms} ms (device status {status})")

@@ -77,11 +77,14 @@ def launch_tq_append(pool: TurboQuantLayerPool, key_states: torch.Tensor, value_
 
 def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, table_dev: torch.Tensor | None,
                      slots: list[int], lengths: list[int], scaling: float, gate: torch.Tensor | None, *,
-                     slots_dev: torch.Tensor | None = None, lengths_dev: torch.Tensor | None = None) -> torch.Tensor:
+                     slots_dev: torch.Tensor | None = None, lengths_dev: torch.Tensor | None = None,
+                     output: torch.Tensor | None = None, peer_outputs: tuple[int, ...] = ()) -> torch.Tensor:
     """Decode ``[B, Hq, 1, D]`` queries against B rows of one layer (packed prefix + window ring).
 
     ``slots_dev`` / ``lengths_dev`` (optional, int64 ``[B]`` on the device) are copies of ``slots`` / ``lengths``
-    that the caller already holds there."""
+    that the caller already holds there.  ``output`` (optional, ``[B, Hq, 1, D]``, last dimension contiguous) receives
+    the result instead of a new tensor; ``peer_outputs`` are device addresses, in other GPUs' memory, of tensors with
+    the strides of ``output`` that receive the same rows (KV-head-sharded decode, see ``sharding.PeerHeadGather``)."""
     _require_cuda(query_states, "TurboQuant decode")
     query = query_states if query_states.stride(3) == 1 else query_states.contiguous()
     if gate is not None and gate.stride(3) != 1:
@@ -95,23 +98,37 @@ def launch_tq_decode(pool: TurboQuantLayerPool, query_states: torch.Tensor, tabl
         meta = MetadataUploader.for_device(device).upload([lengths, slots])
         lengths_dev = meta[0] if lengths_dev is None else lengths_dev
         slots_dev = meta[1] if slots_dev is None else slots_dev
-    out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    if output is None:
+        out = torch.empty((batch, heads, 1, dim), dtype=query.dtype, device=device)
+    else:
+        if tuple(output.shape) != (batch, heads, 1, dim) or output.dtype != query.dtype or output.device != device \
+                or output.stride(3) != 1:
+            raise ValueError("output must be [batch, heads, 1, head_dim] in the query dtype on the query device with "
+                             "a contiguous last dimension")
+        out = output
     table_stride = 0 if table_dev is None else table_dev.stride(0)
     max_blocks = 0 if table_dev is None else int(table_dev.shape[1])
     max_len = max_blocks * pool.block_size + pool.residual_len
     stats, values, capacity, counters = split_scratch(device, batch, heads, dim, pool.kv_heads, max_len,
                                                       turboquant=(max_blocks, pool.block_size, pool.residual_len))
     frags = query_scratch(device, batch, heads, pool.kv_heads, dim)
+    common = (
+        ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
+        ptr(pool.window), ptr(slots_dev), ptr(lengths_dev), ptr(tables.signs1), ptr(tables.signs2),
+        ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
+        0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
+        capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads, pool.kv_heads, dim, pool.block_size,
+        pool.residual_len, pool.bits, pool.value_group, pool.capacity(), max_blocks, float(scaling),
+        dtype_code(query.dtype))
     with on_device(device):
-        _lib.check(_lib.lib().anna_tq_paged_decode(
-            ptr(query), query.stride(0), query.stride(1), ptr(pool.packed_pages), ptr(table_dev), table_stride,
-            ptr(pool.window), ptr(slots_dev), ptr(lengths_dev), ptr(tables.signs1), ptr(tables.signs2),
-            ptr(tables.centroids), ptr(gate), 0 if gate is None else gate.stride(0),
-            0 if gate is None else gate.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(stats), ptr(values),
-            capacity, 0, ptr(counters), ptr(frags), frags.numel(), batch, heads, pool.kv_heads, dim, pool.block_size,
-            pool.residual_len, pool.bits,
-            pool.value_group, pool.capacity(), max_blocks, float(scaling), dtype_code(query.dtype),
-            stream_ptr(device)), "anna_tq_paged_decode")
+        if peer_outputs:
+            import ctypes
+
+            peers = (ctypes.c_void_p * len(peer_outputs))(*peer_outputs)
+            _lib.check(_lib.lib().anna_tq_paged_decode_peers(*common, peers, len(peer_outputs), stream_ptr(device)),
+                       "anna_tq_paged_decode_peers")
+        else:
+            _lib.check(_lib.lib().anna_tq_paged_decode(*common, stream_ptr(device)), "anna_tq_paged_decode")
     return out
 
 

@@ -462,9 +462,10 @@ def run_cfg5_gpu(args, dist: Dist, device) -> dict:
 
 
 def run_kvhead_variant(args, dist: Dist, device) -> dict:
-    """TurboQuant 4-bit decode, all sequences on every rank, Hkv / N KV heads per rank, one all-gather of the outputs
-    per step.  Total work is fixed, so the scaling is "strong"."""
-    from anna_b200.sharding import HeadGather, shard_kv_heads
+    """TurboQuant 4-bit decode, all sequences on every rank, Hkv / N KV heads per rank; the outputs reach every rank by
+    peer stores from the decode kernel's merge epilogue plus one flag exchange (--gather peer, the default) or by one
+    NCCL all-gather (--gather nccl).  Total work is fixed, so the scaling is "strong"."""
+    from anna_b200.sharding import HeadGather, PeerHeadGather, shard_kv_heads
 
     q_heads, kv_heads, dim, page, bits, residual = 32, 8, 128, 16, 4, 128
     batch, context = args.kvhead_batch, args.kvhead_context
@@ -495,6 +496,9 @@ def run_kvhead_variant(args, dist: Dist, device) -> dict:
     part.release()
 
     cache = build(batch, context, slice(shard.kv_start, shard.kv_stop), 11, args.steps + args.warmup + 64)
+    peer = None
+    if dist.enabled and args.gather == "peer":
+        peer = PeerHeadGather(shard, batch=batch, q_heads=q_heads, head_dim=dim, dtype=torch.bfloat16, device=device)
     gen = torch.Generator(device=device).manual_seed(12)
     q = torch.randn(batch, q_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
     k1 = torch.randn(batch, kv_heads, 1, dim, device=device, dtype=torch.bfloat16, generator=gen)
@@ -503,9 +507,28 @@ def run_kvhead_variant(args, dist: Dist, device) -> dict:
 
     def step(_events=None):
         cache.update(k_local, v_local, 0, require_dense_cache=False)
+        if peer is not None:
+            local_out, peer_ptrs = peer.begin()
+            cache.turboquant_single_token_decode_attention(0, q_local, scaling=dim ** -0.5, num_key_value_groups=groups,
+                                                           output=local_out, peer_outputs=peer_ptrs)
+            return peer.finish()
         local = cache.turboquant_single_token_decode_attention(0, q_local, scaling=dim ** -0.5,
                                                                num_key_value_groups=groups)
         return gather(local)
+
+    if peer is not None:
+        # the peer-store path against the collective on the same cache state: every rank must see the same tensor
+        local = cache.turboquant_single_token_decode_attention(0, q_local, scaling=dim ** -0.5,
+                                                               num_key_value_groups=groups)
+        want_full = gather(local).clone()
+        local_out, peer_ptrs = peer.begin()
+        cache.turboquant_single_token_decode_attention(0, q_local, scaling=dim ** -0.5, num_key_value_groups=groups,
+                                                       output=local_out, peer_outputs=peer_ptrs)
+        got_full = peer.finish()
+        torch.cuda.synchronize(device)
+        peer.check()
+        if not torch.equal(got_full, want_full):
+            raise RuntimeError("peer-store gather disagrees with the all-gather of the same outputs")
 
     sampler = ClockSampler(device.index or 0, enabled=dist.rank == 0)
     sampler.start()
@@ -514,6 +537,8 @@ def run_kvhead_variant(args, dist: Dist, device) -> dict:
         out = step()
     step_ms = time_steps(step, None, args.steps, device, dist) / args.steps
     clocks = sampler.stop()
+    if peer is not None:
+        peer.check()
     key_bytes, value_bytes = packed_token_bytes(dim, bits)
     per_rank_bytes = batch * local_kv * ((context - residual) * (key_bytes + value_bytes) + residual * 2 * dim * 2)
     peak, peak_kind = measured_peak_gbs()
@@ -527,11 +552,14 @@ def run_kvhead_variant(args, dist: Dist, device) -> dict:
                    "q_heads": q_heads, "kv_heads": kv_heads, "head_dim": dim, "bits": bits, "context": context,
                    "page_size": page, "residual_len": residual, "append_per_step": 1,
                    "kv_heads_per_rank": local_kv, "q_heads_per_rank": local_q,
-                   "parallelism": f"kv-head-sharded x{dist.world}, one all-gather of [B, Hq/N, D] per step",
+                   "parallelism": f"kv-head-sharded x{dist.world}, " + (
+                       "outputs stored into every rank's [B, Hq, D] tensor by the decode kernel's merge epilogue "
+                       "(peer stores over NVLink) and one flag exchange per step" if peer is not None else
+                       "one all-gather of [B, Hq/N, D] per step"),
                    "l2_policy": f"{per_rank_bytes / 1e6:.0f} MB of packed KV per rank and step exceed the 126 MB L2"},
-        # per step: tq_append, tq_prepare_queries, tq_window_split_mma, tq_decode_split_mma (+ NCCL's all-gather and
-        # one strided copy, which are library kernels and not counted)
-        "gpu_launches": 4 * args.steps, "clocks": clocks,
+        # per step: tq_append, tq_prepare_queries, tq_window_split_mma, tq_decode_split_mma, and either the flag
+        # exchange kernel or NCCL's all-gather with one strided copy (library kernels, not counted)
+        "gpu_launches": (5 if peer is not None else 4) * args.steps, "clocks": clocks,
         "self_check": {"max_abs_vs_unsharded": check_err, "rows": check_rows, "context": check_tokens},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
@@ -949,8 +977,15 @@ def cpu_cfg5_row_step_seconds(rows: int, steps: int, seed: int) -> tuple[float, 
     spec = cfg5_spec()
     q_heads, kv_heads, dim = spec["q_heads"], spec["kv_heads"], spec["head_dim"]
     bits, residual, page, context = spec["bits"], spec["residual_len"], spec["page_size"], spec["context"]
-    threads = os.cpu_count() or 1
+    from threadpoolctl import threadpool_limits
+
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
+    # a launcher that exports OMP_NUM_THREADS=1 for its ranks must not turn this into a single-threaded baseline
+    blas_threads = threadpool_limits(limits=threads)
     rng = np.random.default_rng(seed)
     t0 = time.perf_counter()
     cpu_rows = []
@@ -976,7 +1011,9 @@ def cpu_cfg5_row_step_seconds(rows: int, steps: int, seed: int) -> tuple[float, 
     t0 = time.perf_counter()
     for _ in range(steps):
         one_step()
-    return (time.perf_counter() - t0) / (steps * rows), threads, prefill_s
+    elapsed = time.perf_counter() - t0
+    blas_threads.restore_original_limits()
+    return elapsed / (steps * rows), threads, prefill_s
 
 
 def cpu_line(rows: int, steps: int) -> dict:
@@ -1106,6 +1143,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extras", action="store_true", help="skip the other benchmark configurations")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--gather", choices=("peer", "nccl"), default="peer",
+                        help="KV-head variant: how the per-rank outputs reach every rank")
     parser.add_argument("--variant", choices=("sequence", "kvhead"), default="sequence",
                         help="sequence: sequences sharded over ranks (default, the headline); kvhead: the same decode "
                              "with KV heads sharded over ranks and an all-gather of the outputs")

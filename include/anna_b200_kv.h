@@ -32,6 +32,7 @@ extern "C" {
 
 /* bits of the device status word written by kernels (OR-ed in, never cleared by the library) */
 #define ANNA_DEV_BAD_PAGE 1u   /* a block-table entry needed by a write was < 0 or >= num_pages */
+#define ANNA_DEV_PEER_TIMEOUT 2u /* anna_peer_signal_wait gave up waiting for another rank's arrival flag */
 
 typedef void* anna_stream_t; /* cudaStream_t */
 
@@ -270,6 +271,39 @@ int anna_tq_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, 
                          int q_heads, int kv_heads, int head_dim, int block_size, int residual_len, int bits,
                          int value_group, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
                          anna_stream_t stream);
+
+/*
+ * KV-head-sharded form of anna_tq_paged_decode for the GPUs of one box: this rank decodes its own KV heads and the
+ * merge that finishes a (row, head group) stores the output row into `out` and, at the same element offset, into
+ * num_peers (0..7) peer tensors -- the output tensors of the other ranks, mapped into this process -- so that no
+ * all-gather follows.  `out` and the peer pointers address this rank's first query head inside [B, Hq_total, D]
+ * tensors of equal strides.  Needs the tensor-core path with the fused merge (16-bit cache, head_dim 128 / 256,
+ * split_counters given); otherwise ANNA_ERR_UNSUPPORTED.  The stores are plain peer stores over NVLink followed by a
+ * system-scope fence; readers on the other ranks synchronise through anna_peer_signal_wait.
+ * The reference is single-device and has no counterpart.
+ */
+int anna_tq_paged_decode_peers(const void* q, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* packed_pages,
+                               const int32_t* block_table, int64_t table_stride, const void* window,
+                               const int64_t* window_slots, const int64_t* lengths, const float* signs1,
+                               const float* signs2, const float* centroids, const void* gate, int64_t gate_stride_b,
+                               int64_t gate_stride_h, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                               float* partial_stats, float* partial_values, int chunk_capacity, int chunk_tokens,
+                               int32_t* split_counters, void* query_scratch, size_t query_scratch_bytes, int batch,
+                               int q_heads, int kv_heads, int head_dim, int block_size, int residual_len, int bits,
+                               int value_group, int64_t num_pages, int64_t max_blocks, float scaling, int dtype,
+                               void* const* peer_outputs, int num_peers, anna_stream_t stream);
+
+/*
+ * Arrival flags between the ranks of one box.  flag_arrays[r] (host array of `world` device pointers, 8-byte aligned)
+ * is rank r's array of `world` uint64 flags in memory every rank can write; entry [rank] is the caller's own.  One warp
+ * stores `step` into flag `rank` of every other rank (release, system scope: everything this stream wrote to peer
+ * memory before is visible first), then waits until the caller's own flags of all other ranks are >= step.  Steps
+ * are positive and must grow from call to call; flags start at 0.  After timeout_ms (1..60000) without the flags the kernel ORs
+ * ANNA_DEV_PEER_TIMEOUT into *status (optional device int32) and returns; the context stays usable.  world == 1
+ * launches nothing.  No counterpart in the reference.
+ */
+int anna_peer_signal_wait(void* const* flag_arrays, int rank, int world, int64_t step, int64_t timeout_ms,
+                          int32_t* status, anna_stream_t stream);
 
 /*
  * De-quantize the packed prefix of each row to dense [B, Hkv, Lq_max, D] keys and values in the cache dtype (element
