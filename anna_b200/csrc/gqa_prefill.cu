@@ -13,6 +13,7 @@
 //   O[16 x D]  += P . V            P re-packed from the C fragments (no shuffle), V by ldmatrix.trans
 // Key tiles above the causal diagonal of the CTA's last query row are never loaded.
 #include "mma_utils.cuh"
+#include "prefill_params.cuh"
 
 namespace anna {
 
@@ -40,20 +41,6 @@ __device__ __forceinline__ float ex2_fast(float x) {
 
 constexpr int kPrefillWarps = 4;
 constexpr int kPrefillThreads = kPrefillWarps * 32;
-
-struct PrefillParams {
-  const void* q;
-  const void* k;
-  const void* v;
-  void* out;
-  const int64_t* key_lengths;
-  int64_t q_stride_b, q_stride_h, q_stride_t;
-  int64_t kv_stride_b, kv_stride_h, kv_stride_t;
-  int64_t out_stride_b, out_stride_h, out_stride_t;
-  int q_len, groups, causal;
-  int64_t key_len;
-  float scale_log2;  // scaling * log2(e)
-};
 
 #ifndef ANNA_PREFILL_MT
 #define ANNA_PREFILL_MT 2
@@ -372,6 +359,7 @@ extern "C" int anna_gqa_prefill(const void* q, int64_t q_stride_b, int64_t q_str
   p.key_len = key_len;
   p.scale_log2 = scaling * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
+  if (prefill_umma_applicable(p, head_dim, dtype)) return launch_prefill_umma(p, batch, q_heads, dtype, s);
 #define ANNA_PREFILL_CASE(TYPE, DIM) \
   if (head_dim == DIM) return launch_prefill<TYPE, DIM>(p, batch, q_heads, s);
   if (dtype == ANNA_DTYPE_BF16) {

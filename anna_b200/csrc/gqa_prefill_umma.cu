@@ -1,0 +1,358 @@
+// Multi-token (prefill / chunked-prefill) grouped-query attention on the 5th-generation tensor cores: tcgen05.mma with
+// both accumulators in tensor memory.  head_dim 128, 16-bit dtypes; same semantics as gqa_prefill.cu
+// (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and :2008-2016).
+//
+// A CTA (8 warps, one SM) owns 128 query rows of one query head; threads t and t + 128 own row t (lane t of tensor
+// memory) and half of its score / output columns each.
+// Per tile of 128 keys:
+//   K / V tile --cp.async (2 stages each, K two tiles ahead, V one; zero-filled past the row's keys)--> shared memory,
+//                                canonical un-swizzled layout
+//   S[128 x 128] = Q . K^T       8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared memory, S in one of
+//                                two 128-column buffers of tensor memory, so the scores of tile t + 1 are computed while
+//                                the threads work on tile t; issued by thread 0, completion through tcgen05.commit
+//   softmax                      every thread reads its row of S into registers (tcgen05.ld): row maximum, exp2, row
+//                                sum; P goes to shared memory as the K-major A operand of the next product.  The running
+//                                maximum moves only when it would grow by more than 2^8, and only then is the row of O
+//                                rescaled in tensor memory (tcgen05.ld / st)
+//   O[128 x 128] += P . V        8 x tcgen05.mma, V MN-major (it is the same byte arrangement as a K-major tile: only
+//                                the descriptor's two strides swap roles), O in tensor memory columns 256..383
+// Key tiles above the causal diagonal of the CTA's last row are never loaded.  Every wait is bounded: when one expires
+// the CTA counts a fault, stops, and still frees its tensor memory.
+#include "mma_utils.cuh"
+#include "prefill_params.cuh"
+#include "umma_utils.cuh"
+
+#include <cstdlib>
+#include <type_traits>
+
+namespace anna {
+
+__device__ int32_t g_prefill_umma_faults;
+
+namespace {
+
+constexpr int kUpThreads = 256;  // two threads per query row: each owns half of the row's score and output columns
+constexpr int kUpRows = 128, kUpKeys = 128, kUpDim = 128;
+// canonical layout of a 128 x 128 16-bit tile: 16-byte chunk c of row r at c * kChunkStride + (r / 8) * 128 + (r % 8) * 16
+// (the 16 extra bytes per chunk plane spread a warp's 16-byte stores over the banks)
+constexpr uint32_t kGroupStride = 128;
+constexpr uint32_t kChunkStride = 16 * kGroupStride + 16;
+constexpr uint32_t kTileBytes = 16 * kChunkStride;
+constexpr uint32_t kOffQ = 0, kOffP = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 4 * kTileBytes;
+constexpr uint32_t kUpSmem = 6 * kTileBytes;  // Q | P | K0 K1 | V0 V1
+constexpr uint32_t kColS = 0, kColO = 256, kTmemCols = 512;  // two score buffers of 128 columns, then O
+constexpr float kLazyLog2 = 8.0f;
+
+__device__ __forceinline__ float up_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// rows [row0, row0 + 128) of a [*, 128] matrix with token stride `stride` -> canonical tile; rows >= limit are zeros.
+// A thread copies the same 16-byte chunk of every 16th row, so one source pointer and one destination offset step
+// through the tile.
+template <typename T>
+__device__ __forceinline__ void up_load_tile(uint32_t dst, const T* base, int64_t stride, int64_t row0, int64_t limit) {
+  constexpr int kRowsPerPass = kUpThreads / 16;
+  const int c = threadIdx.x & 15;
+  const int r0 = threadIdx.x >> 4;  // 0 .. kRowsPerPass - 1
+  const int64_t visible = limit - row0 - r0;  // rows r0 + kRowsPerPass * i with kRowsPerPass * i < visible exist
+  const T* src = base + (row0 + r0) * stride + c * 8;
+  const int64_t step = (int64_t)kRowsPerPass * stride;
+  uint32_t out = dst + c * kChunkStride + (r0 >> 3) * kGroupStride + (r0 & 7) * 16;
+#pragma unroll
+  for (int i = 0; i < kUpRows / kRowsPerPass; ++i) {
+    const bool ok = (int64_t)(kRowsPerPass * i) < visible;
+    cp_async16(out, ok ? src : base, ok ? 16 : 0);
+    src += step;
+    out += (kRowsPerPass / 8) * kGroupStride;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const PrefillParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long bar_storage[3];
+  __shared__ uint32_t tmem_slot;
+  __shared__ float row_exchange[2][kUpRows];  // row maxima (per tile) and row sums (at the end) of the two halves
+
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kUpRows;  // tiles with the most visible keys first
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int kvh = hq / p.groups;
+  const int warp = threadIdx.x >> 5;
+  const int r_local = threadIdx.x & (kUpRows - 1);  // query row inside the tile = lane of tensor memory
+  const int half = threadIdx.x >> 7;                // which 64 score / output columns of the row
+  const int row = m0 + r_local;
+  constexpr int kHalf = kUpKeys / 2;
+
+  int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
+  n_keys = max((int64_t)0, min(n_keys, p.key_len));
+  const int64_t past = n_keys - p.q_len;  // position of the chunk's first query
+  const int last_row = min(m0 + kUpRows, p.q_len) - 1;
+  int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
+  cta_limit = max(cta_limit, (int64_t)0);
+  const int n_tiles = (int)((cta_limit + kUpKeys - 1) / kUpKeys);
+  int64_t lim = 0;  // keys this thread's row sees
+  if (row < p.q_len) lim = max((int64_t)0, p.causal ? min(n_keys, past + row + 1) : n_keys);
+
+  const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + hq * p.q_stride_h;
+  const T* k_base = reinterpret_cast<const T*>(p.k) + b * p.kv_stride_b + kvh * p.kv_stride_h;
+  const T* v_base = reinterpret_cast<const T*>(p.v) + b * p.kv_stride_b + kvh * p.kv_stride_h;
+  T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + hq * p.out_stride_h + (int64_t)row * p.out_stride_t +
+               half * kHalf;
+
+  if (n_tiles == 0) {  // no row of this CTA sees a key: zeros (uniform over the CTA, nothing was allocated yet)
+    if (row < p.q_len)
+      for (int c = 0; c < kHalf / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+
+  const uint32_t smem = smem_u32(smem_raw);
+  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // bar_s0 + 8: the second score buffer
+  const uint32_t bar_o = smem_u32(&bar_storage[2]);
+  if (threadIdx.x == 0) {
+    mbar_init(bar_s0, 1);
+    mbar_init(bar_s0 + 8, 1);
+    mbar_init(bar_o, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
+
+  auto load_k = [&](int tile) {
+    if (tile < n_tiles)
+      up_load_tile<T>(smem + kOffK + (tile & 1) * kTileBytes, k_base, p.kv_stride_t, (int64_t)tile * kUpKeys, n_keys);
+    cp_async_commit();
+  };
+  auto load_v = [&](int tile) {
+    if (tile < n_tiles)
+      up_load_tile<T>(smem + kOffV + (tile & 1) * kTileBytes, v_base, p.kv_stride_t, (int64_t)tile * kUpKeys, n_keys);
+    cp_async_commit();
+  };
+  up_load_tile<T>(smem + kOffQ, q_base, p.q_stride_t, m0, p.q_len);
+  load_k(0);
+  load_v(0);
+  load_k(1);
+  cp_async_wait<0>();
+  fence_async_smem();
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  // this warp's quarter of the lanes (warps w and w + 4 share it), this thread's half of the columns
+  const uint32_t t_row = tmem_addr(tmem, 32 * (warp & 3), half * kHalf);
+
+  constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
+  constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
+  constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
+  // S(tile) = Q . K(tile)^T into score buffer tile & 1; issued by thread 0
+  auto issue_scores = [&](int tile) {
+    tcgen05_fence_after_sync();
+#pragma unroll
+    for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction = two 16-byte chunks
+      umma_f16(tmem + kColS + (tile & 1) * kUpKeys,
+               umma_smem_desc(smem + kOffQ + 2 * k * kChunkStride, kChunkStride, kGroupStride),
+               umma_smem_desc(smem + kOffK + (tile & 1) * kTileBytes + 2 * k * kChunkStride, kChunkStride, kGroupStride),
+               idesc_s, k > 0);
+    umma_commit(bar_s0 + (tile & 1) * 8);
+  };
+  if (threadIdx.x == 0) issue_scores(0);
+
+  float m_run = -INFINITY, l_run = 0.0f;  // l_run: this thread's half of the row sum
+  bool ok = true;
+  for (int it = 0; it < n_tiles; ++it) {
+    const int64_t key0 = (int64_t)it * kUpKeys + half * kHalf;  // first key of this thread's columns
+    // (a) S(it) is complete; its K stage is free for tile it + 2
+    ok = __syncthreads_and(mbar_wait(bar_s0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1)));
+    if (!ok) break;
+    tcgen05_fence_after_sync();
+    load_k(it + 2);
+
+    // (b) this thread's half row of S into registers (one round of loads, one wait), mask, local maximum
+    float s[kHalf];
+#pragma unroll
+    for (int c = 0; c < kHalf / 16; ++c) {
+      uint32_t r[16];
+      tmem_ld16(t_row + kColS + (it & 1) * kUpKeys + 16 * c, r);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s[16 * c + i] = __uint_as_float(r[i]);
+    }
+    tmem_wait_ld();
+    if (key0 + kHalf > lim) {
+#pragma unroll
+      for (int i = 0; i < kHalf; ++i)
+        if (key0 + i >= lim) s[i] = -INFINITY;
+    }
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < kHalf; i += 4) {
+      mx4[0] = fmaxf(mx4[0], s[i]);
+      mx4[1] = fmaxf(mx4[1], s[i + 1]);
+      mx4[2] = fmaxf(mx4[2], s[i + 2]);
+      mx4[3] = fmaxf(mx4[3], s[i + 3]);
+    }
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    row_exchange[half][r_local] = mx;
+
+    // (c) K(it + 1) has landed (everything but the newest copy group): the next scores run beside this softmax
+    cp_async_wait<1>();
+    fence_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && it + 1 < n_tiles) issue_scores(it + 1);
+
+    // (d) row maximum of both halves (log2 units), lazy running maximum -- the same decision in both threads of a row
+    mx = fmaxf(mx, row_exchange[half ^ 1][r_local]) * p.scale_log2;  // the scale is positive
+    const bool grew = mx > m_run + kLazyLog2;
+    const float m_new = grew ? mx : m_run;
+    const float alpha = grew ? up_ex2(m_run - m_new) : 1.0f;  // 0 while m_run is -inf
+    m_run = m_new;
+    l_run *= alpha;
+    const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+
+    // (e) P = exp2(S * scale - m) as 16-bit pairs, row sum
+    uint32_t packed[kHalf / 2];
+    float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < kHalf; i += 4) {
+      const float p0 = up_ex2(fmaf(s[i], p.scale_log2, -m_ref));  // exp2(-inf) = 0 for masked keys
+      const float p1 = up_ex2(fmaf(s[i + 1], p.scale_log2, -m_ref));
+      const float p2 = up_ex2(fmaf(s[i + 2], p.scale_log2, -m_ref));
+      const float p3 = up_ex2(fmaf(s[i + 3], p.scale_log2, -m_ref));
+      sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+      packed[i / 2] = pack2<T>(p0, p1);
+      packed[i / 2 + 1] = pack2<T>(p2, p3);
+    }
+    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+
+    // (f) the previous P . V is complete: O may be rescaled, P overwritten, its V stage refilled
+    if (it > 0) {
+      ok = __syncthreads_and(mbar_wait(bar_o, (uint32_t)((it - 1) & 1)));
+      if (!ok) break;
+      tcgen05_fence_after_sync();
+    }
+    load_v(it + 1);
+    if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide; this thread's half of the row of O
+#pragma unroll
+      for (int c = 0; c < kHalf / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(t_row + kColO + 16 * c, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st16(t_row + kColO + 16 * c, r);
+      }
+      tmem_wait_st();
+    }
+
+    // (g) P -> shared memory (K-major A operand), then O += P . V(it)
+    const uint32_t p_row = smem + kOffP + (half * (kHalf / 8)) * kChunkStride + (r_local >> 3) * kGroupStride +
+                           (r_local & 7) * 16;
+#pragma unroll
+    for (int c = 0; c < kHalf / 8; ++c)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kChunkStride), "r"(packed[4 * c]),
+                   "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
+                   : "memory");
+    // V(it) was committed before the newest two copy groups (K(it + 2), V(it + 1))
+    cp_async_wait<2>();
+    fence_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
+        umma_f16(tmem + kColO, umma_smem_desc(smem + kOffP + 2 * k * kChunkStride, kChunkStride, kGroupStride),
+                 umma_smem_desc(smem + kOffV + (it & 1) * kTileBytes + 2 * k * kGroupStride, kGroupStride, kChunkStride),
+                 idesc_o, (it > 0 || k > 0) ? 1u : 0u);
+      umma_commit(bar_o);
+    }
+  }
+  cp_async_wait<0>();
+  row_exchange[half][r_local] = l_run;
+  if (ok) {
+    ok = __syncthreads_and(mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1)));
+    tcgen05_fence_after_sync();
+  }
+  if (ok) {
+    const float l_row = l_run + row_exchange[half ^ 1][r_local];
+    const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+#pragma unroll
+    for (int c = 0; c < kHalf / 16; ++c) {
+      uint32_t r[16];
+      tmem_ld16(t_row + kColO + 16 * c, r);
+      tmem_wait_ld();
+      if (row < p.q_len) {
+        uint4 lo, hi;
+        lo.x = pack2<T>(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+        lo.y = pack2<T>(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+        lo.z = pack2<T>(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+        lo.w = pack2<T>(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+        hi.x = pack2<T>(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+        hi.y = pack2<T>(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+        hi.z = pack2<T>(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+        hi.w = pack2<T>(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+        reinterpret_cast<uint4*>(out_row)[2 * c] = lo;
+        reinterpret_cast<uint4*>(out_row)[2 * c + 1] = hi;
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    atomicAdd(&g_prefill_umma_faults, 1);
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, kTmemCols);
+}
+
+}  // namespace
+
+bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
+  static const bool disabled = [] {
+    const char* flag = std::getenv("ANNA_B200_PREFILL_UMMA");
+    return flag != nullptr && flag[0] == '0';
+  }();
+  if (disabled) return false;
+  if (head_dim != 128 || (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16)) return false;
+  // the output rows are written as 16-byte vectors
+  if (p.out_stride_b % 8 != 0 || p.out_stride_h % 8 != 0 || p.out_stride_t % 8 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return false;
+  return p.q_len >= 64;  // short chunks leave most of a 128-row tile empty: the mma.sync kernel serves them
+}
+
+template <typename T>
+static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
+  auto kernel = gqa_prefill_umma_kernel<T>;
+  static bool configured[64] = {};
+  int device = 0;
+  ANNA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !configured[device]) {
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUpSmem));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  dim3 grid((unsigned)((p.q_len + kUpRows - 1) / kUpRows), (unsigned)q_heads, (unsigned)batch);
+  kernel<<<grid, kUpThreads, kUpSmem, stream>>>(p);
+  return check_launch("gqa_prefill_umma_kernel");
+}
+
+int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int dtype, cudaStream_t stream) {
+  return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_t<__nv_bfloat16>(p, batch, q_heads, stream)
+                                  : launch_prefill_umma_t<__half>(p, batch, q_heads, stream);
+}
+
+int prefill_umma_faults(int* count) {
+  int32_t value = 0;
+  ANNA_CUDA_CHECK(cudaMemcpyFromSymbol(&value, g_prefill_umma_faults, sizeof(value)));
+  *count = (int)value;
+  return ANNA_OK;
+}
+
+}  // namespace anna

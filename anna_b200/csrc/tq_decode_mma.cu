@@ -19,6 +19,7 @@
 #include "dense_mma_body.cuh"
 #include "mbarrier_utils.cuh"
 #include "tq_common.cuh"
+#include "prefill_params.cuh"
 #include "tq_decode_params.cuh"
 
 #include <cstdlib>
@@ -1118,10 +1119,11 @@ extern "C" int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream) 
 // since the library was loaded (0 in a healthy run).  Synchronises the device.
 extern "C" int anna_kv_device_faults(int* count) {
   ANNA_REQUIRE(count != nullptr, "anna_kv_device_faults: null output pointer");
-  int mma = 0, umma = 0;
+  int mma = 0, umma = 0, prefill = 0;
   int rc = anna::tq_decode_mma_faults(&mma);
   if (rc == ANNA_OK) rc = anna::tq_decode_umma_faults(&umma);
+  if (rc == ANNA_OK) rc = anna::prefill_umma_faults(&prefill);
   if (rc != ANNA_OK) return rc;
-  *count = mma + umma;
+  *count = mma + umma + prefill;
   return ANNA_OK;
 }

@@ -42,6 +42,10 @@ def _oracle(q, k, v, lengths, causal):
     (torch.float16, 4, 4, 64, 33, 33, (33, 20), True),           # a row shorter than the chunk: queries without keys
     (torch.bfloat16, 6, 2, 128, 5, 90, (90, 64, 7), False),      # key padding only
     (torch.float32, 8, 2, 128, 16, 48, (48, 30), True),          # fp32 cache: row-by-row path through the decode kernel
+    # head_dim 128 with 64 or more queries runs on tcgen05 / tensor memory (128-key tiles)
+    (torch.float16, 8, 2, 128, 300, 900, (900, 411, 64), False),  # key padding only, a row shorter than one key tile
+    (torch.bfloat16, 4, 1, 128, 130, 130, (130, 70), True),       # a row shorter than the chunk: queries without keys
+    (torch.bfloat16, 8, 8, 128, 512, 3000, (3000, 1500), True),   # 24 key tiles: the running maximum moves, O is rescaled
 ])
 def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len, key_len, lengths, causal):
     gen = torch.Generator().manual_seed(heads * 1000 + q_len)
@@ -60,6 +64,23 @@ def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len,
     # the same call with the lengths given directly (no mask is read)
     again = grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=n, causal=causal)
     assert torch.equal(again, out)
+
+
+def test_tensor_memory_kernel_reported_no_expired_wait(cuda_device):
+    """Runs after the cases above in this file: none of the bounded waits of the copy-engine / tensor-memory kernels may
+    have run out."""
+    import ctypes
+
+    from anna_b200 import _lib
+
+    q = torch.randn(1, 4, 128, 128, device=cuda_device, dtype=torch.bfloat16)
+    k = torch.randn(1, 1, 256, 128, device=cuda_device, dtype=torch.bfloat16)
+    out = grouped_query_attention(q, k, k, scaling=128 ** -0.5, key_lengths=torch.tensor([256], device=cuda_device),
+                                  causal=True)
+    assert bool(torch.isfinite(out).all())
+    count = ctypes.c_int(-1)
+    _lib.check(_lib.lib().anna_kv_device_faults(ctypes.byref(count)), "anna_kv_device_faults")
+    assert count.value == 0
 
 
 @pytest.mark.parametrize("case", ["chunk", "full", "padding_only"])
