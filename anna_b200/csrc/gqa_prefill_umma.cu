@@ -2,20 +2,22 @@
 // both accumulators in tensor memory.  head_dim 128, 16-bit dtypes; same semantics as gqa_prefill.cu
 // (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and :2008-2016).
 //
-// A CTA (8 warps, one SM) owns 128 query rows of one query head; threads t and t + 128 own row t (lane t of tensor
-// memory) and half of its score / output columns each.
-// Per tile of 128 keys:
-//   K / V tile --cp.async (2 stages each, K two tiles ahead, V one; zero-filled past the row's keys)--> shared memory,
-//                                canonical un-swizzled layout
-//   S[128 x 128] = Q . K^T       8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared memory, S in one of
-//                                two 128-column buffers of tensor memory, so the scores of tile t + 1 are computed while
+// A CTA (16 warps, one per SM) owns 256 rows = two query tiles of 128 rows (one set of accumulators in tensor memory
+// each): consecutive query positions of the (up to 16) query heads that share one KV head, so that a K / V tile fetched
+// from L2 serves all of them (with 128 rows per K / V tile the copies from L2 bound the kernel at 3.3 TB/s); threads t and
+// t + 256 own row t (lane t & 127 of query tile t >> 7) and half of its score / output columns.
+// Per tile of 64 keys:
+//   K / V tile --cp.async (K two stages and two tiles ahead, V one stage; zero-filled past the row's keys)--> shared
+//                                memory, canonical un-swizzled layout
+//   S[128 x 64] = Q . K^T        8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared memory, S in one of
+//                                two 64-column buffers of tensor memory, so the scores of tile t + 1 are computed while
 //                                the threads work on tile t; issued by thread 0, completion through tcgen05.commit
 //   softmax                      every thread reads its row of S into registers (tcgen05.ld): row maximum, exp2, row
 //                                sum; P goes to shared memory as the K-major A operand of the next product.  The running
 //                                maximum moves only when it would grow by more than 2^8, and only then is the row of O
 //                                rescaled in tensor memory (tcgen05.ld / st)
-//   O[128 x 128] += P . V        8 x tcgen05.mma, V MN-major (it is the same byte arrangement as a K-major tile: only
-//                                the descriptor's two strides swap roles), O in tensor memory columns 256..383
+//   O[128 x 128] += P . V        4 x tcgen05.mma, V MN-major (it is the same byte arrangement as a K-major tile: only
+//                                the descriptor's two strides swap roles), O in tensor memory columns 128..255
 // Key tiles above the causal diagonal of the CTA's last row are never loaded.  Every wait is bounded: when one expires
 // the CTA counts a fault, stops, and still frees its tensor memory.
 #include "mma_utils.cuh"
@@ -31,16 +33,23 @@ __device__ int32_t g_prefill_umma_faults;
 
 namespace {
 
-constexpr int kUpThreads = 256;  // two threads per query row: each owns half of the row's score and output columns
-constexpr int kUpRows = 128, kUpKeys = 128, kUpDim = 128;
-// canonical layout of a 128 x 128 16-bit tile: 16-byte chunk c of row r at c * kChunkStride + (r / 8) * 128 + (r % 8) * 16
-// (the 16 extra bytes per chunk plane spread a warp's 16-byte stores over the banks)
+constexpr int kUpQTiles = 2;      // query tiles (128 rows = one accumulator in tensor memory each) per CTA
+constexpr int kUpRows = 128, kUpKeys = 64, kUpDim = 128;
+constexpr int kUpCtaRows = kUpQTiles * kUpRows;
+constexpr int kUpThreads = 2 * kUpCtaRows;  // two threads per query row: each owns half of its score / output columns
+// canonical layout of an R x 128 (or 128 x C) 16-bit tile: 16-byte chunk c of row r at
+// c * chunk_stride + (r / 8) * 128 + (r % 8) * 16, chunk_stride = (R / 8) * 128 + 16 (the 16 extra bytes per chunk
+// plane spread a warp's 16-byte stores over the banks)
 constexpr uint32_t kGroupStride = 128;
-constexpr uint32_t kChunkStride = 16 * kGroupStride + 16;
-constexpr uint32_t kTileBytes = 16 * kChunkStride;
-constexpr uint32_t kOffQ = 0, kOffP = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 4 * kTileBytes;
-constexpr uint32_t kUpSmem = 6 * kTileBytes;  // Q | P | K0 K1 | V0 V1
-constexpr uint32_t kColS = 0, kColO = 256, kTmemCols = 512;  // two score buffers of 128 columns, then O
+constexpr uint32_t kRowChunkStride = (kUpRows / 8) * kGroupStride + 16;  // tiles of 128 rows: Q, P
+constexpr uint32_t kKeyChunkStride = (kUpKeys / 8) * kGroupStride + 16;  // tiles of 64 keys: K, V
+constexpr uint32_t kQBytes = (kUpDim / 8) * kRowChunkStride;             // 128 rows x 16 chunks
+constexpr uint32_t kPBytes = (kUpKeys / 8) * kRowChunkStride;            // 128 rows x 8 chunks
+constexpr uint32_t kKvBytes = (kUpDim / 8) * kKeyChunkStride;            // 64 keys x 16 chunks
+constexpr uint32_t kOffQ = 0, kOffP = kUpQTiles * kQBytes, kOffK = kOffP + kUpQTiles * kPBytes, kOffV = kOffK + 2 * kKvBytes;
+constexpr uint32_t kUpSmem = kOffV + 2 * kKvBytes;  // Q0 Q1 | P0 P1 | K0 K1 | V0 V1
+// tensor memory per query tile: two score buffers of 64 columns, then O (128 columns)
+constexpr uint32_t kColS = 0, kColO = 2 * kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
 constexpr float kLazyLog2 = 8.0f;
 
 __device__ __forceinline__ float up_ex2(float x) {
@@ -57,24 +66,47 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
-// rows [row0, row0 + 128) of a [*, 128] matrix with token stride `stride` -> canonical tile; rows >= limit are zeros.
+// rows [row0, row0 + ROWS) of a [*, 128] matrix with token stride `stride` -> canonical tile; rows >= limit are zeros.
 // A thread copies the same 16-byte chunk of every 16th row, so one source pointer and one destination offset step
 // through the tile.
-template <typename T>
+template <typename T, int ROWS>
 __device__ __forceinline__ void up_load_tile(uint32_t dst, const T* base, int64_t stride, int64_t row0, int64_t limit) {
   constexpr int kRowsPerPass = kUpThreads / 16;
+  constexpr uint32_t kStride = (ROWS / 8) * kGroupStride + 16;
   const int c = threadIdx.x & 15;
   const int r0 = threadIdx.x >> 4;  // 0 .. kRowsPerPass - 1
   const int64_t visible = limit - row0 - r0;  // rows r0 + kRowsPerPass * i with kRowsPerPass * i < visible exist
   const T* src = base + (row0 + r0) * stride + c * 8;
   const int64_t step = (int64_t)kRowsPerPass * stride;
-  uint32_t out = dst + c * kChunkStride + (r0 >> 3) * kGroupStride + (r0 & 7) * 16;
+  uint32_t out = dst + c * kStride + (r0 >> 3) * kGroupStride + (r0 & 7) * 16;
 #pragma unroll
-  for (int i = 0; i < kUpRows / kRowsPerPass; ++i) {
+  for (int i = 0; i < ROWS / kRowsPerPass; ++i) {
     const bool ok = (int64_t)(kRowsPerPass * i) < visible;
     cp_async16(out, ok ? src : base, ok ? 16 : 0);
     src += step;
     out += (kRowsPerPass / 8) * kGroupStride;
+  }
+}
+
+// Largest power of two (at most 16) that divides the number of query heads per KV head.
+__host__ __device__ inline int head_shift_of(int groups) {
+  int shift = 0;
+  while (shift < 4 && groups % (2 << shift) == 0) ++shift;
+  return shift;
+}
+
+// The query tile: row r is position m0 + (r >> head_shift) of head r & ((1 << head_shift) - 1) (relative to `base`).
+template <typename T>
+__device__ __forceinline__ void up_load_queries(uint32_t dst, const T* base, int64_t stride_h, int64_t stride_t, int m0,
+                                                int q_len, int head_shift) {
+  const int c = threadIdx.x & 15;
+  for (int r = threadIdx.x >> 4; r < kUpCtaRows; r += kUpThreads / 16) {
+    const int pos = m0 + (r >> head_shift);
+    const int head = r & ((1 << head_shift) - 1);
+    const bool ok = pos < q_len;
+    const T* src = base + (ok ? head * stride_h + pos * stride_t + c * 8 : 0);
+    cp_async16(dst + (r >> 7) * kQBytes + c * kRowChunkStride + ((r & 127) >> 3) * kGroupStride + (r & 7) * 16, src,
+               ok ? 16 : 0);
   }
 }
 
@@ -83,37 +115,46 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) unsigned long long bar_storage[3];
   __shared__ uint32_t tmem_slot;
-  __shared__ float row_exchange[2][kUpRows];  // row maxima (per tile) and row sums (at the end) of the two halves
+  __shared__ float row_exchange[2][kUpCtaRows];  // row maxima (per tile) and row sums (at the end) of the two halves
 
-  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kUpRows;  // tiles with the most visible keys first
-  const int hq = blockIdx.y;
+  // The 128 rows of the CTA are 128 >> head_shift consecutive query positions of 1 << head_shift query heads that share
+  // one KV head (row r = position r >> head_shift, head r & mask), so a K / V tile read from L2 serves all of them.
+  const int head_shift = head_shift_of(p.groups);
+  const int heads_here = 1 << head_shift;
+  const int positions = kUpCtaRows >> head_shift;
+  const int head_sets = p.groups >> head_shift;
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * positions;  // tiles with the most visible keys first
+  const int kvh = blockIdx.y / head_sets;
+  const int hq0 = kvh * p.groups + (blockIdx.y % head_sets) * heads_here;
   const int b = blockIdx.z;
-  const int kvh = hq / p.groups;
   const int warp = threadIdx.x >> 5;
-  const int r_local = threadIdx.x & (kUpRows - 1);  // query row inside the tile = lane of tensor memory
-  const int half = threadIdx.x >> 7;                // which 64 score / output columns of the row
-  const int row = m0 + r_local;
-  constexpr int kHalf = kUpKeys / 2;
+  const int r_local = threadIdx.x & (kUpCtaRows - 1);  // row of the CTA; lane r_local & 127 of query tile r_local >> 7
+  const int half = threadIdx.x / kUpCtaRows;           // which half of the row's score / output columns
+  const int qtile = r_local >> 7;
+  const int row = m0 + (r_local >> head_shift);     // query position of this thread's row
+  const int hq = hq0 + (r_local & (heads_here - 1));
+  constexpr int kHalf = kUpKeys / 2;   // score columns per thread
+  constexpr int kOutHalf = kUpDim / 2;  // output columns per thread
 
   int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
   n_keys = max((int64_t)0, min(n_keys, p.key_len));
   const int64_t past = n_keys - p.q_len;  // position of the chunk's first query
-  const int last_row = min(m0 + kUpRows, p.q_len) - 1;
+  const int last_row = min(m0 + positions, p.q_len) - 1;
   int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
   cta_limit = max(cta_limit, (int64_t)0);
   const int n_tiles = (int)((cta_limit + kUpKeys - 1) / kUpKeys);
   int64_t lim = 0;  // keys this thread's row sees
   if (row < p.q_len) lim = max((int64_t)0, p.causal ? min(n_keys, past + row + 1) : n_keys);
 
-  const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + hq * p.q_stride_h;
+  const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + (int64_t)hq0 * p.q_stride_h;
   const T* k_base = reinterpret_cast<const T*>(p.k) + b * p.kv_stride_b + kvh * p.kv_stride_h;
   const T* v_base = reinterpret_cast<const T*>(p.v) + b * p.kv_stride_b + kvh * p.kv_stride_h;
-  T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + hq * p.out_stride_h + (int64_t)row * p.out_stride_t +
-               half * kHalf;
+  T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + (int64_t)hq * p.out_stride_h +
+               (int64_t)row * p.out_stride_t + half * kOutHalf;
 
   if (n_tiles == 0) {  // no row of this CTA sees a key: zeros (uniform over the CTA, nothing was allocated yet)
     if (row < p.q_len)
-      for (int c = 0; c < kHalf / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+      for (int c = 0; c < kOutHalf / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
     return;
   }
 
@@ -128,17 +169,19 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   }
   if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
 
-  auto load_k = [&](int tile) {
+  auto load_k = [&](int tile) {  // two stages
     if (tile < n_tiles)
-      up_load_tile<T>(smem + kOffK + (tile & 1) * kTileBytes, k_base, p.kv_stride_t, (int64_t)tile * kUpKeys, n_keys);
+      up_load_tile<T, kUpKeys>(smem + kOffK + (tile & 1) * kKvBytes, k_base, p.kv_stride_t, (int64_t)tile * kUpKeys,
+                               n_keys);
     cp_async_commit();
   };
-  auto load_v = [&](int tile) {
+  auto load_v = [&](int tile) {  // two stages
     if (tile < n_tiles)
-      up_load_tile<T>(smem + kOffV + (tile & 1) * kTileBytes, v_base, p.kv_stride_t, (int64_t)tile * kUpKeys, n_keys);
+      up_load_tile<T, kUpKeys>(smem + kOffV + (tile & 1) * kKvBytes, v_base, p.kv_stride_t, (int64_t)tile * kUpKeys,
+                               n_keys);
     cp_async_commit();
   };
-  up_load_tile<T>(smem + kOffQ, q_base, p.q_stride_t, m0, p.q_len);
+  up_load_queries<T>(smem + kOffQ, q_base, p.q_stride_h, p.q_stride_t, m0, p.q_len, head_shift);
   load_k(0);
   load_v(0);
   load_k(1);
@@ -148,8 +191,10 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  // this warp's quarter of the lanes (warps w and w + 4 share it), this thread's half of the columns
-  const uint32_t t_row = tmem_addr(tmem, 32 * (warp & 3), half * kHalf);
+  // this warp's quarter of the lanes (warps w and w + 4 share it); this thread's half of the score / output columns
+  const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
+  const uint32_t t_s = t_lane + kColS + half * kHalf;
+  const uint32_t t_o = t_lane + kColO + half * kOutHalf;
 
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
   constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
@@ -158,11 +203,14 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   auto issue_scores = [&](int tile) {
     tcgen05_fence_after_sync();
 #pragma unroll
-    for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction = two 16-byte chunks
-      umma_f16(tmem + kColS + (tile & 1) * kUpKeys,
-               umma_smem_desc(smem + kOffQ + 2 * k * kChunkStride, kChunkStride, kGroupStride),
-               umma_smem_desc(smem + kOffK + (tile & 1) * kTileBytes + 2 * k * kChunkStride, kChunkStride, kGroupStride),
-               idesc_s, k > 0);
+    for (int qt = 0; qt < kUpQTiles; ++qt)
+#pragma unroll
+      for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction = two 16-byte chunks
+        umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
+                 umma_smem_desc(smem + kOffQ + qt * kQBytes + 2 * k * kRowChunkStride, kRowChunkStride, kGroupStride),
+                 umma_smem_desc(smem + kOffK + (tile & 1) * kKvBytes + 2 * k * kKeyChunkStride, kKeyChunkStride,
+                                kGroupStride),
+                 idesc_s, k > 0);
     umma_commit(bar_s0 + (tile & 1) * 8);
   };
   if (threadIdx.x == 0) issue_scores(0);
@@ -171,18 +219,22 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   bool ok = true;
   for (int it = 0; it < n_tiles; ++it) {
     const int64_t key0 = (int64_t)it * kUpKeys + half * kHalf;  // first key of this thread's columns
-    // (a) S(it) is complete; its K stage is free for tile it + 2
-    ok = __syncthreads_and(mbar_wait(bar_s0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1)));
+    // (a) S(it) and the previous P . V are complete: the K stage of tile it is free for tile it + 2, the V stage of
+    // tile it - 1 for tile it + 1, P may be overwritten and O rescaled
+    bool landed = mbar_wait(bar_s0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1));
+    if (it > 0) landed = mbar_wait(bar_o, (uint32_t)((it - 1) & 1)) && landed;
+    ok = __syncthreads_and(landed);
     if (!ok) break;
     tcgen05_fence_after_sync();
     load_k(it + 2);
+    load_v(it + 1);
 
     // (b) this thread's half row of S into registers (one round of loads, one wait), mask, local maximum
     float s[kHalf];
 #pragma unroll
     for (int c = 0; c < kHalf / 16; ++c) {
       uint32_t r[16];
-      tmem_ld16(t_row + kColS + (it & 1) * kUpKeys + 16 * c, r);
+      tmem_ld16(t_s + (it & 1) * kUpKeys + 16 * c, r);
 #pragma unroll
       for (int i = 0; i < 16; ++i) s[16 * c + i] = __uint_as_float(r[i]);
     }
@@ -203,8 +255,8 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     row_exchange[half][r_local] = mx;
 
-    // (c) K(it + 1) has landed (everything but the newest copy group): the next scores run beside this softmax
-    cp_async_wait<1>();
+    // (c) K(it + 1) has landed (everything but the newest two copy groups): the next scores run beside this softmax
+    cp_async_wait<2>();
     fence_async_smem();
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -234,32 +286,26 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     }
     l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
-    // (f) the previous P . V is complete: O may be rescaled, P overwritten, its V stage refilled
-    if (it > 0) {
-      ok = __syncthreads_and(mbar_wait(bar_o, (uint32_t)((it - 1) & 1)));
-      if (!ok) break;
-      tcgen05_fence_after_sync();
-    }
-    load_v(it + 1);
-    if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide; this thread's half of the row of O
+    // (f) rescale this thread's half of the row of O when the running maximum moved
+    if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
 #pragma unroll
-      for (int c = 0; c < kHalf / 16; ++c) {
+      for (int c = 0; c < kOutHalf / 16; ++c) {
         uint32_t r[16];
-        tmem_ld16(t_row + kColO + 16 * c, r);
+        tmem_ld16(t_o + 16 * c, r);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st16(t_row + kColO + 16 * c, r);
+        tmem_st16(t_o + 16 * c, r);
       }
       tmem_wait_st();
     }
 
     // (g) P -> shared memory (K-major A operand), then O += P . V(it)
-    const uint32_t p_row = smem + kOffP + (half * (kHalf / 8)) * kChunkStride + (r_local >> 3) * kGroupStride +
-                           (r_local & 7) * 16;
+    const uint32_t p_row = smem + kOffP + qtile * kPBytes + (half * (kHalf / 8)) * kRowChunkStride +
+                           ((r_local & 127) >> 3) * kGroupStride + (r_local & 7) * 16;
 #pragma unroll
     for (int c = 0; c < kHalf / 8; ++c)
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kChunkStride), "r"(packed[4 * c]),
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kRowChunkStride), "r"(packed[4 * c]),
                    "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
                    : "memory");
     // V(it) was committed before the newest two copy groups (K(it + 2), V(it + 1))
@@ -270,10 +316,14 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     if (threadIdx.x == 0) {
       tcgen05_fence_after_sync();
 #pragma unroll
-      for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
-        umma_f16(tmem + kColO, umma_smem_desc(smem + kOffP + 2 * k * kChunkStride, kChunkStride, kGroupStride),
-                 umma_smem_desc(smem + kOffV + (it & 1) * kTileBytes + 2 * k * kGroupStride, kGroupStride, kChunkStride),
-                 idesc_o, (it > 0 || k > 0) ? 1u : 0u);
+      for (int qt = 0; qt < kUpQTiles; ++qt)
+#pragma unroll
+        for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
+          umma_f16(tmem + qt * kColsPerQTile + kColO,
+                   umma_smem_desc(smem + kOffP + qt * kPBytes + 2 * k * kRowChunkStride, kRowChunkStride, kGroupStride),
+                   umma_smem_desc(smem + kOffV + (it & 1) * kKvBytes + 2 * k * kGroupStride, kGroupStride,
+                                  kKeyChunkStride),
+                   idesc_o, (it > 0 || k > 0) ? 1u : 0u);
       umma_commit(bar_o);
     }
   }
@@ -287,9 +337,9 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     const float l_row = l_run + row_exchange[half ^ 1][r_local];
     const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
 #pragma unroll
-    for (int c = 0; c < kHalf / 16; ++c) {
+    for (int c = 0; c < kOutHalf / 16; ++c) {
       uint32_t r[16];
-      tmem_ld16(t_row + kColO + 16 * c, r);
+      tmem_ld16(t_o + 16 * c, r);
       tmem_wait_ld();
       if (row < p.q_len) {
         uint4 lo, hi;
@@ -338,7 +388,9 @@ static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads,
     ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUpSmem));
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  dim3 grid((unsigned)((p.q_len + kUpRows - 1) / kUpRows), (unsigned)q_heads, (unsigned)batch);
+  const int head_shift = head_shift_of(p.groups);
+  const int positions = kUpCtaRows >> head_shift;
+  dim3 grid((unsigned)((p.q_len + positions - 1) / positions), (unsigned)(q_heads >> head_shift), (unsigned)batch);
   kernel<<<grid, kUpThreads, kUpSmem, stream>>>(p);
   return check_launch("gqa_prefill_umma_kernel");
 }

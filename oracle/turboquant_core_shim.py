@@ -67,13 +67,10 @@ class TurboQuantIP:
         idx = mse_indices.detach().cpu().numpy().astype(np.uint8).reshape(-1, self.dim)
         sign = qjl_signs.detach().cpu().numpy().astype(np.uint8).reshape(-1, self.dim)
         rn = residual_norms.detach().float().cpu().numpy().reshape(-1)
-        if not sign.any() and not rn.any():
-            # turboquant.py:318-320 asks for the MSE-only reconstruction by zeroing signs and residual norms
-            out = oracle.dequantize_keys(idx, None, norms.detach().float().cpu().numpy().reshape(-1), None,
-                                         self.bits, "ip")
-        else:
-            out = oracle.dequantize_keys(idx, sign, norms.detach().float().cpu().numpy().reshape(-1), rn, self.bits,
-                                         "ip")
+        # turboquant.py:318-320 asks for the index-only reconstruction by zeroing signs and residual norms: a zero
+        # residual norm removes the sign term whatever the signs are, so no case analysis on the values is needed
+        # (tests/test_quantizer_properties.py checks that both forms agree bit for bit)
+        out = oracle.dequantize_keys(idx, sign, norms.detach().float().cpu().numpy().reshape(-1), rn, self.bits, "ip")
         return torch.from_numpy(out).reshape(shape).to(self.device)
 
 
