@@ -199,18 +199,24 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
   constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
   constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
+  // Descriptors of the first 16-wide K step of every operand; a later step, stage or query tile is the same descriptor
+  // with its byte offset (in 16-byte units) added to the address field, so the issuing thread spends two additions per
+  // instruction instead of rebuilding descriptors.
+  const uint64_t desc_q = umma_smem_desc(smem + kOffQ, kRowChunkStride, kGroupStride);
+  const uint64_t desc_k = umma_smem_desc(smem + kOffK, kKeyChunkStride, kGroupStride);
+  const uint64_t desc_p = umma_smem_desc(smem + kOffP, kRowChunkStride, kGroupStride);
+  const uint64_t desc_v = umma_smem_desc(smem + kOffV, kGroupStride, kKeyChunkStride);
   // S(tile) = Q . K(tile)^T into score buffer tile & 1; issued by thread 0
   auto issue_scores = [&](int tile) {
     tcgen05_fence_after_sync();
+    const uint64_t k0 = desc_k + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
     for (int qt = 0; qt < kUpQTiles; ++qt)
 #pragma unroll
       for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction = two 16-byte chunks
         umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
-                 umma_smem_desc(smem + kOffQ + qt * kQBytes + 2 * k * kRowChunkStride, kRowChunkStride, kGroupStride),
-                 umma_smem_desc(smem + kOffK + (tile & 1) * kKvBytes + 2 * k * kKeyChunkStride, kKeyChunkStride,
-                                kGroupStride),
-                 idesc_s, k > 0);
+                 desc_q + (uint64_t)((qt * kQBytes + 2 * k * kRowChunkStride) >> 4),
+                 k0 + (uint64_t)((2 * k * kKeyChunkStride) >> 4), idesc_s, k > 0);
     umma_commit(bar_s0 + (tile & 1) * 8);
   };
   if (threadIdx.x == 0) issue_scores(0);
@@ -315,15 +321,13 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     __syncthreads();
     if (threadIdx.x == 0) {
       tcgen05_fence_after_sync();
+      const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);
 #pragma unroll
       for (int qt = 0; qt < kUpQTiles; ++qt)
 #pragma unroll
         for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
-          umma_f16(tmem + qt * kColsPerQTile + kColO,
-                   umma_smem_desc(smem + kOffP + qt * kPBytes + 2 * k * kRowChunkStride, kRowChunkStride, kGroupStride),
-                   umma_smem_desc(smem + kOffV + (it & 1) * kKvBytes + 2 * k * kGroupStride, kGroupStride,
-                                  kKeyChunkStride),
-                   idesc_o, (it > 0 || k > 0) ? 1u : 0u);
+          umma_f16(tmem + qt * kColsPerQTile + kColO, desc_p + (uint64_t)((qt * kPBytes + 2 * k * kRowChunkStride) >> 4),
+                   v0 + (uint64_t)((2 * k * kGroupStride) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
       umma_commit(bar_o);
     }
   }
