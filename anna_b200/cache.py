@@ -57,6 +57,7 @@ class Qwen3PageAllocator:
                 self.block_size,
                 on_page_freed=lambda pid, li=layer_idx: self.prefix_block_pool.discard_page(li, pid),
                 on_trim=lambda li=layer_idx: self.prefix_block_pool.clear_layer(li),
+                listening=lambda: len(self.prefix_block_pool) > 0,
             )
             for layer_idx in range(config.num_hidden_layers)
         ]
@@ -65,7 +66,8 @@ class Qwen3PageAllocator:
         self.turboquant_layers = [
             TurboQuantLayerPool(
                 self.block_size,
-                on_page_freed=lambda pid, li=layer_idx: self.packed_prefix_block_pool.discard_page(li, pid))
+                on_page_freed=lambda pid, li=layer_idx: self.packed_prefix_block_pool.discard_page(li, pid),
+                listening=lambda: len(self.packed_prefix_block_pool) > 0)
             for layer_idx in range(config.num_hidden_layers)
         ]
         # The reference keeps a contiguous dense mirror of full-attention layers by default; this build gathers the
@@ -317,9 +319,11 @@ class Qwen3DynamicCache:
             capacity = max(required, max(1, self.page_table_capacities[layer_idx] * 2))
             # host mirror of the device table; a full build goes up through the pinned staging ring in one copy
             host = np.full((batch_size, capacity), -1, dtype=np.int32)
+            tq_rows = self.turboquant_rows[layer_idx] if self.uses_turboquant_for_layer(layer_idx) else None
             for row_idx, table in enumerate(tables):
                 if table:
-                    host[row_idx, : len(table)] = table
+                    row = None if tq_rows is None else tq_rows[row_idx]
+                    host[row_idx, : len(table)] = table if row is None else row.table_array()
             if device.type == "cuda":
                 buffer = MetadataUploader.for_device(device).upload_i32(host.reshape(-1)).view(batch_size, capacity)
             else:  # host-side bookkeeping of a cache that holds no device memory

@@ -22,10 +22,13 @@ def resolve_value_group_size(head_dim: int) -> int:
 
 
 class _PageBook:
-    def __init__(self, on_page_freed: Callable[[int], None] | None = None) -> None:
+    def __init__(self, on_page_freed: Callable[[int], None] | None = None,
+                 listening: Callable[[], bool] | None = None) -> None:
         self.free_pages: list[int] = []
         self.refcount: dict[int, int] = {}
         self._on_page_freed = on_page_freed
+        self._listening = listening  # optional: False while the callback has nothing to do (an empty registry)
+        self._shared = 0  # pages with more than one owner
 
     def take(self, num_pages: int, capacity: int) -> tuple[list[int], int, list[int]]:
         """Pop up to num_pages from the free list; returns (page ids, new capacity, ids created by growth)."""
@@ -64,7 +67,10 @@ class _PageBook:
         return new_capacity
 
     def retain(self, page_id: int) -> None:
-        self.refcount[page_id] = self.refcount.get(page_id, 0) + 1
+        rc = self.refcount.get(page_id, 0)
+        self.refcount[page_id] = rc + 1
+        if rc == 1:
+            self._shared += 1
 
     def release(self, page_id: int) -> None:
         rc = self.refcount.get(page_id, 0)
@@ -77,27 +83,40 @@ class _PageBook:
                 self._on_page_freed(page_id)
         else:
             self.refcount[page_id] = rc - 1
+            if rc == 2:
+                self._shared -= 1
 
-    def release_many(self, page_ids) -> None:
-        """release() for every id of `page_ids`, in the given order, in one pass."""
+    def release_many(self, page_ids, *, notify: bool = True) -> None:
+        """release() for every id of `page_ids`, in the given order, in one pass.  `notify=False` skips the per-page
+        callback (for callers that know nobody listens, e.g. an empty prefix registry)."""
         refcount = self.refcount
-        freed: list[int] = []
-        for page_id in page_ids:
-            rc = refcount.get(page_id, 0)
-            if rc == 1:
-                del refcount[page_id]
-                freed.append(page_id)
-            elif rc > 1:
-                refcount[page_id] = rc - 1
+        ids = page_ids if isinstance(page_ids, list) else list(page_ids)
+        if self._shared == 0 and refcount.keys() >= set(ids) and len(set(ids)) == len(ids):
+            # nothing is shared and every id is held exactly once: all of them become free, at C speed
+            for _ in map(refcount.__delitem__, ids):
+                pass
+            freed = ids
+        else:
+            freed = []
+            for page_id in ids:
+                rc = refcount.get(page_id, 0)
+                if rc == 1:
+                    del refcount[page_id]
+                    freed.append(page_id)
+                elif rc > 1:
+                    refcount[page_id] = rc - 1
+                    if rc == 2:
+                        self._shared -= 1
         if freed:
             self.free_pages.extend(freed)
-            if self._on_page_freed is not None:
+            if notify and self._on_page_freed is not None and (self._listening is None or self._listening()):
                 for page_id in freed:
                     self._on_page_freed(page_id)
 
     def clear(self) -> None:
         self.free_pages.clear()
         self.refcount.clear()
+        self._shared = 0
 
 
 def _grown(old: torch.Tensor | None, shape: tuple[int, ...], like: torch.Tensor, dtype: torch.dtype | None = None):
@@ -111,10 +130,10 @@ class Qwen3PagedLayerAllocator:
     """Un-quantized page pool of one layer: ``key_pages`` / ``value_pages`` ``[P, Hkv, S, D]`` (ops.py:92-245)."""
 
     def __init__(self, block_size: int, *, on_page_freed: Callable[[int], None] | None = None,
-                 on_trim: Callable[[], None] | None = None) -> None:
+                 on_trim: Callable[[], None] | None = None, listening: Callable[[], bool] | None = None) -> None:
         self.block_size = block_size
         self._on_trim = on_trim
-        self._book = _PageBook(on_page_freed)
+        self._book = _PageBook(on_page_freed, listening)
         self.key_pages: torch.Tensor | None = None
         self.value_pages: torch.Tensor | None = None
 
@@ -191,9 +210,10 @@ class Qwen3PagedLayerAllocator:
 class TurboQuantLayerPool:
     """Packed page pool + window rings of one TurboQuant layer (geometry fixed by the first append)."""
 
-    def __init__(self, block_size: int, *, on_page_freed: Callable[[int], None] | None = None) -> None:
+    def __init__(self, block_size: int, *, on_page_freed: Callable[[int], None] | None = None,
+                 listening: Callable[[], bool] | None = None) -> None:
         self.block_size = int(block_size)
-        self._book = _PageBook(on_page_freed)
+        self._book = _PageBook(on_page_freed, listening)
         self.packed_pages: torch.Tensor | None = None  # uint8 [P, Hkv, chunk_bytes]
         self.window: torch.Tensor | None = None        # dtype [slots, 2, Hkv, R, D]
         self.free_slots: list[int] = []

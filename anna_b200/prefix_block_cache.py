@@ -21,6 +21,9 @@ class PrefixBlockPool:
         self._page_of: dict[BlockKey, int] = {}
         self._keys_of: dict[tuple[int, int], set[BlockKey]] = {}
 
+    def __len__(self) -> int:
+        return len(self._page_of)
+
     def lookup(self, layer_idx: int, token_block: tuple[int, ...]) -> int | None:
         return self._page_of.get((layer_idx, token_block))
 

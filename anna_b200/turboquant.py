@@ -331,6 +331,8 @@ class TurboQuantKVRow:
         self.pool: TurboQuantLayerPool | None = None
         self.slot = -1
         self.block_table: list[int] = []
+        self._table_np = None   # int32 mirror of block_table (see table_array)
+        self._table_np_valid = 0
         self._length = 0
         self._privatized_block: int | None = None  # block whose page id changed by copy on write (see _reserve_blocks)
 
@@ -380,6 +382,7 @@ class TurboQuantKVRow:
         assert pool.packed_pages is not None
         pool.packed_pages[private].copy_(pool.packed_pages[shared])
         self.block_table[blk] = private
+        self._table_np_valid = min(self._table_np_valid, blk)
         pool.release_pages([shared])
         self._privatized_block = blk
 
@@ -391,6 +394,25 @@ class TurboQuantKVRow:
         need = (quantized + self.pool.block_size - 1) // self.pool.block_size
         if need > len(self.block_table):
             self.block_table.extend(self.pool.allocate(need - len(self.block_table)))
+
+    def table_array(self):
+        """``block_table`` as an int32 numpy array.  The array is kept between calls and only entries added (or
+        replaced by copy on write) since the last call are converted, so rebuilding the device table of a re-stacked
+        batch costs a memory copy per row instead of a list conversion."""
+        import numpy as np
+
+        n = len(self.block_table)
+        arr = self._table_np
+        valid = min(self._table_np_valid, n)
+        if arr is None or arr.shape[0] < n:
+            grown = np.empty(max(n, 16, 0 if arr is None else 2 * arr.shape[0]), dtype=np.int32)
+            if valid:
+                grown[:valid] = arr[:valid]
+            arr = self._table_np = grown
+        if valid < n:
+            arr[valid:n] = self.block_table[valid:n]
+        self._table_np_valid = n
+        return arr[:n]
 
     def _table_on_device(self) -> torch.Tensor | None:
         if not self.block_table:
@@ -492,6 +514,7 @@ class TurboQuantKVRow:
             self.pool.release_pages(self.block_table)
             self.pool.release_slot(self.slot)
         self.block_table = []
+        self._table_np_valid = 0
         self.slot = -1
         self._length = 0
 

@@ -382,3 +382,52 @@ def test_turboquant_clone_shares_packed_pages_until_the_partial_block_is_written
     assert [list(row.block_table) for row in source.turboquant_rows[0]] == tables
     clone.release()
     assert pool.used_pages() == 4 and all(pool.page_owners(pid) == 1 for t in tables for pid in t)
+
+
+def test_one_pass_release_equals_page_by_page_release():
+    """release_many (both its all-private fast path and its general path) leaves the free list, the owner counts and
+    the callbacks exactly as releasing the pages one by one does (ops.py:214-233 semantics: unknown ids are ignored,
+    a shared page only loses an owner)."""
+    import random
+
+    from anna_b200.pools import _PageBook
+
+    rng = random.Random(3)
+    for case in range(40):
+        freed_a: list[int] = []
+        freed_b: list[int] = []
+        a, b = _PageBook(freed_a.append), _PageBook(freed_b.append)
+        for book in (a, b):
+            book.take(64, 0)
+        shared = rng.sample(range(64), rng.choice([0, 0, 3, 10]))
+        for page in shared:
+            a.retain(page)
+            b.retain(page)
+        for _ in range(4):
+            ids = rng.sample(range(80), rng.randint(1, 40))  # ids above 63 were never handed out
+            if rng.random() < 0.3:
+                ids = ids + ids[:2]                           # a page named twice in one call
+            a.release_many(list(ids))
+            for page in ids:
+                b.release(page)
+            assert a.free_pages == b.free_pages and a.refcount == b.refcount and freed_a == freed_b, case
+            assert a._shared == sum(1 for rc in a.refcount.values() if rc > 1)
+
+
+def test_block_table_array_follows_the_list():
+    """TurboQuantKVRow.table_array(): an int32 mirror that converts only what changed since the last call."""
+    from anna_b200.turboquant import TurboQuantKVRow
+
+    row = TurboQuantKVRow(bits=4, residual_len=8)
+    assert row.table_array().tolist() == []
+    row.block_table.extend([5, 9, 2])
+    assert row.table_array().tolist() == [5, 9, 2] and row.table_array().dtype == np.int32
+    row.block_table.extend(range(100, 140))                      # grows past the first allocation
+    assert row.table_array().tolist() == row.block_table
+    row.block_table[1] = 77                                      # what copy on write does ...
+    row._table_np_valid = min(row._table_np_valid, 1)            # ... together with this
+    assert row.table_array().tolist() == row.block_table
+    row.block_table = []                                         # release()
+    row._table_np_valid = 0
+    row.block_table.extend([4, 4, 4])
+    assert row.table_array().tolist() == [4, 4, 4]
