@@ -7,8 +7,10 @@
 // from L2 serves all of them (with 128 rows per K / V tile the copies from L2 bound the kernel at 3.3 TB/s); threads t and
 // t + 256 own row t (lane t & 127 of query tile t >> 7) and half of its score / output columns.
 // Per tile of 64 keys:
-//   K / V tile --cp.async (K two stages and two tiles ahead, V one stage; zero-filled past the row's keys)--> shared
-//                                memory, canonical un-swizzled layout
+//   K / V tile --tiled TMA (two boxes of 64 values x 64 keys each, 128-byte swizzle; K two stages and two tiles
+//                                ahead, V two stages and one ahead)--> shared memory; the rows of the one V tile that
+//                                straddles the end of a row's keys are zeroed in shared memory (K needs nothing: its
+//                                scores are masked)
 //   S[128 x 64] = Q . K^T        8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared memory, S in one of
 //                                two 64-column buffers of tensor memory, so the scores of tile t + 1 are computed while
 //                                the threads work on tile t; issued by thread 0, completion through tcgen05.commit
@@ -22,6 +24,7 @@
 // the CTA counts a fault, stops, and still frees its tensor memory.
 #include "mma_utils.cuh"
 #include "prefill_params.cuh"
+#include "tma_utils.cuh"
 #include "umma_utils.cuh"
 
 #include <cstdlib>
@@ -37,17 +40,18 @@ constexpr int kUpQTiles = 2;      // query tiles (128 rows = one accumulator in 
 constexpr int kUpRows = 128, kUpKeys = 64, kUpDim = 128;
 constexpr int kUpCtaRows = kUpQTiles * kUpRows;
 constexpr int kUpThreads = 2 * kUpCtaRows;  // two threads per query row: each owns half of its score / output columns
-// canonical layout of an R x 128 (or 128 x C) 16-bit tile: 16-byte chunk c of row r at
-// c * chunk_stride + (r / 8) * 128 + (r % 8) * 16, chunk_stride = (R / 8) * 128 + 16 (the 16 extra bytes per chunk
-// plane spread a warp's 16-byte stores over the banks)
+// P (written by the threads): canonical un-swizzled layout of a 128 x 64 16-bit tile, 16-byte chunk c of row r at
+// c * kRowChunkStride + (r / 8) * 128 + (r % 8) * 16 (the 16 extra bytes per chunk plane spread a warp's 16-byte stores
+// over the banks).  Q, K, V (written by TMA): boxes of 64 values x R rows, rows of 128 bytes with the 128-byte swizzle,
+// every box on a 1024-byte boundary.
 constexpr uint32_t kGroupStride = 128;
-constexpr uint32_t kRowChunkStride = (kUpRows / 8) * kGroupStride + 16;  // tiles of 128 rows: Q, P
-constexpr uint32_t kKeyChunkStride = (kUpKeys / 8) * kGroupStride + 16;  // tiles of 64 keys: K, V
-constexpr uint32_t kQBytes = (kUpDim / 8) * kRowChunkStride;             // 128 rows x 16 chunks
-constexpr uint32_t kPBytes = (kUpKeys / 8) * kRowChunkStride;            // 128 rows x 8 chunks
-constexpr uint32_t kKvBytes = (kUpDim / 8) * kKeyChunkStride;            // 64 keys x 16 chunks
-constexpr uint32_t kOffQ = 0, kOffP = kUpQTiles * kQBytes, kOffK = kOffP + kUpQTiles * kPBytes, kOffV = kOffK + 2 * kKvBytes;
-constexpr uint32_t kUpSmem = kOffV + 2 * kKvBytes;  // Q0 Q1 | P0 P1 | K0 K1 | V0 V1
+constexpr uint32_t kRowChunkStride = (kUpRows / 8) * kGroupStride + 16;
+constexpr uint32_t kPBytes = (kUpKeys / 8) * kRowChunkStride;   // 128 rows x 8 chunks
+constexpr uint32_t kQBoxBytes = kUpCtaRows * 128;                // 64 values of all 256 rows
+constexpr uint32_t kKvBoxBytes = kUpKeys * 128;                  // 64 values of 64 keys
+constexpr uint32_t kKvBytes = 2 * kKvBoxBytes;                   // one K or V tile
+constexpr uint32_t kOffQ = 0, kOffK = 2 * kQBoxBytes, kOffV = kOffK + 2 * kKvBytes, kOffP = kOffV + 2 * kKvBytes;
+constexpr uint32_t kUpSmem = kOffP + kUpQTiles * kPBytes + 1024;  // Q | K0 K1 | V0 V1 | P0 P1, + room to align
 // tensor memory per query tile: two score buffers of 64 columns, then O (128 columns)
 constexpr uint32_t kColS = 0, kColO = 2 * kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
 constexpr float kLazyLog2 = 8.0f;
@@ -66,28 +70,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
-// rows [row0, row0 + ROWS) of a [*, 128] matrix with token stride `stride` -> canonical tile; rows >= limit are zeros.
-// A thread copies the same 16-byte chunk of every 16th row, so one source pointer and one destination offset step
-// through the tile.
-template <typename T, int ROWS>
-__device__ __forceinline__ void up_load_tile(uint32_t dst, const T* base, int64_t stride, int64_t row0, int64_t limit) {
-  constexpr int kRowsPerPass = kUpThreads / 16;
-  constexpr uint32_t kStride = (ROWS / 8) * kGroupStride + 16;
-  const int c = threadIdx.x & 15;
-  const int r0 = threadIdx.x >> 4;  // 0 .. kRowsPerPass - 1
-  const int64_t visible = limit - row0 - r0;  // rows r0 + kRowsPerPass * i with kRowsPerPass * i < visible exist
-  const T* src = base + (row0 + r0) * stride + c * 8;
-  const int64_t step = (int64_t)kRowsPerPass * stride;
-  uint32_t out = dst + c * kStride + (r0 >> 3) * kGroupStride + (r0 & 7) * 16;
-#pragma unroll
-  for (int i = 0; i < ROWS / kRowsPerPass; ++i) {
-    const bool ok = (int64_t)(kRowsPerPass * i) < visible;
-    cp_async16(out, ok ? src : base, ok ? 16 : 0);
-    src += step;
-    out += (kRowsPerPass / 8) * kGroupStride;
-  }
-}
-
 // Largest power of two (at most 16) that divides the number of query heads per KV head.
 __host__ __device__ inline int head_shift_of(int groups) {
   int shift = 0;
@@ -95,30 +77,18 @@ __host__ __device__ inline int head_shift_of(int groups) {
   return shift;
 }
 
-// The query tile: row r is position m0 + (r >> head_shift) of head r & ((1 << head_shift) - 1) (relative to `base`).
 template <typename T>
-__device__ __forceinline__ void up_load_queries(uint32_t dst, const T* base, int64_t stride_h, int64_t stride_t, int m0,
-                                                int q_len, int head_shift) {
-  const int c = threadIdx.x & 15;
-  for (int r = threadIdx.x >> 4; r < kUpCtaRows; r += kUpThreads / 16) {
-    const int pos = m0 + (r >> head_shift);
-    const int head = r & ((1 << head_shift) - 1);
-    const bool ok = pos < q_len;
-    const T* src = base + (ok ? head * stride_h + pos * stride_t + c * 8 : 0);
-    cp_async16(dst + (r >> 7) * kQBytes + c * kRowChunkStride + ((r & 127) >> 3) * kGroupStride + (r & 7) * 16, src,
-               ok ? 16 : 0);
-  }
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kUpThreads, 1)
+    gqa_prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+                            const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_storage[3];
+  __shared__ __align__(8) unsigned long long bar_storage[8];  // S0 S1 | O | Q | K0 K1 | V0 V1
   __shared__ uint32_t tmem_slot;
   __shared__ float row_exchange[2][kUpCtaRows];  // row maxima (per tile) and row sums (at the end) of the two halves
 
-  // The 128 rows of the CTA are 128 >> head_shift consecutive query positions of 1 << head_shift query heads that share
-  // one KV head (row r = position r >> head_shift, head r & mask), so a K / V tile read from L2 serves all of them.
+  // The 256 rows of the CTA are 256 >> head_shift consecutive query positions of 1 << head_shift query heads that share
+  // one KV head (row r = head r / positions, position r % positions: the order in which one TMA box of the query tensor
+  // lands), so a K / V tile read from L2 serves all of them.
   const int head_shift = head_shift_of(p.groups);
   const int heads_here = 1 << head_shift;
   const int positions = kUpCtaRows >> head_shift;
@@ -131,8 +101,8 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   const int r_local = threadIdx.x & (kUpCtaRows - 1);  // row of the CTA; lane r_local & 127 of query tile r_local >> 7
   const int half = threadIdx.x / kUpCtaRows;           // which half of the row's score / output columns
   const int qtile = r_local >> 7;
-  const int row = m0 + (r_local >> head_shift);     // query position of this thread's row
-  const int hq = hq0 + (r_local & (heads_here - 1));
+  const int row = m0 + (r_local & (positions - 1));  // query position of this thread's row
+  const int hq = hq0 + r_local / positions;
   constexpr int kHalf = kUpKeys / 2;   // score columns per thread
   constexpr int kOutHalf = kUpDim / 2;  // output columns per thread
 
@@ -146,9 +116,6 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   int64_t lim = 0;  // keys this thread's row sees
   if (row < p.q_len) lim = max((int64_t)0, p.causal ? min(n_keys, past + row + 1) : n_keys);
 
-  const T* q_base = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + (int64_t)hq0 * p.q_stride_h;
-  const T* k_base = reinterpret_cast<const T*>(p.k) + b * p.kv_stride_b + kvh * p.kv_stride_h;
-  const T* v_base = reinterpret_cast<const T*>(p.v) + b * p.kv_stride_b + kvh * p.kv_stride_h;
   T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + (int64_t)hq * p.out_stride_h +
                (int64_t)row * p.out_stride_t + half * kOutHalf;
 
@@ -158,38 +125,46 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     return;
   }
 
-  const uint32_t smem = smem_u32(smem_raw);
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;  // TMA boxes with the 128-byte swizzle start on 1 KB
   const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // bar_s0 + 8: the second score buffer
   const uint32_t bar_o = smem_u32(&bar_storage[2]);
+  const uint32_t bar_q = smem_u32(&bar_storage[3]);
+  const uint32_t bar_k0 = smem_u32(&bar_storage[4]);  // + 8: the second K stage
+  const uint32_t bar_v0 = smem_u32(&bar_storage[6]);  // + 8: the second V stage
   if (threadIdx.x == 0) {
-    mbar_init(bar_s0, 1);
-    mbar_init(bar_s0 + 8, 1);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 8; ++i) mbar_init(bar_s0 + 8 * i, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
 
-  auto load_k = [&](int tile) {  // two stages
-    if (tile < n_tiles)
-      up_load_tile<T, kUpKeys>(smem + kOffK + (tile & 1) * kKvBytes, k_base, p.kv_stride_t, (int64_t)tile * kUpKeys,
-                               n_keys);
-    cp_async_commit();
-  };
-  auto load_v = [&](int tile) {  // two stages
-    if (tile < n_tiles)
-      up_load_tile<T, kUpKeys>(smem + kOffV + (tile & 1) * kKvBytes, v_base, p.kv_stride_t, (int64_t)tile * kUpKeys,
-                               n_keys);
-    cp_async_commit();
-  };
-  up_load_queries<T>(smem + kOffQ, q_base, p.q_stride_h, p.q_stride_t, m0, p.q_len, head_shift);
-  load_k(0);
-  load_v(0);
-  load_k(1);
-  cp_async_wait<0>();
-  fence_async_smem();
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
+  // Copies are issued by thread 0 alone: two boxes (the two halves of head_dim) per tile, counted in bytes on the
+  // stage's barrier; a tile past the last one is not loaded and never waited for.
+  auto load_k = [&](int tile) {
+    if (threadIdx.x != 0 || tile >= n_tiles) return;
+    const uint32_t bar = bar_k0 + (tile & 1) * 8, dst = smem + kOffK + (tile & 1) * kKvBytes;
+    mbar_expect_tx(bar, kKvBytes);
+    tma_load_4d(dst, &map_k, 0, tile * kUpKeys, kvh, b, bar);
+    tma_load_4d(dst + kKvBoxBytes, &map_k, 64, tile * kUpKeys, kvh, b, bar);
+  };
+  auto load_v = [&](int tile) {
+    if (threadIdx.x != 0 || tile >= n_tiles) return;
+    const uint32_t bar = bar_v0 + (tile & 1) * 8, dst = smem + kOffV + (tile & 1) * kKvBytes;
+    mbar_expect_tx(bar, kKvBytes);
+    tma_load_4d(dst, &map_v, 0, tile * kUpKeys, kvh, b, bar);
+    tma_load_4d(dst + kKvBoxBytes, &map_v, 64, tile * kUpKeys, kvh, b, bar);
+  };
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar_q, 2 * kQBoxBytes);  // positions past the chunk's end arrive as zeros
+    tma_load_4d(smem + kOffQ, &map_q, 0, m0, hq0, b, bar_q);
+    tma_load_4d(smem + kOffQ + kQBoxBytes, &map_q, 64, m0, hq0, b, bar_q);
+  }
+  load_k(0);
+  load_v(0);
+  load_k(1);
+  bool ok = __syncthreads_and(mbar_wait(bar_q, 0u) && mbar_wait(bar_k0, 0u));
   const uint32_t tmem = tmem_slot;
   // this warp's quarter of the lanes (warps w and w + 4 share it); this thread's half of the score / output columns
   const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
@@ -200,12 +175,12 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
   constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
   constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
   // Descriptors of the first 16-wide K step of every operand; a later step, stage or query tile is the same descriptor
-  // with its byte offset (in 16-byte units) added to the address field, so the issuing thread spends two additions per
-  // instruction instead of rebuilding descriptors.
-  const uint64_t desc_q = umma_smem_desc(smem + kOffQ, kRowChunkStride, kGroupStride);
-  const uint64_t desc_k = umma_smem_desc(smem + kOffK, kKeyChunkStride, kGroupStride);
+  // with its byte offset (in 16-byte units) added to the address field.  Q and K: K-major rows of 128 bytes (eight
+  // rows = 1024 bytes); V: MN-major, the next 64 values of head_dim are the next box; P: un-swizzled K-major.
+  const uint64_t desc_q = umma_smem_desc_sw128(smem + kOffQ, 16, 1024);
+  const uint64_t desc_k = umma_smem_desc_sw128(smem + kOffK, 16, 1024);
+  const uint64_t desc_v = umma_smem_desc_sw128(smem + kOffV, kKvBoxBytes, 1024);
   const uint64_t desc_p = umma_smem_desc(smem + kOffP, kRowChunkStride, kGroupStride);
-  const uint64_t desc_v = umma_smem_desc(smem + kOffV, kGroupStride, kKeyChunkStride);
   // S(tile) = Q . K(tile)^T into score buffer tile & 1; issued by thread 0
   auto issue_scores = [&](int tile) {
     tcgen05_fence_after_sync();
@@ -213,17 +188,16 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
 #pragma unroll
     for (int qt = 0; qt < kUpQTiles; ++qt)
 #pragma unroll
-      for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction = two 16-byte chunks
+      for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
         umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
-                 desc_q + (uint64_t)((qt * kQBytes + 2 * k * kRowChunkStride) >> 4),
-                 k0 + (uint64_t)((2 * k * kKeyChunkStride) >> 4), idesc_s, k > 0);
+                 desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
+                 k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
     umma_commit(bar_s0 + (tile & 1) * 8);
   };
-  if (threadIdx.x == 0) issue_scores(0);
+  if (ok && threadIdx.x == 0) issue_scores(0);
 
   float m_run = -INFINITY, l_run = 0.0f;  // l_run: this thread's half of the row sum
-  bool ok = true;
-  for (int it = 0; it < n_tiles; ++it) {
+  for (int it = 0; it < n_tiles && ok; ++it) {
     const int64_t key0 = (int64_t)it * kUpKeys + half * kHalf;  // first key of this thread's columns
     // (a) S(it) and the previous P . V are complete: the K stage of tile it is free for tile it + 2, the V stage of
     // tile it - 1 for tile it + 1, P may be overwritten and O rescaled
@@ -261,11 +235,10 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
     float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     row_exchange[half][r_local] = mx;
 
-    // (c) K(it + 1) has landed (everything but the newest two copy groups): the next scores run beside this softmax
-    cp_async_wait<2>();
-    fence_async_smem();
+    // (c) K(it + 1) has landed: the next scores run beside this softmax
     tcgen05_fence_before_sync();
-    __syncthreads();
+    ok = __syncthreads_and(it + 1 >= n_tiles || mbar_wait(bar_k0 + ((it + 1) & 1) * 8, (uint32_t)(((it + 1) >> 1) & 1)));
+    if (!ok) break;
     if (threadIdx.x == 0 && it + 1 < n_tiles) issue_scores(it + 1);
 
     // (d) row maximum of both halves (log2 units), lazy running maximum -- the same decision in both threads of a row
@@ -314,24 +287,36 @@ __global__ void __launch_bounds__(kUpThreads, 1) gqa_prefill_umma_kernel(const P
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kRowChunkStride), "r"(packed[4 * c]),
                    "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
                    : "memory");
-    // V(it) was committed before the newest two copy groups (K(it + 2), V(it + 1))
-    cp_async_wait<2>();
+    // V(it) has landed; in the tile that holds the row's last key the rows behind it may hold anything (they are inside
+    // the tensor but past this row's length), and 0 x NaN would poison O, so they are zeroed (whole 128-byte rows: the
+    // swizzle permutes inside a row)
+    ok = mbar_wait(bar_v0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1));
+    const int64_t tile_key0 = (int64_t)it * kUpKeys;
+    if (ok && tile_key0 + kUpKeys > n_keys) {
+      const int first = (int)max((int64_t)0, n_keys - tile_key0);
+      uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kOffV + (it & 1) * kKvBytes;
+      for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpThreads) {
+        const int r = first + (i >> 4), piece = i & 15;  // 8 pieces of 16 bytes in each of the two boxes
+        *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kKvBoxBytes + r * 128 + (piece & 7) * 16) =
+            make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
     fence_async_smem();
     tcgen05_fence_before_sync();
-    __syncthreads();
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
     if (threadIdx.x == 0) {
       tcgen05_fence_after_sync();
-      const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);
+      const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);  // 16 keys = 16 rows of 128 bytes per step
 #pragma unroll
       for (int qt = 0; qt < kUpQTiles; ++qt)
 #pragma unroll
         for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
           umma_f16(tmem + qt * kColsPerQTile + kColO, desc_p + (uint64_t)((qt * kPBytes + 2 * k * kRowChunkStride) >> 4),
-                   v0 + (uint64_t)((2 * k * kGroupStride) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
+                   v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
       umma_commit(bar_o);
     }
   }
-  cp_async_wait<0>();
   row_exchange[half][r_local] = l_run;
   if (ok) {
     ok = __syncthreads_and(mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1)));
@@ -379,12 +364,37 @@ bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
   // the output rows are written as 16-byte vectors
   if (p.out_stride_b % 8 != 0 || p.out_stride_h % 8 != 0 || p.out_stride_t % 8 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return false;
-  return p.q_len >= 64;  // short chunks leave most of a 128-row tile empty: the mma.sync kernel serves them
+  if (p.key_len <= 0) return false;
+  return p.q_len >= 64;  // short chunks leave most of a 256-row tile empty: the mma.sync kernel serves them
+}
+
+// Tensor map of a [B, H, L, 128] 16-bit tensor given by element strides, seen as (128, L, H, B).
+static bool prefill_tensor_map(CUtensorMap* out, const void* base, int64_t len, int heads, int batch, int64_t stride_t,
+                               int64_t stride_h, int64_t stride_b, uint32_t box_len, uint32_t box_heads) {
+  if (len <= 0 || heads <= 0 || batch <= 0) return false;
+  const uint64_t extents[4] = {(uint64_t)kUpDim, (uint64_t)len, (uint64_t)heads, (uint64_t)batch};
+  uint64_t strides[3] = {(uint64_t)stride_t * 2, (uint64_t)stride_h * 2, (uint64_t)stride_b * 2};
+  const uint64_t used[3] = {(uint64_t)len, (uint64_t)heads, (uint64_t)batch};
+  for (int i = 0; i < 3; ++i) {
+    if (used[i] == 1 && strides[i] == 0) strides[i] = 256;  // never stepped along
+    if (strides[i] == 0 || strides[i] % 16 != 0 || strides[i] >= ((uint64_t)1 << 40)) return false;
+  }
+  const uint32_t box[4] = {64, box_len, box_heads, 1};
+  return encode_map_16bit(out, base, 4, extents, strides, box);
 }
 
 template <typename T>
 static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
   auto kernel = gqa_prefill_umma_kernel<T>;
+  const int head_shift = head_shift_of(p.groups);
+  const int positions = kUpCtaRows >> head_shift;
+  CUtensorMap map_q, map_k, map_v;
+  const int kv_heads = q_heads / p.groups;
+  if (!prefill_tensor_map(&map_q, p.q, p.q_len, q_heads, batch, p.q_stride_t, p.q_stride_h, p.q_stride_b,
+                          (uint32_t)positions, 1u << head_shift) ||
+      !prefill_tensor_map(&map_k, p.k, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kUpKeys, 1) ||
+      !prefill_tensor_map(&map_v, p.v, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kUpKeys, 1))
+    return kPrefillNotServed;  // no encoder in this driver, or a layout it refuses: the mma.sync kernel takes over
   static bool configured[64] = {};
   int device = 0;
   ANNA_CUDA_CHECK(cudaGetDevice(&device));
@@ -392,10 +402,8 @@ static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads,
     ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUpSmem));
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  const int head_shift = head_shift_of(p.groups);
-  const int positions = kUpCtaRows >> head_shift;
   dim3 grid((unsigned)((p.q_len + positions - 1) / positions), (unsigned)(q_heads >> head_shift), (unsigned)batch);
-  kernel<<<grid, kUpThreads, kUpSmem, stream>>>(p);
+  kernel<<<grid, kUpThreads, kUpSmem, stream>>>(p, map_q, map_k, map_v);
   return check_launch("gqa_prefill_umma_kernel");
 }
 

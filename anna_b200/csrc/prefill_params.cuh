@@ -19,6 +19,8 @@ struct PrefillParams {
   float scale_log2;  // scaling * log2(e)
 };
 
+constexpr int kPrefillNotServed = -1;  // launch_prefill_umma: the caller should use the mma.sync kernel instead
+
 // true when the tensor-memory kernel serves this problem (head_dim 128, 16-bit, not switched off)
 bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype);
 int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int dtype, cudaStream_t stream);

@@ -4,6 +4,7 @@
 //   D2[128 x 16] = A2[128 x 128]^T . B2[128 x 16]    f16 operands, both MN-major          (values: dims x heads)
 // Operands arrive as plain row-major device arrays, the kernel re-tiles them into the canonical shared-memory layouts
 // with the padded strides of the real kernel, multiplies, and returns the accumulators.  No counterpart in the reference.
+#include "tma_utils.cuh"
 #include "umma_utils.cuh"
 
 namespace anna {
@@ -85,6 +86,76 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const uint8_t* a1, c
   if (warp == 0) tmem_free(tmem, 32);
 }
 
+// Second self-test: operands brought in by tiled TMA loads with the 128-byte swizzle and read through swizzled
+// descriptors, in the two arrangements of the tensor-memory prefill kernel:
+//   D1[128 x 128] = A[128 x 128] . B1[128 x 128]^T     bf16, A and B1 K-major (rows of A / B1 are rows of the tensors)
+//   D2[128 x 128] = A[128 x 128] . B2[128 x 128]       bf16, B2 MN-major (its rows are K indices, as V's rows are keys)
+constexpr uint32_t kTmaBox = 128 * 128;   // bytes of one box: 128 rows x 64 values
+__global__ void __launch_bounds__(128) umma_tma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                const __grid_constant__ CUtensorMap map_b1,
+                                                                const __grid_constant__ CUtensorMap map_b2, float* d1,
+                                                                float* d2, int32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) unsigned long long bar_storage[2];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t base = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t s_a = base, s_b1 = base + 2 * kTmaBox, s_b2 = base + 4 * kTmaBox;
+  const uint32_t bar_load = smem_u32(&bar_storage[0]), bar_mma = smem_u32(&bar_storage[1]);
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar_load, 6 * kTmaBox);
+    for (int h = 0; h < 2; ++h) {  // columns [64h, 64h + 64) of all 128 rows
+      tma_load_2d(s_a + h * kTmaBox, &map_a, 64 * h, 0, bar_load);
+      tma_load_2d(s_b1 + h * kTmaBox, &map_b1, 64 * h, 0, bar_load);
+      tma_load_2d(s_b2 + h * kTmaBox, &map_b2, 64 * h, 0, bar_load);
+    }
+  }
+  bool ok = __syncthreads_and(mbar_wait(bar_load, 0u));
+  if (ok && threadIdx.x == 0) {
+    tcgen05_fence_after_sync();
+    constexpr uint32_t idesc1 = umma_idesc(kUmmaBF16, kUmmaBF16, false, false, 128, 128);
+    constexpr uint32_t idesc2 = umma_idesc(kUmmaBF16, kUmmaBF16, false, true, 128, 128);
+    for (int k = 0; k < 8; ++k) {  // 16 values of K per instruction: 32 bytes inside a 128-byte row, 4 per box
+      const uint32_t off = (k / 4) * kTmaBox + (k % 4) * 32;
+      umma_f16(tmem, umma_smem_desc_sw128(s_a + off, 16, 1024), umma_smem_desc_sw128(s_b1 + off, 16, 1024), idesc1, k > 0);
+    }
+    for (int k = 0; k < 8; ++k) {  // 16 K indices = 16 rows of B2 = 2048 bytes; the second 64 columns are the next box
+      const uint32_t off = (k / 4) * kTmaBox + (k % 4) * 32;
+      umma_f16(tmem + 128, umma_smem_desc_sw128(s_a + off, 16, 1024),
+               umma_smem_desc_sw128(s_b2 + k * 2048, kTmaBox, 1024), idesc2, k > 0);
+    }
+    umma_commit(bar_mma);
+  }
+  if (ok) ok = __syncthreads_and(mbar_wait(bar_mma, 0u));
+  tcgen05_fence_after_sync();
+  if (ok) {
+    for (int c = 0; c < 16; ++c) {
+      uint32_t r[16];
+      tmem_ld16(tmem_addr(tmem, 32 * warp, 16 * c), r);
+      tmem_wait_ld();
+      for (int j = 0; j < 16; ++j) {
+        if (c < 8) d1[threadIdx.x * 128 + 16 * c + j] = __uint_as_float(r[j]);
+        else d2[threadIdx.x * 128 + 16 * (c - 8) + j] = __uint_as_float(r[j]);
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    *status = 1;
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 256);
+}
+
 }  // namespace anna
 
 // a1 uint8 [128][128] (e4m3 bytes), b1 uint8 [16][128], a2 f16 [128 (K)][128 (rows)], b2 f16 [128 (K)][16]:
@@ -111,6 +182,44 @@ extern "C" int anna_kv_selftest_umma(const void* a1, const void* b1, const void*
   if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
   cudaFree(flag);
   if (err != cudaSuccess) return set_error(ANNA_ERR_CUDA, "tensor-memory self-test failed: %s", cudaGetErrorString(err));
+  *status = (int)value;
+  return ANNA_OK;
+}
+
+// a, b1, b2: bf16 [128][128] row-major device arrays (16-byte aligned); d1 = a . b1^T, d2 = a . b2 (float [128][128]).
+// The operands travel by tiled TMA loads with the 128-byte swizzle.  *status = 1 when a bounded wait ran out, 2 when the
+// driver's tensor-map encoder is not available.  Synchronises the stream.  No counterpart in the reference.
+extern "C" int anna_kv_selftest_umma_tma(const void* a, const void* b1, const void* b2, float* d1, float* d2, int* status,
+                                         anna_stream_t stream) {
+  using namespace anna;
+  ANNA_REQUIRE(a && b1 && b2 && d1 && d2 && status, "anna_kv_selftest_umma_tma: null pointer argument");
+  CUtensorMap maps[3];
+  const void* bases[3] = {a, b1, b2};
+  const uint64_t extents[2] = {128, 128};
+  const uint64_t strides[1] = {256};
+  const uint32_t box[2] = {64, 128};
+  for (int i = 0; i < 3; ++i)
+    if (!encode_map_16bit(&maps[i], bases[i], 2, extents, strides, box)) {
+      *status = 2;
+      return ANNA_OK;
+    }
+  int32_t* flag = nullptr;
+  ANNA_CUDA_CHECK(cudaMalloc(&flag, sizeof(int32_t)));
+  constexpr int kSmem = 6 * (int)kTmaBox + 1024;
+  cudaError_t err = cudaMemsetAsync(flag, 0, sizeof(int32_t), (cudaStream_t)stream);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(umma_tma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (err == cudaSuccess) {
+    umma_tma_selftest_kernel<<<1, 128, kSmem, (cudaStream_t)stream>>>(maps[0], maps[1], maps[2], d1, d2, flag);
+    err = cudaGetLastError();
+  }
+  int32_t value = -1;
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(&value, flag, sizeof(value), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
+  cudaFree(flag);
+  if (err != cudaSuccess)
+    return set_error(ANNA_ERR_CUDA, "tensor-memory / TMA self-test failed: %s", cudaGetErrorString(err));
   *status = (int)value;
   return ANNA_OK;
 }

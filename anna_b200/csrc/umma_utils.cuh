@@ -24,6 +24,15 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
 }
 
+// The same descriptor for operands in the 128-byte-swizzled layout a tiled TMA load writes (rows of 128 bytes, the eight
+// 16-byte units of a row permuted by the row index modulo 8; the tile starts on a 1024-byte boundary).
+//   K-major  (a row = 64 values of K): sbo = 1024 (eight rows), lbo unused; the next 16 values of K are 32 bytes further
+//   MN-major (a row = 64 values of M or N for one K index): sbo = 1024 (eight K indices), lbo = distance of the next 64
+//            values of M / N (the next box)
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return umma_smem_desc(smem_addr, lbo_bytes, sbo_bytes) | ((uint64_t)2 << 61);
+}
+
 enum UmmaFormat : uint32_t { kUmmaF16 = 0, kUmmaBF16 = 1, kUmmaE4M3 = 0, kUmmaE5M2 = 1 };
 
 // 32-bit instruction descriptor: fp32 accumulate, dense, A / B formats and majors, N >> 3 at bit 17, M >> 4 at bit 24.

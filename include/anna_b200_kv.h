@@ -65,6 +65,16 @@ int anna_kv_selftest_wait_expiry(int* expired, anna_stream_t stream);
 int anna_kv_selftest_umma(const void* a1, const void* b1, const void* a2, const void* b2, float* d1, float* d2,
                           int* status, anna_stream_t stream);
 
+/*
+ * Second self-test of the tensor-memory primitives: bf16 operands a, b1, b2 [128][128] (row-major, 16-byte aligned)
+ * travel to shared memory by tiled TMA loads with the 128-byte swizzle and are read through swizzled descriptors;
+ * d1 = a . b1^T (both K-major), d2 = a . b2 (b2 MN-major: its rows are K indices), float [128][128].  *status = 1 when a
+ * bounded wait ran out, 2 when the driver's tensor-map encoder is unavailable.  Synchronises the stream.  No counterpart
+ * in the reference.
+ */
+int anna_kv_selftest_umma_tma(const void* a, const void* b1, const void* b2, float* d1, float* d2, int* status,
+                              anna_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
  * (row, query head, chunk) leaves a partial in caller-owned float32 buffers

@@ -66,6 +66,28 @@ def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len,
     assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("dim,q_len", [(128, 200), (128, 40), (256, 48)])
+def test_keys_behind_a_rows_length_may_hold_anything(cuda_device, dim, q_len):
+    """K / V rows past key_lengths[b] are inside the tensors but not part of the row: NaNs there must not reach the
+    output (the TMA-fed kernel reads them and zeroes the value rows of the boundary tile; the others never load them)."""
+    gen = torch.Generator().manual_seed(dim + q_len)
+    heads, kv_heads, key_len = 8, 2, 700
+    lengths = (700, 333, q_len)
+    batch = len(lengths)
+    q = torch.randn(batch, heads, q_len, dim, generator=gen).to(torch.bfloat16).to(cuda_device)
+    k = torch.randn(batch, kv_heads, key_len, dim, generator=gen).to(torch.bfloat16).to(cuda_device)
+    v = torch.randn(batch, kv_heads, key_len, dim, generator=gen).to(torch.bfloat16).to(cuda_device)
+    n = torch.tensor(lengths, dtype=torch.long, device=cuda_device)
+    expected = _oracle(q, k, v, n, True)
+    for b, length in enumerate(lengths):
+        k[b, :, length:] = float("nan")
+        v[b, :, length:] = float("nan")
+    out = grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=n, causal=True)
+    assert bool(torch.isfinite(out).all())
+    max_abs, rel_l2 = error_stats(to_np(out), expected)
+    assert max_abs <= ATOL[torch.bfloat16], (max_abs, rel_l2)
+
+
 def test_tensor_memory_kernel_reported_no_expired_wait(cuda_device):
     """Runs after the cases above in this file: none of the bounded waits of the copy-engine / tensor-memory kernels may
     have run out."""

@@ -43,3 +43,24 @@ def test_umma_products_match_fp32_reference(cuda_device):
     sub_rows = a2.float().t()[0::4] @ b2.float()
     torch.testing.assert_close(d2[0::4], sub_rows, atol=0.0, rtol=2e-3)
     assert float(d2[0::4].abs().max()) > 0.0
+
+
+def test_tma_fed_products_match_fp32_reference(cuda_device):
+    """anna_kv_selftest_umma_tma: bf16 operands brought in by tiled TMA loads with the 128-byte swizzle and read through
+    swizzled descriptors, K-major (the Q . K^T arrangement of the prefill kernel) and MN-major (its P . V one)."""
+    gen = torch.Generator(device=cuda_device).manual_seed(12)
+    a = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.bfloat16)
+    b1 = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.bfloat16)
+    b2 = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.bfloat16)
+    d1 = torch.zeros(128, 128, device=cuda_device, dtype=torch.float32)
+    d2 = torch.zeros(128, 128, device=cuda_device, dtype=torch.float32)
+    status = ctypes.c_int(-1)
+    with torch.cuda.device(cuda_device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(_lib.lib().anna_kv_selftest_umma_tma(
+            ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b1.data_ptr()), ctypes.c_void_p(b2.data_ptr()),
+            ctypes.c_void_p(d1.data_ptr()), ctypes.c_void_p(d2.data_ptr()), ctypes.byref(status), stream),
+            "anna_kv_selftest_umma_tma")
+    assert status.value == 0
+    torch.testing.assert_close(d1, a.float() @ b1.float().t(), atol=1e-3, rtol=1e-4)
+    torch.testing.assert_close(d2, a.float() @ b2.float(), atol=1e-3, rtol=1e-4)
