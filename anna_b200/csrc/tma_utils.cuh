@@ -1,6 +1,6 @@
 // Tiled TMA loads (cp.async.bulk.tensor) and the host-side tensor-map encoder, looked up at run time so that nothing
 // links against libcuda.  Coordinates: the innermost one times the element size must be a multiple of 16 bytes; loads
-// may start past the tensor's extent and read zeros there.  No multicast anywhere.
+// may start past the tensor's extent and read zeros there.  Every load is addressed to the issuing CTA alone.
 #pragma once
 
 #include <cuda.h>  // CUtensorMap and its enums
