@@ -62,9 +62,12 @@ __device__ __forceinline__ uint32_t and_or_regs(uint32_t x, uint32_t mask, uint3
   return r;
 }
 
-// fp16 pair (+-1, +-1) from bits b and b + 16 of x (0 <= b <= 15): a set bit gives +1.  One shift and one logic op.
-__device__ __forceinline__ uint32_t pm_one_pair(uint32_t x, int b) {
-  return ((x << (15 - b)) & 0x80008000u) ^ 0xBC00BC00u;
+// fp16 pair (+-1, +-1) from bits b and b + 16 of x (0 <= b <= 15): a set bit gives +1.  One shift and one logic op,
+// ((x << (15 - b)) & 0x80008000) ^ 0xBC00BC00 with both constants in registers (`sign_bits`, `minus_one`).
+__device__ __forceinline__ uint32_t pm_one_pair(uint32_t x, int b, uint32_t sign_bits, uint32_t minus_one) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(r) : "r"(x << (15 - b)), "r"(sign_bits), "r"(minus_one));
+  return r;
 }
 // mma.sync m16n8k16 (fp16 in, fp32 accumulate) without the volatile qualifier: a pure function of its operands, so
 // the compiler may interleave the independent accumulation chains of this kernel
@@ -532,9 +535,17 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
   }
 
   // loop constants held in registers
-  const uint32_t nib_mask = pinned_u32(0x03C003C0u, lane), magic16 = pinned_u32(0x4C004C00u, lane);
-  const uint32_t kTwo = pinned_u32(0x02020202u, lane), kIdxMask = pinned_u32(0x77777777u, lane);
-  (void)nib_mask; (void)magic16; (void)kTwo; (void)kIdxMask;
+  // (only the ones this instantiation uses are created)
+  const uint32_t nib_mask = BITS != 2 ? pinned_u32(0x03C003C0u, lane) : 0u;    // 4-bit value codes
+  const uint32_t magic16 = BITS != 2 ? pinned_u32(0x4C004C00u, lane) : 0u;
+  const uint32_t kTwo = BITS == 4 ? pinned_u32(0x02020202u, lane) : 0u;        // 4-bit key codes
+  const uint32_t kIdxMask = BITS == 4 ? pinned_u32(0x77777777u, lane) : 0u;
+  const uint32_t kSignBits = BITS != 4 ? pinned_u32(0x80008000u, lane) : 0u;   // +-1 fragments of 2- and 3-bit key codes
+  const uint32_t kMinusOne = BITS != 4 ? pinned_u32(0xBC00BC00u, lane) : 0u;
+  const uint32_t kTwoBitMask = BITS == 2 ? pinned_u32(0x03000300u, lane) : 0u;  // 2-bit value codes
+  const uint32_t kMagic4 = BITS == 2 ? pinned_u32(0x44004400u, lane) : 0u;
+  (void)nib_mask; (void)magic16; (void)kTwo; (void)kIdxMask; (void)kSignBits; (void)kMinusOne; (void)kTwoBitMask;
+  (void)kMagic4;
 
   const uint32_t warp_smem_u32 = smem_u32(smem_raw + warp * Cfg::kWarpSmem);
   const uint8_t* warp_smem = smem_raw + warp * Cfg::kWarpSmem;
@@ -706,15 +717,15 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
-            const uint32_t a[4] = {pm_one_pair(xl, 4 * h), pm_one_pair(xh, 4 * h), pm_one_pair(xl, 4 * h + 2),
-                                   pm_one_pair(xh, 4 * h + 2)};
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h, kSignBits, kMinusOne), pm_one_pair(xh, 4 * h, kSignBits, kMinusOne), pm_one_pair(xl, 4 * h + 2, kSignBits, kMinusOne),
+                                   pm_one_pair(xh, 4 * h + 2, kSignBits, kMinusOne)};
             mma_f16(s1[u], a, q1f[s][0], q1f[s][1]);
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const uint32_t xl = iw_lo[u][s / 4], xh = iw_hi[u][s / 4];
-            const uint32_t a[4] = {pm_one_pair(xl, 4 * h + 1), pm_one_pair(xh, 4 * h + 1), pm_one_pair(xl, 4 * h + 3),
-                                   pm_one_pair(xh, 4 * h + 3)};
+            const uint32_t a[4] = {pm_one_pair(xl, 4 * h + 1, kSignBits, kMinusOne), pm_one_pair(xh, 4 * h + 1, kSignBits, kMinusOne), pm_one_pair(xl, 4 * h + 3, kSignBits, kMinusOne),
+                                   pm_one_pair(xh, 4 * h + 3, kSignBits, kMinusOne)};
             mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
         }
@@ -745,8 +756,8 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
             // sign plane: bits 2h, 2h + 1 (and + 16) of word s / 8, h = s % 8
             const uint32_t xl = sw_lo[u][s / 8], xh = sw_hi[u][s / 8];
             const int h = s % 8;
-            const uint32_t a[4] = {pm_one_pair(xl, 2 * h), pm_one_pair(xh, 2 * h), pm_one_pair(xl, 2 * h + 1),
-                                   pm_one_pair(xh, 2 * h + 1)};
+            const uint32_t a[4] = {pm_one_pair(xl, 2 * h, kSignBits, kMinusOne), pm_one_pair(xh, 2 * h, kSignBits, kMinusOne), pm_one_pair(xl, 2 * h + 1, kSignBits, kMinusOne),
+                                   pm_one_pair(xh, 2 * h + 1, kSignBits, kMinusOne)};
             mma_f16(s2[u], a, q2f[s][0], q2f[s][1]);
           }
         }
@@ -874,8 +885,13 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
         }
       }
     } else {
-      // 2-bit codes: one 16-bit half-word = 8 dims
-      constexpr uint32_t kM0 = 0x64006400u, kM1 = 0x5C005C00u, kM2 = 0x54005400u, kM3 = 0x4C004C00u, kM4 = 0x44004400u;
+      // 2-bit codes: one 16-bit half-word = 8 dims.  A code moved to bits 8..9 under the exponent of 4 reads as the fp16
+      // number 4 + code, so one fused multiply-add de-quantises a pair: (4 + code) * scale + (zero - 4 * scale); the
+      // left shifts run on the multiply pipe.
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) zp_pair[u][pr] = hfma2_u32(sc_pair[u][pr], 0xC400C400u, zp_pair[u][pr]);
 #pragma unroll
       for (int hw = 0; hw < Cfg::kValWords * 2; ++hw) {
         const uint32_t sel = (hw % 2) ? 0x7632u : 0x5410u;
@@ -885,16 +901,15 @@ __global__ void __launch_bounds__(kMmaThreads, TqMmaCfg<T, D, BITS>::kMinBlocks)
 #pragma unroll
           for (int pr = 0; pr < 2; ++pr) {
             const uint32_t x = prmt(vw[u][2 * pr][hw / 2], vw[u][2 * pr + 1][hw / 2], sel);
-            const uint32_t y = x >> 10;
             const uint32_t scl = sc_pair[u][pr], zpt = zp_pair[u][pr];
-            r[pr][0] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00030003u, kM0), kM0), scl, zpt);
-            r[pr][1] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x000C000Cu, kM1), kM1), scl, zpt);
-            r[pr][2] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00300030u, kM2), kM2), scl, zpt);
-            r[pr][3] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x00C000C0u, kM3), kM3), scl, zpt);
-            r[pr][4] = hfma2_u32(hsub2_u32(lop3_and_or(x, 0x03000300u, kM4), kM4), scl, zpt);
-            r[pr][5] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00030003u, kM0), kM0), scl, zpt);
-            r[pr][6] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x000C000Cu, kM1), kM1), scl, zpt);
-            r[pr][7] = hfma2_u32(hsub2_u32(lop3_and_or(y, 0x00300030u, kM2), kM2), scl, zpt);
+            r[pr][0] = hfma2_u32(and_or_regs(x << 8, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][1] = hfma2_u32(and_or_regs(x << 6, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][2] = hfma2_u32(and_or_regs(x << 4, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][3] = hfma2_u32(and_or_regs(x << 2, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][4] = hfma2_u32(and_or_regs(x, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][5] = hfma2_u32(and_or_regs(x >> 2, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][6] = hfma2_u32(and_or_regs(x >> 4, kTwoBitMask, kMagic4), scl, zpt);
+            r[pr][7] = hfma2_u32(and_or_regs(x >> 6, kTwoBitMask, kMagic4), scl, zpt);
           }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {  // dims 8hw + {2q, 2q+1} -> m-tile 4hw + q
