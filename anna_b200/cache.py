@@ -338,24 +338,32 @@ class Qwen3DynamicCache:
         # scatter kernel writes them into the device table, so a step in which a few rows of a ragged batch take a page
         # moves a few dozen bytes and never waits for the GPU.  Entries are write-once while a row lives.
         host = self._table_host[layer_idx]
-        triples: list[int] = []
+        tq_rows = self.turboquant_rows[layer_idx] if self.uses_turboquant_for_layer(layer_idx) else None
+        pieces: list[np.ndarray] = []
         for row_idx, table in enumerate(tables):
             have = synced[row_idx]
             n = len(table)
             if n > have:
-                host[row_idx, have:n] = table[have:]
+                row = None if tq_rows is None else tq_rows[row_idx]
+                new_pages = np.asarray(table[have:], dtype=np.int32) if row is None else row.table_array()[have:n]
+                host[row_idx, have:n] = new_pages
                 synced[row_idx] = n
-                for col in range(have, n):
-                    triples.extend((row_idx, col, table[col]))
-        if triples and device.type != "cuda":  # host-side bookkeeping of a cache that holds no device memory
-            patch = np.asarray(triples, dtype=np.int64).reshape(-1, 3)
-            buffer[patch[:, 0], patch[:, 1]] = torch.from_numpy(patch[:, 2]).to(torch.int32)
-        elif triples:
-            entries = MetadataUploader.for_device(device).upload_i32(np.asarray(triples, dtype=np.int32))
-            with on_device(device):
-                _lib.check(_lib.lib().anna_block_table_patch(
-                    ptr(buffer), buffer.stride(0), int(buffer.shape[0]), int(buffer.shape[1]), ptr(entries),
-                    len(triples) // 3, stream_ptr(device)), "anna_block_table_patch")
+                piece = np.empty((n - have, 3), dtype=np.int32)
+                piece[:, 0] = row_idx
+                piece[:, 1] = np.arange(have, n, dtype=np.int32)
+                piece[:, 2] = new_pages
+                pieces.append(piece)
+        if pieces:
+            patch = pieces[0] if len(pieces) == 1 else np.concatenate(pieces)
+            if device.type != "cuda":  # host-side bookkeeping of a cache that holds no device memory
+                buffer[patch[:, 0].astype(np.int64), patch[:, 1].astype(np.int64)] = torch.from_numpy(
+                    np.ascontiguousarray(patch[:, 2]))
+            else:
+                entries = MetadataUploader.for_device(device).upload_i32(patch.reshape(-1))
+                with on_device(device):
+                    _lib.check(_lib.lib().anna_block_table_patch(
+                        ptr(buffer), buffer.stride(0), int(buffer.shape[0]), int(buffer.shape[1]), ptr(entries),
+                        int(patch.shape[0]), stream_ptr(device)), "anna_block_table_patch")
         self._table_blocks_total[layer_idx] = total
         return buffer[:, :required]
 
