@@ -2,10 +2,11 @@
 // both accumulators in tensor memory.  head_dim 128, 16-bit dtypes; same semantics as gqa_prefill.cu
 // (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and :2008-2016).
 //
-// A CTA (16 warps, one per SM) owns 256 rows = two query tiles of 128 rows (one set of accumulators in tensor memory
+// A CTA (8 softmax warps + 1 issuing warp, one CTA per SM) owns 256 rows = two query tiles of 128 rows (one set of accumulators in tensor memory
 // each): consecutive query positions of the (up to 16) query heads that share one KV head, so that a K / V tile fetched
-// from L2 serves all of them (with 128 rows per K / V tile the copies from L2 bound the kernel at 3.3 TB/s); threads t and
-// t + 256 own row t (lane t & 127 of query tile t >> 7) and half of its score / output columns.
+// from L2 serves all of them (with 128 rows per K / V tile the copies from L2 bound the kernel at 3.3 TB/s); thread t owns
+// row t (lane t & 127 of query tile t >> 7); a ninth warp only issues the copies and the products, so that their issue
+// (which proceeds at the pace of the tensor pipe) runs beside the softmax instead of in front of it.
 // Per tile of 64 keys:
 //   K / V tile --tiled TMA (two boxes of 64 values x 64 keys each, 128-byte swizzle; K two stages and two tiles
 //                                ahead, V two stages and one ahead)--> shared memory; the rows of the one V tile that
@@ -39,7 +40,8 @@ namespace {
 constexpr int kUpQTiles = 2;      // query tiles (128 rows = one accumulator in tensor memory each) per CTA
 constexpr int kUpRows = 128, kUpKeys = 64, kUpDim = 128;
 constexpr int kUpCtaRows = kUpQTiles * kUpRows;
-constexpr int kUpThreads = 2 * kUpCtaRows;  // two threads per query row: each owns half of its score / output columns
+constexpr int kUpSoftmaxThreads = kUpCtaRows;       // one thread per query row (lane of tensor memory)
+constexpr int kUpThreads = kUpSoftmaxThreads + 32;  // and one more warp whose first lane issues every copy and product
 // P (written by the threads): canonical un-swizzled layout of a 128 x 64 16-bit tile, 16-byte chunk c of row r at
 // c * kRowChunkStride + (r / 8) * 128 + (r % 8) * 16 (the 16 extra bytes per chunk plane spread a warp's 16-byte stores
 // over the banks).  Q, K, V (written by TMA): boxes of 64 values x R rows, rows of 128 bytes with the 128-byte swizzle,
@@ -51,7 +53,7 @@ constexpr uint32_t kQBoxBytes = kUpCtaRows * 128;                // 64 values of
 constexpr uint32_t kKvBoxBytes = kUpKeys * 128;                  // 64 values of 64 keys
 constexpr uint32_t kKvBytes = 2 * kKvBoxBytes;                   // one K or V tile
 constexpr uint32_t kOffQ = 0, kOffK = 2 * kQBoxBytes, kOffV = kOffK + 2 * kKvBytes, kOffP = kOffV + 2 * kKvBytes;
-constexpr uint32_t kUpSmem = kOffP + kUpQTiles * kPBytes + 1024;  // Q | K0 K1 | V0 V1 | P0 P1, + room to align
+constexpr uint32_t kUpSmem = kOffP + 2 * kUpQTiles * kPBytes + 1024;  // Q | K0 K1 | V0 V1 | two buffers of P0 P1, + room to align
 // tensor memory per query tile: two score buffers of 64 columns, then O (128 columns)
 constexpr uint32_t kColS = 0, kColO = 2 * kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
 constexpr float kLazyLog2 = 8.0f;
@@ -70,6 +72,21 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// True in exactly one lane of a converged warp.  Unlike a comparison of the lane index, the instruction tells the compiler
+// that the guarded region runs in a single thread, so descriptors and addresses of the tensor-core and copy
+// instructions issued there can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(chosen));
+  return chosen != 0;
+}
+
 // Largest power of two (at most 16) that divides the number of query heads per KV head.
 __host__ __device__ inline int head_shift_of(int groups) {
   int shift = 0;
@@ -82,9 +99,9 @@ __global__ void __launch_bounds__(kUpThreads, 1)
     gqa_prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_storage[8];  // S0 S1 | O | Q | K0 K1 | V0 V1
+  __shared__ __align__(8) unsigned long long bar_storage[11];  // S0 S1 | O0 O1 | Q | K0 K1 | V0 V1 | P0 P1
   __shared__ uint32_t tmem_slot;
-  __shared__ float row_exchange[2][kUpCtaRows];  // row maxima (per tile) and row sums (at the end) of the two halves
+  __shared__ int abort_flag;  // set by the first wait that expires; every later wait of the CTA gives up at once
 
   // The 256 rows of the CTA are 256 >> head_shift consecutive query positions of 1 << head_shift query heads that share
   // one KV head (row r = head r / positions, position r % positions: the order in which one TMA box of the query tensor
@@ -97,14 +114,12 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   const int kvh = blockIdx.y / head_sets;
   const int hq0 = kvh * p.groups + (blockIdx.y % head_sets) * heads_here;
   const int b = blockIdx.z;
-  const int warp = threadIdx.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool softmax = threadIdx.x < kUpSoftmaxThreads;  // warps 0..7; warp 8 issues the copies and the products
   const int r_local = threadIdx.x & (kUpCtaRows - 1);  // row of the CTA; lane r_local & 127 of query tile r_local >> 7
-  const int half = threadIdx.x / kUpCtaRows;           // which half of the row's score / output columns
   const int qtile = r_local >> 7;
   const int row = m0 + (r_local & (positions - 1));  // query position of this thread's row
   const int hq = hq0 + r_local / positions;
-  constexpr int kHalf = kUpKeys / 2;   // score columns per thread
-  constexpr int kOutHalf = kUpDim / 2;  // output columns per thread
 
   int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
   n_keys = max((int64_t)0, min(n_keys, p.key_len));
@@ -117,22 +132,26 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   if (row < p.q_len) lim = max((int64_t)0, p.causal ? min(n_keys, past + row + 1) : n_keys);
 
   T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + (int64_t)hq * p.out_stride_h +
-               (int64_t)row * p.out_stride_t + half * kOutHalf;
+               (int64_t)row * p.out_stride_t;
 
   if (n_tiles == 0) {  // no row of this CTA sees a key: zeros (uniform over the CTA, nothing was allocated yet)
-    if (row < p.q_len)
-      for (int c = 0; c < kOutHalf / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (softmax && row < p.q_len)
+      for (int c = 0; c < kUpDim / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
     return;
   }
 
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;  // TMA boxes with the 128-byte swizzle start on 1 KB
-  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // bar_s0 + 8: the second score buffer
-  const uint32_t bar_o = smem_u32(&bar_storage[2]);
-  const uint32_t bar_q = smem_u32(&bar_storage[3]);
-  const uint32_t bar_k0 = smem_u32(&bar_storage[4]);  // + 8: the second K stage
-  const uint32_t bar_v0 = smem_u32(&bar_storage[6]);  // + 8: the second V stage
+  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 8: the second score buffer
+  const uint32_t bar_o0 = smem_u32(&bar_storage[2]);  // + 8: products of odd tiles
+  const uint32_t bar_q = smem_u32(&bar_storage[4]);
+  const uint32_t bar_k0 = smem_u32(&bar_storage[5]);  // + 8: the second K stage
+  const uint32_t bar_v0 = smem_u32(&bar_storage[7]);  // + 8: the second V stage
+  const uint32_t bar_p0 = smem_u32(&bar_storage[9]);  // + 8: the second P buffer; one arrival per softmax warp
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 8; ++i) mbar_init(bar_s0 + 8 * i, 1);
+    for (int i = 0; i < 9; ++i) mbar_init(bar_s0 + 8 * i, 1);
+    mbar_init(bar_p0, kUpSoftmaxThreads / 32);
+    mbar_init(bar_p0 + 8, kUpSoftmaxThreads / 32);
+    abort_flag = 0;
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
@@ -140,215 +159,256 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
-  // Copies are issued by thread 0 alone: two boxes (the two halves of head_dim) per tile, counted in bytes on the
-  // stage's barrier; a tile past the last one is not loaded and never waited for.
-  auto load_k = [&](int tile) {
-    if (threadIdx.x != 0 || tile >= n_tiles) return;
-    const uint32_t bar = bar_k0 + (tile & 1) * 8, dst = smem + kOffK + (tile & 1) * kKvBytes;
-    mbar_expect_tx(bar, kKvBytes);
-    tma_load_4d(dst, &map_k, 0, tile * kUpKeys, kvh, b, bar);
-    tma_load_4d(dst + kKvBoxBytes, &map_k, 64, tile * kUpKeys, kvh, b, bar);
-  };
-  auto load_v = [&](int tile) {
-    if (threadIdx.x != 0 || tile >= n_tiles) return;
-    const uint32_t bar = bar_v0 + (tile & 1) * 8, dst = smem + kOffV + (tile & 1) * kKvBytes;
-    mbar_expect_tx(bar, kKvBytes);
-    tma_load_4d(dst, &map_v, 0, tile * kUpKeys, kvh, b, bar);
-    tma_load_4d(dst + kKvBoxBytes, &map_v, 64, tile * kUpKeys, kvh, b, bar);
-  };
-  if (threadIdx.x == 0) {
-    mbar_expect_tx(bar_q, 2 * kQBoxBytes);  // positions past the chunk's end arrive as zeros
-    tma_load_4d(smem + kOffQ, &map_q, 0, m0, hq0, b, bar_q);
-    tma_load_4d(smem + kOffQ + kQBoxBytes, &map_q, 64, m0, hq0, b, bar_q);
-  }
-  load_k(0);
-  load_v(0);
-  load_k(1);
-  bool ok = __syncthreads_and(mbar_wait(bar_q, 0u) && mbar_wait(bar_k0, 0u));
   const uint32_t tmem = tmem_slot;
-  // this warp's quarter of the lanes (warps w and w + 4 share it); this thread's half of the score / output columns
-  const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
-  const uint32_t t_s = t_lane + kColS + half * kHalf;
-  const uint32_t t_o = t_lane + kColO + half * kOutHalf;
 
-  constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
-  constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
-  constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
-  // Descriptors of the first 16-wide K step of every operand; a later step, stage or query tile is the same descriptor
-  // with its byte offset (in 16-byte units) added to the address field.  Q and K: K-major rows of 128 bytes (eight
-  // rows = 1024 bytes); V: MN-major, the next 64 values of head_dim are the next box; P: un-swizzled K-major.
-  const uint64_t desc_q = umma_smem_desc_sw128(smem + kOffQ, 16, 1024);
-  const uint64_t desc_k = umma_smem_desc_sw128(smem + kOffK, 16, 1024);
-  const uint64_t desc_v = umma_smem_desc_sw128(smem + kOffV, kKvBoxBytes, 1024);
-  const uint64_t desc_p = umma_smem_desc(smem + kOffP, kRowChunkStride, kGroupStride);
-  // S(tile) = Q . K(tile)^T into score buffer tile & 1; issued by thread 0
-  auto issue_scores = [&](int tile) {
-    tcgen05_fence_after_sync();
-    const uint64_t k0 = desc_k + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
-#pragma unroll
-    for (int qt = 0; qt < kUpQTiles; ++qt)
-#pragma unroll
-      for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
-        umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
-                 desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
-                 k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
-    umma_commit(bar_s0 + (tile & 1) * 8);
+  // Bounded wait that also ends as soon as another thread of the CTA has given up.  Called by whole warps; the answer
+  // is the same in every lane, so the warp-wide tensor-memory instructions behind it never run in a part of a warp.
+  auto wait = [&](uint32_t bar, int use) -> bool {  // `use`: how many times the barrier completed before this phase
+    const uint32_t parity = (uint32_t)(use & 1);
+    bool landed = false;
+    for (uint32_t spin = 0; spin < kWaitSpins && !landed; ++spin) {
+      uint32_t done;
+      asm volatile(
+          "{\n"
+          ".reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+          "selp.u32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(done)
+          : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+          : "memory");
+      landed = done != 0;
+      if (!landed && *(volatile int*)&abort_flag != 0) break;
+    }
+    if (!landed) *(volatile int*)&abort_flag = 1;
+    return __all_sync(0xffffffffu, landed);
   };
-  if (ok && threadIdx.x == 0) issue_scores(0);
 
-  float m_run = -INFINITY, l_run = 0.0f;  // l_run: this thread's half of the row sum
-  for (int it = 0; it < n_tiles && ok; ++it) {
-    const int64_t key0 = (int64_t)it * kUpKeys + half * kHalf;  // first key of this thread's columns
-    // (a) S(it) and the previous P . V are complete: the K stage of tile it is free for tile it + 2, the V stage of
-    // tile it - 1 for tile it + 1, P may be overwritten and O rescaled
-    bool landed = mbar_wait(bar_s0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1));
-    if (it > 0) landed = mbar_wait(bar_o, (uint32_t)((it - 1) & 1)) && landed;
-    ok = __syncthreads_and(landed);
-    if (!ok) break;
-    tcgen05_fence_after_sync();
-    load_k(it + 2);
-    load_v(it + 1);
-
-    // (b) this thread's half row of S into registers (one round of loads, one wait), mask, local maximum
-    float s[kHalf];
-#pragma unroll
-    for (int c = 0; c < kHalf / 16; ++c) {
-      uint32_t r[16];
-      tmem_ld16(t_s + (it & 1) * kUpKeys + 16 * c, r);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) s[16 * c + i] = __uint_as_float(r[i]);
-    }
-    tmem_wait_ld();
-    if (key0 + kHalf > lim) {
-#pragma unroll
-      for (int i = 0; i < kHalf; ++i)
-        if (key0 + i >= lim) s[i] = -INFINITY;
-    }
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < kHalf; i += 4) {
-      mx4[0] = fmaxf(mx4[0], s[i]);
-      mx4[1] = fmaxf(mx4[1], s[i + 1]);
-      mx4[2] = fmaxf(mx4[2], s[i + 2]);
-      mx4[3] = fmaxf(mx4[3], s[i + 3]);
-    }
-    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    row_exchange[half][r_local] = mx;
-
-    // (c) K(it + 1) has landed: the next scores run beside this softmax
-    tcgen05_fence_before_sync();
-    ok = __syncthreads_and(it + 1 >= n_tiles || mbar_wait(bar_k0 + ((it + 1) & 1) * 8, (uint32_t)(((it + 1) >> 1) & 1)));
-    if (!ok) break;
-    if (threadIdx.x == 0 && it + 1 < n_tiles) issue_scores(it + 1);
-
-    // (d) row maximum of both halves (log2 units), lazy running maximum -- the same decision in both threads of a row
-    mx = fmaxf(mx, row_exchange[half ^ 1][r_local]) * p.scale_log2;  // the scale is positive
-    const bool grew = mx > m_run + kLazyLog2;
-    const float m_new = grew ? mx : m_run;
-    const float alpha = grew ? up_ex2(m_run - m_new) : 1.0f;  // 0 while m_run is -inf
-    m_run = m_new;
-    l_run *= alpha;
-    const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
-
-    // (e) P = exp2(S * scale - m) as 16-bit pairs, row sum
-    uint32_t packed[kHalf / 2];
-    float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-    for (int i = 0; i < kHalf; i += 4) {
-      const float p0 = up_ex2(fmaf(s[i], p.scale_log2, -m_ref));  // exp2(-inf) = 0 for masked keys
-      const float p1 = up_ex2(fmaf(s[i + 1], p.scale_log2, -m_ref));
-      const float p2 = up_ex2(fmaf(s[i + 2], p.scale_log2, -m_ref));
-      const float p3 = up_ex2(fmaf(s[i + 3], p.scale_log2, -m_ref));
-      sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
-      packed[i / 2] = pack2<T>(p0, p1);
-      packed[i / 2 + 1] = pack2<T>(p2, p3);
-    }
-    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-
-    // (f) rescale this thread's half of the row of O when the running maximum moved
-    if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
-#pragma unroll
-      for (int c = 0; c < kOutHalf / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(t_o + 16 * c, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st16(t_o + 16 * c, r);
-      }
-      tmem_wait_st();
-    }
-
-    // (g) P -> shared memory (K-major A operand), then O += P . V(it)
-    const uint32_t p_row = smem + kOffP + qtile * kPBytes + (half * (kHalf / 8)) * kRowChunkStride +
-                           ((r_local & 127) >> 3) * kGroupStride + (r_local & 7) * 16;
-#pragma unroll
-    for (int c = 0; c < kHalf / 8; ++c)
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kRowChunkStride), "r"(packed[4 * c]),
-                   "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                   : "memory");
-    // V(it) has landed; in the tile that holds the row's last key the rows behind it may hold anything (they are inside
-    // the tensor but past this row's length), and 0 x NaN would poison O, so they are zeroed (whole 128-byte rows: the
-    // swizzle permutes inside a row)
-    ok = mbar_wait(bar_v0 + (it & 1) * 8, (uint32_t)((it >> 1) & 1));
-    const int64_t tile_key0 = (int64_t)it * kUpKeys;
-    if (ok && tile_key0 + kUpKeys > n_keys) {
-      const int first = (int)max((int64_t)0, n_keys - tile_key0);
-      uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kOffV + (it & 1) * kKvBytes;
-      for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpThreads) {
-        const int r = first + (i >> 4), piece = i & 15;  // 8 pieces of 16 bytes in each of the two boxes
-        *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kKvBoxBytes + r * 128 + (piece & 7) * 16) =
-            make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-    fence_async_smem();
-    tcgen05_fence_before_sync();
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    if (threadIdx.x == 0) {
+  if (!softmax) {
+    // ---- issuing warp: the whole warp walks the loop, its first lane issues ------------------------------------------
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
+    constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
+    constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
+    // Descriptors of the first 16-wide K step of every operand; a later step, stage or query tile is the same
+    // descriptor with its byte offset (in 16-byte units) added to the address field.  Q and K: K-major rows of 128
+    // bytes (eight rows = 1024 bytes); V: MN-major, the next 64 values of head_dim are the next box; P: un-swizzled
+    // K-major.
+    const uint64_t desc_q = umma_smem_desc_sw128(smem + kOffQ, 16, 1024);
+    const uint64_t desc_k = umma_smem_desc_sw128(smem + kOffK, 16, 1024);
+    const uint64_t desc_v = umma_smem_desc_sw128(smem + kOffV, kKvBoxBytes, 1024);
+    const uint64_t desc_p = umma_smem_desc(smem + kOffP, kRowChunkStride, kGroupStride);
+    // Two boxes (the two halves of head_dim) per tile, counted in bytes on the stage's barrier; a tile past the last
+    // one is not loaded and never waited for.
+    auto load_k = [&](int tile) {
+      if (tile >= n_tiles || !elect_one()) return;
+      const uint32_t bar = bar_k0 + (tile & 1) * 8, dst = smem + kOffK + (tile & 1) * kKvBytes;
+      mbar_expect_tx(bar, kKvBytes);
+      tma_load_4d(dst, &map_k, 0, tile * kUpKeys, kvh, b, bar);
+      tma_load_4d(dst + kKvBoxBytes, &map_k, 64, tile * kUpKeys, kvh, b, bar);
+    };
+    auto load_v = [&](int tile) {
+      if (tile >= n_tiles || !elect_one()) return;
+      const uint32_t bar = bar_v0 + (tile & 1) * 8, dst = smem + kOffV + (tile & 1) * kKvBytes;
+      mbar_expect_tx(bar, kKvBytes);
+      tma_load_4d(dst, &map_v, 0, tile * kUpKeys, kvh, b, bar);
+      tma_load_4d(dst + kKvBoxBytes, &map_v, 64, tile * kUpKeys, kvh, b, bar);
+    };
+    // S(tile) = Q . K(tile)^T into score buffer tile & 1
+    auto issue_scores = [&](int tile) {
+      if (!elect_one()) return;
       tcgen05_fence_after_sync();
-      const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);  // 16 keys = 16 rows of 128 bytes per step
+      const uint64_t k0 = desc_k + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
       for (int qt = 0; qt < kUpQTiles; ++qt)
 #pragma unroll
-        for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
-          umma_f16(tmem + qt * kColsPerQTile + kColO, desc_p + (uint64_t)((qt * kPBytes + 2 * k * kRowChunkStride) >> 4),
-                   v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
-      umma_commit(bar_o);
+        for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
+          umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
+                   desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
+                   k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
+      umma_commit(bar_s0 + (tile & 1) * 8);
+    };
+    if (elect_one()) {
+      mbar_expect_tx(bar_q, 2 * kQBoxBytes);  // positions past the chunk's end arrive as zeros
+      tma_load_4d(smem + kOffQ, &map_q, 0, m0, hq0, b, bar_q);
+      tma_load_4d(smem + kOffQ + kQBoxBytes, &map_q, 64, m0, hq0, b, bar_q);
     }
-  }
-  row_exchange[half][r_local] = l_run;
-  if (ok) {
-    ok = __syncthreads_and(mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1)));
-    tcgen05_fence_after_sync();
-  }
-  if (ok) {
-    const float l_row = l_run + row_exchange[half ^ 1][r_local];
-    const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+    load_k(0);
+    load_v(0);
+    load_k(1);
+    load_v(1);
+    bool ok = wait(bar_q, 0) && wait(bar_k0, 0);
+    if (ok) issue_scores(0);
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      // S(it + 1) as soon as its K tile is there: its score buffer was read by the softmax of tile it - 1, whose P this
+      // warp has already waited for
+      if (it + 1 < n_tiles) {
+        ok = wait(bar_k0 + ((it + 1) & 1) * 8, (it + 1) >> 1);
+        if (!ok) break;
+        issue_scores(it + 1);
+      }
+      // P(it) is in shared memory (so S(it) is complete and read: the K stage of tile it is free), O is rescaled
+      ok = wait(bar_p0 + (it & 1) * 8, it >> 1);
+      if (!ok) break;
+      load_k(it + 2);
+      ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
+      if (!ok) break;
+      if (elect_one()) {
+        tcgen05_fence_after_sync();
+        const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);  // 16 keys = 16 rows of 128 bytes per step
+        const uint64_t p0 = desc_p + (uint64_t)(((it & 1) * kUpQTiles * kPBytes) >> 4);
 #pragma unroll
-    for (int c = 0; c < kOutHalf / 16; ++c) {
-      uint32_t r[16];
-      tmem_ld16(t_o + 16 * c, r);
-      tmem_wait_ld();
-      if (row < p.q_len) {
-        uint4 lo, hi;
-        lo.x = pack2<T>(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-        lo.y = pack2<T>(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-        lo.z = pack2<T>(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-        lo.w = pack2<T>(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-        hi.x = pack2<T>(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
-        hi.y = pack2<T>(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
-        hi.z = pack2<T>(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
-        hi.w = pack2<T>(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
-        reinterpret_cast<uint4*>(out_row)[2 * c] = lo;
-        reinterpret_cast<uint4*>(out_row)[2 * c + 1] = hi;
+        for (int qt = 0; qt < kUpQTiles; ++qt)
+#pragma unroll
+          for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
+            umma_f16(tmem + qt * kColsPerQTile + kColO, p0 + (uint64_t)((qt * kPBytes + 2 * k * kRowChunkStride) >> 4),
+                     v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_o0 + (it & 1) * 8);
+      }
+      __syncwarp();
+      // the V stage of tile it - 1 is free for tile it + 1 once its product is complete
+      if (it >= 1) {
+        ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+        if (!ok) break;
+        load_v(it + 1);
       }
     }
-  } else if (threadIdx.x == 0) {
-    atomicAdd(&g_prefill_umma_faults, 1);
+  } else {
+    // ---- softmax warps: thread t owns row t ---------------------------------------------------------------------------
+    // this warp's quarter of the lanes, its query tile's columns
+    const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
+    const uint32_t t_s = t_lane + kColS;
+    const uint32_t t_o = t_lane + kColO;
+    const uint32_t p_row0 = smem + kOffP + qtile * kPBytes + ((r_local & 127) >> 3) * kGroupStride + (r_local & 7) * 16;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int64_t key0 = (int64_t)it * kUpKeys;  // first key of the tile
+      ok = wait(bar_s0 + (it & 1) * 8, it >> 1);
+      if (!ok) break;
+      tcgen05_fence_after_sync();
+
+      // (a) this thread's row of S into registers (one round of loads, one wait), mask, row maximum
+      float s[kUpKeys];
+#pragma unroll
+      for (int c = 0; c < kUpKeys / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(t_s + (it & 1) * kUpKeys + 16 * c, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[16 * c + i] = __uint_as_float(r[i]);
+      }
+      tmem_wait_ld();
+      if (key0 + kUpKeys > lim) {
+#pragma unroll
+        for (int i = 0; i < kUpKeys; ++i)
+          if (key0 + i >= lim) s[i] = -INFINITY;
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < kUpKeys; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]);
+        mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]);
+        mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
+
+      // (b) lazy running maximum (log2 units); the row of O is rescaled only when it moved, and only then does the
+      // thread have to know that the previous product is complete
+      const bool grew = mx > m_run + kLazyLog2;
+      const float m_new = grew ? mx : m_run;
+      const float alpha = grew ? up_ex2(m_run - m_new) : 1.0f;  // 0 while m_run is -inf
+      m_run = m_new;
+      l_run *= alpha;
+      const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+      if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
+        ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+        if (!ok) break;
+        tcgen05_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kUpDim / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld16(t_o + 16 * c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st16(t_o + 16 * c, r);
+        }
+        tmem_wait_st();
+      }
+
+      // (c) P = exp2(S * scale - m) as 16-bit pairs, row sum
+      uint32_t packed[kUpKeys / 2];
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < kUpKeys; i += 4) {
+        const float p0 = up_ex2(fmaf(s[i], p.scale_log2, -m_ref));  // exp2(-inf) = 0 for masked keys
+        const float p1 = up_ex2(fmaf(s[i + 1], p.scale_log2, -m_ref));
+        const float p2 = up_ex2(fmaf(s[i + 2], p.scale_log2, -m_ref));
+        const float p3 = up_ex2(fmaf(s[i + 3], p.scale_log2, -m_ref));
+        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+        packed[i / 2] = pack2<T>(p0, p1);
+        packed[i / 2 + 1] = pack2<T>(p2, p3);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+
+      // (d) P -> shared memory (K-major A operand), buffer it & 1: free once the product of tile it - 2 is complete
+      if (it >= 2) {
+        ok = wait(bar_o0 + (it & 1) * 8, (it - 2) >> 1);
+        if (!ok) break;
+      }
+      const uint32_t p_row = p_row0 + (it & 1) * kUpQTiles * kPBytes;
+#pragma unroll
+      for (int c = 0; c < kUpKeys / 8; ++c)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kRowChunkStride), "r"(packed[4 * c]),
+                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
+                     : "memory");
+      // In the tile that holds the last key the V rows behind it may hold anything (they are inside the tensor but past
+      // this row's length), and 0 x NaN would poison O, so they are zeroed (whole 128-byte rows: the swizzle permutes
+      // inside a row)
+      if (key0 + kUpKeys > n_keys) {
+        ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
+        if (!ok) break;
+        const int first = (int)max((int64_t)0, n_keys - key0);
+        uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kOffV + (it & 1) * kKvBytes;
+        for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpSoftmaxThreads) {
+          const int r = first + (i >> 4), piece = i & 15;  // 8 pieces of 16 bytes in each of the two boxes
+          *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kKvBoxBytes + r * 128 + (piece & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      fence_async_smem();
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p0 + (it & 1) * 8);
+    }
+    if (ok) ok = wait(bar_o0 + ((n_tiles - 1) & 1) * 8, (n_tiles - 1) >> 1);
+    if (ok) {
+      tcgen05_fence_after_sync();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll
+      for (int c = 0; c < kUpDim / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(t_o + 16 * c, r);
+        tmem_wait_ld();
+        if (row < p.q_len) {
+          uint4 lo, hi;
+          lo.x = pack2<T>(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          lo.y = pack2<T>(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          lo.z = pack2<T>(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          lo.w = pack2<T>(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          hi.x = pack2<T>(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          hi.y = pack2<T>(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          hi.z = pack2<T>(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          hi.w = pack2<T>(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          reinterpret_cast<uint4*>(out_row)[2 * c] = lo;
+          reinterpret_cast<uint4*>(out_row)[2 * c + 1] = hi;
+        }
+      }
+    }
   }
   tcgen05_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && abort_flag != 0) atomicAdd(&g_prefill_umma_faults, 1);
   if (warp == 0) tmem_free(tmem, kTmemCols);
 }
 
