@@ -73,6 +73,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                            c_i64, c_i64, c_f32, c_i32, c_ptr, c_i32, c_ptr]),
     "anna_peer_signal_wait": (c_i32, [c_ptr, c_i32, c_i32, c_i64, c_i64, c_ptr, c_ptr]),
     "anna_kv_selftest_umma_tma": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, ctypes.POINTER(c_i32), c_ptr]),
+    "anna_kv_selftest_umma_ts": (c_i32, [c_ptr, c_ptr, c_ptr, ctypes.POINTER(c_i32), c_ptr]),
     "anna_tq_decode_plan": (c_i32, [c_i32, c_i32, c_i64, c_i32, c_i32, ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)]),
     "anna_tq_query_scratch_bytes": (c_size, [c_i32, c_i32, c_i32, c_i32]),
     "anna_gqa_decode_turboquant_values": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, c_i64,

@@ -38,24 +38,19 @@ __device__ int32_t g_prefill_umma_faults;
 namespace {
 
 constexpr int kUpQTiles = 2;      // query tiles (128 rows = one accumulator in tensor memory each) per CTA
-constexpr int kUpRows = 128, kUpKeys = 64, kUpDim = 128;
+constexpr int kUpRows = 128, kUpKeys = 128, kUpDim = 128;
 constexpr int kUpCtaRows = kUpQTiles * kUpRows;
 constexpr int kUpSoftmaxThreads = kUpCtaRows;       // one thread per query row (lane of tensor memory)
 constexpr int kUpThreads = kUpSoftmaxThreads + 32;  // and one more warp whose first lane issues every copy and product
-// P (written by the threads): canonical un-swizzled layout of a 128 x 64 16-bit tile, 16-byte chunk c of row r at
-// c * kRowChunkStride + (r / 8) * 128 + (r % 8) * 16 (the 16 extra bytes per chunk plane spread a warp's 16-byte stores
-// over the banks).  Q, K, V (written by TMA): boxes of 64 values x R rows, rows of 128 bytes with the 128-byte swizzle,
-// every box on a 1024-byte boundary.
-constexpr uint32_t kGroupStride = 128;
-constexpr uint32_t kRowChunkStride = (kUpRows / 8) * kGroupStride + 16;
-constexpr uint32_t kPBytes = (kUpKeys / 8) * kRowChunkStride;   // 128 rows x 8 chunks
+// Q, K, V (written by TMA): boxes of 64 values x R rows, rows of 128 bytes with the 128-byte swizzle, every box on a
+// 1024-byte boundary.
 constexpr uint32_t kQBoxBytes = kUpCtaRows * 128;                // 64 values of all 256 rows
-constexpr uint32_t kKvBoxBytes = kUpKeys * 128;                  // 64 values of 64 keys
+constexpr uint32_t kKvBoxBytes = kUpKeys * 128;                  // 64 values of 128 keys
 constexpr uint32_t kKvBytes = 2 * kKvBoxBytes;                   // one K or V tile
-constexpr uint32_t kOffQ = 0, kOffK = 2 * kQBoxBytes, kOffV = kOffK + 2 * kKvBytes, kOffP = kOffV + 2 * kKvBytes;
-constexpr uint32_t kUpSmem = kOffP + 2 * kUpQTiles * kPBytes + 1024;  // Q | K0 K1 | V0 V1 | two buffers of P0 P1, + room to align
-// tensor memory per query tile: two score buffers of 64 columns, then O (128 columns)
-constexpr uint32_t kColS = 0, kColO = 2 * kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
+constexpr uint32_t kOffQ = 0, kOffK = 2 * kQBoxBytes, kOffV = kOffK + 2 * kKvBytes;
+constexpr uint32_t kUpSmem = kOffV + 2 * kKvBytes + 1024;        // Q | K0 K1 | V0 V1, + room to align
+// tensor memory per query tile: S (128 columns; P overwrites the first 64 of them), then O (128 columns)
+constexpr uint32_t kColS = 0, kColO = kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
 constexpr float kLazyLog2 = 8.0f;
 
 __device__ __forceinline__ float up_ex2(float x) {
@@ -63,15 +58,6 @@ __device__ __forceinline__ float up_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16};\n" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-
 // True in exactly one lane of a converged warp.  Unlike a comparison of the lane index, the instruction tells the compiler
 // that the guarded region runs in a single thread, so descriptors and addresses of the tensor-core and copy
 // instructions issued there can live in uniform registers.
@@ -99,7 +85,7 @@ __global__ void __launch_bounds__(kUpThreads, 1)
     gqa_prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_storage[11];  // S0 S1 | O0 O1 | Q | K0 K1 | V0 V1 | P0 P1
+  __shared__ __align__(8) unsigned long long bar_storage[11];  // S: tile 0, 1 | O: 0, 1 | P: 0, 1 | Q | K0 K1 | V0 V1
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;  // set by the first wait that expires; every later wait of the CTA gives up at once
 
@@ -141,16 +127,14 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   }
 
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;  // TMA boxes with the 128-byte swizzle start on 1 KB
-  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 8: the second score buffer
-  const uint32_t bar_o0 = smem_u32(&bar_storage[2]);  // + 8: products of odd tiles
-  const uint32_t bar_q = smem_u32(&bar_storage[4]);
-  const uint32_t bar_k0 = smem_u32(&bar_storage[5]);  // + 8: the second K stage
-  const uint32_t bar_v0 = smem_u32(&bar_storage[7]);  // + 8: the second V stage
-  const uint32_t bar_p0 = smem_u32(&bar_storage[9]);  // + 8: the second P buffer; one arrival per softmax warp
+  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 8: the second query tile
+  const uint32_t bar_o0 = smem_u32(&bar_storage[2]);  // + 8: the second query tile
+  const uint32_t bar_p0 = smem_u32(&bar_storage[4]);  // + 8: the second query tile; one arrival per warp of the tile
+  const uint32_t bar_q = smem_u32(&bar_storage[6]);
+  const uint32_t bar_k0 = smem_u32(&bar_storage[7]);  // + 8: the second K stage
+  const uint32_t bar_v0 = smem_u32(&bar_storage[9]);  // + 8: the second V stage
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 9; ++i) mbar_init(bar_s0 + 8 * i, 1);
-    mbar_init(bar_p0, kUpSoftmaxThreads / 32);
-    mbar_init(bar_p0 + 8, kUpSoftmaxThreads / 32);
+    for (int i = 0; i < 11; ++i) mbar_init(bar_s0 + 8 * i, (i == 4 || i == 5) ? kUpRows / 32 : 1);
     abort_flag = 0;
     mbar_init_fence();
   }
@@ -185,18 +169,16 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   };
 
   if (!softmax) {
-    // ---- issuing warp: the whole warp walks the loop, its first lane issues ------------------------------------------
+    // ---- issuing warp: the whole warp walks the loop, one elected lane issues -----------------------------------------
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
     constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
     constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kUpRows, kUpDim);
     // Descriptors of the first 16-wide K step of every operand; a later step, stage or query tile is the same
     // descriptor with its byte offset (in 16-byte units) added to the address field.  Q and K: K-major rows of 128
-    // bytes (eight rows = 1024 bytes); V: MN-major, the next 64 values of head_dim are the next box; P: un-swizzled
-    // K-major.
+    // bytes (eight rows = 1024 bytes); V: MN-major, the next 64 values of head_dim are the next box.
     const uint64_t desc_q = umma_smem_desc_sw128(smem + kOffQ, 16, 1024);
     const uint64_t desc_k = umma_smem_desc_sw128(smem + kOffK, 16, 1024);
     const uint64_t desc_v = umma_smem_desc_sw128(smem + kOffV, kKvBoxBytes, 1024);
-    const uint64_t desc_p = umma_smem_desc(smem + kOffP, kRowChunkStride, kGroupStride);
     // Two boxes (the two halves of head_dim) per tile, counted in bytes on the stage's barrier; a tile past the last
     // one is not loaded and never waited for.
     auto load_k = [&](int tile) {
@@ -213,19 +195,28 @@ __global__ void __launch_bounds__(kUpThreads, 1)
       tma_load_4d(dst, &map_v, 0, tile * kUpKeys, kvh, b, bar);
       tma_load_4d(dst + kKvBoxBytes, &map_v, 64, tile * kUpKeys, kvh, b, bar);
     };
-    // S(tile) = Q . K(tile)^T into score buffer tile & 1
-    auto issue_scores = [&](int tile) {
+    // S_qt(tile) = Q_qt . K(tile)^T into the score columns of query tile qt
+    auto issue_scores = [&](int qt, int tile) {
       if (!elect_one()) return;
       tcgen05_fence_after_sync();
       const uint64_t k0 = desc_k + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
-      for (int qt = 0; qt < kUpQTiles; ++qt)
+      for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
+        umma_f16(tmem + qt * kColsPerQTile + kColS,
+                 desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
+                 k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
+      umma_commit(bar_s0 + qt * 8);
+    };
+    // O_qt += P_qt(tile) . V(tile): P sits in the first 64 score columns (two keys per column)
+    auto issue_values = [&](int qt, int tile) {
+      if (!elect_one()) return;
+      tcgen05_fence_after_sync();
+      const uint64_t v0 = desc_v + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
-        for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
-          umma_f16(tmem + qt * kColsPerQTile + kColS + (tile & 1) * kUpKeys,
-                   desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
-                   k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
-      umma_commit(bar_s0 + (tile & 1) * 8);
+      for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: eight columns of P, 16 rows of V = 2048 bytes
+        umma_f16_ts(tmem + qt * kColsPerQTile + kColO, tmem + qt * kColsPerQTile + kColS + 8 * k,
+                    v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (tile > 0 || k > 0) ? 1u : 0u);
+      umma_commit(bar_o0 + qt * 8);
     };
     if (elect_one()) {
       mbar_expect_tx(bar_q, 2 * kQBoxBytes);  // positions past the chunk's end arrive as zeros
@@ -237,78 +228,69 @@ __global__ void __launch_bounds__(kUpThreads, 1)
     load_k(1);
     load_v(1);
     bool ok = wait(bar_q, 0) && wait(bar_k0, 0);
-    if (ok) issue_scores(0);
+    if (ok) {
+      issue_scores(0, 0);
+      issue_scores(1, 0);
+    }
+    // Order on the tensor pipe: ... P0.V | S0(next) | P1.V | S1(next) ...  The pipe runs in issue order, so S_qt(next)
+    // overwrites the columns of P_qt only after the product that reads them, and while the threads of one query tile
+    // are busy with their softmax the pipe works for the other tile.
     for (int it = 0; it < n_tiles && ok; ++it) {
-      // S(it + 1) as soon as its K tile is there: its score buffer was read by the softmax of tile it - 1, whose P this
-      // warp has already waited for
-      if (it + 1 < n_tiles) {
-        ok = wait(bar_k0 + ((it + 1) & 1) * 8, (it + 1) >> 1);
+      for (int qt = 0; qt < kUpQTiles && ok; ++qt) {
+        ok = wait(bar_p0 + qt * 8, it);  // P_qt(it) is in tensor memory, O_qt is rescaled
+        if (ok && qt == 0) ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
         if (!ok) break;
-        issue_scores(it + 1);
+        issue_values(qt, it);
+        if (it + 1 < n_tiles) {
+          if (qt == 0) ok = wait(bar_k0 + ((it + 1) & 1) * 8, (it + 1) >> 1);
+          if (!ok) break;
+          issue_scores(qt, it + 1);
+        }
       }
-      // P(it) is in shared memory (so S(it) is complete and read: the K stage of tile it is free), O is rescaled
-      ok = wait(bar_p0 + (it & 1) * 8, it >> 1);
       if (!ok) break;
+      // both softmaxes have read their S(it): the K stage is free; the V stage once the second product is complete
       load_k(it + 2);
-      ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
-      if (!ok) break;
-      if (elect_one()) {
-        tcgen05_fence_after_sync();
-        const uint64_t v0 = desc_v + (uint64_t)(((it & 1) * kKvBytes) >> 4);  // 16 keys = 16 rows of 128 bytes per step
-        const uint64_t p0 = desc_p + (uint64_t)(((it & 1) * kUpQTiles * kPBytes) >> 4);
-#pragma unroll
-        for (int qt = 0; qt < kUpQTiles; ++qt)
-#pragma unroll
-          for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: two chunks of P, two 8-key groups of V
-            umma_f16(tmem + qt * kColsPerQTile + kColO, p0 + (uint64_t)((qt * kPBytes + 2 * k * kRowChunkStride) >> 4),
-                     v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_o0 + (it & 1) * 8);
-      }
-      __syncwarp();
-      // the V stage of tile it - 1 is free for tile it + 1 once its product is complete
-      if (it >= 1) {
-        ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+      if (it + 2 < n_tiles) {
+        ok = wait(bar_o0 + 8, it);
         if (!ok) break;
-        load_v(it + 1);
+        load_v(it + 2);
       }
     }
   } else {
-    // ---- softmax warps: thread t owns row t ---------------------------------------------------------------------------
-    // this warp's quarter of the lanes, its query tile's columns
+    // ---- softmax warps: thread t owns row t; warps 0..3 query tile 0, warps 4..7 query tile 1 --------------------------
     const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
     const uint32_t t_s = t_lane + kColS;
     const uint32_t t_o = t_lane + kColO;
-    const uint32_t p_row0 = smem + kOffP + qtile * kPBytes + ((r_local & 127) >> 3) * kGroupStride + (r_local & 7) * 16;
+    const uint32_t my_s = bar_s0 + qtile * 8, my_o = bar_o0 + qtile * 8, my_p = bar_p0 + qtile * 8;
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int it = 0; it < n_tiles; ++it) {
       const int64_t key0 = (int64_t)it * kUpKeys;  // first key of the tile
-      ok = wait(bar_s0 + (it & 1) * 8, it >> 1);
+      const bool ragged = key0 + kUpKeys > lim;    // some key of the tile is hidden from this row
+      ok = wait(my_s, it);
       if (!ok) break;
       tcgen05_fence_after_sync();
 
-      // (a) this thread's row of S into registers (one round of loads, one wait), mask, row maximum
-      float s[kUpKeys];
-#pragma unroll
-      for (int c = 0; c < kUpKeys / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(t_s + (it & 1) * kUpKeys + 16 * c, r);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) s[16 * c + i] = __uint_as_float(r[i]);
-      }
-      tmem_wait_ld();
-      if (key0 + kUpKeys > lim) {
-#pragma unroll
-        for (int i = 0; i < kUpKeys; ++i)
-          if (key0 + i >= lim) s[i] = -INFINITY;
-      }
+      // (a) first pass over the row of S: its maximum (32 columns at a time; the row is read again below, which costs
+      // tensor-memory bandwidth that is plentiful instead of 128 registers)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kUpKeys; i += 4) {
-        mx4[0] = fmaxf(mx4[0], s[i]);
-        mx4[1] = fmaxf(mx4[1], s[i + 1]);
-        mx4[2] = fmaxf(mx4[2], s[i + 2]);
-        mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      for (int c = 0; c < kUpKeys / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + 32 * c, r);
+        tmem_wait_ld();
+        if (ragged) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + 32 * c + i >= lim) r[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
+        }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
 
@@ -321,7 +303,7 @@ __global__ void __launch_bounds__(kUpThreads, 1)
       l_run *= alpha;
       const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
       if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
-        ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+        ok = wait(my_o, it - 1);
         if (!ok) break;
         tcgen05_fence_after_sync();
 #pragma unroll
@@ -333,55 +315,57 @@ __global__ void __launch_bounds__(kUpThreads, 1)
           for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
           tmem_st16(t_o + 16 * c, r);
         }
-        tmem_wait_st();
       }
 
-      // (c) P = exp2(S * scale - m) as 16-bit pairs, row sum
-      uint32_t packed[kUpKeys / 2];
+      // (c) second pass: P = exp2(S * scale - m) as 16-bit pairs over the columns just read (P of keys 32c .. 32c + 31
+      // lands in columns 16c .. 16c + 15, which hold scores that were already consumed), row sum
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int i = 0; i < kUpKeys; i += 4) {
-        const float p0 = up_ex2(fmaf(s[i], p.scale_log2, -m_ref));  // exp2(-inf) = 0 for masked keys
-        const float p1 = up_ex2(fmaf(s[i + 1], p.scale_log2, -m_ref));
-        const float p2 = up_ex2(fmaf(s[i + 2], p.scale_log2, -m_ref));
-        const float p3 = up_ex2(fmaf(s[i + 3], p.scale_log2, -m_ref));
-        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
-        packed[i / 2] = pack2<T>(p0, p1);
-        packed[i / 2 + 1] = pack2<T>(p2, p3);
+      for (int c = 0; c < kUpKeys / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + 32 * c, r);
+        tmem_wait_ld();
+        if (ragged) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + 32 * c + i >= lim) r[i] = 0xff800000u;  // exp2(-inf) = 0
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float p0 = up_ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_ref));
+          const float p1 = up_ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_ref));
+          const float p2 = up_ex2(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, -m_ref));
+          const float p3 = up_ex2(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
+          sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+          packed[i / 2] = pack2<T>(p0, p1);
+          packed[i / 2 + 1] = pack2<T>(p2, p3);
+        }
+        tmem_st16(t_s + 16 * c, packed);
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_wait_st();
 
-      // (d) P -> shared memory (K-major A operand), buffer it & 1: free once the product of tile it - 2 is complete
-      if (it >= 2) {
-        ok = wait(bar_o0 + (it & 1) * 8, (it - 2) >> 1);
-        if (!ok) break;
-      }
-      const uint32_t p_row = p_row0 + (it & 1) * kUpQTiles * kPBytes;
-#pragma unroll
-      for (int c = 0; c < kUpKeys / 8; ++c)
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + c * kRowChunkStride), "r"(packed[4 * c]),
-                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                     : "memory");
       // In the tile that holds the last key the V rows behind it may hold anything (they are inside the tensor but past
-      // this row's length), and 0 x NaN would poison O, so they are zeroed (whole 128-byte rows: the swizzle permutes
-      // inside a row)
-      if (key0 + kUpKeys > n_keys) {
+      // this row's length), and 0 x NaN would poison O, so the threads of query tile 0 (whose product is issued first)
+      // zero them (whole 128-byte rows: the swizzle permutes inside a row)
+      if (qtile == 0 && key0 + kUpKeys > n_keys) {
         ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
         if (!ok) break;
         const int first = (int)max((int64_t)0, n_keys - key0);
         uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kOffV + (it & 1) * kKvBytes;
-        for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpSoftmaxThreads) {
+        for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpRows) {
           const int r = first + (i >> 4), piece = i & 15;  // 8 pieces of 16 bytes in each of the two boxes
           *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kKvBoxBytes + r * 128 + (piece & 7) * 16) =
               make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_async_smem();
       }
-      fence_async_smem();
       tcgen05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p0 + (it & 1) * 8);
+      if (lane == 0) mbar_arrive(my_p);
     }
-    if (ok) ok = wait(bar_o0 + ((n_tiles - 1) & 1) * 8, (n_tiles - 1) >> 1);
+    if (ok) ok = wait(my_o, n_tiles - 1);
     if (ok) {
       tcgen05_fence_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;

@@ -156,6 +156,65 @@ __global__ void __launch_bounds__(128) umma_tma_selftest_kernel(const __grid_con
   if (warp == 0) tmem_free(tmem, 256);
 }
 
+// Third self-test: the A operand in tensor memory (the P . V arrangement of the prefill kernel once P stays there):
+//   D[128 x 128] = A[128 x 128] . B[128 x 128]     bf16; thread r packs row r of A into 64 columns of its lane with
+//                                                  tcgen05.st, B arrives by TMA, MN-major
+__global__ void __launch_bounds__(128) umma_ts_selftest_kernel(const __nv_bfloat16* a, const __grid_constant__ CUtensorMap map_b,
+                                                               float* d, int32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) unsigned long long bar_storage[2];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t s_b = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t bar_load = smem_u32(&bar_storage[0]), bar_mma = smem_u32(&bar_storage[1]);
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar_load, 2 * kTmaBox);
+    for (int h = 0; h < 2; ++h) tma_load_2d(s_b + h * kTmaBox, &map_b, 64 * h, 0, bar_load);
+  }
+  // row threadIdx.x of A: 128 values = 64 columns (two per column, the lower K index in the lower half)
+  const uint32_t* a_row = reinterpret_cast<const uint32_t*>(a + threadIdx.x * 128);
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[16];
+    for (int j = 0; j < 16; ++j) r[j] = a_row[16 * c + j];
+    tmem_st16(tmem_addr(tmem, 32 * warp, 16 * c), r);
+  }
+  tmem_wait_st();
+  tcgen05_fence_before_sync();
+  bool ok = __syncthreads_and(mbar_wait(bar_load, 0u));
+  if (ok && threadIdx.x == 0) {
+    tcgen05_fence_after_sync();
+    constexpr uint32_t idesc = umma_idesc(kUmmaBF16, kUmmaBF16, false, true, 128, 128);
+    for (int k = 0; k < 8; ++k)  // 16 K indices: eight columns of A, 16 rows of B = 2048 bytes
+      umma_f16_ts(tmem + 128, tmem + 8 * k, umma_smem_desc_sw128(s_b + k * 2048, kTmaBox, 1024), idesc, k > 0);
+    umma_commit(bar_mma);
+  }
+  if (ok) ok = __syncthreads_and(mbar_wait(bar_mma, 0u));
+  tcgen05_fence_after_sync();
+  if (ok) {
+    for (int c = 0; c < 8; ++c) {
+      uint32_t r[16];
+      tmem_ld16(tmem_addr(tmem, 32 * warp, 128 + 16 * c), r);
+      tmem_wait_ld();
+      for (int j = 0; j < 16; ++j) d[threadIdx.x * 128 + 16 * c + j] = __uint_as_float(r[j]);
+    }
+  } else if (threadIdx.x == 0) {
+    *status = 1;
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 256);
+}
+
 }  // namespace anna
 
 // a1 uint8 [128][128] (e4m3 bytes), b1 uint8 [16][128], a2 f16 [128 (K)][128 (rows)], b2 f16 [128 (K)][16]:
@@ -220,6 +279,41 @@ extern "C" int anna_kv_selftest_umma_tma(const void* a, const void* b1, const vo
   cudaFree(flag);
   if (err != cudaSuccess)
     return set_error(ANNA_ERR_CUDA, "tensor-memory / TMA self-test failed: %s", cudaGetErrorString(err));
+  *status = (int)value;
+  return ANNA_OK;
+}
+
+// a, b: bf16 [128][128] row-major device arrays (16-byte aligned); d = a . b (float [128][128]) with a held in tensor
+// memory and b brought in by TMA.  *status as for anna_kv_selftest_umma_tma.  Synchronises the stream.  No counterpart in
+// the reference.
+extern "C" int anna_kv_selftest_umma_ts(const void* a, const void* b, float* d, int* status, anna_stream_t stream) {
+  using namespace anna;
+  ANNA_REQUIRE(a && b && d && status, "anna_kv_selftest_umma_ts: null pointer argument");
+  CUtensorMap map;
+  const uint64_t extents[2] = {128, 128};
+  const uint64_t strides[1] = {256};
+  const uint32_t box[2] = {64, 128};
+  if (!encode_map_16bit(&map, b, 2, extents, strides, box)) {
+    *status = 2;
+    return ANNA_OK;
+  }
+  int32_t* flag = nullptr;
+  ANNA_CUDA_CHECK(cudaMalloc(&flag, sizeof(int32_t)));
+  constexpr int kSmem = 2 * (int)kTmaBox + 1024;
+  cudaError_t err = cudaMemsetAsync(flag, 0, sizeof(int32_t), (cudaStream_t)stream);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(umma_ts_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (err == cudaSuccess) {
+    umma_ts_selftest_kernel<<<1, 128, kSmem, (cudaStream_t)stream>>>(static_cast<const __nv_bfloat16*>(a), map, d, flag);
+    err = cudaGetLastError();
+  }
+  int32_t value = -1;
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(&value, flag, sizeof(value), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
+  cudaFree(flag);
+  if (err != cudaSuccess)
+    return set_error(ANNA_ERR_CUDA, "tensor-memory operand self-test failed: %s", cudaGetErrorString(err));
   *status = (int)value;
   return ANNA_OK;
 }

@@ -75,6 +75,13 @@ int anna_kv_selftest_umma(const void* a1, const void* b1, const void* a2, const 
 int anna_kv_selftest_umma_tma(const void* a, const void* b1, const void* b2, float* d1, float* d2, int* status,
                               anna_stream_t stream);
 
+/*
+ * Third self-test: d = a . b (bf16 [128][128] operands, float [128][128] result) with a packed into tensor memory by the
+ * threads (the A operand of the instruction read from there) and b brought in by TMA, MN-major.  *status as above.
+ * Synchronises the stream.  No counterpart in the reference.
+ */
+int anna_kv_selftest_umma_ts(const void* a, const void* b, float* d, int* status, anna_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Split-K scratch shared by all decode entry points.  The context is cut into chunks of `chunk_tokens` tokens; every
  * (row, query head, chunk) leaves a partial in caller-owned float32 buffers

@@ -64,3 +64,20 @@ def test_tma_fed_products_match_fp32_reference(cuda_device):
     assert status.value == 0
     torch.testing.assert_close(d1, a.float() @ b1.float().t(), atol=1e-3, rtol=1e-4)
     torch.testing.assert_close(d2, a.float() @ b2.float(), atol=1e-3, rtol=1e-4)
+
+
+def test_tensor_memory_operand_product_matches_fp32_reference(cuda_device):
+    """anna_kv_selftest_umma_ts: the A operand packed into tensor memory by the threads (two bf16 values per column), B by
+    TMA and MN-major -- the P . V arrangement of the prefill kernel."""
+    gen = torch.Generator(device=cuda_device).manual_seed(13)
+    a = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.bfloat16)
+    b = torch.randn(128, 128, device=cuda_device, generator=gen).to(torch.bfloat16)
+    d = torch.zeros(128, 128, device=cuda_device, dtype=torch.float32)
+    status = ctypes.c_int(-1)
+    with torch.cuda.device(cuda_device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(_lib.lib().anna_kv_selftest_umma_ts(
+            ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(d.data_ptr()),
+            ctypes.byref(status), stream), "anna_kv_selftest_umma_ts")
+    assert status.value == 0
+    torch.testing.assert_close(d, a.float() @ b.float(), atol=1e-3, rtol=1e-4)
