@@ -52,12 +52,28 @@ constexpr uint32_t kUpSmem = kOffV + 2 * kKvBytes + 1024;        // Q | K0 K1 | 
 // tensor memory per query tile: S (128 columns; P overwrites the first 64 of them), then O (128 columns)
 constexpr uint32_t kColS = 0, kColO = kUpKeys, kColsPerQTile = 256, kTmemCols = kUpQTiles * kColsPerQTile;
 constexpr float kLazyLog2 = 8.0f;
+constexpr uint32_t kUpWaitSpins = 1u << 18;  // tries of a wait before the CTA gives up (each suspends for a system-chosen time)
 
 __device__ __forceinline__ float up_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// The two values of a 2 x 16-bit register.
+template <typename T>
+__device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t v, float& lo, float& hi) {
+  lo = __uint_as_float(v << 16);
+  hi = __uint_as_float(v & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t v, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+  lo = f.x;
+  hi = f.y;
+}
+
 // True in exactly one lane of a converged warp.  Unlike a comparison of the lane index, the instruction tells the compiler
 // that the guarded region runs in a single thread, so descriptors and addresses of the tensor-core and copy
 // instructions issued there can live in uniform registers.
@@ -114,8 +130,10 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
   cta_limit = max(cta_limit, (int64_t)0);
   const int n_tiles = (int)((cta_limit + kUpKeys - 1) / kUpKeys);
-  int64_t lim = 0;  // keys this thread's row sees
-  if (row < p.q_len) lim = max((int64_t)0, p.causal ? min(n_keys, past + row + 1) : n_keys);
+  // key positions are tensor-map coordinates: they fit 32 bits
+  const int n_keys32 = (int)min(n_keys, (int64_t)0x7fffffff);
+  int lim = 0;  // keys this thread's row sees
+  if (row < p.q_len) lim = (int)max((int64_t)0, p.causal ? min((int64_t)n_keys32, past + row + 1) : (int64_t)n_keys32);
 
   T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + (int64_t)hq * p.out_stride_h +
                (int64_t)row * p.out_stride_t;
@@ -150,16 +168,16 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   auto wait = [&](uint32_t bar, int use) -> bool {  // `use`: how many times the barrier completed before this phase
     const uint32_t parity = (uint32_t)(use & 1);
     bool landed = false;
-    for (uint32_t spin = 0; spin < kWaitSpins && !landed; ++spin) {
+    for (uint32_t spin = 0; spin < kUpWaitSpins && !landed; ++spin) {
       uint32_t done;
-      asm volatile(
+      asm volatile(  // no suspend-time hint: with one the waits of a healthy CTA were measured 4 % slower
           "{\n"
           ".reg .pred p;\n"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
           "selp.u32 %0, 1, 0, p;\n"
           "}\n"
           : "=r"(done)
-          : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+          : "r"(bar), "r"(parity)
           : "memory");
       landed = done != 0;
       if (!landed && *(volatile int*)&abort_flag != 0) break;
@@ -265,94 +283,101 @@ __global__ void __launch_bounds__(kUpThreads, 1)
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int it = 0; it < n_tiles; ++it) {
-      const int64_t key0 = (int64_t)it * kUpKeys;  // first key of the tile
-      const bool ragged = key0 + kUpKeys > lim;    // some key of the tile is hidden from this row
+      const int key0 = it * kUpKeys;  // first key of the tile
+      const int visible = max(0, min(kUpKeys, lim - key0));  // keys of the tile this row sees
+      constexpr int kChunk = 32;  // score columns per tensor-memory load
       ok = wait(my_s, it);
       if (!ok) break;
       tcgen05_fence_after_sync();
 
-      // (a) first pass over the row of S: its maximum (32 columns at a time; the row is read again below, which costs
-      // tensor-memory bandwidth that is plentiful instead of 128 registers)
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < kUpKeys / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + 32 * c, r);
-        tmem_wait_ld();
-        if (ragged) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (key0 + 32 * c + i >= lim) r[i] = 0xff800000u;  // -inf
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
-          mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
-          mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
-          mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
-        }
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
-
-      // (b) lazy running maximum (log2 units); the row of O is rescaled only when it moved, and only then does the
-      // thread have to know that the previous product is complete
-      const bool grew = mx > m_run + kLazyLog2;
-      const float m_new = grew ? mx : m_run;
-      const float alpha = grew ? up_ex2(m_run - m_new) : 1.0f;  // 0 while m_run is -inf
-      m_run = m_new;
-      l_run *= alpha;
-      const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
-      if (it > 0 && __any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
-        ok = wait(my_o, it - 1);
-        if (!ok) break;
-        tcgen05_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < kUpDim / 16; ++c) {
-          uint32_t r[16];
-          tmem_ld16(t_o + 16 * c, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st16(t_o + 16 * c, r);
-        }
-      }
-
-      // (c) second pass: P = exp2(S * scale - m) as 16-bit pairs over the columns just read (P of keys 32c .. 32c + 31
-      // lands in columns 16c .. 16c + 15, which hold scores that were already consumed), row sum
+      // One pass over the row of S, 32 columns at a time (the next 32 are on their way from tensor memory meanwhile):
+      // P = exp2(S * scale - m) against the running maximum as it stands, packed to 16-bit pairs and stored over scores
+      // that were already consumed (keys 32c .. 32c + 31 into columns 16c .. 16c + 15).  The maximum of every 32 scores
+      // is taken before they are exponentiated; only when a row of the warp would move its running maximum by more than
+      // 2^8 (never, after the first tiles, on ordinary inputs) does the warp stop to rescale O, the row sum and the part
+      // of P it has stored.
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t r[2][kChunk];
+      tmem_ld32(t_s, r[0]);
 #pragma unroll
-      for (int c = 0; c < kUpKeys / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + 32 * c, r);
+      for (int c = 0; c < kUpKeys / kChunk; ++c) {
         tmem_wait_ld();
-        if (ragged) {
+        if (c + 1 < kUpKeys / kChunk) tmem_ld32(t_s + kChunk * (c + 1), r[(c + 1) & 1]);
+        uint32_t(&x)[kChunk] = r[c & 1];
+        if (kChunk * c + kChunk > visible) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (key0 + 32 * c + i >= lim) r[i] = 0xff800000u;  // exp2(-inf) = 0
+          for (int i = 0; i < kChunk; ++i)
+            if (kChunk * c + i >= visible) x[i] = 0xff800000u;  // -inf: exp2 gives 0
         }
-        uint32_t packed[16];
+        float mx4[4] = {__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]), __uint_as_float(x[3])};
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float p0 = up_ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_ref));
-          const float p1 = up_ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_ref));
-          const float p2 = up_ex2(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, -m_ref));
-          const float p3 = up_ex2(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
+        for (int i = 4; i < kChunk; i += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(x[i]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(x[i + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(x[i + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(x[i + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
+        const bool grew = mx > m_run + kLazyLog2;
+        if (__any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
+          const float alpha = grew ? up_ex2(m_run - mx) : 1.0f;  // 0 while m_run is -inf
+          if (grew) m_run = mx;
+          l_run *= alpha;
+          sum4[0] *= alpha; sum4[1] *= alpha; sum4[2] *= alpha; sum4[3] *= alpha;
+          if (it > 0) {  // the rows of O, for which the previous product has to be complete
+            ok = wait(my_o, it - 1);
+            if (!ok) break;
+            tcgen05_fence_after_sync();
+#pragma unroll 1
+            for (int cc = 0; cc < kUpDim / 16; ++cc) {
+              uint32_t o[16];
+              tmem_ld16(t_o + 16 * cc, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st16(t_o + 16 * cc, o);
+            }
+          }
+#pragma unroll 1
+          for (int cc = 0; cc < c; ++cc) {  // the part of P already stored
+            uint32_t q[16];
+            tmem_ld16(t_s + 16 * cc, q);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float lo, hi;
+              unpack2<T>(q[i], lo, hi);
+              q[i] = pack2<T>(lo * alpha, hi * alpha);
+            }
+            tmem_st16(t_s + 16 * cc, q);
+          }
+          tmem_wait_ld();  // the scores on their way are in registers before the next instruction touches them
+        }
+        const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+        uint32_t packed[kChunk / 2];
+#pragma unroll
+        for (int i = 0; i < kChunk; i += 4) {
+          const float p0 = up_ex2(fmaf(__uint_as_float(x[i]), p.scale_log2, -m_ref));
+          const float p1 = up_ex2(fmaf(__uint_as_float(x[i + 1]), p.scale_log2, -m_ref));
+          const float p2 = up_ex2(fmaf(__uint_as_float(x[i + 2]), p.scale_log2, -m_ref));
+          const float p3 = up_ex2(fmaf(__uint_as_float(x[i + 3]), p.scale_log2, -m_ref));
           sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
           packed[i / 2] = pack2<T>(p0, p1);
           packed[i / 2 + 1] = pack2<T>(p2, p3);
         }
-        tmem_st16(t_s + 16 * c, packed);
+        tmem_st16(t_s + (kChunk / 2) * c, packed);
       }
+      if (!ok) break;
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
 
       // In the tile that holds the last key the V rows behind it may hold anything (they are inside the tensor but past
       // this row's length), and 0 x NaN would poison O, so the threads of query tile 0 (whose product is issued first)
       // zero them (whole 128-byte rows: the swizzle permutes inside a row)
-      if (qtile == 0 && key0 + kUpKeys > n_keys) {
+      if (qtile == 0 && key0 + kUpKeys > n_keys32) {
         ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
         if (!ok) break;
-        const int first = (int)max((int64_t)0, n_keys - key0);
+        const int first = max(0, n_keys32 - key0);
         uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kOffV + (it & 1) * kKvBytes;
         for (int i = threadIdx.x; i < (kUpKeys - first) * 16; i += kUpRows) {
           const int r = first + (i >> 4), piece = i & 15;  // 8 pieces of 16 bytes in each of the two boxes
