@@ -88,6 +88,29 @@ def test_keys_behind_a_rows_length_may_hold_anything(cuda_device, dim, q_len):
     assert max_abs <= ATOL[torch.bfloat16], (max_abs, rel_l2)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scores_that_keep_growing_along_the_keys(cuda_device, dtype):
+    """Keys whose scale steps up every 80 positions: a row's running maximum moves by far more than the 2^8 the
+    tensor-memory kernel tolerates without rescaling, inside key tiles (after part of P was stored) and between them
+    (after O was accumulated), so its rescaling of O, of the row sum and of the stored part of P is what is compared."""
+    gen = torch.Generator().manual_seed(77)
+    batch, heads, kv_heads, dim, q_len, key_len = 2, 8, 2, 128, 192, 1000
+    q = torch.randn(batch, heads, q_len, dim, generator=gen)
+    k = torch.randn(batch, kv_heads, key_len, dim, generator=gen)
+    v = torch.randn(batch, kv_heads, key_len, dim, generator=gen) * 0.25   # nearly one-hot rows: outputs are single values
+    steps = (torch.arange(key_len) // 80).float()
+    k = k * (1.0 + 3.0 * steps)[None, None, :, None]          # scores up to 38 times larger at the far end
+    k[1, :, 500:] *= -1.0                                      # second row: they shrink again for queries that agree
+    q, k, v = (t.to(dtype).to(cuda_device) for t in (q, k, v))
+    n = torch.tensor((key_len, 901), dtype=torch.long, device=cuda_device)
+    for causal in (True, False):
+        out = grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=n, causal=causal)
+        expected = _oracle(q, k, v, n, causal)
+        assert bool(torch.isfinite(out).all())
+        max_abs, rel_l2 = error_stats(to_np(out), expected)
+        assert max_abs <= ATOL[dtype], (causal, max_abs, rel_l2)
+
+
 def test_tensor_memory_kernel_reported_no_expired_wait(cuda_device):
     """Runs after the cases above in this file: none of the bounded waits of the copy-engine / tensor-memory kernels may
     have run out."""
