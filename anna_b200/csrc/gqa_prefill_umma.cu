@@ -41,7 +41,14 @@ constexpr int kUpQTiles = 2;      // query tiles (128 rows = one accumulator in 
 constexpr int kUpRows = 128, kUpKeys = 128, kUpDim = 128;
 constexpr int kUpCtaRows = kUpQTiles * kUpRows;
 constexpr int kUpSoftmaxThreads = kUpCtaRows;       // one thread per query row (lane of tensor memory)
-constexpr int kUpThreads = kUpSoftmaxThreads + 32;  // and one more warp whose first lane issues every copy and product
+constexpr int kUpThreads = kUpSoftmaxThreads + 128;  // and a third group of four warps, one of which issues every copy and product
+// Registers move between the groups of four warps: the issuing group keeps 72 per thread and the softmax groups take
+// 216, enough for a whole row of scores.  The CTA's pool is what it was launched with (384 threads x 168, the most the
+// compiler may use at this CTA size); a group that asked for more than the pool holds would wait for ever.
+constexpr int kUpLaunchRegs = 168, kUpIssuerRegs = 72, kUpSoftmaxRegs = 216;
+static_assert(128 * kUpIssuerRegs + kUpSoftmaxThreads * kUpSoftmaxRegs <= kUpThreads * kUpLaunchRegs,
+              "register split exceeds the CTA's pool");
+static_assert(kUpLaunchRegs == (65536 / kUpThreads) / 8 * 8, "launch registers per thread");
 // Q, K, V (written by TMA): boxes of 64 values x R rows, rows of 128 bytes with the 128-byte swizzle, every box on a
 // 1024-byte boundary.
 constexpr uint32_t kQBoxBytes = kUpCtaRows * 128;                // 64 values of all 256 rows
@@ -59,21 +66,6 @@ __device__ __forceinline__ float up_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// The two values of a 2 x 16-bit register.
-template <typename T>
-__device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi);
-template <>
-__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t v, float& lo, float& hi) {
-  lo = __uint_as_float(v << 16);
-  hi = __uint_as_float(v & 0xffff0000u);
-}
-template <>
-__device__ __forceinline__ void unpack2<__half>(uint32_t v, float& lo, float& hi) {
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
-  lo = f.x;
-  hi = f.y;
-}
-
 // True in exactly one lane of a converged warp.  Unlike a comparison of the lane index, the instruction tells the compiler
 // that the guarded region runs in a single thread, so descriptors and addresses of the tensor-core and copy
 // instructions issued there can live in uniform registers.
@@ -187,6 +179,12 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   };
 
   if (!softmax) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kUpIssuerRegs));
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kUpSoftmaxRegs));
+  }
+  if (!softmax) {
+    if (warp == kUpSoftmaxThreads / 32) {
     // ---- issuing warp: the whole warp walks the loop, one elected lane issues -----------------------------------------
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
     constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kUpRows, kUpKeys);
@@ -274,6 +272,7 @@ __global__ void __launch_bounds__(kUpThreads, 1)
         load_v(it + 2);
       }
     }
+    }
   } else {
     // ---- softmax warps: thread t owns row t; warps 0..3 query tile 0, warps 4..7 query tile 1 --------------------------
     const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsPerQTile);
@@ -290,84 +289,68 @@ __global__ void __launch_bounds__(kUpThreads, 1)
       if (!ok) break;
       tcgen05_fence_after_sync();
 
-      // One pass over the row of S, 32 columns at a time (the next 32 are on their way from tensor memory meanwhile):
-      // P = exp2(S * scale - m) against the running maximum as it stands, packed to 16-bit pairs and stored over scores
-      // that were already consumed (keys 32c .. 32c + 31 into columns 16c .. 16c + 15).  The maximum of every 32 scores
-      // is taken before they are exponentiated; only when a row of the warp would move its running maximum by more than
-      // 2^8 (never, after the first tiles, on ordinary inputs) does the warp stop to rescale O, the row sum and the part
-      // of P it has stored.
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t r[2][kChunk];
-      tmem_ld32(t_s, r[0]);
+      // The whole row of S into registers (four loads in flight, one wait), mask, row maximum
+      uint32_t x[kUpKeys];
 #pragma unroll
-      for (int c = 0; c < kUpKeys / kChunk; ++c) {
-        tmem_wait_ld();
-        if (c + 1 < kUpKeys / kChunk) tmem_ld32(t_s + kChunk * (c + 1), r[(c + 1) & 1]);
-        uint32_t(&x)[kChunk] = r[c & 1];
-        if (kChunk * c + kChunk > visible) {
+      for (int c = 0; c < kUpKeys / kChunk; ++c) tmem_ld32(t_s + kChunk * c, *reinterpret_cast<uint32_t(*)[kChunk]>(&x[kChunk * c]));
+      tmem_wait_ld();
+      if (visible < kUpKeys) {
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i)
-            if (kChunk * c + i >= visible) x[i] = 0xff800000u;  // -inf: exp2 gives 0
-        }
-        float mx4[4] = {__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]), __uint_as_float(x[3])};
+        for (int i = 0; i < kUpKeys; ++i)
+          if (i >= visible) x[i] = 0xff800000u;  // -inf: exp2 gives 0
+      }
+      float mx4[4] = {__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]), __uint_as_float(x[3])};
 #pragma unroll
-        for (int i = 4; i < kChunk; i += 4) {
-          mx4[0] = fmaxf(mx4[0], __uint_as_float(x[i]));
-          mx4[1] = fmaxf(mx4[1], __uint_as_float(x[i + 1]));
-          mx4[2] = fmaxf(mx4[2], __uint_as_float(x[i + 2]));
-          mx4[3] = fmaxf(mx4[3], __uint_as_float(x[i + 3]));
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
-        const bool grew = mx > m_run + kLazyLog2;
-        if (__any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
-          const float alpha = grew ? up_ex2(m_run - mx) : 1.0f;  // 0 while m_run is -inf
-          if (grew) m_run = mx;
-          l_run *= alpha;
-          sum4[0] *= alpha; sum4[1] *= alpha; sum4[2] *= alpha; sum4[3] *= alpha;
-          if (it > 0) {  // the rows of O, for which the previous product has to be complete
-            ok = wait(my_o, it - 1);
-            if (!ok) break;
-            tcgen05_fence_after_sync();
+      for (int i = 4; i < kUpKeys; i += 4) {
+        mx4[0] = fmaxf(mx4[0], __uint_as_float(x[i]));
+        mx4[1] = fmaxf(mx4[1], __uint_as_float(x[i + 1]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(x[i + 2]));
+        mx4[3] = fmaxf(mx4[3], __uint_as_float(x[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
+
+      // Lazy running maximum (log2 units): it moves only when it would grow by more than 2^8, and only then is the row
+      // of O rescaled, for which the previous product has to be complete
+      const bool grew = mx > m_run + kLazyLog2;
+      if (__any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
+        const float alpha = grew ? up_ex2(m_run - mx) : 1.0f;  // 0 while m_run is -inf
+        if (grew) m_run = mx;
+        l_run *= alpha;
+        if (it > 0) {
+          ok = wait(my_o, it - 1);
+          if (!ok) break;
+          tcgen05_fence_after_sync();
 #pragma unroll 1
-            for (int cc = 0; cc < kUpDim / 16; ++cc) {
-              uint32_t o[16];
-              tmem_ld16(t_o + 16 * cc, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st16(t_o + 16 * cc, o);
-            }
-          }
-#pragma unroll 1
-          for (int cc = 0; cc < c; ++cc) {  // the part of P already stored
-            uint32_t q[16];
-            tmem_ld16(t_s + 16 * cc, q);
+          for (int cc = 0; cc < kUpDim / 16; ++cc) {
+            uint32_t o[16];
+            tmem_ld16(t_o + 16 * cc, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float lo, hi;
-              unpack2<T>(q[i], lo, hi);
-              q[i] = pack2<T>(lo * alpha, hi * alpha);
-            }
-            tmem_st16(t_s + 16 * cc, q);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(t_o + 16 * cc, o);
           }
-          tmem_wait_ld();  // the scores on their way are in registers before the next instruction touches them
         }
-        const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+      }
+      const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+
+      // P = exp2(S * scale - m) as 16-bit pairs over the scores (keys 32c .. 32c + 31 into columns 16c .. 16c + 15),
+      // row sum
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < kUpKeys / kChunk; ++c) {
         uint32_t packed[kChunk / 2];
 #pragma unroll
         for (int i = 0; i < kChunk; i += 4) {
-          const float p0 = up_ex2(fmaf(__uint_as_float(x[i]), p.scale_log2, -m_ref));
-          const float p1 = up_ex2(fmaf(__uint_as_float(x[i + 1]), p.scale_log2, -m_ref));
-          const float p2 = up_ex2(fmaf(__uint_as_float(x[i + 2]), p.scale_log2, -m_ref));
-          const float p3 = up_ex2(fmaf(__uint_as_float(x[i + 3]), p.scale_log2, -m_ref));
+          const float p0 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i]), p.scale_log2, -m_ref));
+          const float p1 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 1]), p.scale_log2, -m_ref));
+          const float p2 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 2]), p.scale_log2, -m_ref));
+          const float p3 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 3]), p.scale_log2, -m_ref));
           sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
           packed[i / 2] = pack2<T>(p0, p1);
           packed[i / 2 + 1] = pack2<T>(p2, p3);
         }
         tmem_st16(t_s + (kChunk / 2) * c, packed);
       }
-      if (!ok) break;
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
 
