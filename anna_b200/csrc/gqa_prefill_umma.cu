@@ -42,10 +42,10 @@ constexpr int kUpRows = 128, kUpKeys = 128, kUpDim = 128;
 constexpr int kUpCtaRows = kUpQTiles * kUpRows;
 constexpr int kUpSoftmaxThreads = kUpCtaRows;       // one thread per query row (lane of tensor memory)
 constexpr int kUpThreads = kUpSoftmaxThreads + 128;  // and a third group of four warps, one of which issues every copy and product
-// Registers move between the groups of four warps: the issuing group keeps 72 per thread and the softmax groups take
-// 216, enough for a whole row of scores.  The CTA's pool is what it was launched with (384 threads x 168, the most the
+// Registers move between the groups of four warps: the issuing group keeps 136 per thread (its descriptors) and the softmax groups take
+// 184, enough for a whole row of scores.  The CTA's pool is what it was launched with (384 threads x 168, the most the
 // compiler may use at this CTA size); a group that asked for more than the pool holds would wait for ever.
-constexpr int kUpLaunchRegs = 168, kUpIssuerRegs = 72, kUpSoftmaxRegs = 216;
+constexpr int kUpLaunchRegs = 168, kUpIssuerRegs = 136, kUpSoftmaxRegs = 184;
 static_assert(128 * kUpIssuerRegs + kUpSoftmaxThreads * kUpSoftmaxRegs <= kUpThreads * kUpLaunchRegs,
               "register split exceeds the CTA's pool");
 static_assert(kUpLaunchRegs == (65536 / kUpThreads) / 8 * 8, "launch registers per thread");
@@ -195,83 +195,101 @@ __global__ void __launch_bounds__(kUpThreads, 1)
     const uint64_t desc_q = umma_smem_desc_sw128(smem + kOffQ, 16, 1024);
     const uint64_t desc_k = umma_smem_desc_sw128(smem + kOffK, 16, 1024);
     const uint64_t desc_v = umma_smem_desc_sw128(smem + kOffV, kKvBoxBytes, 1024);
+    // The stage of a tile (tile & 1), the query tile and "first tile" are compile-time constants in everything below (the
+    // loop over the tiles is unrolled by two): descriptors, tensor-memory addresses and barrier addresses are then
+    // loop-invariant bases plus constants, which the compiler keeps in uniform registers.  With the stage taken from the
+    // loop counter every product cost about 125 clocks to issue, twice the 64 it takes the tensor pipe to execute.
     // Two boxes (the two halves of head_dim) per tile, counted in bytes on the stage's barrier; a tile past the last
     // one is not loaded and never waited for.
-    auto load_k = [&](int tile) {
+    auto load_k = [&](auto stage_c, int tile) {
+      constexpr int kStage = decltype(stage_c)::value;
       if (tile >= n_tiles || !elect_one()) return;
-      const uint32_t bar = bar_k0 + (tile & 1) * 8, dst = smem + kOffK + (tile & 1) * kKvBytes;
+      const uint32_t bar = bar_k0 + kStage * 8, dst = smem + kOffK + kStage * kKvBytes;
       mbar_expect_tx(bar, kKvBytes);
       tma_load_4d(dst, &map_k, 0, tile * kUpKeys, kvh, b, bar);
       tma_load_4d(dst + kKvBoxBytes, &map_k, 64, tile * kUpKeys, kvh, b, bar);
     };
-    auto load_v = [&](int tile) {
+    auto load_v = [&](auto stage_c, int tile) {
+      constexpr int kStage = decltype(stage_c)::value;
       if (tile >= n_tiles || !elect_one()) return;
-      const uint32_t bar = bar_v0 + (tile & 1) * 8, dst = smem + kOffV + (tile & 1) * kKvBytes;
+      const uint32_t bar = bar_v0 + kStage * 8, dst = smem + kOffV + kStage * kKvBytes;
       mbar_expect_tx(bar, kKvBytes);
       tma_load_4d(dst, &map_v, 0, tile * kUpKeys, kvh, b, bar);
       tma_load_4d(dst + kKvBoxBytes, &map_v, 64, tile * kUpKeys, kvh, b, bar);
     };
-    // S_qt(tile) = Q_qt . K(tile)^T into the score columns of query tile qt
-    auto issue_scores = [&](int qt, int tile) {
+    // S_qt = Q_qt . K(stage)^T into the score columns of query tile qt
+    auto issue_scores = [&](auto qt_c, auto stage_c) {
+      constexpr int kQt = decltype(qt_c)::value, kStage = decltype(stage_c)::value;
       if (!elect_one()) return;
       tcgen05_fence_after_sync();
-      const uint64_t k0 = desc_k + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
       for (int k = 0; k < kUpDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
-        umma_f16(tmem + qt * kColsPerQTile + kColS,
-                 desc_q + (uint64_t)(((k / 4) * kQBoxBytes + qt * (kUpRows * 128) + (k % 4) * 32) >> 4),
-                 k0 + (uint64_t)(((k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s, k > 0);
-      umma_commit(bar_s0 + qt * 8);
+        umma_f16(tmem + kQt * kColsPerQTile + kColS,
+                 desc_q + (uint64_t)(((k / 4) * kQBoxBytes + kQt * (kUpRows * 128) + (k % 4) * 32) >> 4),
+                 desc_k + (uint64_t)((kStage * kKvBytes + (k / 4) * kKvBoxBytes + (k % 4) * 32) >> 4), idesc_s,
+                 k > 0 ? 1u : 0u);
+      umma_commit(bar_s0 + kQt * 8);
     };
-    // O_qt += P_qt(tile) . V(tile): P sits in the first 64 score columns (two keys per column)
-    auto issue_values = [&](int qt, int tile) {
+    // O_qt += P_qt . V(stage): P sits in the first 64 score columns (two keys per column)
+    auto issue_values = [&](auto qt_c, auto stage_c, auto first_c) {
+      constexpr int kQt = decltype(qt_c)::value, kStage = decltype(stage_c)::value;
+      constexpr bool kFirst = decltype(first_c)::value;
       if (!elect_one()) return;
       tcgen05_fence_after_sync();
-      const uint64_t v0 = desc_v + (uint64_t)(((tile & 1) * kKvBytes) >> 4);
 #pragma unroll
       for (int k = 0; k < kUpKeys / 16; ++k)  // 16 keys per instruction: eight columns of P, 16 rows of V = 2048 bytes
-        umma_f16_ts(tmem + qt * kColsPerQTile + kColO, tmem + qt * kColsPerQTile + kColS + 8 * k,
-                    v0 + (uint64_t)((k * 16 * 128) >> 4), idesc_o, (tile > 0 || k > 0) ? 1u : 0u);
-      umma_commit(bar_o0 + qt * 8);
+        umma_f16_ts(tmem + kQt * kColsPerQTile + kColO, tmem + kQt * kColsPerQTile + kColS + 8 * k,
+                    desc_v + (uint64_t)((kStage * kKvBytes + k * 16 * 128) >> 4), idesc_o, (!kFirst || k > 0) ? 1u : 0u);
+      umma_commit(bar_o0 + kQt * 8);
     };
+    using Zero = std::integral_constant<int, 0>;
+    using One = std::integral_constant<int, 1>;
     if (elect_one()) {
       mbar_expect_tx(bar_q, 2 * kQBoxBytes);  // positions past the chunk's end arrive as zeros
       tma_load_4d(smem + kOffQ, &map_q, 0, m0, hq0, b, bar_q);
       tma_load_4d(smem + kOffQ + kQBoxBytes, &map_q, 64, m0, hq0, b, bar_q);
     }
-    load_k(0);
-    load_v(0);
-    load_k(1);
-    load_v(1);
+    load_k(Zero{}, 0);
+    load_v(Zero{}, 0);
+    load_k(One{}, 1);
+    load_v(One{}, 1);
     bool ok = wait(bar_q, 0) && wait(bar_k0, 0);
     if (ok) {
-      issue_scores(0, 0);
-      issue_scores(1, 0);
+      issue_scores(Zero{}, Zero{});
+      issue_scores(One{}, Zero{});
     }
     // Order on the tensor pipe: ... P0.V | S0(next) | P1.V | S1(next) ...  The pipe runs in issue order, so S_qt(next)
     // overwrites the columns of P_qt only after the product that reads them, and while the threads of one query tile
     // are busy with their softmax the pipe works for the other tile.
-    for (int it = 0; it < n_tiles && ok; ++it) {
-      for (int qt = 0; qt < kUpQTiles && ok; ++qt) {
-        ok = wait(bar_p0 + qt * 8, it);  // P_qt(it) is in tensor memory, O_qt is rescaled
-        if (ok && qt == 0) ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
-        if (!ok) break;
-        issue_values(qt, it);
-        if (it + 1 < n_tiles) {
-          if (qt == 0) ok = wait(bar_k0 + ((it + 1) & 1) * 8, (it + 1) >> 1);
-          if (!ok) break;
-          issue_scores(qt, it + 1);
-        }
+    auto step = [&](auto stage_c, auto first_c, int it) -> bool {
+      constexpr int kStage = decltype(stage_c)::value;  // it & 1
+      using Next = std::integral_constant<int, 1 - kStage>;
+      // query tile 0: P_0(it) is in tensor memory and O_0 rescaled; V(it) has landed
+      if (!wait(bar_p0, it) || !wait(bar_v0 + kStage * 8, it >> 1)) return false;
+      issue_values(Zero{}, stage_c, first_c);
+      if (it + 1 < n_tiles) {
+        if (!wait(bar_k0 + (1 - kStage) * 8, (it + 1) >> 1)) return false;
+        issue_scores(Zero{}, Next{});
       }
-      if (!ok) break;
+      // query tile 1
+      if (!wait(bar_p0 + 8, it)) return false;
+      issue_values(One{}, stage_c, first_c);
+      if (it + 1 < n_tiles) issue_scores(One{}, Next{});
       // both softmaxes have read their S(it): the K stage is free; the V stage once the second product is complete
-      load_k(it + 2);
+      load_k(stage_c, it + 2);
       if (it + 2 < n_tiles) {
-        ok = wait(bar_o0 + 8, it);
-        if (!ok) break;
-        load_v(it + 2);
+        if (!wait(bar_o0 + 8, it)) return false;
+        load_v(stage_c, it + 2);
       }
+      return true;
+    };
+    if (ok) ok = step(Zero{}, std::true_type{}, 0);
+    int it = 1;
+    for (; ok && it + 1 < n_tiles; it += 2) {
+      ok = step(One{}, std::false_type{}, it);
+      if (ok) ok = step(Zero{}, std::false_type{}, it + 1);
     }
+    if (ok && it < n_tiles) ok = step(One{}, std::false_type{}, it);
     }
   } else {
     // ---- softmax warps: thread t owns row t; warps 0..3 query tile 0, warps 4..7 query tile 1 --------------------------
