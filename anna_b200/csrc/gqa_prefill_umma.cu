@@ -66,6 +66,31 @@ __device__ __forceinline__ float up_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Pairs of fp32 values in one 64-bit register and the arithmetic on both at once.
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 // True in exactly one lane of a converged warp.  Unlike a comparison of the lane index, the instruction tells the compiler
 // that the guarded region runs in a single thread, so descriptors and addresses of the tensor-core and copy
 // instructions issued there can live in uniform registers.
@@ -319,12 +344,14 @@ __global__ void __launch_bounds__(kUpThreads, 1)
       }
       float mx4[4] = {__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]), __uint_as_float(x[3])};
 #pragma unroll
-      for (int i = 4; i < kUpKeys; i += 4) {
-        mx4[0] = fmaxf(mx4[0], __uint_as_float(x[i]));
-        mx4[1] = fmaxf(mx4[1], __uint_as_float(x[i + 1]));
-        mx4[2] = fmaxf(mx4[2], __uint_as_float(x[i + 2]));
-        mx4[3] = fmaxf(mx4[3], __uint_as_float(x[i + 3]));
+      for (int i = 4; i + 8 <= kUpKeys; i += 8) {  // two new values per instruction
+        mx4[0] = max3(mx4[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+        mx4[1] = max3(mx4[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+        mx4[2] = max3(mx4[2], __uint_as_float(x[i + 4]), __uint_as_float(x[i + 5]));
+        mx4[3] = max3(mx4[3], __uint_as_float(x[i + 6]), __uint_as_float(x[i + 7]));
       }
+      mx4[0] = max3(mx4[0], __uint_as_float(x[kUpKeys - 4]), __uint_as_float(x[kUpKeys - 3]));
+      mx4[1] = max3(mx4[1], __uint_as_float(x[kUpKeys - 2]), __uint_as_float(x[kUpKeys - 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
 
       // Lazy running maximum (log2 units): it moves only when it would grow by more than 2^8, and only then is the row
@@ -352,22 +379,30 @@ __global__ void __launch_bounds__(kUpThreads, 1)
       const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
 
       // P = exp2(S * scale - m) as 16-bit pairs over the scores (keys 32c .. 32c + 31 into columns 16c .. 16c + 15),
-      // row sum
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // row sum; the scaling and the sums run on pairs of values (one instruction for two)
+      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2), shift2 = pack_f2(-m_ref, -m_ref);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four pairs of +0.0f
 #pragma unroll
       for (int c = 0; c < kUpKeys / kChunk; ++c) {
         uint32_t packed[kChunk / 2];
 #pragma unroll
-        for (int i = 0; i < kChunk; i += 4) {
-          const float p0 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i]), p.scale_log2, -m_ref));
-          const float p1 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 1]), p.scale_log2, -m_ref));
-          const float p2 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 2]), p.scale_log2, -m_ref));
-          const float p3 = up_ex2(fmaf(__uint_as_float(x[kChunk * c + i + 3]), p.scale_log2, -m_ref));
-          sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
-          packed[i / 2] = pack2<T>(p0, p1);
-          packed[i / 2 + 1] = pack2<T>(p2, p3);
+        for (int j = 0; j < kChunk / 2; ++j) {
+          const int i = kChunk * c + 2 * j;
+          const uint64_t arg = fma2(pack_f2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])), scale2, shift2);
+          float lo, hi;
+          unpack_f2(arg, lo, hi);
+          lo = up_ex2(lo);  // exp2(-inf) = 0 for hidden keys
+          hi = up_ex2(hi);
+          sum2[j % 4] = add2(sum2[j % 4], pack_f2(lo, hi));
+          packed[j] = pack2<T>(lo, hi);
         }
         tmem_st16(t_s + (kChunk / 2) * c, packed);
+      }
+      float sum4[4];
+      {
+        const uint64_t total = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+        unpack_f2(total, sum4[0], sum4[1]);
+        sum4[2] = sum4[3] = 0.0f;
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
