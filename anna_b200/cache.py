@@ -734,9 +734,8 @@ class Qwen3DynamicCache:
         lengths = self.layer_lengths[layer_idx]
         max_length = max(lengths, default=0)
         if self.uses_turboquant_for_layer(layer_idx):
-            visible = torch.tensor(lengths, dtype=torch.long)
             if max_length <= 0:
-                return None, None, visible
+                return None, None, torch.tensor(lengths, dtype=torch.long)
             rows = self.turboquant_rows[layer_idx]
             if any(row is None for row in rows):
                 raise RuntimeError(f"TurboQuant cache row for layer {layer_idx} is missing.")
@@ -744,9 +743,8 @@ class Qwen3DynamicCache:
             device = pool.device
             assert device is not None
             table_dev = self._sync_page_table_layer_buffer(layer_idx, batch_size=batch_size, device=device)
-            keys, values = launch_tq_gather_dense(pool, table_dev, [row.slot for row in rows], list(lengths),
-                                                  max_length)
-            return keys, values, visible.to(device)
+            # the lengths come back as the device tensor the launch read them from (no second host-to-device copy)
+            return launch_tq_gather_dense(pool, table_dev, [row.slot for row in rows], list(lengths), max_length)
         layer = self.allocator.layers[layer_idx]
         if layer.key_pages is None or layer.value_pages is None or max_length <= 0:
             return None, None, torch.tensor(lengths, dtype=torch.long)

@@ -152,9 +152,9 @@ def launch_tq_materialize(pool: TurboQuantLayerPool, table_dev: torch.Tensor, qu
 
 
 def launch_tq_gather_dense(pool: TurboQuantLayerPool, table_dev: torch.Tensor | None, slots: list[int], lengths: list[int],
-                           max_len: int) -> tuple[torch.Tensor, torch.Tensor]:
+                           max_len: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Dense ``[B, Hkv, max_len, D]`` keys and values of B rows of one layer in one launch: de-quantized prefix, window
-    tokens, zero padding."""
+    tokens, zero padding; and the rows' lengths as the int64 device tensor the launch read them from."""
     assert pool.window is not None and pool.device is not None and pool.dtype is not None
     device = pool.device
     batch = len(lengths)
@@ -171,7 +171,7 @@ def launch_tq_gather_dense(pool: TurboQuantLayerPool, table_dev: torch.Tensor | 
             keys.stride(1), keys.stride(2), batch, pool.kv_heads, pool.head_dim, pool.block_size, pool.residual_len,
             pool.bits, pool.value_group, pool.capacity(), max_blocks, int(max_len), dtype_code(pool.dtype),
             stream_ptr(device)), "anna_tq_gather_dense")
-    return keys, values
+    return keys, values, meta[0]
 
 
 class TurboQuantTensorRow:
