@@ -952,11 +952,28 @@ def run_prefill_extra(device, *, batch: int = 8, q_heads: int = 16, kv_heads: in
     except Exception:  # noqa: BLE001
         pass
     tflops = flops / (ms / 1e3) / 1e12
-    return {"workload": f"cfg4 prefill attention: {batch} seq x {chunk}-token chunk over {past} cached tokens, "
-                        f"{q_heads}q/{kv_heads}kv heads, D={dim}, bf16 dense K/V",
-            "prefill_ms": ms, "prefill_tokens_per_s": batch * chunk / (ms / 1e3), "algorithmic_flops": flops,
-            "TFLOPs": tflops, "frac_of_measured_bf16_peak": None if peak_tflops is None else tflops / peak_tflops,
-            "bound": "tensor"}
+    out = {"workload": f"cfg4 prefill attention: {batch} seq x {chunk}-token chunk over {past} cached tokens, "
+                       f"{q_heads}q/{kv_heads}kv heads, D={dim}, bf16 dense K/V",
+           "prefill_ms": ms, "prefill_tokens_per_s": batch * chunk / (ms / 1e3), "algorithmic_flops": flops,
+           "TFLOPs": tflops, "frac_of_measured_bf16_peak": None if peak_tflops is None else tflops / peak_tflops,
+           "bound": "tensor"}
+    del k, v
+    # The same chunk on a quantized cache (cfg4: 3-bit): the dense view update(require_dense_cache=True) builds first
+    # (de-quantized prefix + window, one launch), through the cache's own call.
+    from anna_b200 import KVCacheConfig, Qwen3DynamicCache
+
+    cache = Qwen3DynamicCache(KVCacheConfig(num_hidden_layers=1, cache_block_size=16), batch_size=batch,
+                              kv_cache_quantization="turboquant", kv_cache_quant_bits=3, kv_cache_residual_len=128)
+    kq = torch.randn(batch, kv_heads, total, dim, device=device, dtype=torch.bfloat16, generator=gen)
+    cache.update(kq, torch.randn(kq.shape, device=device, dtype=torch.bfloat16, generator=gen), 0,
+                 require_dense_cache=False)
+    del kq
+    view_ms = _time_device(lambda: cache.visible_key_cache(0), iters=iters, warmup=3)
+    written = 2.0 * batch * kv_heads * total * dim * 2
+    out["dense_view"] = {"workload": f"de-quantized dense K and V of the same {batch} x {total} tokens from a 3-bit cache",
+                         "ms": view_ms, "written_GBps": written / (view_ms / 1e3) / 1e9, "bound": "instruction issue"}
+    cache.release()
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------------------
