@@ -46,6 +46,10 @@ def _oracle(q, k, v, lengths, causal):
     (torch.float16, 8, 2, 128, 300, 900, (900, 411, 64), False),  # key padding only, a row shorter than one key tile
     (torch.bfloat16, 4, 1, 128, 130, 130, (130, 70), True),       # a row shorter than the chunk: queries without keys
     (torch.bfloat16, 8, 8, 128, 512, 3000, (3000, 1500), True),   # 24 key tiles: the running maximum moves, O is rescaled
+    (torch.bfloat16, 16, 1, 128, 64, 64, (64, 1), True),          # 16 heads per KV head: 16 positions per CTA; one key tile
+    (torch.float16, 3, 3, 128, 257, 400, (400, 257), True),       # one head per KV head, 256 positions per CTA + 1
+    (torch.bfloat16, 6, 2, 128, 100, 333, (333, 0, 129), False),  # three heads per KV head (odd), a row without keys
+    (torch.bfloat16, 8, 2, 128, 1024, 1024, (1024,), True),       # full prefill: every CTA ends on its diagonal tile
 ])
 def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len, key_len, lengths, causal):
     gen = torch.Generator().manual_seed(heads * 1000 + q_len)
