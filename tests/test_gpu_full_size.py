@@ -192,3 +192,36 @@ def test_config3_full_size_ragged_rows_match_oracle(cuda_device):
     _check_rows_against_oracle(cache, host_kv, sample_rows, query, bits=bits, residual=residual, heads=heads,
                                kv_heads=kv_heads, dim=dim, page=page)
     cache.release()
+
+
+def test_config4_prefill_chunk_over_long_context_matches_fp32_attention(cuda_device):
+    """cfg4's prefill attention at a length the oracle does not finish in seconds: a 512-token chunk over 32 256 cached
+    tokens (253 key tiles of the tensor-memory kernel, 16 q / 4 kv heads, D=128), ragged: the second row is 9 000 tokens
+    long.  Floating-point kernel, so the check is a plain fp32 torch attention on the same bf16 inputs: 2e-2 absolute on
+    bf16 outputs (values are N(0, 1); rows average thousands of them, so outputs are small and the bound is loose in
+    relative terms) and 4e-3 relative L2: the output and P are each rounded to bf16 once (2^-9 / sqrt(3) = 1.1e-3 rms
+    each, and on near-uniform rows the error of P does not average out against the output, which is itself a random
+    walk over the values), measured 2.3e-3."""
+    from anna_b200 import grouped_query_attention
+
+    gen = torch.Generator(device=cuda_device).manual_seed(404)
+    batch, heads, kv_heads, dim, q_len, key_len = 2, 16, 4, 128, 512, 32768
+    lengths = torch.tensor([key_len, 9000], device=cuda_device)
+    q = torch.randn(batch, heads, q_len, dim, device=cuda_device, generator=gen).to(torch.bfloat16)
+    k = torch.randn(batch, kv_heads, key_len, dim, device=cuda_device, generator=gen).to(torch.bfloat16)
+    v = torch.randn(batch, kv_heads, key_len, dim, device=cuda_device, generator=gen).to(torch.bfloat16)
+    out = grouped_query_attention(q, k, v, scaling=dim ** -0.5, key_lengths=lengths, causal=True).float()
+    groups = heads // kv_heads
+    for b in range(batch):
+        n = int(lengths[b])
+        kk = k[b, :, :n].float().repeat_interleave(groups, 0)
+        vv = v[b, :, :n].float().repeat_interleave(groups, 0)
+        scores = q[b].float() @ kk.transpose(-1, -2) * dim ** -0.5                  # [heads, q_len, n]
+        q_pos = n - q_len + torch.arange(q_len, device=cuda_device)
+        hidden = torch.arange(n, device=cuda_device)[None, :] > q_pos[:, None]
+        scores.masked_fill_(hidden[None], float("-inf"))
+        want = torch.softmax(scores, dim=-1) @ vv
+        diff = out[b] - want
+        max_abs = float(diff.abs().max())
+        rel_l2 = float(diff.pow(2).sum().sqrt() / want.pow(2).sum().sqrt())
+        assert max_abs <= 2e-2 and rel_l2 <= 4e-3, (b, max_abs, rel_l2)
