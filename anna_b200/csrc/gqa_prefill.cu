@@ -360,7 +360,7 @@ extern "C" int anna_gqa_prefill(const void* q, int64_t q_stride_b, int64_t q_str
   p.scale_log2 = scaling * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   if (prefill_umma_applicable(p, head_dim, dtype)) {
-    const int rc = launch_prefill_umma(p, batch, q_heads, dtype, s);
+    const int rc = launch_prefill_umma(p, batch, q_heads, head_dim, dtype, s);
     if (rc != kPrefillNotServed) return rc;
   }
 #define ANNA_PREFILL_CASE(TYPE, DIM) \

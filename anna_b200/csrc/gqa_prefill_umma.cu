@@ -457,6 +457,311 @@ __global__ void __launch_bounds__(kUpThreads, 1)
   if (warp == 0) tmem_free(tmem, kTmemCols);
 }
 
+// ---- head_dim 256 ------------------------------------------------------------------------------------------------------
+// O alone fills half of tensor memory (256 columns), so a CTA owns ONE 128-row query tile and the other half holds two
+// score buffers of 64 columns: S(t + 1) is computed while the threads work on tile t, and the only thing the tensor
+// pipe ever waits for is P.  64-key tiles (a K or V tile is 32 KB; two stages of each and Q make 192 KB).  Warp 4 issues
+// the products, warp 5 the copies (eight boxes and two byte counts per tile: on the issuing warp they would cost more
+// than the products of the tile), warps 0..3 are the softmax, thread t = row t.
+constexpr int kWdDim = 256, kWdRows = 128, kWdKeys = 64, kWdStages = 2;
+constexpr int kWdThreads = 256;
+constexpr uint32_t kWdQBoxBytes = kWdRows * 128;        // 64 values of the 128 rows
+constexpr uint32_t kWdKvBoxBytes = kWdKeys * 128;       // 64 values of 64 keys
+constexpr uint32_t kWdKvBytes = (kWdDim / 64) * kWdKvBoxBytes;  // one K or V tile: four boxes
+constexpr uint32_t kWdOffQ = 0, kWdOffK = (kWdDim / 64) * kWdQBoxBytes, kWdOffV = kWdOffK + kWdStages * kWdKvBytes;
+constexpr uint32_t kWdSmem = kWdOffV + kWdStages * kWdKvBytes + 1024;
+constexpr uint32_t kWdColS = 0, kWdColO = 2 * kWdKeys, kWdTmemCols = 512;  // S0 | S1 | O (256) | 128 unused
+
+template <typename T>
+__global__ void __launch_bounds__(kWdThreads, 1)
+    gqa_prefill_umma256_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+                               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long bar_storage[11];  // S, P, O [tile parity] | Q | K landed [stage] | V landed [stage]
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int head_shift = head_shift_of(p.groups);
+  const int heads_here = 1 << head_shift;
+  const int positions = kWdRows >> head_shift;
+  const int head_sets = p.groups >> head_shift;
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * positions;  // tiles with the most visible keys first
+  const int kvh = blockIdx.y / head_sets;
+  const int hq0 = kvh * p.groups + (blockIdx.y % head_sets) * heads_here;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r_local = threadIdx.x & (kWdRows - 1);
+  const int row = m0 + (r_local & (positions - 1));  // query position of this thread's row
+  const int hq = hq0 + r_local / positions;
+
+  int64_t n_keys = p.key_lengths != nullptr ? p.key_lengths[b] : p.key_len;
+  n_keys = max((int64_t)0, min(n_keys, p.key_len));
+  const int64_t past = n_keys - p.q_len;
+  const int last_row = min(m0 + positions, p.q_len) - 1;
+  int64_t cta_limit = p.causal ? min(n_keys, past + last_row + 1) : n_keys;
+  cta_limit = max(cta_limit, (int64_t)0);
+  const int n_tiles = (int)((cta_limit + kWdKeys - 1) / kWdKeys);
+  const int n_keys32 = (int)min(n_keys, (int64_t)0x7fffffff);
+  int lim = 0;  // keys this thread's row sees
+  if (row < p.q_len) lim = (int)max((int64_t)0, p.causal ? min((int64_t)n_keys32, past + row + 1) : (int64_t)n_keys32);
+  T* out_row = reinterpret_cast<T*>(p.out) + b * p.out_stride_b + (int64_t)hq * p.out_stride_h +
+               (int64_t)row * p.out_stride_t;
+
+  if (n_tiles == 0) {  // no row of this CTA sees a key: zeros (uniform over the CTA, nothing was allocated yet)
+    if (warp < 4 && row < p.q_len)
+      for (int c = 0; c < kWdDim / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 8 * (tile & 1) for S, P and O
+  const uint32_t bar_p0 = smem_u32(&bar_storage[2]);
+  const uint32_t bar_o0 = smem_u32(&bar_storage[4]);
+  const uint32_t bar_q = smem_u32(&bar_storage[6]);
+  const uint32_t bar_k0 = smem_u32(&bar_storage[7]);  // + 8 * stage
+  const uint32_t bar_v0 = smem_u32(&bar_storage[9]);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 11; ++i) mbar_init(bar_s0 + 8 * i, (i == 2 || i == 3) ? kWdRows / 32 : 1);
+    abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, kWdTmemCols);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  auto wait = [&](uint32_t bar, int use) -> bool {  // as in the head_dim 128 kernel
+    const uint32_t parity = (uint32_t)(use & 1);
+    bool landed = false;
+    for (uint32_t spin = 0; spin < kUpWaitSpins && !landed; ++spin) {
+      uint32_t done;
+      asm volatile(
+          "{\n"
+          ".reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+          "selp.u32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(done)
+          : "r"(bar), "r"(parity)
+          : "memory");
+      landed = done != 0;
+      if (!landed && *(volatile int*)&abort_flag != 0) break;
+    }
+    if (!landed) *(volatile int*)&abort_flag = 1;
+    return __all_sync(0xffffffffu, landed);
+  };
+  using Zero = std::integral_constant<int, 0>;
+  using One = std::integral_constant<int, 1>;
+
+  if (warp == 5) {
+    // ---- copies: K(t) goes where K(t - 2) was once S(t - 2) is complete, V(t) where V(t - 2) was once P.V(t - 2) is --
+    // (the waits come in the order the tensor pipe completes them: S(t - 2), P.V(t - 2), S(t - 1), ...)
+    auto load_tile = [&](auto stage_c, int t, bool keys) {
+      constexpr int kStage = decltype(stage_c)::value;
+      if (!elect_one()) return;
+      const uint32_t bar = (keys ? bar_k0 : bar_v0) + kStage * 8;
+      const uint32_t dst = smem + (keys ? kWdOffK : kWdOffV) + kStage * kWdKvBytes;
+      mbar_expect_tx(bar, kWdKvBytes);
+#pragma unroll
+      for (int i = 0; i < kWdDim / 64; ++i)
+        tma_load_4d(dst + i * kWdKvBoxBytes, keys ? &map_k : &map_v, 64 * i, t * kWdKeys, kvh, b, bar);
+    };
+    if (elect_one()) {
+      mbar_expect_tx(bar_q, (kWdDim / 64) * kWdQBoxBytes);  // positions past the chunk's end arrive as zeros
+#pragma unroll
+      for (int i = 0; i < kWdDim / 64; ++i) tma_load_4d(smem + kWdOffQ + i * kWdQBoxBytes, &map_q, 64 * i, m0, hq0, b, bar_q);
+    }
+    bool ok = true;
+    auto produce = [&](auto stage_c, int t) {
+      constexpr int kStage = decltype(stage_c)::value;  // t & 1
+      if (t >= 2) ok = wait(bar_s0 + kStage * 8, (t - 2) >> 1);
+      if (!ok) return;
+      load_tile(stage_c, t, true);
+      if (t >= 2) ok = wait(bar_o0 + kStage * 8, (t - 2) >> 1);
+      if (!ok) return;
+      load_tile(stage_c, t, false);
+    };
+    for (int t = 0; t < n_tiles && ok; t += 2) {
+      produce(Zero{}, t);
+      if (ok && t + 1 < n_tiles) produce(One{}, t + 1);
+    }
+  } else if (warp == 4) {
+    // ---- products -----------------------------------------------------------------------------------------------------
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
+    constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kWdRows, kWdKeys);
+    constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kWdRows, kWdDim);
+    const uint64_t desc_q = umma_smem_desc_sw128(smem + kWdOffQ, 16, 1024);
+    const uint64_t desc_k = umma_smem_desc_sw128(smem + kWdOffK, 16, 1024);
+    const uint64_t desc_v = umma_smem_desc_sw128(smem + kWdOffV, kWdKvBoxBytes, 1024);  // next 64 values: next box
+    auto issue_scores = [&](auto stage_c) {
+      constexpr int kStage = decltype(stage_c)::value;  // = score buffer
+      if (!elect_one()) return;
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int k = 0; k < kWdDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
+        umma_f16(tmem + kWdColS + kStage * kWdKeys,
+                 desc_q + (uint64_t)(((k / 4) * kWdQBoxBytes + (k % 4) * 32) >> 4),
+                 desc_k + (uint64_t)((kStage * kWdKvBytes + (k / 4) * kWdKvBoxBytes + (k % 4) * 32) >> 4), idesc_s,
+                 k > 0 ? 1u : 0u);
+      umma_commit(bar_s0 + kStage * 8);
+    };
+    auto issue_values = [&](auto stage_c, auto first_c) {
+      constexpr int kStage = decltype(stage_c)::value;
+      constexpr bool kFirst = decltype(first_c)::value;
+      if (!elect_one()) return;
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int k = 0; k < kWdKeys / 16; ++k)  // 16 keys per instruction: eight columns of P, 16 rows of V = 2048 bytes
+        umma_f16_ts(tmem + kWdColO, tmem + kWdColS + kStage * kWdKeys + 8 * k,
+                    desc_v + (uint64_t)((kStage * kWdKvBytes + k * 16 * 128) >> 4), idesc_o, (!kFirst || k > 0) ? 1u : 0u);
+      umma_commit(bar_o0 + kStage * 8);
+    };
+    bool ok = wait(bar_q, 0) && wait(bar_k0, 0);
+    if (ok) issue_scores(Zero{});
+    auto step = [&](auto stage_c, auto first_c, int t) -> bool {
+      constexpr int kStage = decltype(stage_c)::value;
+      using Next = std::integral_constant<int, 1 - kStage>;
+      if (t + 1 < n_tiles) {  // S(t + 1): its buffer held P(t - 1), which the product issued before this one has read
+        if (!wait(bar_k0 + (1 - kStage) * 8, (t + 1) >> 1)) return false;
+        issue_scores(Next{});
+      }
+      if (!wait(bar_p0 + kStage * 8, t >> 1) || !wait(bar_v0 + kStage * 8, t >> 1)) return false;
+      issue_values(stage_c, first_c);
+      return true;
+    };
+    if (ok) ok = step(Zero{}, std::true_type{}, 0);
+    int t = 1;
+    for (; ok && t + 1 < n_tiles; t += 2) {
+      ok = step(One{}, std::false_type{}, t);
+      if (ok) ok = step(Zero{}, std::false_type{}, t + 1);
+    }
+    if (ok && t < n_tiles) ok = step(One{}, std::false_type{}, t);
+  } else if (warp < 4) {
+    // ---- softmax: thread t owns row t -----------------------------------------------------------------------------------
+    constexpr int kChunk = 32;
+    const uint32_t t_lane = tmem_addr(tmem, 32 * warp, 0);
+    const uint32_t t_o = t_lane + kWdColO;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int key0 = it * kWdKeys;
+      const int visible = max(0, min(kWdKeys, lim - key0));
+      const uint32_t t_s = t_lane + kWdColS + (it & 1) * kWdKeys;
+      ok = wait(bar_s0 + (it & 1) * 8, it >> 1);
+      if (!ok) break;
+      tcgen05_fence_after_sync();
+      uint32_t x[kWdKeys];
+#pragma unroll
+      for (int c = 0; c < kWdKeys / kChunk; ++c) tmem_ld32(t_s + kChunk * c, *reinterpret_cast<uint32_t(*)[kChunk]>(&x[kChunk * c]));
+      tmem_wait_ld();
+      if (visible < kWdKeys) {
+#pragma unroll
+        for (int i = 0; i < kWdKeys; ++i)
+          if (i >= visible) x[i] = 0xff800000u;  // -inf: exp2 gives 0
+      }
+      float mx4[4] = {__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]), __uint_as_float(x[3])};
+#pragma unroll
+      for (int i = 4; i + 8 <= kWdKeys; i += 8) {
+        mx4[0] = max3(mx4[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+        mx4[1] = max3(mx4[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+        mx4[2] = max3(mx4[2], __uint_as_float(x[i + 4]), __uint_as_float(x[i + 5]));
+        mx4[3] = max3(mx4[3], __uint_as_float(x[i + 6]), __uint_as_float(x[i + 7]));
+      }
+      mx4[0] = max3(mx4[0], __uint_as_float(x[kWdKeys - 4]), __uint_as_float(x[kWdKeys - 3]));
+      mx4[1] = max3(mx4[1], __uint_as_float(x[kWdKeys - 2]), __uint_as_float(x[kWdKeys - 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // the scale is positive
+      const bool grew = mx > m_run + kLazyLog2;
+      if (__any_sync(0xffffffffu, grew)) {  // tcgen05.ld / st are warp-wide
+        const float alpha = grew ? up_ex2(m_run - mx) : 1.0f;  // 0 while m_run is -inf
+        if (grew) m_run = mx;
+        l_run *= alpha;
+        if (it > 0) {  // the row of O, for which the previous product has to be complete
+          ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+          if (!ok) break;
+          tcgen05_fence_after_sync();
+#pragma unroll 1
+          for (int cc = 0; cc < kWdDim / 16; ++cc) {
+            uint32_t o[16];
+            tmem_ld16(t_o + 16 * cc, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(t_o + 16 * cc, o);
+          }
+        }
+      }
+      const float m_ref = m_run == -INFINITY ? 0.0f : m_run;
+      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2), shift2 = pack_f2(-m_ref, -m_ref);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+      for (int c = 0; c < kWdKeys / kChunk; ++c) {
+        uint32_t packed[kChunk / 2];
+#pragma unroll
+        for (int j = 0; j < kChunk / 2; ++j) {
+          const int i = kChunk * c + 2 * j;
+          const uint64_t arg = fma2(pack_f2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])), scale2, shift2);
+          float lo, hi;
+          unpack_f2(arg, lo, hi);
+          lo = up_ex2(lo);
+          hi = up_ex2(hi);
+          sum2[j % 4] = add2(sum2[j % 4], pack_f2(lo, hi));
+          packed[j] = pack2<T>(lo, hi);
+        }
+        tmem_st16(t_s + (kChunk / 2) * c, packed);
+      }
+      float s_lo, s_hi;
+      unpack_f2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), s_lo, s_hi);
+      l_run += s_lo + s_hi;
+      tmem_wait_st();
+      // the V rows behind the last key may hold anything: zero them in the tile that straddles it (see the other kernel)
+      if (key0 + kWdKeys > n_keys32) {
+        ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
+        if (!ok) break;
+        const int first = max(0, n_keys32 - key0);
+        uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kWdOffV + (it & 1) * kWdKvBytes;
+        for (int i = threadIdx.x; i < (kWdKeys - first) * 32; i += kWdRows) {
+          const int r = first + (i >> 5), piece = i & 31;  // 8 pieces of 16 bytes in each of the four boxes
+          *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kWdKvBoxBytes + r * 128 + (piece & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_async_smem();
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p0 + (it & 1) * 8);
+    }
+    if (ok) ok = wait(bar_o0 + ((n_tiles - 1) & 1) * 8, (n_tiles - 1) >> 1);
+    if (ok) {
+      tcgen05_fence_after_sync();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 4
+      for (int c = 0; c < kWdDim / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(t_o + 16 * c, r);
+        tmem_wait_ld();
+        if (row < p.q_len) {
+          uint4 lo, hi;
+          lo.x = pack2<T>(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          lo.y = pack2<T>(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          lo.z = pack2<T>(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          lo.w = pack2<T>(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          hi.x = pack2<T>(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          hi.y = pack2<T>(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          hi.z = pack2<T>(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          hi.w = pack2<T>(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          reinterpret_cast<uint4*>(out_row)[2 * c] = lo;
+          reinterpret_cast<uint4*>(out_row)[2 * c + 1] = hi;
+        }
+      }
+    }
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag != 0) atomicAdd(&g_prefill_umma_faults, 1);
+  if (warp == 0) tmem_free(tmem, kWdTmemCols);
+}
+
 }  // namespace
 
 bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
@@ -465,7 +770,7 @@ bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
     return flag != nullptr && flag[0] == '0';
   }();
   if (disabled) return false;
-  if (head_dim != 128 || (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16)) return false;
+  if ((head_dim != 128 && head_dim != 256) || (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16)) return false;
   // the output rows are written as 16-byte vectors
   if (p.out_stride_b % 8 != 0 || p.out_stride_h % 8 != 0 || p.out_stride_t % 8 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return false;
@@ -473,11 +778,12 @@ bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
   return p.q_len >= 64;  // short chunks leave most of a 256-row tile empty: the mma.sync kernel serves them
 }
 
-// Tensor map of a [B, H, L, 128] 16-bit tensor given by element strides, seen as (128, L, H, B).
+// Tensor map of a [B, H, L, dim] 16-bit tensor given by element strides, seen as (dim, L, H, B).
 static bool prefill_tensor_map(CUtensorMap* out, const void* base, int64_t len, int heads, int batch, int64_t stride_t,
-                               int64_t stride_h, int64_t stride_b, uint32_t box_len, uint32_t box_heads) {
+                               int64_t stride_h, int64_t stride_b, uint32_t box_len, uint32_t box_heads,
+                               int dim = kUpDim) {
   if (len <= 0 || heads <= 0 || batch <= 0) return false;
-  const uint64_t extents[4] = {(uint64_t)kUpDim, (uint64_t)len, (uint64_t)heads, (uint64_t)batch};
+  const uint64_t extents[4] = {(uint64_t)dim, (uint64_t)len, (uint64_t)heads, (uint64_t)batch};
   uint64_t strides[3] = {(uint64_t)stride_t * 2, (uint64_t)stride_h * 2, (uint64_t)stride_b * 2};
   const uint64_t used[3] = {(uint64_t)len, (uint64_t)heads, (uint64_t)batch};
   for (int i = 0; i < 3; ++i) {
@@ -512,7 +818,36 @@ static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads,
   return check_launch("gqa_prefill_umma_kernel");
 }
 
-int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int dtype, cudaStream_t stream) {
+template <typename T>
+static int launch_prefill_umma256_t(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
+  auto kernel = gqa_prefill_umma256_kernel<T>;
+  const int head_shift = head_shift_of(p.groups);
+  const int positions = kWdRows >> head_shift;
+  CUtensorMap map_q, map_k, map_v;
+  const int kv_heads = q_heads / p.groups;
+  if (!prefill_tensor_map(&map_q, p.q, p.q_len, q_heads, batch, p.q_stride_t, p.q_stride_h, p.q_stride_b,
+                          (uint32_t)positions, 1u << head_shift, kWdDim) ||
+      !prefill_tensor_map(&map_k, p.k, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kWdKeys, 1,
+                          kWdDim) ||
+      !prefill_tensor_map(&map_v, p.v, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kWdKeys, 1,
+                          kWdDim))
+    return kPrefillNotServed;
+  static bool configured[64] = {};
+  int device = 0;
+  ANNA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !configured[device]) {
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWdSmem));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  dim3 grid((unsigned)((p.q_len + positions - 1) / positions), (unsigned)(q_heads >> head_shift), (unsigned)batch);
+  kernel<<<grid, kWdThreads, kWdSmem, stream>>>(p, map_q, map_k, map_v);
+  return check_launch("gqa_prefill_umma256_kernel");
+}
+
+int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int head_dim, int dtype, cudaStream_t stream) {
+  if (head_dim == 256)
+    return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma256_t<__nv_bfloat16>(p, batch, q_heads, stream)
+                                    : launch_prefill_umma256_t<__half>(p, batch, q_heads, stream);
   return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_t<__nv_bfloat16>(p, batch, q_heads, stream)
                                   : launch_prefill_umma_t<__half>(p, batch, q_heads, stream);
 }

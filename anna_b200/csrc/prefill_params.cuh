@@ -23,7 +23,7 @@ constexpr int kPrefillNotServed = -1;  // launch_prefill_umma: the caller should
 
 // true when the tensor-memory kernel serves this problem (head_dim 128, 16-bit, not switched off)
 bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype);
-int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int dtype, cudaStream_t stream);
+int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int head_dim, int dtype, cudaStream_t stream);
 int prefill_umma_faults(int* count);
 
 }  // namespace anna

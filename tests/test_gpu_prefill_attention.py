@@ -50,6 +50,11 @@ def _oracle(q, k, v, lengths, causal):
     (torch.float16, 3, 3, 128, 257, 400, (400, 257), True),       # one head per KV head, 256 positions per CTA + 1
     (torch.bfloat16, 6, 2, 128, 100, 333, (333, 0, 129), False),  # three heads per KV head (odd), a row without keys
     (torch.bfloat16, 8, 2, 128, 1024, 1024, (1024,), True),       # full prefill: every CTA ends on its diagonal tile
+    # head_dim 256 with 64 or more queries: one 128-row query tile per CTA, 64-key tiles, two score buffers
+    (torch.bfloat16, 16, 2, 256, 200, 700, (700, 333, 65), True),  # eight heads per KV head (16 positions per CTA)
+    (torch.float16, 4, 4, 256, 130, 130, (130, 70), True),         # one head per KV head, queries without keys
+    (torch.bfloat16, 6, 2, 256, 100, 333, (333, 0, 129), False),   # three heads per KV head, key padding only
+    (torch.bfloat16, 16, 2, 256, 256, 2100, (2100, 1111), True),   # 33 key tiles
 ])
 def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len, key_len, lengths, causal):
     gen = torch.Generator().manual_seed(heads * 1000 + q_len)
@@ -70,7 +75,7 @@ def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len,
     assert torch.equal(again, out)
 
 
-@pytest.mark.parametrize("dim,q_len", [(128, 200), (128, 40), (256, 48)])
+@pytest.mark.parametrize("dim,q_len", [(128, 200), (128, 40), (256, 48), (256, 200)])
 def test_keys_behind_a_rows_length_may_hold_anything(cuda_device, dim, q_len):
     """K / V rows past key_lengths[b] are inside the tensors but not part of the row: NaNs there must not reach the
     output (the TMA-fed kernel reads them and zeroes the value rows of the boundary tile; the others never load them)."""
@@ -92,13 +97,13 @@ def test_keys_behind_a_rows_length_may_hold_anything(cuda_device, dim, q_len):
     assert max_abs <= ATOL[torch.bfloat16], (max_abs, rel_l2)
 
 
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_scores_that_keep_growing_along_the_keys(cuda_device, dtype):
+@pytest.mark.parametrize("dtype,dim", [(torch.bfloat16, 128), (torch.float16, 128), (torch.bfloat16, 256)])
+def test_scores_that_keep_growing_along_the_keys(cuda_device, dtype, dim):
     """Keys whose scale steps up every 80 positions: a row's running maximum moves by far more than the 2^8 the
     tensor-memory kernel tolerates without rescaling, inside key tiles (after part of P was stored) and between them
     (after O was accumulated), so its rescaling of O, of the row sum and of the stored part of P is what is compared."""
     gen = torch.Generator().manual_seed(77)
-    batch, heads, kv_heads, dim, q_len, key_len = 2, 8, 2, 128, 192, 1000
+    batch, heads, kv_heads, q_len, key_len = 2, 8, 2, 192, 1000
     q = torch.randn(batch, heads, q_len, dim, generator=gen)
     k = torch.randn(batch, kv_heads, key_len, dim, generator=gen)
     v = torch.randn(batch, kv_heads, key_len, dim, generator=gen) * 0.25   # nearly one-hot rows: outputs are single values
