@@ -1,5 +1,5 @@
 // Multi-token (prefill / chunked-prefill) grouped-query attention on the 5th-generation tensor cores: tcgen05.mma with
-// both accumulators in tensor memory.  head_dim 128, 16-bit dtypes; same semantics as gqa_prefill.cu
+// both accumulators in tensor memory.  head_dim 128 (this kernel) and 256 (the second kernel of the file), 16-bit dtypes; same semantics as gqa_prefill.cu
 // (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and :2008-2016).
 //
 // A CTA (8 softmax warps + 1 issuing warp, one CTA per SM) owns 256 rows = two query tiles of 128 rows (one set of accumulators in tensor memory

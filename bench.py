@@ -958,6 +958,18 @@ def run_prefill_extra(device, *, batch: int = 8, q_heads: int = 16, kv_heads: in
            "TFLOPs": tflops, "frac_of_measured_bf16_peak": None if peak_tflops is None else tflops / peak_tflops,
            "bound": "tensor"}
     del k, v
+    # The same chunk shape with cfg3's heads (16 q / 2 kv, head_dim 256): the other tensor-memory kernel
+    dim2, kv2 = 256, 2
+    q2 = torch.randn(batch, q_heads, chunk, dim2, device=device, dtype=torch.bfloat16, generator=gen)
+    k2 = torch.randn(batch, kv2, total, dim2, device=device, dtype=torch.bfloat16, generator=gen)
+    v2 = torch.randn(batch, kv2, total, dim2, device=device, dtype=torch.bfloat16, generator=gen)
+    ms2 = _time_device(lambda: grouped_query_attention(q2, k2, v2, scaling=dim2 ** -0.5, key_lengths=lengths, causal=True),
+                       iters=iters, warmup=3)
+    tflops2 = 4.0 * visible_pairs * dim2 / (ms2 / 1e3) / 1e12
+    out["head_dim_256"] = {"workload": f"the same chunk with {q_heads}q/{kv2}kv heads, D={dim2}", "prefill_ms": ms2,
+                           "TFLOPs": tflops2,
+                           "frac_of_measured_bf16_peak": None if peak_tflops is None else tflops2 / peak_tflops}
+    del q2, k2, v2
     # The same chunk on a quantized cache (cfg4: 3-bit): the dense view update(require_dense_cache=True) builds first
     # (de-quantized prefix + window, one launch), through the cache's own call.
     from anna_b200 import KVCacheConfig, Qwen3DynamicCache
