@@ -1,26 +1,27 @@
 // Multi-token (prefill / chunked-prefill) grouped-query attention on the 5th-generation tensor cores: tcgen05.mma with
-// both accumulators in tensor memory.  head_dim 128 (this kernel) and 256 (the second kernel of the file), 16-bit dtypes; same semantics as gqa_prefill.cu
-// (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and :2008-2016).
+// S, P and O in tensor memory.  head_dim 128 (first kernel) and 256 (second kernel), 16-bit dtypes; same semantics as
+// gqa_prefill.cu (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and
+// :2008-2016).
 //
-// A CTA (8 softmax warps + 1 issuing warp, one CTA per SM) owns 256 rows = two query tiles of 128 rows (one set of accumulators in tensor memory
-// each): consecutive query positions of the (up to 16) query heads that share one KV head, so that a K / V tile fetched
-// from L2 serves all of them (with 128 rows per K / V tile the copies from L2 bound the kernel at 3.3 TB/s); thread t owns
-// row t (lane t & 127 of query tile t >> 7); a ninth warp only issues the copies and the products, so that their issue
-// (which proceeds at the pace of the tensor pipe) runs beside the softmax instead of in front of it.
-// Per tile of 64 keys:
-//   K / V tile --tiled TMA (two boxes of 64 values x 64 keys each, 128-byte swizzle; K two stages and two tiles
-//                                ahead, V two stages and one ahead)--> shared memory; the rows of the one V tile that
-//                                straddles the end of a row's keys are zeroed in shared memory (K needs nothing: its
-//                                scores are masked)
-//   S[128 x 64] = Q . K^T        8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared memory, S in one of
-//                                two 64-column buffers of tensor memory, so the scores of tile t + 1 are computed while
-//                                the threads work on tile t; issued by thread 0, completion through tcgen05.commit
+// head_dim 128.  A CTA (one per SM) owns 256 rows = two query tiles of 128 rows: consecutive query positions of the (up
+// to 16) query heads that share one KV head, so that a K / V tile fetched from L2 serves all of them (with 128 rows per
+// K / V tile the copies from L2 bound an earlier version).  Eight softmax warps (thread t owns row t: lane t & 127 of
+// query tile t >> 7) and one warp that issues every copy and every product from an elected lane; the parties meet on
+// mbarriers only.  Per tile of 128 keys:
+//   K / V tile --tiled TMA (two boxes of 64 values x 128 keys each, 128-byte swizzle, two stages each)--> shared memory;
+//                                the rows of the one V tile that straddles the end of a row's keys are zeroed there (K
+//                                needs nothing: its scores are masked)
+//   S[128 x 128] = Q . K^T       per query tile 8 x tcgen05.mma kind::f16 (K = 16 each), Q and K K-major in shared
+//                                memory, S in the tile's 128 score columns of tensor memory
 //   softmax                      every thread reads its row of S into registers (tcgen05.ld): row maximum, exp2, row
-//                                sum; P goes to shared memory as the K-major A operand of the next product.  The running
+//                                sum; P (16-bit pairs) overwrites the first 64 score columns (tcgen05.st).  The running
 //                                maximum moves only when it would grow by more than 2^8, and only then is the row of O
-//                                rescaled in tensor memory (tcgen05.ld / st)
-//   O[128 x 128] += P . V        4 x tcgen05.mma, V MN-major (it is the same byte arrangement as a K-major tile: only
-//                                the descriptor's two strides swap roles), O in tensor memory columns 128..255
+//                                rescaled in tensor memory
+//   O[128 x 128] += P . V        per query tile 8 x tcgen05.mma with P read from tensor memory (the A operand) and V
+//                                MN-major in shared memory (the same byte arrangement as a K-major tile: only the
+//                                descriptor's two strides swap roles), O in the tile's other 128 columns
+// The tensor pipe sees P0.V | S0(next) | P1.V | S1(next): it runs in issue order, so S(next) overwrites P only after
+// the product that reads it, and one query tile's products run during the other's softmax.
 // Key tiles above the causal diagonal of the CTA's last row are never loaded.  Every wait is bounded: when one expires
 // the CTA counts a fault, stops, and still frees its tensor memory.
 #include "mma_utils.cuh"
