@@ -464,34 +464,50 @@ __global__ void __launch_bounds__(kUpThreads, 1)
 // pipe ever waits for is P.  64-key tiles (a K or V tile is 32 KB; two stages of each and Q make 192 KB).  Warp 4 issues
 // the products, warp 5 the copies (eight boxes and two byte counts per tile: on the issuing warp they would cost more
 // than the products of the tile), warps 0..3 are the softmax, thread t = row t.
-constexpr int kWdDim = 256, kWdRows = 128, kWdKeys = 64, kWdStages = 2;
-constexpr int kWdThreads = 256;
-constexpr uint32_t kWdQBoxBytes = kWdRows * 128;        // 64 values of the 128 rows
-constexpr uint32_t kWdKvBoxBytes = kWdKeys * 128;       // 64 values of 64 keys
-constexpr uint32_t kWdKvBytes = (kWdDim / 64) * kWdKvBoxBytes;  // one K or V tile: four boxes
-constexpr uint32_t kWdOffQ = 0, kWdOffK = (kWdDim / 64) * kWdQBoxBytes, kWdOffV = kWdOffK + kWdStages * kWdKvBytes;
-constexpr uint32_t kWdSmem = kWdOffV + kWdStages * kWdKvBytes + 1024;
-constexpr uint32_t kWdColS = 0, kWdColO = 2 * kWdKeys, kWdTmemCols = 512;  // S0 | S1 | O (256) | 128 unused
+// The same structure also runs head_dim 128 with two query tiles per CTA (`WideCfg<128, 2>`: 256 rows per K / V tile, 256
+// columns of tensor memory per query tile, eight softmax warps): correct, 1.10 ms on the case the kernel above takes
+// 1.03 ms for, so it is not instantiated.
+template <int D, int QT>
+struct WideCfg {
+  static constexpr int kDim = D, kQTiles = QT, kRows = 128, kCtaRows = QT * 128, kKeys = 64, kStages = 2;
+  static constexpr int kSoftmaxWarps = 4 * QT;
+  static constexpr int kThreads = (kSoftmaxWarps + 2 + 3) / 4 * 4 * 32;  // softmax warps, issuing warp, copy warp
+  static constexpr uint32_t kQBoxBytes = kCtaRows * 128;            // 64 values of all rows
+  static constexpr uint32_t kKvBoxBytes = kKeys * 128;              // 64 values of 64 keys
+  static constexpr uint32_t kKvBytes = (D / 64) * kKvBoxBytes;      // one K or V tile
+  static constexpr uint32_t kOffQ = 0, kOffK = (D / 64) * kQBoxBytes, kOffV = kOffK + kStages * kKvBytes;
+  static constexpr uint32_t kSmem = kOffV + kStages * kKvBytes + 1024;
+  // tensor memory per query tile: S0 | S1 (64 columns each) | O (D columns)
+  static constexpr uint32_t kColS = 0, kColO = 2 * kKeys, kColsPerQTile = D == 128 ? 256 : 512, kTmemCols = 512;
+  static_assert(kColO + D <= kColsPerQTile && QT * kColsPerQTile <= 512, "tensor memory layout");
+};
 
-template <typename T>
-__global__ void __launch_bounds__(kWdThreads, 1)
-    gqa_prefill_umma256_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+template <typename T, int D, int QT>
+__global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
+    gqa_prefill_umma_wide_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
                                const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  using Cfg = WideCfg<D, QT>;
+  constexpr int kWdDim = Cfg::kDim, kWdRows = Cfg::kRows, kWdKeys = Cfg::kKeys;
+  constexpr uint32_t kWdQBoxBytes = Cfg::kQBoxBytes, kWdKvBoxBytes = Cfg::kKvBoxBytes, kWdKvBytes = Cfg::kKvBytes;
+  constexpr uint32_t kWdOffQ = Cfg::kOffQ, kWdOffK = Cfg::kOffK, kWdOffV = Cfg::kOffV, kWdColS = Cfg::kColS, kWdColO = Cfg::kColO;
+  constexpr uint32_t kWdTmemCols = Cfg::kTmemCols, kColsQ = Cfg::kColsPerQTile;
+  constexpr int kSoftmaxWarps = Cfg::kSoftmaxWarps;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_storage[11];  // S, P, O [tile parity] | Q | K landed [stage] | V landed [stage]
+  __shared__ __align__(8) unsigned long long bar_storage[6 * QT + 5];  // S, P, O [query tile][tile parity] | Q | K landed [stage] | V landed [stage]
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int head_shift = head_shift_of(p.groups);
   const int heads_here = 1 << head_shift;
-  const int positions = kWdRows >> head_shift;
+  const int positions = Cfg::kCtaRows >> head_shift;
   const int head_sets = p.groups >> head_shift;
   const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * positions;  // tiles with the most visible keys first
   const int kvh = blockIdx.y / head_sets;
   const int hq0 = kvh * p.groups + (blockIdx.y % head_sets) * heads_here;
   const int b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r_local = threadIdx.x & (kWdRows - 1);
+  const int r_local = threadIdx.x & (Cfg::kCtaRows - 1);
+  const int qtile = r_local >> 7;
   const int row = m0 + (r_local & (positions - 1));  // query position of this thread's row
   const int hq = hq0 + r_local / positions;
 
@@ -509,20 +525,20 @@ __global__ void __launch_bounds__(kWdThreads, 1)
                (int64_t)row * p.out_stride_t;
 
   if (n_tiles == 0) {  // no row of this CTA sees a key: zeros (uniform over the CTA, nothing was allocated yet)
-    if (warp < 4 && row < p.q_len)
+    if (warp < kSoftmaxWarps && row < p.q_len)
       for (int c = 0; c < kWdDim / 8; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
     return;
   }
 
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 8 * (tile & 1) for S, P and O
-  const uint32_t bar_p0 = smem_u32(&bar_storage[2]);
-  const uint32_t bar_o0 = smem_u32(&bar_storage[4]);
-  const uint32_t bar_q = smem_u32(&bar_storage[6]);
-  const uint32_t bar_k0 = smem_u32(&bar_storage[7]);  // + 8 * stage
-  const uint32_t bar_v0 = smem_u32(&bar_storage[9]);
+  const uint32_t bar_s0 = smem_u32(&bar_storage[0]);  // + 16 * query tile + 8 * (tile & 1) for S, P and O
+  const uint32_t bar_p0 = smem_u32(&bar_storage[2 * QT]);
+  const uint32_t bar_o0 = smem_u32(&bar_storage[4 * QT]);
+  const uint32_t bar_q = smem_u32(&bar_storage[6 * QT]);
+  const uint32_t bar_k0 = smem_u32(&bar_storage[6 * QT + 1]);  // + 8 * stage
+  const uint32_t bar_v0 = smem_u32(&bar_storage[6 * QT + 3]);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) mbar_init(bar_s0 + 8 * i, (i == 2 || i == 3) ? kWdRows / 32 : 1);
+    for (int i = 0; i < 6 * QT + 5; ++i) mbar_init(bar_s0 + 8 * i, (i >= 2 * QT && i < 4 * QT) ? kWdRows / 32 : 1);
     abort_flag = 0;
     mbar_init_fence();
   }
@@ -555,7 +571,7 @@ __global__ void __launch_bounds__(kWdThreads, 1)
   using Zero = std::integral_constant<int, 0>;
   using One = std::integral_constant<int, 1>;
 
-  if (warp == 5) {
+  if (warp == kSoftmaxWarps + 1) {
     // ---- copies: K(t) goes where K(t - 2) was once S(t - 2) is complete, V(t) where V(t - 2) was once P.V(t - 2) is --
     // (the waits come in the order the tensor pipe completes them: S(t - 2), P.V(t - 2), S(t - 1), ...)
     auto load_tile = [&](auto stage_c, int t, bool keys) {
@@ -576,10 +592,10 @@ __global__ void __launch_bounds__(kWdThreads, 1)
     bool ok = true;
     auto produce = [&](auto stage_c, int t) {
       constexpr int kStage = decltype(stage_c)::value;  // t & 1
-      if (t >= 2) ok = wait(bar_s0 + kStage * 8, (t - 2) >> 1);
+      if (t >= 2) ok = wait(bar_s0 + (QT - 1) * 16 + kStage * 8, (t - 2) >> 1);
       if (!ok) return;
       load_tile(stage_c, t, true);
-      if (t >= 2) ok = wait(bar_o0 + kStage * 8, (t - 2) >> 1);
+      if (t >= 2) ok = wait(bar_o0 + (QT - 1) * 16 + kStage * 8, (t - 2) >> 1);
       if (!ok) return;
       load_tile(stage_c, t, false);
     };
@@ -587,7 +603,7 @@ __global__ void __launch_bounds__(kWdThreads, 1)
       produce(Zero{}, t);
       if (ok && t + 1 < n_tiles) produce(One{}, t + 1);
     }
-  } else if (warp == 4) {
+  } else if (warp == kSoftmaxWarps) {
     // ---- products -----------------------------------------------------------------------------------------------------
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
     constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kWdRows, kWdKeys);
@@ -595,40 +611,48 @@ __global__ void __launch_bounds__(kWdThreads, 1)
     const uint64_t desc_q = umma_smem_desc_sw128(smem + kWdOffQ, 16, 1024);
     const uint64_t desc_k = umma_smem_desc_sw128(smem + kWdOffK, 16, 1024);
     const uint64_t desc_v = umma_smem_desc_sw128(smem + kWdOffV, kWdKvBoxBytes, 1024);  // next 64 values: next box
-    auto issue_scores = [&](auto stage_c) {
-      constexpr int kStage = decltype(stage_c)::value;  // = score buffer
+    auto issue_scores = [&](auto qt_c, auto stage_c) {
+      constexpr int kQt = decltype(qt_c)::value, kStage = decltype(stage_c)::value;  // stage = score buffer
       if (!elect_one()) return;
       tcgen05_fence_after_sync();
 #pragma unroll
       for (int k = 0; k < kWdDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
-        umma_f16(tmem + kWdColS + kStage * kWdKeys,
-                 desc_q + (uint64_t)(((k / 4) * kWdQBoxBytes + (k % 4) * 32) >> 4),
+        umma_f16(tmem + kQt * kColsQ + kWdColS + kStage * kWdKeys,
+                 desc_q + (uint64_t)(((k / 4) * kWdQBoxBytes + kQt * (kWdRows * 128) + (k % 4) * 32) >> 4),
                  desc_k + (uint64_t)((kStage * kWdKvBytes + (k / 4) * kWdKvBoxBytes + (k % 4) * 32) >> 4), idesc_s,
                  k > 0 ? 1u : 0u);
-      umma_commit(bar_s0 + kStage * 8);
+      umma_commit(bar_s0 + kQt * 16 + kStage * 8);
     };
-    auto issue_values = [&](auto stage_c, auto first_c) {
-      constexpr int kStage = decltype(stage_c)::value;
+    auto issue_values = [&](auto qt_c, auto stage_c, auto first_c) {
+      constexpr int kQt = decltype(qt_c)::value, kStage = decltype(stage_c)::value;
       constexpr bool kFirst = decltype(first_c)::value;
       if (!elect_one()) return;
       tcgen05_fence_after_sync();
 #pragma unroll
       for (int k = 0; k < kWdKeys / 16; ++k)  // 16 keys per instruction: eight columns of P, 16 rows of V = 2048 bytes
-        umma_f16_ts(tmem + kWdColO, tmem + kWdColS + kStage * kWdKeys + 8 * k,
+        umma_f16_ts(tmem + kQt * kColsQ + kWdColO, tmem + kQt * kColsQ + kWdColS + kStage * kWdKeys + 8 * k,
                     desc_v + (uint64_t)((kStage * kWdKvBytes + k * 16 * 128) >> 4), idesc_o, (!kFirst || k > 0) ? 1u : 0u);
-      umma_commit(bar_o0 + kStage * 8);
+      umma_commit(bar_o0 + kQt * 16 + kStage * 8);
     };
     bool ok = wait(bar_q, 0) && wait(bar_k0, 0);
-    if (ok) issue_scores(Zero{});
+    if (ok) {
+      issue_scores(Zero{}, Zero{});
+      if constexpr (QT == 2) issue_scores(One{}, Zero{});
+    }
     auto step = [&](auto stage_c, auto first_c, int t) -> bool {
       constexpr int kStage = decltype(stage_c)::value;
       using Next = std::integral_constant<int, 1 - kStage>;
       if (t + 1 < n_tiles) {  // S(t + 1): its buffer held P(t - 1), which the product issued before this one has read
         if (!wait(bar_k0 + (1 - kStage) * 8, (t + 1) >> 1)) return false;
-        issue_scores(Next{});
+        issue_scores(Zero{}, Next{});
+        if constexpr (QT == 2) issue_scores(One{}, Next{});
       }
       if (!wait(bar_p0 + kStage * 8, t >> 1) || !wait(bar_v0 + kStage * 8, t >> 1)) return false;
-      issue_values(stage_c, first_c);
+      issue_values(Zero{}, stage_c, first_c);
+      if constexpr (QT == 2) {
+        if (!wait(bar_p0 + 16 + kStage * 8, t >> 1)) return false;
+        issue_values(One{}, stage_c, first_c);
+      }
       return true;
     };
     if (ok) ok = step(Zero{}, std::true_type{}, 0);
@@ -638,10 +662,11 @@ __global__ void __launch_bounds__(kWdThreads, 1)
       if (ok) ok = step(Zero{}, std::false_type{}, t + 1);
     }
     if (ok && t < n_tiles) ok = step(One{}, std::false_type{}, t);
-  } else if (warp < 4) {
+  } else if (warp < kSoftmaxWarps) {
     // ---- softmax: thread t owns row t -----------------------------------------------------------------------------------
     constexpr int kChunk = 32;
-    const uint32_t t_lane = tmem_addr(tmem, 32 * warp, 0);
+    const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsQ);
+    const uint32_t my_s0 = bar_s0 + qtile * 16, my_p0 = bar_p0 + qtile * 16, my_o0 = bar_o0 + qtile * 16;
     const uint32_t t_o = t_lane + kWdColO;
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
@@ -649,7 +674,7 @@ __global__ void __launch_bounds__(kWdThreads, 1)
       const int key0 = it * kWdKeys;
       const int visible = max(0, min(kWdKeys, lim - key0));
       const uint32_t t_s = t_lane + kWdColS + (it & 1) * kWdKeys;
-      ok = wait(bar_s0 + (it & 1) * 8, it >> 1);
+      ok = wait(my_s0 + (it & 1) * 8, it >> 1);
       if (!ok) break;
       tcgen05_fence_after_sync();
       uint32_t x[kWdKeys];
@@ -678,7 +703,7 @@ __global__ void __launch_bounds__(kWdThreads, 1)
         if (grew) m_run = mx;
         l_run *= alpha;
         if (it > 0) {  // the row of O, for which the previous product has to be complete
-          ok = wait(bar_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
+          ok = wait(my_o0 + ((it - 1) & 1) * 8, (it - 1) >> 1);
           if (!ok) break;
           tcgen05_fence_after_sync();
 #pragma unroll 1
@@ -716,13 +741,14 @@ __global__ void __launch_bounds__(kWdThreads, 1)
       l_run += s_lo + s_hi;
       tmem_wait_st();
       // the V rows behind the last key may hold anything: zero them in the tile that straddles it (see the other kernel)
-      if (key0 + kWdKeys > n_keys32) {
+      if (qtile == 0 && key0 + kWdKeys > n_keys32) {
         ok = wait(bar_v0 + (it & 1) * 8, it >> 1);
         if (!ok) break;
         const int first = max(0, n_keys32 - key0);
         uint8_t* v_stage = smem_raw + (smem - smem_u32(smem_raw)) + kWdOffV + (it & 1) * kWdKvBytes;
-        for (int i = threadIdx.x; i < (kWdKeys - first) * 32; i += kWdRows) {
-          const int r = first + (i >> 5), piece = i & 31;  // 8 pieces of 16 bytes in each of the four boxes
+        constexpr int kPieces = kWdDim / 8;  // 16-byte pieces per key: 8 in each box
+        for (int i = threadIdx.x; i < (kWdKeys - first) * kPieces; i += kWdRows) {
+          const int r = first + i / kPieces, piece = i % kPieces;
           *reinterpret_cast<uint4*>(v_stage + (piece >> 3) * kWdKvBoxBytes + r * 128 + (piece & 7) * 16) =
               make_uint4(0u, 0u, 0u, 0u);
         }
@@ -730,9 +756,9 @@ __global__ void __launch_bounds__(kWdThreads, 1)
       }
       tcgen05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p0 + (it & 1) * 8);
+      if (lane == 0) mbar_arrive(my_p0 + (it & 1) * 8);
     }
-    if (ok) ok = wait(bar_o0 + ((n_tiles - 1) & 1) * 8, (n_tiles - 1) >> 1);
+    if (ok) ok = wait(my_o0 + ((n_tiles - 1) & 1) * 8, (n_tiles - 1) >> 1);
     if (ok) {
       tcgen05_fence_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -819,36 +845,37 @@ static int launch_prefill_umma_t(const PrefillParams& p, int batch, int q_heads,
   return check_launch("gqa_prefill_umma_kernel");
 }
 
-template <typename T>
-static int launch_prefill_umma256_t(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
-  auto kernel = gqa_prefill_umma256_kernel<T>;
+template <typename T, int D, int QT>
+static int launch_prefill_umma_wide_t(const PrefillParams& p, int batch, int q_heads, cudaStream_t stream) {
+  using Cfg = WideCfg<D, QT>;
+  auto kernel = gqa_prefill_umma_wide_kernel<T, D, QT>;
   const int head_shift = head_shift_of(p.groups);
-  const int positions = kWdRows >> head_shift;
+  const int positions = Cfg::kCtaRows >> head_shift;
   CUtensorMap map_q, map_k, map_v;
   const int kv_heads = q_heads / p.groups;
   if (!prefill_tensor_map(&map_q, p.q, p.q_len, q_heads, batch, p.q_stride_t, p.q_stride_h, p.q_stride_b,
-                          (uint32_t)positions, 1u << head_shift, kWdDim) ||
-      !prefill_tensor_map(&map_k, p.k, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kWdKeys, 1,
-                          kWdDim) ||
-      !prefill_tensor_map(&map_v, p.v, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, kWdKeys, 1,
-                          kWdDim))
+                          (uint32_t)positions, 1u << head_shift, D) ||
+      !prefill_tensor_map(&map_k, p.k, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, Cfg::kKeys, 1,
+                          D) ||
+      !prefill_tensor_map(&map_v, p.v, p.key_len, kv_heads, batch, p.kv_stride_t, p.kv_stride_h, p.kv_stride_b, Cfg::kKeys, 1,
+                          D))
     return kPrefillNotServed;
   static bool configured[64] = {};
   int device = 0;
   ANNA_CUDA_CHECK(cudaGetDevice(&device));
   if (device < 0 || device >= 64 || !configured[device]) {
-    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWdSmem));
+    ANNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmem));
     if (device >= 0 && device < 64) configured[device] = true;
   }
   dim3 grid((unsigned)((p.q_len + positions - 1) / positions), (unsigned)(q_heads >> head_shift), (unsigned)batch);
-  kernel<<<grid, kWdThreads, kWdSmem, stream>>>(p, map_q, map_k, map_v);
-  return check_launch("gqa_prefill_umma256_kernel");
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(p, map_q, map_k, map_v);
+  return check_launch("gqa_prefill_umma_wide_kernel");
 }
 
 int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int head_dim, int dtype, cudaStream_t stream) {
   if (head_dim == 256)
-    return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma256_t<__nv_bfloat16>(p, batch, q_heads, stream)
-                                    : launch_prefill_umma256_t<__half>(p, batch, q_heads, stream);
+    return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_wide_t<__nv_bfloat16, 256, 1>(p, batch, q_heads, stream)
+                                    : launch_prefill_umma_wide_t<__half, 256, 1>(p, batch, q_heads, stream);
   return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_t<__nv_bfloat16>(p, batch, q_heads, stream)
                                   : launch_prefill_umma_t<__half>(p, batch, q_heads, stream);
 }
