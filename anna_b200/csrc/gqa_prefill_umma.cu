@@ -469,7 +469,7 @@ __global__ void __launch_bounds__(kUpThreads, 1)
 // 1.03 ms for, so it is not instantiated.
 template <int D, int QT>
 struct WideCfg {
-  static constexpr int kDim = D, kQTiles = QT, kRows = 128, kCtaRows = QT * 128, kKeys = 64, kStages = 2;
+  static constexpr int kDim = D, kRows = 128, kCtaRows = QT * 128, kKeys = 64, kStages = 2;
   static constexpr int kSoftmaxWarps = 4 * QT;
   static constexpr int kThreads = (kSoftmaxWarps + 2 + 3) / 4 * 4 * 32;  // softmax warps, issuing warp, copy warp
   static constexpr uint32_t kQBoxBytes = kCtaRows * 128;            // 64 values of all rows
