@@ -1,5 +1,5 @@
 // Multi-token (prefill / chunked-prefill) grouped-query attention on the 5th-generation tensor cores: tcgen05.mma with
-// S, P and O in tensor memory.  head_dim 128 (first kernel) and 256 (second kernel), 16-bit dtypes; same semantics as
+// S, P and O in tensor memory.  head_dim 128 (first kernel), 256 and 64 (second kernel), 16-bit dtypes; same semantics as
 // gqa_prefill.cu (grouped_query_attention, src/anna/model/ops.py:1552-1574, with the masks of ops.py:1840-1852 and
 // :2008-2016).
 //
@@ -464,9 +464,9 @@ __global__ void __launch_bounds__(kUpThreads, 1)
 // pipe ever waits for is P.  64-key tiles (a K or V tile is 32 KB; two stages of each and Q make 192 KB).  Warp 4 issues
 // the products, warp 5 the copies (eight boxes and two byte counts per tile: on the issuing warp they would cost more
 // than the products of the tile), warps 0..3 are the softmax, thread t = row t.
-// The same structure also runs head_dim 128 with two query tiles per CTA (`WideCfg<128, 2>`: 256 rows per K / V tile, 256
-// columns of tensor memory per query tile, eight softmax warps): correct, 1.10 ms on the case the kernel above takes
-// 1.03 ms for, so it is not instantiated.
+// With two query tiles per CTA (256 rows per K / V tile, 256 columns of tensor memory per query tile, eight softmax
+// warps) the same structure serves head_dim 64 (`WideCfg<64, 2>`).  `WideCfg<128, 2>` is correct too, but takes 1.10 ms
+// on the case the kernel above takes 1.03 ms for, so it is not instantiated.
 template <int D, int QT>
 struct WideCfg {
   static constexpr int kDim = D, kRows = 128, kCtaRows = QT * 128, kKeys = 64, kStages = 2;
@@ -478,7 +478,7 @@ struct WideCfg {
   static constexpr uint32_t kOffQ = 0, kOffK = (D / 64) * kQBoxBytes, kOffV = kOffK + kStages * kKvBytes;
   static constexpr uint32_t kSmem = kOffV + kStages * kKvBytes + 1024;
   // tensor memory per query tile: S0 | S1 (64 columns each) | O (D columns)
-  static constexpr uint32_t kColS = 0, kColO = 2 * kKeys, kColsPerQTile = D == 128 ? 256 : 512, kTmemCols = 512;
+  static constexpr uint32_t kColS = 0, kColO = 2 * kKeys, kColsPerQTile = D <= 128 ? 256 : 512, kTmemCols = 512;
   static_assert(kColO + D <= kColsPerQTile && QT * kColsPerQTile <= 512, "tensor memory layout");
 };
 
@@ -797,7 +797,8 @@ bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
     return flag != nullptr && flag[0] == '0';
   }();
   if (disabled) return false;
-  if ((head_dim != 128 && head_dim != 256) || (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16)) return false;
+  if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || (dtype != ANNA_DTYPE_F16 && dtype != ANNA_DTYPE_BF16))
+    return false;
   // the output rows are written as 16-byte vectors
   if (p.out_stride_b % 8 != 0 || p.out_stride_h % 8 != 0 || p.out_stride_t % 8 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return false;
@@ -876,6 +877,9 @@ int launch_prefill_umma(const PrefillParams& p, int batch, int q_heads, int head
   if (head_dim == 256)
     return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_wide_t<__nv_bfloat16, 256, 1>(p, batch, q_heads, stream)
                                     : launch_prefill_umma_wide_t<__half, 256, 1>(p, batch, q_heads, stream);
+  if (head_dim == 64)
+    return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_wide_t<__nv_bfloat16, 64, 2>(p, batch, q_heads, stream)
+                                    : launch_prefill_umma_wide_t<__half, 64, 2>(p, batch, q_heads, stream);
   return dtype == ANNA_DTYPE_BF16 ? launch_prefill_umma_t<__nv_bfloat16>(p, batch, q_heads, stream)
                                   : launch_prefill_umma_t<__half>(p, batch, q_heads, stream);
 }

@@ -55,6 +55,9 @@ def _oracle(q, k, v, lengths, causal):
     (torch.float16, 4, 4, 256, 130, 130, (130, 70), True),         # one head per KV head, queries without keys
     (torch.bfloat16, 6, 2, 256, 100, 333, (333, 0, 129), False),   # three heads per KV head, key padding only
     (torch.bfloat16, 16, 2, 256, 256, 2100, (2100, 1111), True),   # 33 key tiles
+    # head_dim 64 with 64 or more queries: the same kernel template, two query tiles per CTA
+    (torch.bfloat16, 8, 2, 64, 200, 700, (700, 333, 65), True),
+    (torch.float16, 6, 2, 64, 100, 333, (333, 0, 129), False),
 ])
 def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len, key_len, lengths, causal):
     gen = torch.Generator().manual_seed(heads * 1000 + q_len)
@@ -75,7 +78,7 @@ def test_prefill_matches_oracle(cuda_device, dtype, heads, kv_heads, dim, q_len,
     assert torch.equal(again, out)
 
 
-@pytest.mark.parametrize("dim,q_len", [(128, 200), (128, 40), (256, 48), (256, 200)])
+@pytest.mark.parametrize("dim,q_len", [(128, 200), (128, 40), (256, 48), (256, 200), (64, 200)])
 def test_keys_behind_a_rows_length_may_hold_anything(cuda_device, dim, q_len):
     """K / V rows past key_lengths[b] are inside the tensors but not part of the row: NaNs there must not reach the
     output (the TMA-fed kernel reads them and zeroes the value rows of the boundary tile; the others never load them)."""
