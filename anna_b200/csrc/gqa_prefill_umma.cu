@@ -803,7 +803,11 @@ bool prefill_umma_applicable(const PrefillParams& p, int head_dim, int dtype) {
   if (p.out_stride_b % 8 != 0 || p.out_stride_h % 8 != 0 || p.out_stride_t % 8 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return false;
   if (p.key_len <= 0) return false;
-  return p.q_len >= 64;  // short chunks leave most of a 256-row tile empty: the mma.sync kernel serves them
+  // The rows of a CTA are query positions x the heads that share a KV head (a power of two, at most 16): chunks that
+  // fill less than half a CTA's rows (and are shorter than 64 positions) leave most of the tile empty, and the mma.sync
+  // kernel serves them.
+  const int cta_rows = head_dim == 256 ? 128 : 256;
+  return p.q_len >= 64 || (int64_t)p.q_len * (1 << head_shift_of(p.groups)) * 2 >= cta_rows;
 }
 
 // Tensor map of a [B, H, L, dim] 16-bit tensor given by element strides, seen as (dim, L, H, B).
