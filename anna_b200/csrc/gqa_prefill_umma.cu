@@ -472,14 +472,16 @@ struct WideCfg {
   static constexpr int kDim = D, kRows = 128, kCtaRows = QT * 128, kKeys = 64, kStages = 2;
   static constexpr int kSoftmaxWarps = 4 * QT;
   static constexpr int kThreads = (kSoftmaxWarps + 2 + 3) / 4 * 4 * 32;  // softmax warps, issuing warp, copy warp
-  static constexpr uint32_t kQBoxBytes = kCtaRows * 128;            // 64 values of all rows
   static constexpr uint32_t kKvBoxBytes = kKeys * 128;              // 64 values of 64 keys
   static constexpr uint32_t kKvBytes = (D / 64) * kKvBoxBytes;      // one K or V tile
-  static constexpr uint32_t kOffQ = 0, kOffK = (D / 64) * kQBoxBytes, kOffV = kOffK + kStages * kKvBytes;
+  static constexpr uint32_t kOffK = 0, kOffV = kOffK + kStages * kKvBytes;
   static constexpr uint32_t kSmem = kOffV + kStages * kKvBytes + 1024;
-  // tensor memory per query tile: S0 | S1 (64 columns each) | O (D columns)
-  static constexpr uint32_t kColS = 0, kColO = 2 * kKeys, kColsPerQTile = D <= 128 ? 256 : 512, kTmemCols = 512;
-  static_assert(kColO + D <= kColsPerQTile && QT * kColsPerQTile <= 512, "tensor memory layout");
+  // tensor memory per query tile: S0 | S1 (64 columns each) | O (D columns) | Q (D / 2 columns, two values each).  Q is
+  // the A operand of S = Q . K^T and is read from tensor memory: a 128 x 64 x 16 product that fetches its 4 KB A operand
+  // from shared memory took about 76 clocks here instead of 32, and those products bounded the kernel.
+  static constexpr uint32_t kColS = 0, kColO = 2 * kKeys, kColQ = kColO + D, kColsPerQTile = D <= 128 ? 256 : 512;
+  static constexpr uint32_t kTmemCols = 512;
+  static_assert(kColQ + D / 2 <= kColsPerQTile && QT * kColsPerQTile <= 512, "tensor memory layout");
 };
 
 template <typename T, int D, int QT>
@@ -488,8 +490,8 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
                                const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   using Cfg = WideCfg<D, QT>;
   constexpr int kWdDim = Cfg::kDim, kWdRows = Cfg::kRows, kWdKeys = Cfg::kKeys;
-  constexpr uint32_t kWdQBoxBytes = Cfg::kQBoxBytes, kWdKvBoxBytes = Cfg::kKvBoxBytes, kWdKvBytes = Cfg::kKvBytes;
-  constexpr uint32_t kWdOffQ = Cfg::kOffQ, kWdOffK = Cfg::kOffK, kWdOffV = Cfg::kOffV, kWdColS = Cfg::kColS, kWdColO = Cfg::kColO;
+  constexpr uint32_t kWdKvBoxBytes = Cfg::kKvBoxBytes, kWdKvBytes = Cfg::kKvBytes;
+  constexpr uint32_t kWdOffK = Cfg::kOffK, kWdOffV = Cfg::kOffV, kWdColS = Cfg::kColS, kWdColO = Cfg::kColO, kWdColQ = Cfg::kColQ;
   constexpr uint32_t kWdTmemCols = Cfg::kTmemCols, kColsQ = Cfg::kColsPerQTile;
   constexpr int kSoftmaxWarps = Cfg::kSoftmaxWarps;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -538,7 +540,8 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
   const uint32_t bar_k0 = smem_u32(&bar_storage[6 * QT + 1]);  // + 8 * stage
   const uint32_t bar_v0 = smem_u32(&bar_storage[6 * QT + 3]);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 6 * QT + 5; ++i) mbar_init(bar_s0 + 8 * i, (i >= 2 * QT && i < 4 * QT) ? kWdRows / 32 : 1);
+    for (int i = 0; i < 6 * QT + 5; ++i)
+      mbar_init(bar_s0 + 8 * i, (i >= 2 * QT && i < 4 * QT) ? kWdRows / 32 : (i == 6 * QT ? kSoftmaxWarps : 1));
     abort_flag = 0;
     mbar_init_fence();
   }
@@ -584,11 +587,6 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
       for (int i = 0; i < kWdDim / 64; ++i)
         tma_load_4d(dst + i * kWdKvBoxBytes, keys ? &map_k : &map_v, 64 * i, t * kWdKeys, kvh, b, bar);
     };
-    if (elect_one()) {
-      mbar_expect_tx(bar_q, (kWdDim / 64) * kWdQBoxBytes);  // positions past the chunk's end arrive as zeros
-#pragma unroll
-      for (int i = 0; i < kWdDim / 64; ++i) tma_load_4d(smem + kWdOffQ + i * kWdQBoxBytes, &map_q, 64 * i, m0, hq0, b, bar_q);
-    }
     bool ok = true;
     auto produce = [&](auto stage_c, int t) {
       constexpr int kStage = decltype(stage_c)::value;  // t & 1
@@ -608,7 +606,6 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? kUmmaBF16 : kUmmaF16;
     constexpr uint32_t idesc_s = umma_idesc(kFmt, kFmt, false, false, kWdRows, kWdKeys);
     constexpr uint32_t idesc_o = umma_idesc(kFmt, kFmt, false, true, kWdRows, kWdDim);
-    const uint64_t desc_q = umma_smem_desc_sw128(smem + kWdOffQ, 16, 1024);
     const uint64_t desc_k = umma_smem_desc_sw128(smem + kWdOffK, 16, 1024);
     const uint64_t desc_v = umma_smem_desc_sw128(smem + kWdOffV, kWdKvBoxBytes, 1024);  // next 64 values: next box
     auto issue_scores = [&](auto qt_c, auto stage_c) {
@@ -617,10 +614,9 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
       tcgen05_fence_after_sync();
 #pragma unroll
       for (int k = 0; k < kWdDim / 16; ++k)  // 16 values of K per instruction: 32 bytes of a row, four steps per box
-        umma_f16(tmem + kQt * kColsQ + kWdColS + kStage * kWdKeys,
-                 desc_q + (uint64_t)(((k / 4) * kWdQBoxBytes + kQt * (kWdRows * 128) + (k % 4) * 32) >> 4),
-                 desc_k + (uint64_t)((kStage * kWdKvBytes + (k / 4) * kWdKvBoxBytes + (k % 4) * 32) >> 4), idesc_s,
-                 k > 0 ? 1u : 0u);
+        umma_f16_ts(tmem + kQt * kColsQ + kWdColS + kStage * kWdKeys, tmem + kQt * kColsQ + kWdColQ + 8 * k,
+                    desc_k + (uint64_t)((kStage * kWdKvBytes + (k / 4) * kWdKvBoxBytes + (k % 4) * 32) >> 4), idesc_s,
+                    k > 0 ? 1u : 0u);
       umma_commit(bar_s0 + kQt * 16 + kStage * 8);
     };
     auto issue_values = [&](auto qt_c, auto stage_c, auto first_c) {
@@ -668,6 +664,26 @@ __global__ void __launch_bounds__((WideCfg<D, QT>::kThreads), 1)
     const uint32_t t_lane = tmem_addr(tmem, 32 * (warp & 3), qtile * kColsQ);
     const uint32_t my_s0 = bar_s0 + qtile * 16, my_p0 = bar_p0 + qtile * 16, my_o0 = bar_o0 + qtile * 16;
     const uint32_t t_o = t_lane + kWdColO;
+    {
+      // this thread's row of Q into tensor memory (two values per column, as the A operand of the score products
+      // expects them); rows past the chunk's end are zeros
+      const uint4* q_row = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + b * p.q_stride_b +
+                                                         (int64_t)hq * p.q_stride_h + (int64_t)row * p.q_stride_t);
+#pragma unroll 2
+      for (int c = 0; c < kWdDim / 32; ++c) {  // 32 values = 64 bytes = 16 columns
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = row < p.q_len ? q_row[4 * c + j] : make_uint4(0u, 0u, 0u, 0u);
+          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+        tmem_st16(t_lane + kWdColQ + 16 * c, w);
+      }
+      tmem_wait_st();
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_q);
+    }
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int it = 0; it < n_tiles; ++it) {
